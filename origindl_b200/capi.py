@@ -1,0 +1,106 @@
+"""ctypes binding of libodl_b200.so (the C ABI declared in include/odl_b200.h).
+
+The library is loaded from this package directory; if it has not been built the import of `lib()` raises
+with the build command.  There is no fallback path: every function here ends in a CUDA kernel of the library.
+Pointers are passed as integers (`tensor.data_ptr()`), streams as `torch.cuda.current_stream().cuda_stream`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libodl_b200.so"
+
+OK = 0
+PRECISION_3XTF32 = 0
+PRECISION_TF32 = 1
+EPI_BIAS, EPI_RELU, EPI_MASK, EPI_COLSUM, EPI_SMALL = 1, 2, 4, 8, 16
+W_OUT_IN, W_IN_OUT = 0, 1
+
+_lib = None
+
+
+class OdlError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"odl status {status}: {message}")
+        self.status = status
+
+
+_P = c_void_p
+_I64 = c_int64
+
+_SIGNATURES = {
+    "odl_init": [c_int],
+    "odl_device_status": [_P],
+    "odl_debug_set_tile_n": [c_int],
+    "odl_debug_set_knobs": [c_int, c_int, c_int, _P],
+    "odl_matmul": [_P, _P, _P, _I64, _I64, _I64, _I64, c_int, c_int, _P],
+    "odl_gemm_ex": [c_int, c_int, _I64, _I64, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P,
+                    c_int, c_int, _P],
+    "odl_split_tf32": [_P, _I64, _I64, _I64, _P, _I64, _P, _P, _I64, _P, _P],
+}
+
+
+def declared_symbols() -> list[str]:
+    """Names of every function declared in include/odl_b200.h (parsed from the header)."""
+    import re
+
+    text = (_HERE.parent / "include" / "odl_b200.h").read_text()
+    return sorted(set(re.findall(r"\b(odl_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m origindl_b200.build` (needs nvcc, sm_100a)")
+        L = ctypes.CDLL(str(LIB_PATH))
+        L.odl_last_error.restype = c_char_p
+        L.odl_last_error.argtypes = []
+        L.odl_scratch_bytes.restype = c_int64
+        L.odl_scratch_bytes.argtypes = []
+        for name, args in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise OdlError(status, lib().odl_last_error().decode(errors="replace"))
+
+
+def call(name: str, *args) -> None:
+    check(getattr(lib(), name)(*args))
+
+
+def ptr(t) -> int | None:
+    """Device address of a torch tensor (None passes NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_handle() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+_initialized = False
+
+
+def init(device: int = 0) -> None:
+    global _initialized
+    if not _initialized:
+        call("odl_init", device)
+        _initialized = True
+
+
+def device_status() -> None:
+    call("odl_device_status", stream_handle())

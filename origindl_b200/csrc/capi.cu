@@ -1,0 +1,373 @@
+// extern "C" layer: library state (device binding, error flag, scratch arena) and the GEMM entry points.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/odl_b200.h"
+#include "gemm_tc.cuh"
+#include "host_util.h"
+#include "internal.h"
+
+namespace odl
+{
+
+namespace
+{
+thread_local char g_err[1024] = {0};
+
+struct DeviceState
+{
+    bool ready      = false;
+    int device      = -1;
+    int *err_flag   = nullptr;  // device memory
+    char *arena     = nullptr;
+    size_t capacity = 0;
+    size_t used     = 0;
+};
+DeviceState g_state;
+std::mutex g_mu;
+}  // namespace
+
+void set_last_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+const char *get_last_error()
+{
+    return g_err;
+}
+
+int *device_error_flag()
+{
+    return g_state.err_flag;
+}
+
+bool is_ready()
+{
+    return g_state.ready;
+}
+
+void arena_reset()
+{
+    g_state.used = 0;
+}
+
+// Bump allocation out of one device block.  Growing replaces the block: work already queued may still read the
+// old one, so the device is drained first (this happens a handful of times while sizes warm up, never in steady state).
+void *arena_alloc(size_t bytes)
+{
+    bytes = (bytes + 255) & ~size_t(255);
+    if (g_state.used + bytes > g_state.capacity)
+    {
+        if (g_state.used != 0)
+        {
+            // A call needs more than the block holds and already carved part of it: the caller sizes the
+            // whole call up front with arena_reserve, so reaching this is a programming error.
+            set_last_error("scratch arena: reserve(%zu) was not called before alloc", g_state.used + bytes);
+            return nullptr;
+        }
+        if (cudaDeviceSynchronize() != cudaSuccess)
+            return nullptr;
+        if (g_state.arena)
+            cudaFree(g_state.arena);
+        g_state.arena    = nullptr;
+        g_state.capacity = 0;
+        size_t want      = bytes + (bytes >> 2);
+        void *p          = nullptr;
+        cudaError_t e    = cudaMalloc(&p, want);
+        if (e != cudaSuccess)
+        {
+            set_last_error("scratch arena: cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_state.arena    = static_cast<char *>(p);
+        g_state.capacity = want;
+    }
+    void *out = g_state.arena + g_state.used;
+    g_state.used += bytes;
+    return out;
+}
+
+// Make sure one call's total scratch fits; must be called right after arena_reset().
+int arena_reserve(size_t total_bytes)
+{
+    total_bytes += 4096;
+    if (total_bytes <= g_state.capacity)
+        return kOk;
+    void *p = arena_alloc(total_bytes);
+    if (!p)
+        return kCudaError;
+    g_state.used = 0;
+    return kOk;
+}
+
+namespace
+{
+inline bool misaligned(const void *p, int64_t ld)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15) || (ld & 3);
+}
+inline int64_t pad4(int64_t x)
+{
+    return (x + 3) & ~int64_t(3);
+}
+inline size_t a256(size_t x)
+{
+    return (x + 255) & ~size_t(255);
+}
+
+struct Prepared
+{
+    const float *big;
+    const float *small;
+    int64_t ld;
+};
+
+size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms)
+{
+    if (misaligned(ptr, ld))
+        return a256(rows * pad4(cols) * 4) * (terms == 3 ? 2 : 1);
+    if (terms == 3 && (!small || misaligned(small, ld)))
+        return a256(rows * ld * 4);
+    return 0;
+}
+
+int prepare_operand(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms,
+                    cudaStream_t stream, Prepared *out)
+{
+    if (misaligned(ptr, ld))
+    {
+        const int64_t ldp = pad4(cols);
+        float *big        = static_cast<float *>(arena_alloc(rows * ldp * 4));
+        float *sm         = terms == 3 ? static_cast<float *>(arena_alloc(rows * ldp * 4)) : nullptr;
+        if (!big || (terms == 3 && !sm))
+            return kCudaError;
+        int rc = split_launch(ptr, ld, (int)rows, (int)cols, nullptr, 0, big, sm, ldp, nullptr, stream);
+        if (rc)
+            return rc;
+        *out = Prepared{big, sm, ldp};
+        return kOk;
+    }
+    if (terms == 3 && (!small || misaligned(small, ld)))
+    {
+        float *sm = static_cast<float *>(arena_alloc(rows * ld * 4));
+        if (!sm)
+            return kCudaError;
+        int rc = split_launch(ptr, ld, (int)rows, (int)cols, nullptr, 0, nullptr, sm, ld, nullptr, stream);
+        if (rc)
+            return rc;
+        *out = Prepared{ptr, sm, ld};
+        return kOk;
+    }
+    *out = Prepared{ptr, small, ld};
+    return kOk;
+}
+}  // namespace
+
+// The GEMM every fused entry point funnels into.  `reset_arena` is false when the caller already carved scratch
+// for this call (Linear / conv orchestration) and reserved enough for the operand splits too.
+int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
+                  int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
+                  const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
+                  cudaStream_t stream, bool reset_arena)
+{
+    if (!is_ready())
+    {
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !D)
+    {
+        set_last_error("gemm: invalid argument (M=%lld N=%lld K=%lld A=%p B=%p D=%p)", (long long)M, (long long)N,
+                       (long long)K, (const void *)A, (const void *)B, (void *)D);
+        return kInvalidArgument;
+    }
+    if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    {
+        set_last_error("gemm: dimension exceeds 2^31-1");
+        return kTooLarge;
+    }
+    if (precision != ODL_PRECISION_3XTF32 && precision != ODL_PRECISION_TF32)
+    {
+        set_last_error("gemm: unknown precision %d", precision);
+        return kInvalidArgument;
+    }
+    if (((flags & kEpiBias) && !bias) || ((flags & kEpiMask) && !mask_src) || ((flags & kEpiColsum) && !colsum) ||
+        ((flags & kEpiSmall) && !D_small))
+    {
+        set_last_error("gemm: epilogue flag 0x%x set without its pointer", flags);
+        return kInvalidArgument;
+    }
+    const int terms      = precision == ODL_PRECISION_3XTF32 ? 3 : 1;
+    const int64_t a_rows = transA ? K : M, a_cols = transA ? M : K;
+    const int64_t b_rows = transB ? N : K, b_cols = transB ? K : N;
+    if (lda < a_cols || ldb < b_cols || ldd < N)
+    {
+        set_last_error("gemm: leading dimension smaller than the row length (lda=%lld ldb=%lld ldd=%lld)",
+                       (long long)lda, (long long)ldb, (long long)ldd);
+        return kInvalidArgument;
+    }
+    if (reset_arena)
+    {
+        arena_reset();
+        int rc = arena_reserve(operand_scratch(A, A_small, lda, a_rows, a_cols, terms) +
+                               operand_scratch(B, B_small, ldb, b_rows, b_cols, terms));
+        if (rc)
+            return rc;
+    }
+    Prepared pa, pb;
+    int rc;
+    if ((rc = prepare_operand(A, A_small, lda, a_rows, a_cols, terms, stream, &pa)))
+        return rc;
+    if ((rc = prepare_operand(B, B_small, ldb, b_rows, b_cols, terms, stream, &pb)))
+        return rc;
+    GemmParams p;
+    p.D       = D;
+    p.D_small = D_small;
+    p.bias    = bias;
+    p.aux     = mask_src;
+    p.colsum  = colsum;
+    p.err     = device_error_flag();
+    p.M       = (int)M;
+    p.N       = (int)N;
+    p.K       = (int)K;
+    p.ldd     = (int)ldd;
+    p.ld_aux  = (int)ld_mask;
+    p.flags   = flags;
+    const int a_mn = transA ? 1 : 0;
+    const int b_mn = transB ? 0 : 1;
+    return gemm_tc_launch(pa.big, pa.small, pa.ld, a_mn, pb.big, pb.small, pb.ld, b_mn, p, terms, g_bn_override, stream);
+}
+
+int g_bn_override = 0;
+
+}  // namespace odl
+
+using namespace odl;
+
+extern "C" {
+
+int odl_init(int device)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_state.ready && g_state.device == device)
+        return kOk;
+    if (g_state.ready)
+    {
+        set_last_error("odl_init: already bound to device %d (one device per process)", g_state.device);
+        return kInvalidArgument;
+    }
+    ODL_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    ODL_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+    {
+        set_last_error("odl_init: device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                       prop.minor);
+        return kCudaError;
+    }
+    ODL_CUDA_TRY(cudaMalloc(&g_state.err_flag, sizeof(int)));
+    ODL_CUDA_TRY(cudaMemset(g_state.err_flag, 0, sizeof(int)));
+    g_state.device = device;
+    g_state.ready  = true;
+    return kOk;
+}
+
+const char *odl_last_error(void)
+{
+    return get_last_error();
+}
+
+int odl_device_status(void *stream)
+{
+    if (!is_ready())
+    {
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int flag       = 0;
+    ODL_CUDA_TRY(cudaMemcpyAsync(&flag, g_state.err_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+    ODL_CUDA_TRY(cudaStreamSynchronize(s));
+    if (flag != 0)
+    {
+        ODL_CUDA_TRY(cudaMemsetAsync(g_state.err_flag, 0, sizeof(int), s));
+        ODL_CUDA_TRY(cudaStreamSynchronize(s));
+        set_last_error("a kernel gave up on a bounded wait (pipeline barrier never completed)");
+        return kKernelTimeout;
+    }
+    return kOk;
+}
+
+int64_t odl_scratch_bytes(void)
+{
+    return static_cast<int64_t>(g_state.capacity);
+}
+
+int odl_debug_set_knobs(int lbo_mn, int sbo_mn, int step_mn, float *dump)
+{
+    debug_set_knobs(lbo_mn, sbo_mn, step_mn, dump);
+    return kOk;
+}
+
+// Test hook: force the GEMM column-tile width (64, 128, 256; 0 = automatic).
+int odl_debug_set_tile_n(int bn)
+{
+    g_bn_override = bn;
+    return kOk;
+}
+
+int odl_gemm_ex(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
+                int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
+                const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int epilogue_flags,
+                int precision, void *stream)
+{
+    return gemm_dispatch(transA, transB, M, N, K, A, A_small, lda, B, B_small, ldb, D, D_small, ldd, bias, mask_src,
+                         ld_mask, colsum, epilogue_flags, precision, static_cast<cudaStream_t>(stream), true);
+}
+
+int odl_matmul(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K, int64_t batch, int b_batched,
+               int precision, void *stream)
+{
+    if (batch < 1)
+    {
+        set_last_error("matmul: batch must be >= 1");
+        return kInvalidArgument;
+    }
+    if (batch > 1 && !b_batched)
+    {
+        // [batch, M, K] x [K, N] is one GEMM over batch*M rows
+        return gemm_dispatch(0, 0, batch * M, N, K, A, nullptr, K, B, nullptr, N, C, nullptr, N, nullptr, nullptr, 0,
+                             nullptr, 0, precision, static_cast<cudaStream_t>(stream), true);
+    }
+    for (int64_t i = 0; i < batch; ++i)
+    {
+        int rc = gemm_dispatch(0, 0, M, N, K, A + i * M * K, nullptr, K, B + i * K * N, nullptr, N, C + i * M * N,
+                               nullptr, N, nullptr, nullptr, 0, nullptr, 0, precision,
+                               static_cast<cudaStream_t>(stream), true);
+        if (rc)
+            return rc;
+    }
+    return kOk;
+}
+
+int odl_split_tf32(const float *src, int64_t ld_src, int64_t rows, int64_t cols, const float *mask_src, int64_t ld_mask,
+                   float *dst_big, float *dst_small, int64_t ld_dst, float *colsum, void *stream)
+{
+    if (rows > 0x7fffffff || cols > 0x7fffffff)
+    {
+        set_last_error("split: dimension exceeds 2^31-1");
+        return kTooLarge;
+    }
+    return split_launch(src, ld_src, (int)rows, (int)cols, mask_src, ld_mask, dst_big, dst_small, ld_dst, colsum,
+                        static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,578 @@
+// tcgen05 / TMEM / TMA GEMM for sm_100a:  D[M,N] = A[M,K] * B[N,K]^T  in TF32 or 3xTF32, fp32 accumulate.
+//
+// One CTA computes one 128 x BN tile of D.  Warp roles (192 threads):
+//   warp 0      TMA producer: one elected lane streams 128-byte-swizzled operand tiles into a ring of stages.
+//   warp 1      TMEM owner and MMA issuer: one elected lane issues tcgen05.mma (kind::tf32, operands from
+//               shared-memory descriptors, accumulator in TMEM) and commits stage-free / accumulator-ready barriers.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes of its quarter), transpose
+//               through a padded shared-memory slab, then apply bias / ReLU / ReLU-mask / column sums and write D
+//               (and the low part of its TF32 split) with coalesced 128-bit stores.
+//
+// Operand majorness is a run-time property.  "K-major" means the reduction index is contiguous in memory
+// (A stored [M][K], B stored [N][K]); "MN-major" means the M (or N) index is contiguous (A stored [K][M],
+// B stored [K][N]).  Both are fed to the tensor core without a transpose pass:
+//   K-major : one TMA box {32 k, rows} per tile -> rows x 128 B, SWIZZLE_128B; descriptor SBO = 1024 B,
+//             each K=8 MMA step advances the start address by 32 B inside the swizzled row.
+//   MN-major: boxes {32 mn, 32 k} (4 KB each) laid side by side, written with the 32-byte-chunk variant of the
+//             128-byte swizzle (the only layout the tensor core accepts for MN-major 32-bit operands: its atom
+//             is 4 k-rows x 128 B); descriptor LBO = 4096 B (next 32 mn), SBO = 512 B (next 4 k), each K=8 MMA
+//             step advances the start address by 1024 B.
+//
+// 3xTF32: every operand X comes as two fp32 arrays, X itself (the tensor core reads its top 19 bits, i.e.
+// trunc_tf32(X)) and X_small = tf32(X - trunc_tf32(X)); the accumulator receives
+// A*B + A*B_small + A_small*B, which restores fp32-class accuracy (the dropped term is ~2^-22 relative).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gemm_tc.cuh"
+#include "host_util.h"
+#include "ptx_sm100.cuh"
+
+namespace odl
+{
+
+namespace
+{
+
+constexpr int kBM          = 128;  // rows of D per CTA == TMEM lanes == UMMA M
+constexpr int kBK          = 32;   // fp32 elements per 128-byte swizzle row
+constexpr int kUmmaK       = 8;    // K per tcgen05.mma for kind::tf32
+constexpr int kThreads     = 192;
+constexpr int kEpiWarps    = 4;
+constexpr int kStgLd       = 36;   // padded row length (floats) of the epilogue transpose slab
+constexpr int kGroupM      = 16;   // tile rasterisation: CTAs walk 16 row-tiles before moving to the next column-tile
+constexpr int kSmemBudget  = 227 * 1024;
+constexpr int kAuxBytes    = 1024;  // barriers, TMEM pointer, abort flag
+
+template <int BN>
+struct TileCfg
+{
+    static constexpr int a_bytes   = kBM * kBK * 4;
+    static constexpr int b_bytes   = BN * kBK * 4;
+    static constexpr int epi_bytes = kEpiWarps * 32 * kStgLd * 4;
+    __host__ __device__ static constexpr int stage_bytes(int terms) { return (a_bytes + b_bytes) * (terms == 3 ? 2 : 1); }
+    __host__ __device__ static constexpr int stages(int terms)
+    {
+        int s = (kSmemBudget - 1024 /*alignment slack*/ - kAuxBytes - epi_bytes) / stage_bytes(terms);
+        return s > 8 ? 8 : s;
+    }
+    __host__ __device__ static constexpr int smem_bytes(int terms) { return 1024 + kAuxBytes + epi_bytes + stages(terms) * stage_bytes(terms); }
+    static constexpr int tmem_cols = BN < 32 ? 32 : BN;  // power of two >= 32
+};
+
+// Debug knobs (test hook): overrides of the MN-major descriptor strides, and a dump of stage 0.
+struct DebugKnobs
+{
+    int lbo_mn, sbo_mn, step_mn;
+    float *dump;
+};
+DebugKnobs g_knobs = {4096, 512, 1024, nullptr};
+
+struct alignas(64) TmapPack
+{
+    CUtensorMap a, a_small, b, b_small;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
+               const int stages, const DebugKnobs knobs)
+{
+    using Cfg = TileCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+
+    // ---- carve shared memory (tiles need 1024-byte alignment for the 128-byte swizzle)
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int stage_bytes = Cfg::stage_bytes(terms);
+    uint8_t *tiles        = base;
+    float *stg_all        = reinterpret_cast<float *>(base + stages * stage_bytes);
+    uint8_t *aux_base     = reinterpret_cast<uint8_t *>(stg_all) + Cfg::epi_bytes;
+    uint64_t *full_bar    = reinterpret_cast<uint64_t *>(aux_base);
+    uint64_t *empty_bar   = full_bar + 8;
+    uint64_t *tmem_full   = empty_bar + 8;
+    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(tmem_full + 1);
+    volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *early_out        = const_cast<int *>(abort_f) + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- a launch that follows a timed-out one does nothing
+    if (threadIdx.x == 0)
+    {
+        *early_out = (p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        *abort_f   = 0;
+    }
+    __syncthreads();
+    if (*early_out)
+        return;
+
+    // ---- tile coordinates (grouped rasterisation for L2 reuse)
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    int tile_m, tile_n;
+    {
+        const int per_group = kGroupM * tiles_n;
+        const int g         = blockIdx.x / per_group;
+        const int first_m   = g * kGroupM;
+        const int gsz       = min(tiles_m - first_m, kGroupM);
+        const int local     = blockIdx.x - g * per_group;
+        tile_m              = first_m + local % gsz;
+        tile_n              = local / gsz;
+    }
+    const int m0     = tile_m * kBM;
+    const int n0     = tile_n * BN;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+
+    // ---- one-time setup
+    if (warp == 0 && lane == 0)
+    {
+        ptx::prefetch_tmap(&tm.a);
+        ptx::prefetch_tmap(&tm.b);
+        if (terms == 3)
+        {
+            ptx::prefetch_tmap(&tm.a_small);
+            ptx::prefetch_tmap(&tm.b_small);
+        }
+        for (int s = 0; s < stages; ++s)
+        {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        ptx::mbar_init(tmem_full, 1);
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1)
+    {
+        ptx::tmem_alloc(tmem_slot, Cfg::tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0)
+    {
+        // ================================================================= TMA producer
+        if (lane == 0)
+        {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb)
+            {
+                const int s       = kb % stages;
+                const uint32_t ph = (kb / stages) & 1;
+                if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
+                    break;
+                uint8_t *st = tiles + s * stage_bytes;
+                ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
+                const int k0 = kb * kBK;
+                for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
+                {
+                    uint8_t *sa           = st + t * Cfg::a_bytes;
+                    const CUtensorMap *ma = t ? &tm.a_small : &tm.a;
+                    if (!a_mn)
+                    {
+                        ptx::tma_load_2d(sa, ma, &full_bar[s], k0, m0);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int j = 0; j < kBM / 32; ++j)
+                            ptx::tma_load_2d(sa + j * 4096, ma, &full_bar[s], m0 + 32 * j, k0);
+                    }
+                }
+                uint8_t *sb0 = st + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
+                {
+                    uint8_t *sb           = sb0 + t * Cfg::b_bytes;
+                    const CUtensorMap *mb = t ? &tm.b_small : &tm.b;
+                    if (!b_mn)
+                    {
+                        ptx::tma_load_2d(sb, mb, &full_bar[s], k0, n0);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int j = 0; j < BN / 32; ++j)
+                            ptx::tma_load_2d(sb + j * 4096, mb, &full_bar[s], n0 + 32 * j, k0);
+                    }
+                }
+                ++issued;
+            }
+            if (*abort_f)
+            {
+                // Gave up somewhere: let the copies already in flight land before the CTA's memory is released.
+                const int first = issued > stages ? issued - stages : 0;
+                for (int kb = first; kb < issued; ++kb)
+                    ptx::mbar_wait(&full_bar[kb % stages], (kb / stages) & 1, nullptr);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ================================================================= MMA issuer
+        if (lane == 0)
+        {
+            const uint32_t idesc  = ptx::make_idesc_tf32(kBM, BN, a_mn != 0, b_mn != 0);
+            const uint32_t a_step = a_mn ? knobs.step_mn : 32u;  // bytes per K=8 step
+            const uint32_t b_step = b_mn ? knobs.step_mn : 32u;
+            const uint32_t a_lbo  = a_mn ? knobs.lbo_mn : 16u;
+            const uint32_t b_lbo  = b_mn ? knobs.lbo_mn : 16u;
+            const uint32_t a_sbo  = a_mn ? knobs.sbo_mn : 1024u;
+            const uint32_t b_sbo  = b_mn ? knobs.sbo_mn : 1024u;
+            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            bool ok               = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb)
+            {
+                const int s       = kb % stages;
+                const uint32_t ph = (kb / stages) & 1;
+                if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                const uint32_t sas = sa + Cfg::a_bytes;
+                const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                const uint32_t sbs = sb + Cfg::b_bytes;
+#pragma unroll
+                for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                {
+                    const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                    if (terms == 3)
+                    {
+                        const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
+                        const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
+                        // small cross terms first, the dominant term last
+                        ptx::mma_tf32_ss(tmem_base, das, db, idesc, (kb | kk) != 0);
+                        ptx::mma_tf32_ss(tmem_base, da, dbs, idesc, 1);
+                        ptx::mma_tf32_ss(tmem_base, da, db, idesc, 1);
+                    }
+                    else
+                    {
+                        ptx::mma_tf32_ss(tmem_base, da, db, idesc, (kb | kk) != 0);
+                    }
+                }
+                ptx::mma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+            }
+            if (ok)
+                ptx::mma_commit(tmem_full);  // accumulator complete
+        }
+    }
+    else
+    {
+        // ================================================================= epilogue (warps 2..5)
+        const int q     = warp & 3;  // TMEM lane quarter this warp may read
+        float *stg      = stg_all + (warp - 2) * 32 * kStgLd;
+        const bool have = __all_sync(0xffffffffu, ptx::mbar_wait(tmem_full, 0, abort_f));
+        ptx::tc_fence_after_sync();
+        if (have)
+        {
+            const int cg       = lane & 7;   // column group: columns 4cg..4cg+3 of the 32-column chunk
+            const int rr       = lane >> 3;  // row offset 0..3
+            const bool vec_d   = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+            const bool vec_s   = (p.flags & kEpiSmall) && ((reinterpret_cast<uintptr_t>(p.D_small) & 15) == 0);
+            const bool vec_aux = (p.flags & kEpiMask) && ((p.ld_aux & 3) == 0) &&
+                                 ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
+            for (int c0 = 0; c0 < BN; c0 += 32)
+            {
+                if (n0 + c0 >= p.N)
+                    break;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + c0, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                {
+                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    *reinterpret_cast<float4 *>(&stg[lane * kStgLd + 4 * i]) = v;
+                }
+                __syncwarp();
+
+                const int n = n0 + c0 + 4 * cg;
+                float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (p.flags & kEpiBias)
+                {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N)
+                            bias4[j] = __ldg(p.bias + n + j);
+                }
+                float csum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                {
+                    const int row = rr + 4 * i;
+                    const int m   = m0 + 32 * q + row;
+                    float4 v4     = *reinterpret_cast<const float4 *>(&stg[row * kStgLd + 4 * cg]);
+                    float v[4]    = {v4.x, v4.y, v4.z, v4.w};
+                    if (m < p.M && n < p.N)
+                    {
+                        const bool full4 = (n + 3 < p.N);
+                        if (p.flags & kEpiBias)
+                        {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                v[j] += bias4[j];
+                        }
+                        if (p.flags & kEpiRelu)
+                        {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                v[j] = v[j] > 0.f ? v[j] : 0.f;
+                        }
+                        if (p.flags & kEpiMask)
+                        {
+                            const float *ap = p.aux + static_cast<size_t>(m) * p.ld_aux + n;
+                            float a[4]      = {0.f, 0.f, 0.f, 0.f};
+                            if (vec_aux && full4)
+                            {
+                                const float4 a4 = __ldg(reinterpret_cast<const float4 *>(ap));
+                                a[0] = a4.x, a[1] = a4.y, a[2] = a4.z, a[3] = a4.w;
+                            }
+                            else
+                            {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    if (n + j < p.N)
+                                        a[j] = __ldg(ap + j);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                v[j] = a[j] > 0.f ? v[j] : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (n + j < p.N)
+                                csum[j] += v[j];
+                        float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
+                        if (vec_d && full4)
+                        {
+                            *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (n + j < p.N)
+                                    dp[j] = v[j];
+                        }
+                        if (p.flags & kEpiSmall)
+                        {
+                            float *sp = p.D_small + static_cast<size_t>(m) * p.ldd + n;
+                            if (vec_d && vec_s && full4)
+                            {
+                                *reinterpret_cast<float4 *>(sp) =
+                                    make_float4(tf32_small(v[0]), tf32_small(v[1]), tf32_small(v[2]), tf32_small(v[3]));
+                            }
+                            else
+                            {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    if (n + j < p.N)
+                                        sp[j] = tf32_small(v[j]);
+                            }
+                        }
+                    }
+                }
+                if (p.flags & kEpiColsum)
+                {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                    {
+                        csum[j] += __shfl_xor_sync(0xffffffffu, csum[j], 8);
+                        csum[j] += __shfl_xor_sync(0xffffffffu, csum[j], 16);
+                    }
+                    if (rr == 0)
+                    {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (n + j < p.N)
+                                atomicAdd(p.colsum + n + j, csum[j]);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        ptx::tc_fence_before_sync();
+    }
+
+    // ---- teardown: everyone is done with TMEM before warp 1 releases it
+    __syncthreads();
+    if (knobs.dump != nullptr && blockIdx.x == 0)
+    {
+        const float *src = reinterpret_cast<const float *>(tiles);
+        for (int i = threadIdx.x; i < stage_bytes / 4; i += kThreads)
+            knobs.dump[i] = src[i];
+    }
+    if (warp == 1)
+    {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, Cfg::tmem_cols);
+    }
+    if (threadIdx.x == 0 && *abort_f && p.err != nullptr)
+        atomicExch(p.err, 1);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// Tensor map over a row-major fp32 matrix with `rows` rows of `cols` contiguous elements (row pitch ld elements).
+int make_tmap(CUtensorMap *out, const float *ptr, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows,
+              CUtensorMapSwizzle swizzle)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn)
+    {
+        set_last_error("cuTensorMapEncodeTiled entry point not available");
+        return kCudaError;
+    }
+    cuuint64_t dims[2]    = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+    cuuint32_t box[2]     = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2]    = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+    {
+        set_last_error("cuTensorMapEncodeTiled failed: code %d (rows=%lld cols=%lld ld=%lld box=%dx%d ptr=%p)", (int)r,
+                       (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows, (const void *)ptr);
+        return kCudaError;
+    }
+    return kOk;
+}
+
+template <int BN>
+int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int terms, cudaStream_t stream)
+{
+    using Cfg        = TileCfg<BN>;
+    const int stages = Cfg::stages(terms);
+    const int smem   = Cfg::smem_bytes(terms);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!attr_set[dev])
+    {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             TileCfg<BN>::smem_bytes(1) > TileCfg<BN>::smem_bytes(3)
+                                                 ? TileCfg<BN>::smem_bytes(1)
+                                                 : TileCfg<BN>::smem_bytes(3));
+        if (e != cudaSuccess)
+        {
+            set_last_error("cudaFuncSetAttribute(smem=%d) failed: %s", smem, cudaGetErrorString(e));
+            return kCudaError;
+        }
+        attr_set[dev] = true;
+    }
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    gemm_tc_kernel<BN><<<tiles_m * tiles_n, kThreads, smem, stream>>>(tm, p, a_mn, b_mn, terms, stages, g_knobs);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("gemm_tc_kernel<%d> launch failed: %s", BN, cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
+}  // namespace
+
+void debug_set_knobs(int lbo_mn, int sbo_mn, int step_mn, float *dump)
+{
+    g_knobs = DebugKnobs{lbo_mn, sbo_mn, step_mn, dump};
+}
+
+// A / B operands must already satisfy the tiled-load rules (16-byte aligned base, ld % 4 == 0); the callers in
+// linear.cu stage anything else through padded scratch.  a_mn / b_mn: 0 = K-major storage, 1 = MN-major storage.
+int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
+                   int64_t ldb, int b_mn, const GemmParams &p, int terms, int bn_hint, cudaStream_t stream)
+{
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || !A || !B || !p.D || (terms != 1 && terms != 3))
+    {
+        set_last_error("gemm: invalid argument (M=%d N=%d K=%d terms=%d)", p.M, p.N, p.K, terms);
+        return kInvalidArgument;
+    }
+    if (terms == 3 && (!A_small || !B_small))
+    {
+        set_last_error("gemm: 3xTF32 needs the low parts of both operands");
+        return kInvalidArgument;
+    }
+    auto misaligned = [](const void *ptr, int64_t ld) { return (reinterpret_cast<uintptr_t>(ptr) & 15) || (ld & 3); };
+    if (misaligned(A, lda) || misaligned(B, ldb) || (terms == 3 && (misaligned(A_small, lda) || misaligned(B_small, ldb))))
+    {
+        set_last_error("gemm: operand violates the 16-byte rule (lda=%lld ldb=%lld)", (long long)lda, (long long)ldb);
+        return kMisaligned;
+    }
+    int bn = bn_hint;
+    if (bn != 64 && bn != 128 && bn != 256)
+    {
+        // widest tile that still fills the machine reasonably
+        const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
+        const int64_t tiles128 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 127) / 128);
+        if (p.N > 128 && tiles256 >= 148)
+            bn = 256;
+        else if (p.N > 64 && tiles128 >= 74)
+            bn = 128;
+        else
+            bn = p.N > 128 ? 128 : (p.N > 64 ? 128 : 64);
+    }
+    TmapPack tm;
+    std::memset(&tm, 0, sizeof(tm));
+    int rc;
+    // A: K-major -> matrix [M][K], box {32, 128};  MN-major -> matrix [K][M], box {32, 32}
+    auto mk = [&](CUtensorMap *m, const float *ptr, int64_t ld, int mn, int64_t extent_mn, int box_rows_kmajor) {
+        return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+                  : make_tmap(m, ptr, extent_mn, p.K, ld, 32, box_rows_kmajor, CU_TENSOR_MAP_SWIZZLE_128B);
+    };
+    if ((rc = mk(&tm.a, A, lda, a_mn, p.M, kBM)))
+        return rc;
+    if ((rc = mk(&tm.b, B, ldb, b_mn, p.N, bn)))
+        return rc;
+    if (terms == 3)
+    {
+        if ((rc = mk(&tm.a_small, A_small, lda, a_mn, p.M, kBM)))
+            return rc;
+        if ((rc = mk(&tm.b_small, B_small, ldb, b_mn, p.N, bn)))
+            return rc;
+    }
+    switch (bn)
+    {
+        case 64:
+            return launch_bn<64>(tm, p, a_mn, b_mn, terms, stream);
+        case 128:
+            return launch_bn<128>(tm, p, a_mn, b_mn, terms, stream);
+        default:
+            return launch_bn<256>(tm, p, a_mn, b_mn, terms, stream);
+    }
+}
+
+}  // namespace odl
