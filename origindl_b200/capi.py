@@ -37,7 +37,7 @@ _SIGNATURES = {
     "odl_init": [c_int],
     "odl_device_status": [_P],
     "odl_debug_set_tile_n": [c_int],
-    "odl_debug_set_knobs": [c_int, c_int, c_int, _P],
+    "odl_debug_set_chunk": [c_int],
     "odl_matmul": [_P, _P, _P, _I64, _I64, _I64, _I64, c_int, c_int, _P],
     "odl_gemm_ex": [c_int, c_int, _I64, _I64, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P,
                     c_int, c_int, _P],

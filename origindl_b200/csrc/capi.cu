@@ -311,9 +311,10 @@ int64_t odl_scratch_bytes(void)
     return static_cast<int64_t>(g_state.capacity);
 }
 
-int odl_debug_set_knobs(int lbo_mn, int sbo_mn, int step_mn, float *dump)
+// Test hook: K-blocks of 32 accumulated in TMEM between drains into registers (0 = default).
+int odl_debug_set_chunk(int chunk_kb)
 {
-    debug_set_knobs(lbo_mn, sbo_mn, step_mn, dump);
+    g_chunk_kb = chunk_kb;
     return kOk;
 }
 

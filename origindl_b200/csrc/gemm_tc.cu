@@ -41,46 +41,44 @@ namespace
 constexpr int kBM          = 128;  // rows of D per CTA == TMEM lanes == UMMA M
 constexpr int kBK          = 32;   // fp32 elements per 128-byte swizzle row
 constexpr int kUmmaK       = 8;    // K per tcgen05.mma for kind::tf32
-constexpr int kThreads     = 192;
-constexpr int kEpiWarps    = 4;
+constexpr int kEpiWarps    = 8;    // two warps per TMEM lane quarter, each owning half of the tile's columns
+constexpr int kThreads     = 64 + 32 * kEpiWarps;
 constexpr int kStgLd       = 36;   // padded row length (floats) of the epilogue transpose slab
 constexpr int kGroupM      = 16;   // tile rasterisation: CTAs walk 16 row-tiles before moving to the next column-tile
 constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kAuxBytes    = 1024;  // barriers, TMEM pointer, abort flag
+constexpr int kMaxStages   = 8;
 
 template <int BN>
 struct TileCfg
 {
     static constexpr int a_bytes   = kBM * kBK * 4;
     static constexpr int b_bytes   = BN * kBK * 4;
-    static constexpr int epi_bytes = kEpiWarps * 32 * kStgLd * 4;
     __host__ __device__ static constexpr int stage_bytes(int terms) { return (a_bytes + b_bytes) * (terms == 3 ? 2 : 1); }
     __host__ __device__ static constexpr int stages(int terms)
     {
-        int s = (kSmemBudget - 1024 /*alignment slack*/ - kAuxBytes - epi_bytes) / stage_bytes(terms);
-        return s > 8 ? 8 : s;
+        // the ring (>= 48 KB in every configuration) also hosts the 36 KB of epilogue transpose slabs afterwards
+        int s = (kSmemBudget - 1024 /*alignment slack*/ - kAuxBytes) / stage_bytes(terms);
+        return s > kMaxStages ? kMaxStages : s;
     }
-    __host__ __device__ static constexpr int smem_bytes(int terms) { return 1024 + kAuxBytes + epi_bytes + stages(terms) * stage_bytes(terms); }
-    static constexpr int tmem_cols = BN < 32 ? 32 : BN;  // power of two >= 32
+    __host__ __device__ static constexpr int smem_bytes(int terms) { return 1024 + kAuxBytes + stages(terms) * stage_bytes(terms); }
+    static constexpr int tmem_cols  = 2 * BN;  // two accumulators: the MMAs fill one while the other is drained
+    static constexpr int warp_cols  = BN / 2;  // columns of the tile owned by one epilogue warp
 };
-
-// Debug knobs (test hook): overrides of the MN-major descriptor strides, and a dump of stage 0.
-struct DebugKnobs
-{
-    int lbo_mn, sbo_mn, step_mn;
-    float *dump;
-};
-DebugKnobs g_knobs = {4096, 512, 1024, nullptr};
 
 struct alignas(64) TmapPack
 {
     CUtensorMap a, a_small, b, b_small;
 };
 
+// The accumulator is drained from TMEM into fp32 registers every `chunk_kb` K-blocks.  The tensor core adds into
+// TMEM with truncation, which biases a long running sum towards zero by about 7.5e-9 * (chunk length in K) relative
+// to the largest result; summing short chunks in registers (round-to-nearest) keeps 3xTF32 at fp32-class accuracy
+// for any K.
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
-               const int stages, const DebugKnobs knobs)
+               const int stages, const int chunk_kb)
 {
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -89,12 +87,13 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stage_bytes = Cfg::stage_bytes(terms);
     uint8_t *tiles        = base;
-    float *stg_all        = reinterpret_cast<float *>(base + stages * stage_bytes);
-    uint8_t *aux_base     = reinterpret_cast<uint8_t *>(stg_all) + Cfg::epi_bytes;
+    float *stg_all        = reinterpret_cast<float *>(base);  // reused after the last MMA has read the ring
+    uint8_t *aux_base     = base + stages * stage_bytes;
     uint64_t *full_bar    = reinterpret_cast<uint64_t *>(aux_base);
-    uint64_t *empty_bar   = full_bar + 8;
-    uint64_t *tmem_full   = empty_bar + 8;
-    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(tmem_full + 1);
+    uint64_t *empty_bar   = full_bar + kMaxStages;
+    uint64_t *acc_full    = empty_bar + kMaxStages;  // [2]
+    uint64_t *acc_empty   = acc_full + 2;            // [2]
+    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
     int *early_out        = const_cast<int *>(abort_f) + 1;
 
@@ -124,9 +123,10 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
         tile_m              = first_m + local % gsz;
         tile_n              = local / gsz;
     }
-    const int m0     = tile_m * kBM;
-    const int n0     = tile_n * BN;
-    const int num_kb = (p.K + kBK - 1) / kBK;
+    const int m0      = tile_m * kBM;
+    const int n0      = tile_n * BN;
+    const int num_kb  = (p.K + kBK - 1) / kBK;
+    const int nchunks = (num_kb + chunk_kb - 1) / chunk_kb;
 
     // ---- one-time setup
     if (warp == 0 && lane == 0)
@@ -143,7 +143,11 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
         }
-        ptx::mbar_init(tmem_full, 1);
+        for (int b = 0; b < 2; ++b)
+        {
+            ptx::mbar_init(&acc_full[b], 1);
+            ptx::mbar_init(&acc_empty[b], kEpiWarps);
+        }
         ptx::fence_mbar_init();
     }
     if (warp == 1)
@@ -219,188 +223,241 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
         if (lane == 0)
         {
             const uint32_t idesc  = ptx::make_idesc_tf32(kBM, BN, a_mn != 0, b_mn != 0);
-            const uint32_t a_step = a_mn ? knobs.step_mn : 32u;  // bytes per K=8 step
-            const uint32_t b_step = b_mn ? knobs.step_mn : 32u;
-            const uint32_t a_lbo  = a_mn ? knobs.lbo_mn : 16u;
-            const uint32_t b_lbo  = b_mn ? knobs.lbo_mn : 16u;
-            const uint32_t a_sbo  = a_mn ? knobs.sbo_mn : 1024u;
-            const uint32_t b_sbo  = b_mn ? knobs.sbo_mn : 1024u;
+            const uint32_t a_step = a_mn ? 1024u : 32u;  // bytes per K=8 step
+            const uint32_t b_step = b_mn ? 1024u : 32u;
+            const uint32_t a_lbo  = a_mn ? 4096u : 16u;
+            const uint32_t b_lbo  = b_mn ? 4096u : 16u;
+            const uint32_t a_sbo  = a_mn ? 512u : 1024u;
+            const uint32_t b_sbo  = b_mn ? 512u : 1024u;
             const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
             const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
             bool ok               = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb)
+            int kb                = 0;
+            for (int c = 0; c < nchunks && ok; ++c)
             {
-                const int s       = kb % stages;
-                const uint32_t ph = (kb / stages) & 1;
-                if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
+                const int buf        = c & 1;
+                const uint32_t use   = static_cast<uint32_t>(c >> 1);
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                if (!ptx::mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_f))
                 {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
-                const uint32_t sas = sa + Cfg::a_bytes;
-                const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
-                const uint32_t sbs = sb + Cfg::b_bytes;
-#pragma unroll
-                for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                const int kb_end = min(kb + chunk_kb, num_kb);
+                for (bool first = true; kb < kb_end; ++kb)
                 {
-                    const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
-                    const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
-                    if (terms == 3)
+                    const int s       = kb % stages;
+                    const uint32_t ph = (kb / stages) & 1;
+                    if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
                     {
-                        const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
-                        const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
-                        // small cross terms first, the dominant term last
-                        ptx::mma_tf32_ss(tmem_base, das, db, idesc, (kb | kk) != 0);
-                        ptx::mma_tf32_ss(tmem_base, da, dbs, idesc, 1);
-                        ptx::mma_tf32_ss(tmem_base, da, db, idesc, 1);
+                        ok = false;
+                        break;
                     }
-                    else
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                    const uint32_t sas = sa + Cfg::a_bytes;
+                    const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                    const uint32_t sbs = sb + Cfg::b_bytes;
+#pragma unroll
+                    for (int kk = 0; kk < kBK / kUmmaK; ++kk)
                     {
-                        ptx::mma_tf32_ss(tmem_base, da, db, idesc, (kb | kk) != 0);
+                        const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                        const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                        if (terms == 3)
+                        {
+                            const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
+                            const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
+                            // small cross terms first, the dominant term last
+                            ptx::mma_tf32_ss(tmem_d, das, db, idesc, first ? 0u : 1u);
+                            ptx::mma_tf32_ss(tmem_d, da, dbs, idesc, 1);
+                            ptx::mma_tf32_ss(tmem_d, da, db, idesc, 1);
+                        }
+                        else
+                        {
+                            ptx::mma_tf32_ss(tmem_d, da, db, idesc, first ? 0u : 1u);
+                        }
+                        first = false;
                     }
+                    ptx::mma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
                 }
-                ptx::mma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+                if (ok)
+                    ptx::mma_commit(&acc_full[buf]);  // this chunk's accumulator is complete
             }
-            if (ok)
-                ptx::mma_commit(tmem_full);  // accumulator complete
         }
     }
     else
     {
-        // ================================================================= epilogue (warps 2..5)
-        const int q     = warp & 3;  // TMEM lane quarter this warp may read
-        float *stg      = stg_all + (warp - 2) * 32 * kStgLd;
-        const bool have = __all_sync(0xffffffffu, ptx::mbar_wait(tmem_full, 0, abort_f));
-        ptx::tc_fence_after_sync();
+        // ================================================================= accumulate + epilogue (warps 2..9)
+        const int e  = warp - 2;
+        const int q  = warp & 3;                      // TMEM lane quarter this warp may read
+        const int h  = e >> 2;                        // which half of the tile's columns
+        const int cw = h * Cfg::warp_cols;            // first column owned by this warp
+        float acc[Cfg::warp_cols];
+        bool have = true;
+        for (int c = 0; c < nchunks; ++c)
+        {
+            const int buf      = c & 1;
+            const uint32_t use = static_cast<uint32_t>(c >> 1);
+            have = __all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], use & 1, abort_f));
+            if (!have)
+                break;
+            ptx::tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * BN + cw;
+#pragma unroll
+            for (int j = 0; j < Cfg::warp_cols / 32; ++j)
+            {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(taddr + 32 * j, r);
+                ptx::tmem_ld_wait();
+                if (c == 0)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        acc[32 * j + i] = __uint_as_float(r[i]);
+                }
+                else
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        acc[32 * j + i] += __uint_as_float(r[i]);
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive(&acc_empty[buf]);
+        }
         if (have)
         {
+            // The last acc_full has fired, so every MMA has completed and every tile load was consumed: the operand
+            // ring is dead and its first bytes now serve as per-warp transpose slabs (disjoint between warps).
+            float *stg         = stg_all + e * 32 * kStgLd;
             const int cg       = lane & 7;   // column group: columns 4cg..4cg+3 of the 32-column chunk
             const int rr       = lane >> 3;  // row offset 0..3
             const bool vec_d   = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
             const bool vec_s   = (p.flags & kEpiSmall) && ((reinterpret_cast<uintptr_t>(p.D_small) & 15) == 0);
             const bool vec_aux = (p.flags & kEpiMask) && ((p.ld_aux & 3) == 0) &&
                                  ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
-            for (int c0 = 0; c0 < BN; c0 += 32)
+#pragma unroll
+            for (int j = 0; j < Cfg::warp_cols / 32; ++j)
             {
-                if (n0 + c0 >= p.N)
-                    break;
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + c0, r);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
+                const int c0 = cw + 32 * j;
+                if (n0 + c0 < p.N)
                 {
-                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                    *reinterpret_cast<float4 *>(&stg[lane * kStgLd + 4 * i]) = v;
-                }
-                __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                    {
+                        float4 v = make_float4(acc[32 * j + 4 * i], acc[32 * j + 4 * i + 1], acc[32 * j + 4 * i + 2],
+                                               acc[32 * j + 4 * i + 3]);
+                        *reinterpret_cast<float4 *>(&stg[lane * kStgLd + 4 * i]) = v;
+                    }
+                    __syncwarp();
 
-                const int n = n0 + c0 + 4 * cg;
-                float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-                if (p.flags & kEpiBias)
-                {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (n + j < p.N)
-                            bias4[j] = __ldg(p.bias + n + j);
-                }
-                float csum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                {
-                    const int row = rr + 4 * i;
-                    const int m   = m0 + 32 * q + row;
-                    float4 v4     = *reinterpret_cast<const float4 *>(&stg[row * kStgLd + 4 * cg]);
-                    float v[4]    = {v4.x, v4.y, v4.z, v4.w};
-                    if (m < p.M && n < p.N)
+                    const int n    = n0 + c0 + 4 * cg;
+                    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (p.flags & kEpiBias)
                     {
-                        const bool full4 = (n + 3 < p.N);
-                        if (p.flags & kEpiBias)
-                        {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                v[j] += bias4[j];
-                        }
-                        if (p.flags & kEpiRelu)
-                        {
+                        for (int jj = 0; jj < 4; ++jj)
+                            if (n + jj < p.N)
+                                bias4[jj] = __ldg(p.bias + n + jj);
+                    }
+                    float csum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                v[j] = v[j] > 0.f ? v[j] : 0.f;
-                        }
-                        if (p.flags & kEpiMask)
+                    for (int i = 0; i < 8; ++i)
+                    {
+                        const int row = rr + 4 * i;
+                        const int m   = m0 + 32 * q + row;
+                        float4 v4     = *reinterpret_cast<const float4 *>(&stg[row * kStgLd + 4 * cg]);
+                        float v[4]    = {v4.x, v4.y, v4.z, v4.w};
+                        if (m < p.M && n < p.N)
                         {
-                            const float *ap = p.aux + static_cast<size_t>(m) * p.ld_aux + n;
-                            float a[4]      = {0.f, 0.f, 0.f, 0.f};
-                            if (vec_aux && full4)
+                            const bool full4 = (n + 3 < p.N);
+                            if (p.flags & kEpiBias)
                             {
-                                const float4 a4 = __ldg(reinterpret_cast<const float4 *>(ap));
-                                a[0] = a4.x, a[1] = a4.y, a[2] = a4.z, a[3] = a4.w;
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+                                    v[jj] += bias4[jj];
+                            }
+                            if (p.flags & kEpiRelu)
+                            {
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+                                    v[jj] = v[jj] > 0.f ? v[jj] : 0.f;
+                            }
+                            if (p.flags & kEpiMask)
+                            {
+                                const float *ap = p.aux + static_cast<size_t>(m) * p.ld_aux + n;
+                                float a[4]      = {0.f, 0.f, 0.f, 0.f};
+                                if (vec_aux && full4)
+                                {
+                                    const float4 a4 = __ldg(reinterpret_cast<const float4 *>(ap));
+                                    a[0] = a4.x, a[1] = a4.y, a[2] = a4.z, a[3] = a4.w;
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for (int jj = 0; jj < 4; ++jj)
+                                        if (n + jj < p.N)
+                                            a[jj] = __ldg(ap + jj);
+                                }
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+                                    v[jj] = a[jj] > 0.f ? v[jj] : 0.f;
+                            }
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                if (n + jj < p.N)
+                                    csum[jj] += v[jj];
+                            float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
+                            if (vec_d && full4)
+                            {
+                                *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
                             }
                             else
                             {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    if (n + j < p.N)
-                                        a[j] = __ldg(ap + j);
+                                for (int jj = 0; jj < 4; ++jj)
+                                    if (n + jj < p.N)
+                                        dp[jj] = v[jj];
                             }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                v[j] = a[j] > 0.f ? v[j] : 0.f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (n + j < p.N)
-                                csum[j] += v[j];
-                        float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
-                        if (vec_d && full4)
-                        {
-                            *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                if (n + j < p.N)
-                                    dp[j] = v[j];
-                        }
-                        if (p.flags & kEpiSmall)
-                        {
-                            float *sp = p.D_small + static_cast<size_t>(m) * p.ldd + n;
-                            if (vec_d && vec_s && full4)
+                            if (p.flags & kEpiSmall)
                             {
-                                *reinterpret_cast<float4 *>(sp) =
-                                    make_float4(tf32_small(v[0]), tf32_small(v[1]), tf32_small(v[2]), tf32_small(v[3]));
-                            }
-                            else
-                            {
+                                float *sp = p.D_small + static_cast<size_t>(m) * p.ldd + n;
+                                if (vec_d && vec_s && full4)
+                                {
+                                    *reinterpret_cast<float4 *>(sp) = make_float4(tf32_small(v[0]), tf32_small(v[1]),
+                                                                                  tf32_small(v[2]), tf32_small(v[3]));
+                                }
+                                else
+                                {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    if (n + j < p.N)
-                                        sp[j] = tf32_small(v[j]);
+                                    for (int jj = 0; jj < 4; ++jj)
+                                        if (n + jj < p.N)
+                                            sp[jj] = tf32_small(v[jj]);
+                                }
                             }
                         }
                     }
-                }
-                if (p.flags & kEpiColsum)
-                {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                    {
-                        csum[j] += __shfl_xor_sync(0xffffffffu, csum[j], 8);
-                        csum[j] += __shfl_xor_sync(0xffffffffu, csum[j], 16);
-                    }
-                    if (rr == 0)
+                    if (p.flags & kEpiColsum)
                     {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (n + j < p.N)
-                                atomicAdd(p.colsum + n + j, csum[j]);
+                        for (int jj = 0; jj < 4; ++jj)
+                        {
+                            csum[jj] += __shfl_xor_sync(0xffffffffu, csum[jj], 8);
+                            csum[jj] += __shfl_xor_sync(0xffffffffu, csum[jj], 16);
+                        }
+                        if (rr == 0)
+                        {
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                if (n + jj < p.N)
+                                    atomicAdd(p.colsum + n + jj, csum[jj]);
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
         ptx::tc_fence_before_sync();
@@ -408,12 +465,6 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 
     // ---- teardown: everyone is done with TMEM before warp 1 releases it
     __syncthreads();
-    if (knobs.dump != nullptr && blockIdx.x == 0)
-    {
-        const float *src = reinterpret_cast<const float *>(tiles);
-        for (int i = threadIdx.x; i < stage_bytes / 4; i += kThreads)
-            knobs.dump[i] = src[i];
-    }
     if (warp == 1)
     {
         __syncwarp();
@@ -425,6 +476,10 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 }
 
 // ---------------------------------------------------------------------------------------------- host side
+}  // namespace
+extern int g_chunk_kb;
+namespace
+{
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -494,7 +549,11 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     }
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
-    gemm_tc_kernel<BN><<<tiles_m * tiles_n, kThreads, smem, stream>>>(tm, p, a_mn, b_mn, terms, stages, g_knobs);
+    const int num_kb   = (p.K + kBK - 1) / kBK;
+    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 8 : num_kb);
+    if (chunk_kb > num_kb)
+        chunk_kb = num_kb;
+    gemm_tc_kernel<BN><<<tiles_m * tiles_n, kThreads, smem, stream>>>(tm, p, a_mn, b_mn, terms, stages, chunk_kb);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
@@ -506,10 +565,9 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
 
 }  // namespace
 
-void debug_set_knobs(int lbo_mn, int sbo_mn, int step_mn, float *dump)
-{
-    g_knobs = DebugKnobs{lbo_mn, sbo_mn, step_mn, dump};
-}
+// Test hook: K-blocks (of 32) accumulated in TMEM between two drains into registers; 0 = default
+// (8, i.e. K = 256, for 3xTF32; the whole K for plain TF32).
+int g_chunk_kb = 0;
 
 // A / B operands must already satisfy the tiled-load rules (16-byte aligned base, ld % 4 == 0); the callers in
 // linear.cu stage anything else through padded scratch.  a_mn / b_mn: 0 = K-major storage, 1 = MN-major storage.

@@ -18,7 +18,7 @@ int arena_reserve(size_t total_bytes);
 void *arena_alloc(size_t bytes);
 
 extern int g_bn_override;
-void debug_set_knobs(int lbo_mn, int sbo_mn, int step_mn, float *dump);
+extern int g_chunk_kb;
 
 int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
                    int64_t ldb, int b_mn, const GemmParams &p, int terms, int bn_hint, cudaStream_t stream);
