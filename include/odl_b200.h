@@ -85,6 +85,94 @@ int odl_gemm_ex(int transA, int transB, int64_t M, int64_t N, int64_t K, const f
 int odl_split_tf32(const float *src, int64_t ld_src, int64_t rows, int64_t cols, const float *mask_src, int64_t ld_mask,
                    float *dst_big, float *dst_small, int64_t ld_dst, float *colsum, void *stream);
 
+/* ---- Linear ------------------------------------------------------------------------------------------------- */
+
+/* y[M,N] = relu?(x[M,K] . op(W) + b) in one kernel (GEMM with bias / ReLU epilogue).
+ * w_layout ODL_W_OUT_IN replaces LinearOp::forward / functional::custom_linear (src/operators/custom/linear.cpp:12-144);
+ * ODL_W_IN_OUT replaces nn::Linear::forward = mat_mul + broadcast_to + add (src/nn/layers/linear.cpp:80-106), and with
+ * relu != 0 also the following functional::relu (src/operators/activation/relu.cpp:13-35; MLP::forward,
+ * src/nn/models/mlp.cpp:43-61).  b may be NULL.  x_small / w_small: optional resident low parts (3xTF32);
+ * y_small: optional output, the low part of y for the next layer's GEMM. */
+int odl_linear_forward(const float *x, const float *x_small, const float *w, const float *w_small, const float *b,
+                       float *y, float *y_small, int64_t M, int64_t N, int64_t K, int w_layout, int relu, int precision,
+                       void *stream);
+
+/* Gradients of the layer above for upstream dy[M,N]:  g = y ? dy * (y > 0) : dy;  db[N] = colsum(g);
+ * dx[M,K] = g . W;  dW = g^T . x (same layout as W).  The rule LinearOp::backward leaves unimplemented
+ * (src/operators/custom/linear.cpp:116-121), equal to the chain ReLU::backward (relu.cpp:37-54) ->
+ * Add::backward / BroadcastTo::backward -> sum_to (src/operators/math/add.cpp:29-55, broadcast_to.cpp:29-46) ->
+ * MatMul::backward (src/operators/math/mat_mul.cpp:123-182).  y is the forward OUTPUT when the layer had a ReLU, else NULL.
+ * dx, dw, db may each be NULL (not computed). */
+int odl_linear_backward(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy,
+                        const float *y, float *dx, float *dw, float *db, int64_t M, int64_t N, int64_t K, int w_layout,
+                        int precision, void *stream);
+
+/* Same, for a layer inside an MLP: the dx GEMM's epilogue already applies the PREVIOUS layer's ReLU mask
+ * (prev_y[M,K] > 0), sums the previous layer's bias gradient prev_db[K] and emits dx_small, so the previous layer's
+ * backward needs no preparation pass of its own (pass its y = NULL and db = NULL there and dx here as its dy).
+ * No counterpart in the reference (it runs these as separate kernels). */
+int odl_linear_backward_chain(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
+                              const float *y, float *dx, float *dx_small, const float *prev_y, float *prev_db, float *dw,
+                              float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, void *stream);
+
+/* ---- element-wise pieces of the operator API -------------------------------------------------------------------- */
+
+/* y = x > 0 ? x : 0.  Replaces origin::cuda::relu (include/origin/mat/origin/cuda/cuda_ops.cuh:186). */
+int odl_relu_forward(const float *x, float *y, int64_t n, void *stream);
+/* gx = gy * (x_or_y > 0).  Replaces gt + multiply of ReLU::backward (cuda_ops.cuh:125,:75; relu.cpp:37-54). */
+int odl_relu_backward(const float *gy, const float *x_or_y, float *gx, int64_t n, void *stream);
+/* y[m,n] = x[m,n] + b[n].  Replaces broadcast_to + add (cuda_ops.cuh:304,:57) as used by nn::Linear. */
+int odl_add_bias(const float *x, const float *b, float *y, int64_t M, int64_t N, void *stream);
+/* out[n] = sum_m g[m,n].  Replaces origin::cuda::sum_to for {M,N} -> {1,N} (cuda_ops.cuh:312;
+ * src/mat/origin/cuda/math/sum_to.cu:19-91), without its N <= 1024 launch limit (sum.cu:284-287). */
+int odl_sum_to_row(const float *g, float *out, int64_t M, int64_t N, void *stream);
+
+/* ---- loss ------------------------------------------------------------------------------------------------------- */
+
+/* loss[0] = -(1/B) sum_i log(softmax(logits)[i,t_i] + 1e-8) and/or dlogits = (softmax - onehot) * grad_scale / B, both
+ * on the device in two launches and without host synchronisation.  Replaces SoftmaxCrossEntropy::forward/backward
+ * (src/operators/loss/softmax_cross_entropy.cpp:17-111, ~25 kernels and two .item() syncs).  labels: int32 or int64
+ * (labels_are_int64); an out-of-range label is reported by odl_device_status as ODL_ERR_INVALID_ARGUMENT (the
+ * reference throws from gather, src/mat/origin/cpu/nn/gather.cpp:58-87).  loss or dlogits may be NULL. */
+int odl_softmax_cross_entropy(const float *logits, const void *labels, int labels_are_int64, int64_t B, int64_t C,
+                              float *loss, float *dlogits, float grad_scale, void *stream);
+
+/* ---- optimizers -------------------------------------------------------------------------------------------------- */
+
+/* One fused in-place Adam update of n contiguous parameters at step t (1-based), same operation order and fp32 rounding
+ * as Adam::step_one (src/optim/adam.cpp:19-114) preceded by the WeightDecay hook (include/origin/optim/hooks.h:40-66;
+ * grad += hook_weight_decay * param, written back to grad) when hook_weight_decay > 0.  grad_scale multiplies the
+ * gradient first (1/world_size after a summing all-reduce; 1 otherwise).  param_small: optional output, low part of
+ * the updated parameters for the next 3xTF32 GEMM. */
+int odl_adam_step(float *param, float *grad, float *m, float *v, float *param_small, int64_t n, int t, float lr,
+                  float beta1, float beta2, float eps, float hook_weight_decay, float grad_scale, void *stream);
+
+/* One fused in-place SGD update: SGD::step_one (src/optim/sgd.cpp:18-75) with weight_decay, momentum and Nesterov,
+ * after the optional WeightDecay hook.  momentum_buf may be NULL when momentum == 0. */
+int odl_sgd_step(float *param, float *grad, float *momentum_buf, float *param_small, int64_t n, float lr, float momentum,
+                 float weight_decay, int nesterov, float hook_weight_decay, float grad_scale, void *stream);
+
+/* ---- Conv2d (im2col + GEMM) -------------------------------------------------------------------------------------- */
+
+/* col[N*OH*OW, C*KH*KW] from x[N,C,H,W]; replaces origin::cuda::im2col (cuda_ops.cuh:335; conv2d.cu:32,:255,:417)
+ * without the padded image copy.  C*KH*KW must be a multiple of 4 in this public row-matrix form. */
+int odl_im2col(const float *x, float *col, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int stride, int pad,
+               void *stream);
+/* x[N,C,H,W] = scatter-add of col; replaces origin::cuda::col2im (cuda_ops.cuh:349; conv2d.cu:146,:322) with a gather
+ * that needs no atomics. */
+int odl_col2im(const float *col, float *x, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int stride, int pad,
+               void *stream);
+/* y[N,OC,OH,OW] = conv2d(x, w[OC,C,KH,KW]) + b, optional fused ReLU.  Replaces origin::cuda::conv2d (cuda_ops.cuh:363;
+ * src/mat/origin/cuda/conv/conv2d.cu:563-678): im2col, one GEMM whose epilogue adds the bias and writes NCHW directly. */
+int odl_conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H,
+                       int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int relu, int precision, void *stream);
+/* gx, gw, gb for upstream gy[N,OC,OH,OW]; replaces origin::cuda::conv2d_backward (cuda_ops.cuh:376; conv2d.cu:680-765).
+ * gy_layout 0: gy is permuted to [N*OH*OW, OC] (the gradient of the forward pass); 1: the NCHW buffer is
+ * reinterpreted as [N*OH*OW, OC] exactly as the reference does (conv2d.cu:714).  gx, gw, gb may each be NULL. */
+int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N,
+                        int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int gy_layout,
+                        int precision, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

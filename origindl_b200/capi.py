@@ -42,6 +42,22 @@ _SIGNATURES = {
     "odl_gemm_ex": [c_int, c_int, _I64, _I64, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P, _P, _I64, _P,
                     c_int, c_int, _P],
     "odl_split_tf32": [_P, _I64, _I64, _I64, _P, _I64, _P, _P, _I64, _P, _P],
+    "odl_debug_set_split_k": [c_int],
+    "odl_linear_forward": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, c_int, _P],
+    "odl_linear_backward": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],
+    "odl_linear_backward_chain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],
+    "odl_relu_forward": [_P, _P, _I64, _P],
+    "odl_relu_backward": [_P, _P, _P, _I64, _P],
+    "odl_add_bias": [_P, _P, _P, _I64, _I64, _P],
+    "odl_sum_to_row": [_P, _P, _I64, _I64, _P],
+    "odl_softmax_cross_entropy": [_P, _P, c_int, _I64, _I64, _P, _P, c_float, _P],
+    "odl_adam_step": [_P, _P, _P, _P, _P, _I64, c_int, c_float, c_float, c_float, c_float, c_float, c_float, _P],
+    "odl_sgd_step": [_P, _P, _P, _P, _I64, c_float, c_float, c_float, c_int, c_float, c_float, _P],
+    "odl_im2col": [_P, _P, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, _P],
+    "odl_col2im": [_P, _P, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, _P],
+    "odl_conv2d_forward": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "odl_conv2d_backward": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, c_int,
+                            c_int, _P],
 }
 
 

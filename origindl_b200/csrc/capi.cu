@@ -176,7 +176,7 @@ int prepare_operand(const float *ptr, const float *small, int64_t ld, int64_t ro
 int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
                   int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
                   const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
-                  cudaStream_t stream, bool reset_arena)
+                  cudaStream_t stream, bool reset_arena, int ohw)
 {
     if (!is_ready())
     {
@@ -241,6 +241,8 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
     p.ldd     = (int)ldd;
     p.ld_aux  = (int)ld_mask;
     p.flags   = flags;
+    p.ohw     = ohw;
+    p.kb_per_split = 0;
     const int a_mn = transA ? 1 : 0;
     const int b_mn = transB ? 0 : 1;
     return gemm_tc_launch(pa.big, pa.small, pa.ld, a_mn, pb.big, pb.small, pb.ld, b_mn, p, terms, g_bn_override, stream);
@@ -300,6 +302,11 @@ int odl_device_status(void *stream)
     {
         ODL_CUDA_TRY(cudaMemsetAsync(g_state.err_flag, 0, sizeof(int), s));
         ODL_CUDA_TRY(cudaStreamSynchronize(s));
+        if (flag == 2)
+        {
+            set_last_error("softmax_cross_entropy: label out of range");
+            return kInvalidArgument;
+        }
         set_last_error("a kernel gave up on a bounded wait (pipeline barrier never completed)");
         return kKernelTimeout;
     }
@@ -309,6 +316,12 @@ int odl_device_status(void *stream)
 int64_t odl_scratch_bytes(void)
 {
     return static_cast<int64_t>(g_state.capacity);
+}
+
+int odl_debug_set_split_k(int splits)
+{
+    g_split_k = splits;
+    return kOk;
 }
 
 // Test hook: K-blocks of 32 accumulated in TMEM between drains into registers (0 = default).
@@ -369,6 +382,128 @@ int odl_split_tf32(const float *src, int64_t ld_src, int64_t rows, int64_t cols,
     }
     return split_launch(src, ld_src, (int)rows, (int)cols, mask_src, ld_mask, dst_big, dst_small, ld_dst, colsum,
                         static_cast<cudaStream_t>(stream));
+}
+
+
+#define ST(x) static_cast<cudaStream_t>(x)
+
+int odl_linear_forward(const float *x, const float *x_small, const float *w, const float *w_small, const float *b,
+                       float *y, float *y_small, int64_t M, int64_t N, int64_t K, int w_layout, int relu, int precision,
+                       void *stream)
+{
+    return linear_forward(x, x_small, w, w_small, b, y, y_small, M, N, K, w_layout, relu, precision, ST(stream));
+}
+
+int odl_linear_backward(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy,
+                        const float *y, float *dx, float *dw, float *db, int64_t M, int64_t N, int64_t K, int w_layout,
+                        int precision, void *stream)
+{
+    return linear_backward(x, x_small, w, w_small, dy, nullptr, y, dx, nullptr, nullptr, nullptr, dw, db, M, N, K, w_layout,
+                           precision, ST(stream));
+}
+
+int odl_linear_backward_chain(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
+                              const float *y, float *dx, float *dx_small, const float *prev_y, float *prev_db, float *dw,
+                              float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, void *stream)
+{
+    return linear_backward(x, x_small, w, w_small, dy, dy_small, y, dx, dx_small, prev_y, prev_db, dw, db, M, N, K, w_layout,
+                           precision, ST(stream));
+}
+
+int odl_relu_forward(const float *x, float *y, int64_t n, void *stream)
+{
+    return relu_forward_launch(x, y, nullptr, n, ST(stream));
+}
+
+int odl_relu_backward(const float *gy, const float *x_or_y, float *gx, int64_t n, void *stream)
+{
+    return relu_backward_launch(gy, x_or_y, gx, n, ST(stream));
+}
+
+int odl_add_bias(const float *x, const float *b, float *y, int64_t M, int64_t N, void *stream)
+{
+    return add_bias_launch(x, b, y, M, N, ST(stream));
+}
+
+int odl_sum_to_row(const float *g, float *out, int64_t M, int64_t N, void *stream)
+{
+    if (!g || !out || M <= 0 || N <= 0 || M > 0x7fffffff || N > 0x7fffffff)
+    {
+        set_last_error("sum_to_row: invalid argument");
+        return kInvalidArgument;
+    }
+    ODL_CUDA_TRY(cudaMemsetAsync(out, 0, static_cast<size_t>(N) * 4, ST(stream)));
+    return split_launch(g, N, (int)M, (int)N, nullptr, 0, nullptr, nullptr, N, out, ST(stream));
+}
+
+int odl_softmax_cross_entropy(const float *logits, const void *labels, int labels_are_int64, int64_t B, int64_t C,
+                              float *loss, float *dlogits, float grad_scale, void *stream)
+{
+    if (!is_ready())
+    {
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
+    float *rows = nullptr;
+    if (loss)
+    {
+        arena_reset();
+        int rc = arena_reserve(static_cast<size_t>(B) * 4 + 256);
+        if (rc)
+            return rc;
+        rows = static_cast<float *>(arena_alloc(static_cast<size_t>(B) * 4));
+        if (!rows)
+            return kCudaError;
+    }
+    return softmax_ce_launch(logits, labels_are_int64 ? nullptr : static_cast<const int32_t *>(labels),
+                             labels_are_int64 ? static_cast<const int64_t *>(labels) : nullptr, B, C, loss, dlogits, rows,
+                             grad_scale, ST(stream));
+}
+
+int odl_adam_step(float *param, float *grad, float *m, float *v, float *param_small, int64_t n, int t, float lr,
+                  float beta1, float beta2, float eps, float hook_weight_decay, float grad_scale, void *stream)
+{
+    return adam_launch(param, grad, m, v, param_small, n, t, lr, beta1, beta2, eps, hook_weight_decay, grad_scale,
+                       ST(stream));
+}
+
+int odl_sgd_step(float *param, float *grad, float *momentum_buf, float *param_small, int64_t n, float lr, float momentum,
+                 float weight_decay, int nesterov, float hook_weight_decay, float grad_scale, void *stream)
+{
+    return sgd_launch(param, grad, momentum_buf, param_small, n, lr, momentum, weight_decay, nesterov, hook_weight_decay,
+                      grad_scale, ST(stream));
+}
+
+int odl_im2col(const float *x, float *col, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int stride, int pad,
+               void *stream)
+{
+    // the public form writes rows of exactly C*KH*KW columns, like the reference
+    if ((C * KH * KW) & 3)
+    {
+        set_last_error("im2col: C*KH*KW must be a multiple of 4 for the row-matrix form (got %lld)",
+                       (long long)(C * KH * KW));
+        return kInvalidArgument;
+    }
+    return im2col_launch(x, col, nullptr, N, C, H, W, KH, KW, stride, pad, ST(stream));
+}
+
+int odl_col2im(const float *col, float *x, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int stride, int pad,
+               void *stream)
+{
+    return col2im_launch(col, 0, C * KH * KW, x, N, C, H, W, KH, KW, stride, pad, ST(stream));
+}
+
+int odl_conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H,
+                       int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int relu, int precision, void *stream)
+{
+    return conv2d_forward(x, w, b, y, N, C, H, W, OC, KH, KW, stride, pad, relu, precision, ST(stream));
+}
+
+int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N,
+                        int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int gy_layout,
+                        int precision, void *stream)
+{
+    return conv2d_backward(gy, x, w, gx, gw, gb, N, C, H, W, OC, KH, KW, stride, pad, gy_layout, precision, ST(stream));
 }
 
 }  // extern "C"

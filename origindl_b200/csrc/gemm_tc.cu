@@ -125,8 +125,9 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
     }
     const int m0      = tile_m * kBM;
     const int n0      = tile_n * BN;
-    const int num_kb  = (p.K + kBK - 1) / kBK;
-    const int nchunks = (num_kb + chunk_kb - 1) / chunk_kb;
+    const int kb_first = blockIdx.y * p.kb_per_split;  // split-K: this CTA reduces K-blocks [kb_first, kb_first + num_kb)
+    const int num_kb   = min((p.K + kBK - 1) / kBK - kb_first, p.kb_per_split);
+    const int nchunks  = (num_kb + chunk_kb - 1) / chunk_kb;
 
     // ---- one-time setup
     if (warp == 0 && lane == 0)
@@ -174,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     break;
                 uint8_t *st = tiles + s * stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
-                const int k0 = kb * kBK;
+                const int k0 = (kb_first + kb) * kBK;
                 for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
                 {
                     uint8_t *sa           = st + t * Cfg::a_bytes;
@@ -339,6 +340,33 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
             const bool vec_s   = (p.flags & kEpiSmall) && ((reinterpret_cast<uintptr_t>(p.D_small) & 15) == 0);
             const bool vec_aux = (p.flags & kEpiMask) && ((p.ld_aux & 3) == 0) &&
                                  ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
+            if (BN <= 128 && (p.flags & kEpiNCHW))
+            {
+                // Conv output (the launcher never pairs this flag with the 256-wide tile): lanes hold consecutive rows m = consecutive pixels of one image, so for a fixed column
+                // (output channel) a warp writes 32 consecutive floats of the NCHW tensor straight from registers.
+                const int m = m0 + 32 * q + lane;
+                if (m < p.M)
+                {
+                    const int img = m / p.ohw;
+                    const int r   = m - img * p.ohw;
+                    float *dimg   = p.D + (static_cast<size_t>(img) * p.N) * p.ohw + r;
+#pragma unroll
+                    for (int j = 0; j < (BN <= 128 ? Cfg::warp_cols : 1); ++j)
+                    {
+                        const int n = n0 + cw + j;
+                        if (n < p.N)
+                        {
+                            float v = acc[j];
+                            if (p.flags & kEpiBias)
+                                v += __ldg(p.bias + n);
+                            if (p.flags & kEpiRelu)
+                                v = v > 0.f ? v : 0.f;
+                            dimg[static_cast<size_t>(n) * p.ohw] = v;
+                        }
+                    }
+                }
+            }
+            else
 #pragma unroll
             for (int j = 0; j < Cfg::warp_cols / 32; ++j)
             {
@@ -411,7 +439,14 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                                 if (n + jj < p.N)
                                     csum[jj] += v[jj];
                             float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
-                            if (vec_d && full4)
+                            if (p.flags & kEpiAtomic)
+                            {
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+                                    if (n + jj < p.N)
+                                        atomicAdd(dp + jj, v[jj]);
+                            }
+                            else if (vec_d && full4)
                             {
                                 *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
                             }
@@ -478,6 +513,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 // ---------------------------------------------------------------------------------------------- host side
 }  // namespace
 extern int g_chunk_kb;
+extern int g_split_k;
 namespace
 {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -550,10 +586,34 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_kb   = (p.K + kBK - 1) / kBK;
-    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 8 : num_kb);
-    if (chunk_kb > num_kb)
-        chunk_kb = num_kb;
-    gemm_tc_kernel<BN><<<tiles_m * tiles_n, kThreads, smem, stream>>>(tm, p, a_mn, b_mn, terms, stages, chunk_kb);
+    // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split adds its
+    // partial tile into a zeroed D with atomics, so only the plain epilogue qualifies.
+    GemmParams q = p;
+    int splits   = 1;
+    if (g_split_k != 1 && p.flags == 0 && tiles_m * tiles_n * 2 <= 148 && num_kb >= 32)
+    {
+        splits = g_split_k > 1 ? g_split_k : 148 / (tiles_m * tiles_n);
+        if (splits > num_kb / 8)
+            splits = num_kb / 8;
+        if (splits < 1)
+            splits = 1;
+    }
+    q.kb_per_split = (num_kb + splits - 1) / splits;
+    splits         = (num_kb + q.kb_per_split - 1) / q.kb_per_split;
+    if (splits > 1)
+    {
+        q.flags |= kEpiAtomic;
+        cudaError_t e = cudaMemset2DAsync(q.D, static_cast<size_t>(q.ldd) * 4, 0, static_cast<size_t>(q.N) * 4, q.M, stream);
+        if (e != cudaSuccess)
+        {
+            set_last_error("gemm split-K: clearing D failed: %s", cudaGetErrorString(e));
+            return kCudaError;
+        }
+    }
+    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 8 : q.kb_per_split);
+    if (chunk_kb > q.kb_per_split)
+        chunk_kb = q.kb_per_split;
+    gemm_tc_kernel<BN><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
@@ -568,6 +628,8 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
 // Test hook: K-blocks (of 32) accumulated in TMEM between two drains into registers; 0 = default
 // (8, i.e. K = 256, for 3xTF32; the whole K for plain TF32).
 int g_chunk_kb = 0;
+// Test hook: 0 = automatic split-K, 1 = never split, n > 1 = force n splits where the epilogue allows it.
+int g_split_k = 0;
 
 // A / B operands must already satisfy the tiled-load rules (16-byte aligned base, ld % 4 == 0); the callers in
 // linear.cu stage anything else through padded scratch.  a_mn / b_mn: 0 = K-major storage, 1 = MN-major storage.
@@ -591,12 +653,14 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         return kMisaligned;
     }
     int bn = bn_hint;
+    if ((p.flags & kEpiNCHW) && bn == 256)
+        bn = 128;
     if (bn != 64 && bn != 128 && bn != 256)
     {
         // widest tile that still fills the machine reasonably
         const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
         const int64_t tiles128 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 127) / 128);
-        if (p.N > 128 && tiles256 >= 148)
+        if (p.N > 128 && tiles256 >= 148 && !(p.flags & kEpiNCHW))
             bn = 256;
         else if (p.N > 64 && tiles128 >= 74)
             bn = 128;

@@ -31,6 +31,8 @@ enum EpiFlags : int
     kEpiMask   = 4,
     kEpiColsum = 8,
     kEpiSmall  = 16,
+    kEpiNCHW   = 32,  // D is [M/ohw][N][ohw] (conv output): row m = img*ohw + r goes to D[(img*N + n)*ohw + r]
+    kEpiAtomic = 64,  // split-K: partial tiles are added to a zeroed D with fp32 atomics (set by the launcher)
 };
 
 struct GemmParams
@@ -44,6 +46,8 @@ struct GemmParams
     int M, N, K;
     int ldd, ld_aux;
     int flags;
+    int ohw;           // kEpiNCHW: pixels per image
+    int kb_per_split;  // K-blocks (of 32) handled by one CTA along gridDim.y; >= ceil(K/32) when not split
 };
 
 // The value the tensor core sees when it reads an fp32 container as tf32: low 13 mantissa bits dropped.

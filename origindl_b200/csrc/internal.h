@@ -19,6 +19,7 @@ void *arena_alloc(size_t bytes);
 
 extern int g_bn_override;
 extern int g_chunk_kb;
+extern int g_split_k;
 
 int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
                    int64_t ldb, int b_mn, const GemmParams &p, int terms, int bn_hint, cudaStream_t stream);
@@ -29,6 +30,36 @@ int split_launch(const float *src, int64_t ld_src, int rows, int cols, const flo
 int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
                   int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
                   const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
-                  cudaStream_t stream, bool reset_arena);
+                  cudaStream_t stream, bool reset_arena, int ohw = 0);
+
+int relu_forward_launch(const float *x, float *y, float *y_small, int64_t n, cudaStream_t s);
+int relu_backward_launch(const float *gy, const float *ref, float *gx, int64_t n, cudaStream_t s);
+int add_bias_launch(const float *x, const float *b, float *y, int64_t M, int64_t N, cudaStream_t s);
+int softmax_ce_launch(const float *logits, const int32_t *t32, const int64_t *t64, int64_t B, int64_t C, float *loss,
+                      float *dlogits, float *row_loss_scratch, float grad_scale, cudaStream_t s);
+int adam_launch(float *p, float *g, float *m, float *v, float *p_small, int64_t n, int t, float lr, float b1, float b2,
+                float eps, float hook_wd, float grad_scale, cudaStream_t s);
+int sgd_launch(float *p, float *g, float *buf, float *p_small, int64_t n, float lr, float momentum, float wd,
+               int nesterov, float hook_wd, float grad_scale, cudaStream_t s);
+int conv_out_size(int64_t in, int k, int s, int p);
+int im2col_launch(const float *x, float *col, float *col_small, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,
+                  int S, int P, cudaStream_t s);
+int col2im_launch(const float *col, int transposed, int64_t ld, float *gx, int64_t N, int64_t C, int64_t H, int64_t W,
+                  int KH, int KW, int S, int P, cudaStream_t s);
+int nchw_to_rows_launch(const float *src, float *dst, float *dst_small, int64_t N, int64_t OC, int64_t HW, int64_t ld,
+                        cudaStream_t s);
+int channel_sum_launch(const float *gy, float *gb, int64_t N, int64_t OC, int64_t HW, cudaStream_t s);
+
+int linear_forward(const float *x, const float *x_small, const float *w, const float *w_small, const float *b, float *y,
+                   float *y_small, int64_t M, int64_t N, int64_t K, int w_layout, int relu, int precision,
+                   cudaStream_t stream);
+int linear_backward(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
+                    const float *y, float *dx, float *dx_small, const float *dx_mask_src, float *dx_colsum, float *dw,
+                    float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream);
+int conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H, int64_t W,
+                   int64_t OC, int KH, int KW, int S, int P, int relu, int precision, cudaStream_t stream);
+int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N, int64_t C,
+                    int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int mode, int precision,
+                    cudaStream_t stream);
 
 }  // namespace odl

@@ -1,0 +1,383 @@
+"""GPU parity: the CUDA path (through the C ABI) against the CPU oracle, the golden vectors that came out of the
+unmodified reference, and size-independent properties at the benchmark's full sizes.
+
+Tolerances (metric: max|a-b| / max|ref|, the one the north-star states):
+  3xTF32 (default)  <= 1e-5      plain TF32  <= 5e-3
+Optimizer steps use exactly-rounded fp32 operations in the reference's order and are held to 1e-6.
+"""
+import ctypes
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import _libs
+from _libs import fptr, max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = {0: 1e-5, 1: 5e-3}
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from origindl_b200 import capi, ops as _ops
+
+    capi.init(0)
+    yield _ops
+    capi.device_status()
+
+
+@pytest.fixture(scope="module")
+def orc():
+    return _libs.oracle()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+# ------------------------------------------------------------------------------------------------ known answers
+def test_known_answers_from_reference_unit_tests(ops):
+    ka = json.loads((GOLDEN / "known_answers.json").read_text())
+    for c in ka["matmul"]:
+        a = dev(np.array(c["a"], np.float32).reshape(c["M"], c["K"]))
+        b = dev(np.array(c["b"], np.float32).reshape(c["K"], c["N"]))
+        assert np.allclose(host(ops.matmul(a, b)).ravel(), c["c"], atol=1e-3), c["source"]
+    for c in ka["matmul_backward_ones"]:
+        a = dev(np.array(c["a"], np.float32).reshape(c["M"], c["K"]))
+        b = dev(np.array(c["b"], np.float32).reshape(c["K"], c["N"]))
+        gy = torch.ones((c["M"], c["N"]), device="cuda")
+        ga = ops.gemm(gy, b, trans_b=True)      # gy . b^T
+        gb = ops.gemm(a, gy, trans_a=True)      # a^T . gy
+        assert np.allclose(host(ga).ravel(), c["ga"], atol=1e-3) and np.allclose(host(gb).ravel(), c["gb"], atol=1e-3)
+    for c in ka["custom_linear"]:
+        x = dev(np.array(c["x"], np.float32).reshape(c["M"], c["K"]))
+        w = dev(np.array(c["w"], np.float32).reshape(c["N"], c["K"]))
+        b = None if c["b"] is None else dev(np.array(c["b"], np.float32))
+        assert np.allclose(host(ops.linear_forward(x, w, b)).ravel(), c["y"], atol=1e-3), c["source"]
+    for c in ka["relu"]:
+        x = dev(np.array(c["x"], np.float32))
+        assert np.array_equal(host(ops.relu(x)), np.array(c["y"], np.float32))
+        if "gx" in c:
+            assert np.array_equal(host(ops.relu_backward(torch.ones_like(x), x)), np.array(c["gx"], np.float32))
+    for c in ka["softmax_ce"]:
+        x = dev(np.array(c["x"], np.float32).reshape(c["B"], c["C"]))
+        t = dev(np.array(c["t"], np.int32))
+        loss, _ = ops.softmax_cross_entropy(x, t)
+        assert abs(loss.item() - c["loss"]) < c["tol"]
+    for c in ka["conv2d_forward"]:
+        x = dev(np.array(c["x"], np.float32).reshape(c["N"], c["C"], c["H"], c["W"]))
+        w = dev(np.array(c["w"], np.float32).reshape(c["OC"], c["C"], c["KH"], c["KW"]))
+        b = None if c["b"] is None else dev(np.array(c["b"], np.float32))
+        y = ops.conv2d_forward(x, w, b, c["stride"], c["pad"])
+        assert np.allclose(host(y).ravel(), c["y"], atol=1e-3), c["source"]
+    for c in ka["weight_decay_hook"]:
+        p, g = dev(np.array(c["p"], np.float32)), dev(np.array(c["g"], np.float32))
+        ops.sgd_step(p, g, None, lr=0.01, hook_weight_decay=c["rate"])
+        assert np.allclose(host(g), c["g_after"], atol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (2, 3, 5), (31, 127, 1), (127, 31, 1000), (300, 200, 100), (256, 520, 2080),
+                                   (1, 1000, 1), (1024, 1024, 1024)])
+def test_gemm_all_layouts_vs_oracle(ops, orc, M, N, K, ta, tb, precision):
+    rng = np.random.default_rng(M * 7 + N * 3 + K + ta * 2 + tb)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    d = host(ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), precision=precision))
+    opa = np.ascontiguousarray(a.T) if ta else a
+    opb = np.ascontiguousarray(b.T) if tb else b
+    if M * N * K <= 128 * 128 * 1100:
+        ref = np.empty((M, N), np.float32)
+        orc.oracle_matmul(opa, opb, ref, M, N, K)   # the reference's own fp32 loop
+    else:
+        ref = opa.astype(np.float64) @ opb.astype(np.float64)
+    assert max_rel_err(d, ref) <= TOL[precision]
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("chunk", [1, 3, 0])
+def test_gemm_tile_widths_and_accumulator_drains(ops, bn, chunk):
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(bn + chunk)
+    M, N, K = 257, 515, 1500
+    a, b = rng.standard_normal((M, K), dtype=np.float32), rng.standard_normal((K, N), dtype=np.float32)
+    capi.call("odl_debug_set_tile_n", bn)
+    capi.call("odl_debug_set_chunk", chunk)
+    try:
+        d = host(ops.gemm(dev(a), dev(b)))
+    finally:
+        capi.call("odl_debug_set_tile_n", 0)
+        capi.call("odl_debug_set_chunk", 0)
+    assert max_rel_err(d, a.astype(np.float64) @ b.astype(np.float64)) <= 1e-5
+
+
+@pytest.mark.parametrize("splits", [1, 5, 0])
+def test_gemm_split_k(ops, splits):
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(splits)
+    M, N, K = 16, 108, 40000          # conv weight-gradient shape: tiny output, long reduction
+    a, b = rng.standard_normal((K, M), dtype=np.float32), rng.standard_normal((K, N), dtype=np.float32)
+    capi.call("odl_debug_set_split_k", splits)
+    try:
+        d = host(ops.gemm(dev(a), dev(b), trans_a=True))
+    finally:
+        capi.call("odl_debug_set_split_k", 0)
+    assert max_rel_err(d, a.T.astype(np.float64) @ b.astype(np.float64)) <= 1e-5
+
+
+def test_gemm_epilogues(ops):
+    rng = np.random.default_rng(3)
+    M, N, K = 200, 333, 150
+    a, b = rng.standard_normal((M, K), dtype=np.float32), rng.standard_normal((K, N), dtype=np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    colsum = torch.zeros(N, device="cuda")
+    d, ds = ops.gemm(dev(a), dev(b), bias=dev(bias), relu=True, mask_src=dev(mask), colsum=colsum, want_small=True)
+    ref = np.maximum(a.astype(np.float64) @ b + bias, 0) * (mask > 0)
+    assert max_rel_err(host(d), ref) <= 1e-5
+    assert max_rel_err(host(colsum), ref.sum(0)) <= 1e-5
+    big = host(d).view(np.uint32) & np.uint32(0xFFFFE000)
+    resid = host(d) - big.view(np.float32)
+    # the low part is the residual rounded to tf32: within 2^-11 of it and with 13 zero low bits
+    assert np.all(np.abs(host(ds) - resid) <= np.abs(resid) * 2.0 ** -11 + 1e-45)
+    assert np.all(host(ds).view(np.uint32) & np.uint32(0x1FFF) == 0)
+
+
+def test_batched_matmul_forms(ops, orc):
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((3, 17, 20), dtype=np.float32)
+    b2 = rng.standard_normal((20, 9), dtype=np.float32)
+    b3 = rng.standard_normal((3, 20, 9), dtype=np.float32)
+    assert max_rel_err(host(ops.matmul(dev(a), dev(b2))), a.astype(np.float64) @ b2) <= 1e-5
+    assert max_rel_err(host(ops.matmul(dev(a), dev(b3))), a.astype(np.float64) @ b3) <= 1e-5
+    with pytest.raises(ValueError):
+        ops.matmul(dev(a[0]), dev(b2[:5]))
+
+
+def test_invalid_arguments_are_rejected(ops):
+    from origindl_b200 import capi
+
+    x = torch.zeros((4, 4), device="cuda")
+    with pytest.raises(capi.OdlError):
+        capi.call("odl_gemm_ex", 0, 0, 4, 4, 4, x.data_ptr(), None, 2, x.data_ptr(), None, 4, x.data_ptr(), None, 4, None,
+                  None, 0, None, 0, 0, capi.stream_handle())          # lda < K
+    with pytest.raises(capi.OdlError):
+        capi.call("odl_gemm_ex", 0, 0, 4, 4, 4, x.data_ptr(), None, 4, x.data_ptr(), None, 4, x.data_ptr(), None, 4, None,
+                  None, 0, None, capi.EPI_BIAS, 0, capi.stream_handle())  # flag without pointer
+    with pytest.raises(capi.OdlError):
+        capi.call("odl_matmul", None, x.data_ptr(), x.data_ptr(), 4, 4, 4, 1, 0, 0, capi.stream_handle())
+    with pytest.raises(ValueError):
+        ops.conv2d_forward(torch.zeros((1, 1, 2, 2), device="cuda"), torch.zeros((1, 1, 3, 3), device="cuda"))
+    logits, bad = torch.zeros((2, 3), device="cuda"), torch.tensor([0, 3], device="cuda", dtype=torch.int32)
+    ops.softmax_cross_entropy(logits, bad)
+    with pytest.raises(capi.OdlError):
+        capi.device_status()                                       # label out of range, like the reference's throw
+    capi.device_status()
+
+
+# ------------------------------------------------------------------------------------------------ Linear
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("w_layout", [0, 1])
+@pytest.mark.parametrize("relu", [False, True])
+@pytest.mark.parametrize("M,N,K", [(5, 3, 4), (64, 48, 40), (130, 257, 65), (512, 1000, 784), (512, 10, 1000)])
+def test_linear_fwd_bwd_vs_oracle(ops, orc, M, N, K, w_layout, relu, precision):
+    rng = np.random.default_rng(M + N + K + w_layout)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    w = rng.standard_normal((N, K) if w_layout == 0 else (K, N), dtype=np.float32)
+    b = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    dy = rng.standard_normal((M, N), dtype=np.float32)
+    y_o, dx_o, dw_o, db_o = np.empty((M, N), np.float32), np.empty_like(x), np.empty_like(w), np.empty(N, np.float32)
+    orc.oracle_linear_forward(x, w, fptr(b), y_o, M, N, K, w_layout, int(relu))
+    y = ops.linear_forward(dev(x), dev(w), dev(b), relu=relu, w_layout=w_layout, precision=precision)
+    tol = TOL[precision]
+    assert max_rel_err(host(y), y_o) <= tol
+    # backward takes the mask from the forward output of the SAME implementation, so feed it the oracle's y:
+    # elements within rounding of zero would otherwise flip the mask and dominate the comparison
+    orc.oracle_linear_backward(x, w, fptr(y_o), dy, fptr(dx_o), fptr(dw_o), fptr(db_o), M, N, K, w_layout, int(relu))
+    dx, dw, db = ops.linear_backward(dev(x), dev(w), dev(dy), dev(y_o) if relu else None, w_layout=w_layout,
+                                     precision=precision)
+    assert max_rel_err(host(dx), dx_o) <= tol
+    assert max_rel_err(host(dw), dw_o) <= tol
+    assert max_rel_err(host(db), db_o) <= 1e-5
+
+
+def test_linear_golden_vectors_from_reference(ops):
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    for tag in ("lin_a", "lin_b"):
+        for wl in (0, 1):
+            k = f"{tag}_l{wl}_"
+            y = ops.linear_forward(dev(g[k + "x"]), dev(g[k + "w"]), dev(g[k + "b"]), relu=True, w_layout=wl)
+            assert max_rel_err(host(y), g[k + "y"]) <= 1e-5
+            dx, dw, db = ops.linear_backward(dev(g[k + "x"]), dev(g[k + "w"]), dev(g[k + "dy"]), dev(g[k + "y"]),
+                                             w_layout=wl)
+            assert max_rel_err(host(dx), g[k + "dx"]) <= 1e-5
+            assert max_rel_err(host(dw), g[k + "dw"]) <= 1e-5
+            assert max_rel_err(host(db), g[k + "db"].ravel()) <= 1e-5
+
+
+def test_chained_backward_matches_unfused(ops):
+    """dx epilogue with the previous layer's mask / bias gradient / low part == separate passes."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(21)
+    M, N, K = 192, 160, 224
+    x = np.maximum(rng.standard_normal((M, K), dtype=np.float32), 0)     # previous layer's ReLU output
+    w = rng.standard_normal((K, N), dtype=np.float32)
+    dy = rng.standard_normal((M, N), dtype=np.float32)
+    xd, wd, dyd = dev(x), dev(w), dev(dy)
+    dx_ref, dw_ref, db_ref = ops.linear_backward(xd, wd, dyd, None, w_layout=1)
+    masked = ops.relu_backward(dx_ref, xd)
+    prev_db_ref = ops.sum_to_row(masked)
+    dx, dxs = torch.empty_like(xd), torch.empty_like(xd)
+    dw, db, pdb = torch.empty_like(wd), torch.empty(N, device="cuda"), torch.empty(K, device="cuda")
+    capi.call("odl_linear_backward_chain", xd.data_ptr(), None, wd.data_ptr(), None, dyd.data_ptr(), None, None,
+              dx.data_ptr(), dxs.data_ptr(), xd.data_ptr(), pdb.data_ptr(), dw.data_ptr(), db.data_ptr(), M, N, K, 1, 0,
+              capi.stream_handle())
+    assert torch.equal(dx, masked)
+    assert max_rel_err(host(pdb), host(prev_db_ref).ravel()) <= 1e-5
+    assert torch.equal(dw, dw_ref) and torch.equal(dxs, ops.split_tf32(masked))
+
+
+# ------------------------------------------------------------------------------------------------ loss / optimizers
+@pytest.mark.parametrize("B,C", [(1, 3), (512, 10), (300, 1000), (64, 1024)])
+def test_softmax_ce_vs_oracle(ops, orc, B, C):
+    rng = np.random.default_rng(B + C)
+    x = (3 * rng.standard_normal((B, C))).astype(np.float32)
+    t = rng.integers(0, C, B).astype(np.int32)
+    l_o, d_o = ctypes.c_float(), np.empty_like(x)
+    assert orc.oracle_softmax_ce(x, t, B, C, ctypes.byref(l_o), fptr(d_o)) == 0
+    for labels in (dev(t), dev(t.astype(np.int64))):
+        loss, d = ops.softmax_cross_entropy(dev(x), labels)
+        assert abs(loss.item() - l_o.value) <= 1e-5 * max(1.0, abs(l_o.value))
+        assert max_rel_err(host(d), d_o) <= 1e-5
+
+
+def test_optimizer_trajectories_vs_reference_golden(ops):
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    p0, grads = g["opt_p0"], g["opt_grads"]
+    cases = {"adam_wd": dict(opt=1, lr=1e-3, hook=1e-4), "sgd_mom": dict(opt=0, lr=1e-2, mom=0.9),
+             "sgd_nes_wd": dict(opt=0, lr=1e-2, mom=0.9, wd=1e-2, nes=True)}
+    for tag, c in cases.items():
+        p = dev(p0)
+        m, v, buf = torch.zeros_like(p), torch.zeros_like(p), torch.zeros_like(p)
+        for s in range(grads.shape[0]):
+            gr = dev(grads[s])
+            if c["opt"] == 1:
+                ops.adam_step(p, gr, m, v, s + 1, lr=c["lr"], hook_weight_decay=c.get("hook", 0.0))
+            else:
+                ops.sgd_step(p, gr, buf, lr=c["lr"], momentum=c.get("mom", 0.0), weight_decay=c.get("wd", 0.0),
+                             nesterov=c.get("nes", False))
+        assert max_rel_err(host(p), g["opt_" + tag]) <= 1e-6, tag
+
+
+def test_optimizer_steps_vs_oracle_odd_sizes(ops, orc):
+    rng = np.random.default_rng(8)
+    for n in (1, 3, 1027):
+        p0, g0 = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+        m0, v0 = rng.standard_normal(n).astype(np.float32) * 0.1, rng.uniform(0, 1, n).astype(np.float32)
+        p, g, m, v = p0.copy(), g0.copy(), m0.copy(), v0.copy()
+        orc.oracle_adam_step(p, g, m, v, n, 3, 1e-3, 0.9, 0.999, 1e-8, 1e-4)
+        pd, gd, md, vd, ps = dev(p0), dev(g0), dev(m0), dev(v0), torch.empty(n, device="cuda")
+        ops.adam_step(pd, gd, md, vd, 3, hook_weight_decay=1e-4, p_small=ps)
+        assert max_rel_err(host(pd), p) <= 1e-6 and np.array_equal(host(gd), g)
+        assert np.array_equal(host(md), m) and np.array_equal(host(vd), v)
+        assert torch.equal(ps, ops.split_tf32(pd.reshape(1, -1)).reshape(-1))
+
+
+# ------------------------------------------------------------------------------------------------ Conv2d
+CONV_CASES = [(1, 1, 3, 3, 1, 2, 1, 0), (2, 3, 9, 7, 4, 3, 1, 1), (2, 3, 16, 16, 8, 3, 2, 1), (1, 2, 12, 12, 5, 6, 2, 2),
+              (2, 4, 5, 5, 3, 1, 1, 0), (2, 16, 20, 20, 32, 3, 2, 1), (1, 64, 10, 10, 64, 3, 1, 1)]
+
+
+@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", CONV_CASES)
+def test_conv2d_vs_oracle(ops, orc, N, C, H, W, OC, k, s, p):
+    rng = np.random.default_rng(N + C + H + OC + k)
+    x = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = (0.1 * rng.standard_normal(OC)).astype(np.float32)
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    dy = rng.standard_normal((N, OC, OH, OW)).astype(np.float32)
+    y_o = np.empty_like(dy)
+    orc.oracle_conv2d_forward(x, w, fptr(b), y_o, N, C, H, W, OC, k, k, s, p)
+    y = ops.conv2d_forward(dev(x), dev(w), dev(b), s, p)
+    assert max_rel_err(host(y), y_o) <= 1e-5
+    for mode in (0, 1):
+        dx_o, dw_o, db_o = np.empty_like(x), np.empty_like(w), np.empty_like(b)
+        orc.oracle_conv2d_backward(dy, x, w, fptr(dx_o), fptr(dw_o), fptr(db_o), N, C, H, W, OC, k, k, s, p, mode)
+        gx, gw, gb = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=mode)
+        assert max_rel_err(host(gx), dx_o) <= 1e-5
+        assert max_rel_err(host(gw), dw_o) <= 1e-5
+        assert max_rel_err(host(gb), db_o) <= 1e-5
+
+
+def test_conv2d_golden_vectors_from_reference(ops):
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    N, C, H, W, OC, k, s, p = (int(v) for v in g["conv_cfg"])
+    y = ops.conv2d_forward(dev(g["conv_x"]), dev(g["conv_w"]), dev(g["conv_b"]), s, p)
+    assert max_rel_err(host(y), g["conv_y"]) <= 1e-5
+    gx, gw, gb = ops.conv2d_backward(dev(g["conv_dy"]), dev(g["conv_x"]), dev(g["conv_w"]), s, p, gy_layout=1)
+    assert max_rel_err(host(gx), g["conv_dx_reflayout"]) <= 1e-5
+    assert max_rel_err(host(gw), g["conv_dw_reflayout"]) <= 1e-5
+    assert max_rel_err(host(gb), g["conv_db"]) <= 1e-5
+
+
+def test_im2col_col2im_pair(ops, orc):
+    rng = np.random.default_rng(2)
+    N, C, H, W, k, s, p = 2, 4, 9, 11, 3, 2, 1
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    col_o = np.empty((N * OH * OW, C * k * k), np.float32)
+    orc.oracle_im2col(x, col_o, N, C, H, W, k, k, s, p)
+    col = ops.im2col(dev(x), k, s, p)
+    assert np.array_equal(host(col), col_o)                          # pure data movement: bit exact
+    back_o = np.empty_like(x)
+    orc.oracle_col2im(col_o, back_o, N, C, H, W, k, k, s, p)
+    assert np.array_equal(host(ops.col2im(col, x.shape, k, s, p)), back_o)   # same (kh, kw) accumulation order
+
+
+# ------------------------------------------------------------------------------------------------ full-size properties
+def test_full_size_linearity_and_row_samples(ops):
+    """M = N = K = 8192: sampled rows against float64, and linearity D(a1 + a2) == D(a1) + D(a2) to 3xTF32 accuracy."""
+    torch.manual_seed(0)
+    n = 8192
+    a, b = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+    d = ops.gemm(a, b, trans_b=True)
+    rows = torch.randint(0, n, (48,), device="cuda")
+    ref = a[rows].double() @ b.double().t()
+    assert ((d[rows].double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
+    a2 = torch.randn(n, n, device="cuda")
+    d2 = ops.gemm(a2, b, trans_b=True)
+    d12 = ops.gemm(a + a2, b, trans_b=True)
+    assert ((d12 - (d + d2)).abs().max() / d12.abs().max()).item() <= 2e-5
+    # plain TF32 stays inside its own bound
+    dt = ops.gemm(a, b, trans_b=True, precision=1)
+    assert ((dt[rows].double() - ref).abs().max() / ref.abs().max()).item() <= 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(65536, 1024, 1024), (256, 8192, 8192)])
+def test_skinny_linear_backward_row_samples(ops, M, N, K):
+    torch.manual_seed(1)
+    x, w = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda")
+    dy = torch.randn(M, N, device="cuda")
+    dx, dw, db = ops.linear_backward(x, w, dy, None, w_layout=0)
+    r = torch.randint(0, M, (32,), device="cuda")
+    ref = dy[r].double() @ w.double()
+    assert ((dx[r].double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
+    c = torch.randint(0, N, (32,), device="cuda")
+    ref = dy[:, c].double().t() @ x.double()
+    assert ((dw[c].double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
+    ref = dy.double().sum(0)
+    assert ((db.double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
