@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the dense hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched once per rank by torch.distributed.run)
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Workload (config.workload): data-parallel MLP training, 4 x (8192 -> 8192, ReLU) + 8192 -> 1024 head, softmax-CE, Adam
+(lr 1e-3), 8192 samples per GPU (weak scaling: global batch 8192 x N), fp32 parameters, 3xTF32 GEMMs, synthetic
+N(0,1) inputs and uniform labels, seed 0.  `value` = samples/s over all ranks with inputs resident in HBM; `e2e` =
+the same step fed from pinned HOST buffers through the public API (H2D copy of every batch and a D2H read of the loss
+inside the timed region).  At N = 1 the line also carries the second half of the headline metric, Linear
+forward+backward at M = N = K = 8192 (`linear_fwd_bwd`), the roofline of the dominant kernel (the tcgen05 GEMM) and
+the reference's CPU backend timed on the host (`cpu_baseline`).
+
+One step = forward (5 GEMMs), loss, backward (9 GEMMs), all-reduce of the gradient buckets (N > 1), one fused Adam
+launch; nothing is skipped.  Inputs (2 x 256 MiB per rank, alternated) exceed the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "MLP train samples/s @1/2/4/8 B200; Linear fwd+bwd TFLOP/s vs TF32 peak"
+SIZES = [8192, 8192, 8192, 8192, 8192, 1024]
+PER_GPU_BATCH = 8192
+LR = 1e-3
+LIN = 8192  # M = N = K of the Linear forward+backward leg
+
+
+def flops_per_sample(sizes):
+    return 6 * sum(a * b for a, b in zip(sizes[:-1], sizes[1:]))
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------ clock sampling
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, device_index: int):
+        import torch
+
+        self.uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+        self.proc = None
+        self.tmp = None
+
+    def start(self):
+        try:
+            self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.tmp,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [r.strip().split(",") for r in Path(self.tmp.name).read_text().splitlines() if r.strip()]
+        os.unlink(self.tmp.name)
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(self.NAMES, r[3:7]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        if sm:
+            out.update({"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                        "samples": len(sm)})
+        return out
+
+
+# ------------------------------------------------------------------------------------------------ reference (CPU) arm
+def time_reference_cpu(steps: int, warmup: int):
+    """Times the UNMODIFIED reference (oracle/_ref/libodl_ref.so: nn::MLP + softmax_cross_entropy + backward + Adam on
+    its CPU backend, one host thread -- the reference has no threading) on a bounded sample of the workload:
+    the same depth and optimizer at width/8 and 32 samples per step, then scaled to the full-size unit by the ratio
+    of flops per sample (the reference's scalar ijk GEMM has the same cost per flop at any width)."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import numpy as np
+
+    import _libs
+
+    ref = _libs.reference()
+    if ref is None:
+        return None
+    sizes = [s // 8 for s in SIZES]
+    B = 32
+    rng = np.random.default_rng(0)
+    params = _libs.mlp_params(rng, sizes)
+    x = rng.standard_normal((1, B, sizes[0])).astype(np.float32)
+    t = rng.integers(0, sizes[-1], (1, B)).astype(np.int32)
+    arr = np.array(sizes, np.int32)
+    losses = np.empty(max(steps, warmup, 1), np.float32)
+    if warmup > 0:
+        _libs.ref_check(ref.odlref_mlp_train(arr, len(sizes), params, x, t, B, 1, warmup, 1, LR, 0.0, 0.0, losses, None))
+    t0 = time.perf_counter()
+    _libs.ref_check(ref.odlref_mlp_train(arr, len(sizes), params, x, t, B, 1, steps, 1, LR, 0.0, 0.0, losses, None))
+    dt = time.perf_counter() - t0
+    twin_sps = B * steps / dt
+    full_sps = twin_sps * flops_per_sample(sizes) / flops_per_sample(SIZES)
+    return {"value": full_sps, "unit": "samples/s", "cores": 1, "kind": "reference",
+            "sample": f"reference CPU backend, {steps} Adam steps of the width/8 twin {sizes} at batch {B} "
+                      f"({dt:.1f} s, {twin_sps:.1f} samples/s), extrapolated to full width by flops per sample",
+            "host_cores_available": os.cpu_count(), "seconds": dt}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    res = time_reference_cpu(steps, max(1, min(args.warmup, 2)))
+    if res is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libodl_ref.so is not built on this machine"}))
+        return
+    line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": "samples/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * res["seconds"] / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": res["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(n):
+    return {"workload": "data-parallel MLP training (BASELINE config 5 at 8192 samples per GPU) + Linear fwd+bwd "
+                        "M=N=K=8192 (BASELINE config 2)",
+            "layers": SIZES, "per_gpu_batch": PER_GPU_BATCH, "global_batch": PER_GPU_BATCH * n, "optimizer": "adam",
+            "precision": "3xTF32", "parallelism": f"dp{n}", "l2": "inputs (2 x 256 MiB per rank) larger than L2"}
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local)
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        pg = dist.group.WORLD
+    from origindl_b200 import capi, ops
+    from origindl_b200.trainer import MLPTrainer
+
+    capi.init(local)
+    L = capi.lib()
+    dev = torch.device("cuda", local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- synthetic inputs: identical parameters on every rank (seed 0), rank-specific batches
+    rng = np.random.default_rng(0)
+    parts = []
+    for a, b in zip(SIZES[:-1], SIZES[1:]):
+        bound = np.sqrt(6.0 / a)
+        parts.append(rng.uniform(-bound, bound, a * b).astype(np.float32))
+        parts.append(np.zeros(b, np.float32))
+    params = np.concatenate(parts)
+    del parts
+    tr = MLPTrainer(SIZES, PER_GPU_BATCH, optimizer="adam", lr=LR, device=local, process_group=pg)
+    tr.set_params(params)
+    del params
+    g = torch.Generator(device=dev)
+    g.manual_seed(1000 + rank)
+    n_batches = 2
+    xs = torch.randn((n_batches, PER_GPU_BATCH, SIZES[0]), device=dev, generator=g)
+    ts = torch.randint(0, SIZES[-1], (n_batches, PER_GPU_BATCH), device=dev, generator=g, dtype=torch.int32)
+
+    # ---- device-resident timing
+    for s in range(args.warmup):
+        tr.train_step(xs[s % n_batches], ts[s % n_batches])
+    capi.device_status()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    if sampler:
+        sampler.start()
+    launches0 = L.odl_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.steps):
+        loss = tr.train_step(xs[s % n_batches], ts[s % n_batches])
+    e1.record()
+    barrier()
+    launches = L.odl_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    capi.device_status()
+    final_loss = float(loss.item())
+    ms_per_step = ms_total / args.steps
+    value = world * PER_GPU_BATCH * args.steps / (ms_total / 1e3)
+
+    # ---- end to end: pinned host batches -> H2D on a copy stream (double buffered) -> step -> loss D2H
+    hx = [torch.randn((PER_GPU_BATCH, SIZES[0])).pin_memory() for _ in range(n_batches)]
+    ht = [torch.randint(0, SIZES[-1], (PER_GPU_BATCH,), dtype=torch.int32).pin_memory() for _ in range(n_batches)]
+    dbuf_x = [torch.empty((PER_GPU_BATCH, SIZES[0]), device=dev) for _ in range(2)]
+    dbuf_t = [torch.empty((PER_GPU_BATCH,), device=dev, dtype=torch.int32) for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    host_loss = torch.empty((1,), dtype=torch.float32).pin_memory()
+    compute = torch.cuda.current_stream()
+
+    consumed = [None, None]  # per slot: event recorded after the step that last read the slot
+
+    def stage(step):
+        slot = step % 2
+        with torch.cuda.stream(copy_stream):
+            if consumed[slot] is not None:
+                copy_stream.wait_event(consumed[slot])  # do not overwrite a batch that is still being read
+            dbuf_x[slot].copy_(hx[step % n_batches], non_blocking=True)
+            dbuf_t[slot].copy_(ht[step % n_batches], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+        return ev
+
+    def e2e_loop(n_steps):
+        ev = stage(0)
+        for s in range(n_steps):
+            nxt = stage(s + 1) if s + 1 < n_steps else None  # next batch crosses PCIe while this step computes
+            compute.wait_event(ev)
+            lv = tr.train_step(dbuf_x[s % 2], dbuf_t[s % 2])
+            done = torch.cuda.Event()
+            done.record(compute)
+            consumed[s % 2] = done
+            host_loss.copy_(lv.reshape(1), non_blocking=True)
+            ev = nxt
+        torch.cuda.synchronize()
+        return float(host_loss.item())
+
+    e2e_loop(min(2, args.warmup))
+    barrier()
+    e0.record()
+    e2e_loop(args.steps)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = world * PER_GPU_BATCH * args.steps / (e2e_ms / 1e3)
+    h2d = PER_GPU_BATCH * SIZES[0] * 4 + PER_GPU_BATCH * 4
+    tr.close()
+    del xs, dbuf_x, hx
+    torch.cuda.empty_cache()
+
+    line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)", "data": "synthetic",
+            "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": int(launches), "final_loss": final_loss,
+            "mlp_tflops_per_gpu": flops_per_sample(SIZES) * PER_GPU_BATCH / (ms_per_step / 1e3) / 1e12}
+    if clocks is not None:
+        line["clocks"] = clocks
+
+    # ---- N = 1 extras: Linear fwd+bwd at 8192^3, roofline of the GEMM, CPU baseline
+    if world == 1:
+        peaks = measured_peaks()
+        n = LIN
+        x = torch.randn((n, n), device=dev, generator=g)
+        w = torch.randn((n, n), device=dev, generator=g)
+        b = 0.1 * torch.randn((n,), device=dev, generator=g)
+        dy = torch.randn((n, n), device=dev, generator=g)
+
+        def lin_step():
+            # everything a caller needs for one Linear forward + backward in 3xTF32, operand splits included
+            xs_ = ops.split_tf32(x)
+            ws_ = ops.split_tf32(w)
+            y = ops.linear_forward(x, w, b, relu=True, x_small=xs_, w_small=ws_)
+            return ops.linear_backward(x, w, dy, y, x_small=xs_, w_small=ws_)
+
+        for _ in range(max(3, args.warmup)):
+            lin_step()
+        torch.cuda.synchronize()
+        k = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(k):
+            lin_step()
+        e1.record()
+        torch.cuda.synchronize()
+        lin_ms = e0.elapsed_time(e1) / k
+        lin_tflops = 6 * n ** 3 / (lin_ms / 1e3) / 1e12
+        # the GEMM alone (operands already split): CUDA events around each launch, on the launching stream
+        xs_, ws_ = ops.split_tf32(x), ops.split_tf32(w)
+        d = torch.empty((n, n), device=dev)
+        s_ = capi.stream_handle()
+        durations = []
+        for i in range(3 + 3 * k):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            capi.call("odl_gemm_ex", 0, 1, n, n, n, x.data_ptr(), xs_.data_ptr(), n, w.data_ptr(), ws_.data_ptr(), n,
+                      d.data_ptr(), None, n, None, None, 0, None, 0, capi.PRECISION_3XTF32, s_)
+            a1.record()
+            durations.append((a0, a1))
+        torch.cuda.synchronize()
+        gemm_ms = statistics.mean(a.elapsed_time(b_) for a, b_ in durations[3:])
+        capi.device_status()
+        achieved = 2 * n ** 3 / (gemm_ms / 1e3) / 1e12
+        tf32_peak = peaks["bf16_tflops"] / 2.0           # dense TF32 issues at half the bf16 rate
+        peak = tf32_peak / 3.0                           # three MMAs per algorithmic product in 3xTF32
+        line["linear_fwd_bwd"] = {"M": n, "N": n, "K": n, "ms": lin_ms, "tflops": lin_tflops,
+                                  "frac_of_tf32_roofline_div3": lin_tflops / peak,
+                                  "includes": "operand splits of x and W, fused bias+ReLU forward, mask/db pass, dX, dW"}
+        line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel<256> (3xTF32, M=N=K=8192)",
+                            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                            "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
+                            "traffic": GEMM_DRAM_TRAFFIC_BYTES}
+        try:
+            cb = time_reference_cpu(4, 1)
+        except Exception as ex:  # the checker must never take the measured arm down
+            cb = {"error": repr(ex)}
+        if cb is not None:
+            cb.pop("seconds", None)
+            line["cpu_baseline"] = cb
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one 8192^3 3xTF32 GEMM launch: scaled from the ncu capture summarised in
+# profiles/gemm_tc_3xtf32.md; None until that capture exists.
+GEMM_DRAM_TRAFFIC_BYTES = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

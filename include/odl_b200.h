@@ -61,6 +61,10 @@ int odl_device_status(void *stream);
 /* Bytes currently held by the library's device scratch arena (operand splits, padded copies, im2col columns). */
 int64_t odl_scratch_bytes(void);
 
+/* Number of kernels this library has launched in the process so far (a benchmark reports the delta over its timed
+ * region).  No counterpart in the reference. */
+long long odl_launch_count(void);
+
 /* ---- GEMM ---------------------------------------------------------------------------------------------------- */
 
 /* C[M,N] = A[M,K] . B[K,N].  Replaces origin::cuda::matmul (include/origin/mat/origin/cuda/cuda_ops.cuh:264,
@@ -172,6 +176,38 @@ int odl_conv2d_forward(const float *x, const float *w, const float *b, float *y,
 int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N,
                         int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int gy_layout,
                         int precision, void *stream);
+
+/* ---- MLP training state (nn::MLP + loss + autograd + optimizer, device-resident) ----------------------------- */
+
+/* Build an MLP with layer widths sizes[0..n_sizes) (ReLU after every layer but the last, like nn::MLP,
+ * src/nn/models/mlp.cpp:11-61) for a fixed batch, with its optimizer: 0 = SGD(lr, momentum), 1 = Adam(lr, 0.9, 0.999,
+ * 1e-8); hook_weight_decay > 0 adds the WeightDecay hook (tests/example/mnist/mlp_mnist.cpp:406-408).  Parameters,
+ * gradients and optimizer state live in flat device buffers allocated here, once. */
+int odl_mlp_create(const int32_t *sizes, int n_sizes, int64_t batch, int optimizer, float lr, float momentum,
+                   float hook_weight_decay, int precision, void **handle);
+int odl_mlp_destroy(void *handle);
+/* Number of parameters in packed form (sum of in*out + out). */
+int64_t odl_mlp_param_count(void *handle);
+/* Install parameters from a packed HOST array [W_0 {in,out}, b_0 {1,out}, W_1, ...] (the order of
+ * Module::named_parameters: layer_i.weight, layer_i.bias); resets the optimizer state. */
+int odl_mlp_set_params(void *handle, const float *host_packed, void *stream);
+/* Copy parameters (which = 0) or the gradients of the last backward (which = 1) to a packed HOST array. */
+int odl_mlp_get_packed(void *handle, int which, float *host_packed, void *stream);
+/* model(x) and softmax_cross_entropy(y, t) for x[batch, sizes[0]] and labels[batch] on the device; also starts the
+ * backward pass (d loss / d logits and the head's bias gradient). */
+int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
+/* loss.backward(), one layer at a time from the head (layer = L-1) down to 0, so that a data-parallel caller can
+ * all-reduce layer l's gradient bucket while layer l-1 is still computing. */
+int odl_mlp_backward_layer(void *handle, int layer, void *stream);
+/* optimizer.step(): one fused launch over the flat buffers; grad_scale multiplies the gradients first. */
+int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream);
+/* forward_loss + backward of every layer + optimizer_step. */
+int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
+/* Device pointers to the scalar loss and to the logits [batch, sizes[n-1]] of the last forward. */
+float *odl_mlp_loss_ptr(void *handle);
+float *odl_mlp_logits_ptr(void *handle);
+/* Contiguous device range [dW_layer, db_layer] of the flat gradient buffer (layer = -1: the whole buffer). */
+int odl_mlp_grad_bucket(void *handle, int layer, float **ptr, int64_t *count);
 
 #ifdef __cplusplus
 }

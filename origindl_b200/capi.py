@@ -84,6 +84,7 @@ def lib() -> ctypes.CDLL:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        _declare_extra(L)
         _lib = L
     return _lib
 
@@ -120,3 +121,30 @@ def init(device: int = 0) -> None:
 
 def device_status() -> None:
     call("odl_device_status", stream_handle())
+
+
+# ---- MLP training state -----------------------------------------------------------------------------------------
+_MLP_SIGNATURES = {
+    "odl_mlp_create": [ctypes.POINTER(ctypes.c_int32), c_int, _I64, c_int, c_float, c_float, c_float, c_int,
+                       ctypes.POINTER(c_void_p)],
+    "odl_mlp_destroy": [_P],
+    "odl_mlp_set_params": [_P, _P, _P],
+    "odl_mlp_get_packed": [_P, c_int, _P, _P],
+    "odl_mlp_forward_loss": [_P, _P, _P, c_int, _P],
+    "odl_mlp_backward_layer": [_P, c_int, _P],
+    "odl_mlp_optimizer_step": [_P, c_float, _P],
+    "odl_mlp_train_step": [_P, _P, _P, c_int, _P],
+    "odl_mlp_grad_bucket": [_P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)],
+}
+_SIGNATURES.update(_MLP_SIGNATURES)
+_POINTER_RETURNS = {"odl_mlp_loss_ptr": [_P], "odl_mlp_logits_ptr": [_P]}
+_I64_RETURNS = {"odl_mlp_param_count": [_P], "odl_launch_count": []}
+
+
+def _declare_extra(L: ctypes.CDLL) -> None:
+    for name, args in _POINTER_RETURNS.items():
+        fn = getattr(L, name)
+        fn.argtypes, fn.restype = args, c_void_p
+    for name, args in _I64_RETURNS.items():
+        fn = getattr(L, name)
+        fn.argtypes, fn.restype = args, c_int64

@@ -130,7 +130,7 @@ struct Prepared
     int64_t ld;
 };
 
-size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms)
+size_t operand_scratch_impl(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms)
 {
     if (misaligned(ptr, ld))
         return a256(rows * pad4(cols) * 4) * (terms == 3 ? 2 : 1);
@@ -170,6 +170,12 @@ int prepare_operand(const float *ptr, const float *small, int64_t ld, int64_t ro
     return kOk;
 }
 }  // namespace
+
+// Scratch bytes gemm_dispatch will carve for one operand (padded copy and/or low part).
+size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms)
+{
+    return operand_scratch_impl(ptr, small, ld, rows, cols, terms);
+}
 
 // The GEMM every fused entry point funnels into.  `reset_arena` is false when the caller already carved scratch
 // for this call (Linear / conv orchestration) and reserved enough for the operand splits too.
@@ -217,8 +223,8 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
     if (reset_arena)
     {
         arena_reset();
-        int rc = arena_reserve(operand_scratch(A, A_small, lda, a_rows, a_cols, terms) +
-                               operand_scratch(B, B_small, ldb, b_rows, b_cols, terms));
+        int rc = arena_reserve(operand_scratch_impl(A, A_small, lda, a_rows, a_cols, terms) +
+                               operand_scratch_impl(B, B_small, ldb, b_rows, b_cols, terms));
         if (rc)
             return rc;
     }
@@ -249,6 +255,7 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
 }
 
 int g_bn_override = 0;
+long long g_launch_count = 0;
 
 }  // namespace odl
 
@@ -507,3 +514,8 @@ int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *
 }
 
 }  // extern "C"
+
+extern "C" long long odl_launch_count(void)
+{
+    return odl::g_launch_count;
+}

@@ -35,6 +35,7 @@ inline bool al16(const void *p)
 }
 
 #define ODL_LAUNCH_CHECK(name)                                                      \
+    ++::odl::g_launch_count;                                                        \
     do                                                                              \
     {                                                                               \
         cudaError_t _e = cudaGetLastError();                                        \

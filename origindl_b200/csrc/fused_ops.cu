@@ -79,8 +79,16 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
     const bool need_g    = (y != nullptr);                  // masked copy of dy
     const bool need_gs   = (terms == 3) && (dx || dw) && !(dy_small && !need_g);  // low part of g
     arena_reset();
-    int rc = arena_reserve((need_g ? mn : 0) + (need_gs ? mn : 0) + operand_worst(M, N) + operand_worst(M, K) +
-                           operand_worst(N, K));
+    // exact scratch: the masked copy / low part of dy, plus whatever the two GEMMs must stage for x and W
+    // (g itself is either dy or an arena buffer with N % 4 == 0 handled by the GEMM's own staging)
+    const int64_t ldw = w_layout == ODL_W_OUT_IN ? K : N;
+    const int64_t wr  = w_layout == ODL_W_OUT_IN ? N : K;
+    size_t need = (need_g ? mn : 0) + (need_gs ? mn : 0) + 2 * operand_scratch(dy, nullptr, N, M, N, terms);
+    if (dx)
+        need += operand_scratch(w, w_small, ldw, wr, ldw, terms);
+    if (dw)
+        need += operand_scratch(x, x_small, K, M, K, terms);
+    int rc = arena_reserve(need);
     if (rc)
         return rc;
     const float *g  = dy;

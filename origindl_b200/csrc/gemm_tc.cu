@@ -610,10 +610,11 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
             return kCudaError;
         }
     }
-    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 8 : q.kb_per_split);
+    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 2 : q.kb_per_split);
     if (chunk_kb > q.kb_per_split)
         chunk_kb = q.kb_per_split;
     gemm_tc_kernel<BN><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb);
+    ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {

@@ -11,6 +11,9 @@ namespace odl
 void set_last_error(const char *fmt, ...);
 const char *get_last_error();
 
+// Number of kernels this library has launched in the process (the benchmark reports the delta over its timed region).
+extern long long g_launch_count;
+
 // Per-device int the kernels raise when a bounded wait runs out.  Allocated by odl_init.
 int *device_error_flag();
 

@@ -17,6 +17,8 @@ void arena_reset();
 int arena_reserve(size_t total_bytes);
 void *arena_alloc(size_t bytes);
 
+size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms);
+
 extern int g_bn_override;
 extern int g_chunk_kb;
 extern int g_split_k;

@@ -1,0 +1,353 @@
+// Device-resident MLP training state behind the C ABI: the fused equivalent of
+//   nn::MLP::forward (src/nn/models/mlp.cpp:43-61)  ->  functional::softmax_cross_entropy
+//   -> Tensor::backward (src/core/tensor_impl.cpp:78-278)  ->  Optimizer::step (src/optim/optimizer.cpp:19-53)
+// of the reference, with every tensor of the step living in buffers allocated once:
+//   * one flat parameter buffer [W_0 {in,out}, b_0, W_1, b_1, ...] (segments padded to 64 floats) with matching
+//     flat buffers for the low TF32 parts, the gradients and the optimizer moments, so the optimizer is ONE launch
+//     and a layer's gradient bucket [dW_l, db_l] is one contiguous range for the all-reduce;
+//   * per-layer activations y_l (+ low parts, written by the forward GEMM's epilogue) and two ping-pong buffers for
+//     the back-propagated gradient (+ low parts, written by the dX GEMM's epilogue together with the ReLU mask and
+//     the bias gradient of the layer below).
+// Per step: 1 split of the input, L forward GEMMs, 2 loss launches, 1 split of dlogits, 2L-1 backward GEMMs, 1 optimizer.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <vector>
+
+#include "../../include/odl_b200.h"
+#include "gemm_tc.cuh"
+#include "host_util.h"
+#include "internal.h"
+
+namespace odl
+{
+
+namespace
+{
+inline int64_t pad64(int64_t x)
+{
+    return (x + 63) & ~int64_t(63);
+}
+
+struct Mlp
+{
+    std::vector<int> sizes;
+    int L          = 0;
+    int64_t batch  = 0;
+    int optimizer  = 1;  // 0 SGD, 1 Adam
+    float lr = 1e-3f, momentum = 0.f, hook_wd = 0.f;
+    float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f;
+    int precision  = ODL_PRECISION_3XTF32;
+    int step_count = 0;
+    std::vector<int64_t> w_off, b_off;  // offsets (floats) into the flat buffers
+    int64_t total = 0;
+    float *params = nullptr, *params_small = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+    float *x_small = nullptr;
+    std::vector<float *> act, act_small;  // y_l, l = 0..L-1 (act[L-1] = logits)
+    float *gbuf[2] = {nullptr, nullptr}, *gbuf_small[2] = {nullptr, nullptr};
+    float *row_loss = nullptr, *loss = nullptr;
+    const float *cur_x = nullptr;
+    int64_t max_width = 0;
+    std::vector<void *> allocs;
+
+    template <typename T>
+    int alloc(T **p, size_t count)
+    {
+        void *q       = nullptr;
+        cudaError_t e = cudaMalloc(&q, count * sizeof(T));
+        if (e != cudaSuccess)
+        {
+            set_last_error("mlp: cudaMalloc(%zu) failed: %s", count * sizeof(T), cudaGetErrorString(e));
+            return kCudaError;
+        }
+        allocs.push_back(q);
+        *p = static_cast<T *>(q);
+        return kOk;
+    }
+    ~Mlp()
+    {
+        for (void *q : allocs)
+            cudaFree(q);
+    }
+};
+
+inline bool three(const Mlp *h)
+{
+    return h->precision == ODL_PRECISION_3XTF32;
+}
+}  // namespace
+}  // namespace odl
+
+using namespace odl;
+#define ST(x) static_cast<cudaStream_t>(x)
+#define H(x) static_cast<Mlp *>(x)
+
+extern "C" {
+
+int odl_mlp_create(const int32_t *sizes, int n_sizes, int64_t batch, int optimizer, float lr, float momentum,
+                   float hook_weight_decay, int precision, void **handle)
+{
+    if (!is_ready())
+    {
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
+    if (!sizes || n_sizes < 2 || batch <= 0 || !handle || (optimizer != 0 && optimizer != 1))
+    {
+        set_last_error("MLP requires at least 2 layer sizes (input and output), but got %d", n_sizes);
+        return kInvalidArgument;
+    }
+    Mlp *h       = new Mlp();
+    h->sizes.assign(sizes, sizes + n_sizes);
+    h->L         = n_sizes - 1;
+    h->batch     = batch;
+    h->optimizer = optimizer;
+    h->lr = lr, h->momentum = momentum, h->hook_wd = hook_weight_decay, h->precision = precision;
+    int64_t off = 0;
+    for (int l = 0; l < h->L; ++l)
+    {
+        if (sizes[l] <= 0 || sizes[l + 1] <= 0)
+        {
+            delete h;
+            set_last_error("mlp: layer sizes must be positive");
+            return kInvalidArgument;
+        }
+        h->w_off.push_back(off);
+        off += pad64(static_cast<int64_t>(sizes[l]) * sizes[l + 1]);
+        h->b_off.push_back(off);
+        off += pad64(sizes[l + 1]);
+        if (sizes[l + 1] > h->max_width)
+            h->max_width = sizes[l + 1];
+    }
+    h->total = off;
+    int rc   = 0;
+    rc |= h->alloc(&h->params, off);
+    rc |= h->alloc(&h->grads, off);
+    rc |= h->alloc(&h->m, off);  // Adam first moment / SGD momentum buffer
+    if (optimizer == 1)
+        rc |= h->alloc(&h->v, off);
+    if (three(h))
+    {
+        rc |= h->alloc(&h->params_small, off);
+        rc |= h->alloc(&h->x_small, static_cast<size_t>(batch) * sizes[0]);
+    }
+    h->act.resize(h->L, nullptr);
+    h->act_small.resize(h->L, nullptr);
+    for (int l = 0; l < h->L && !rc; ++l)
+    {
+        rc |= h->alloc(&h->act[l], static_cast<size_t>(batch) * sizes[l + 1]);
+        if (three(h) && l + 1 < h->L)
+            rc |= h->alloc(&h->act_small[l], static_cast<size_t>(batch) * sizes[l + 1]);
+    }
+    for (int i = 0; i < 2 && !rc; ++i)
+    {
+        rc |= h->alloc(&h->gbuf[i], static_cast<size_t>(batch) * h->max_width);
+        if (three(h))
+            rc |= h->alloc(&h->gbuf_small[i], static_cast<size_t>(batch) * h->max_width);
+    }
+    rc |= h->alloc(&h->row_loss, static_cast<size_t>(batch));
+    rc |= h->alloc(&h->loss, 1);
+    if (rc)
+    {
+        delete h;
+        return kCudaError;
+    }
+    cudaMemset(h->params, 0, off * 4);
+    cudaMemset(h->grads, 0, off * 4);
+    cudaMemset(h->m, 0, off * 4);
+    if (h->v)
+        cudaMemset(h->v, 0, off * 4);
+    if (h->params_small)
+        cudaMemset(h->params_small, 0, off * 4);
+    *handle = h;
+    return kOk;
+}
+
+int odl_mlp_destroy(void *handle)
+{
+    cudaDeviceSynchronize();
+    delete H(handle);
+    return kOk;
+}
+
+int64_t odl_mlp_param_count(void *handle)
+{
+    int64_t n = 0;
+    Mlp *h    = H(handle);
+    for (int l = 0; l < h->L; ++l)
+        n += static_cast<int64_t>(h->sizes[l]) * h->sizes[l + 1] + h->sizes[l + 1];
+    return n;
+}
+
+// Packed host layout: [W_0 {in,out} row-major, b_0 {1,out}, W_1, b_1, ...] without padding (what
+// Module::named_parameters yields layer by layer, src/nn/models/mlp.cpp:32-33).
+int odl_mlp_set_params(void *handle, const float *host_packed, void *stream)
+{
+    Mlp *h = H(handle);
+    int64_t o = 0;
+    for (int l = 0; l < h->L; ++l)
+    {
+        const int64_t nw = static_cast<int64_t>(h->sizes[l]) * h->sizes[l + 1], nb = h->sizes[l + 1];
+        ODL_CUDA_TRY(cudaMemcpyAsync(h->params + h->w_off[l], host_packed + o, nw * 4, cudaMemcpyHostToDevice, ST(stream)));
+        o += nw;
+        ODL_CUDA_TRY(cudaMemcpyAsync(h->params + h->b_off[l], host_packed + o, nb * 4, cudaMemcpyHostToDevice, ST(stream)));
+        o += nb;
+    }
+    if (three(h))
+    {
+        int rc = split_launch(h->params, h->total, 1, (int)h->total, nullptr, 0, nullptr, h->params_small, h->total,
+                              nullptr, ST(stream));
+        if (rc)
+            return rc;
+    }
+    h->step_count = 0;
+    ODL_CUDA_TRY(cudaMemsetAsync(h->m, 0, h->total * 4, ST(stream)));
+    if (h->v)
+        ODL_CUDA_TRY(cudaMemsetAsync(h->v, 0, h->total * 4, ST(stream)));
+    ODL_CUDA_TRY(cudaStreamSynchronize(ST(stream)));
+    return kOk;
+}
+
+// which: 0 parameters, 1 gradients of the last backward (after the optimizer's hook, like Parameter::grad()).
+int odl_mlp_get_packed(void *handle, int which, float *host_packed, void *stream)
+{
+    Mlp *h           = H(handle);
+    const float *src = which == 0 ? h->params : h->grads;
+    int64_t o        = 0;
+    for (int l = 0; l < h->L; ++l)
+    {
+        const int64_t nw = static_cast<int64_t>(h->sizes[l]) * h->sizes[l + 1], nb = h->sizes[l + 1];
+        ODL_CUDA_TRY(cudaMemcpyAsync(host_packed + o, src + h->w_off[l], nw * 4, cudaMemcpyDeviceToHost, ST(stream)));
+        o += nw;
+        ODL_CUDA_TRY(cudaMemcpyAsync(host_packed + o, src + h->b_off[l], nb * 4, cudaMemcpyDeviceToHost, ST(stream)));
+        o += nb;
+    }
+    ODL_CUDA_TRY(cudaStreamSynchronize(ST(stream)));
+    return kOk;
+}
+
+// Forward through all layers, loss and d loss / d logits (scaled by grad_scale / batch), bias gradient of the head.
+int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
+{
+    Mlp *h         = H(handle);
+    cudaStream_t s = ST(stream);
+    const int64_t B = h->batch;
+    int rc;
+    h->cur_x = x;
+    if (three(h))
+    {
+        rc = split_launch(x, h->sizes[0], (int)B, h->sizes[0], nullptr, 0, nullptr, h->x_small, h->sizes[0], nullptr, s);
+        if (rc)
+            return rc;
+    }
+    const float *in = x, *in_s = h->x_small;
+    for (int l = 0; l < h->L; ++l)
+    {
+        const bool last = (l + 1 == h->L);
+        rc = linear_forward(in, in_s, h->params + h->w_off[l], three(h) ? h->params_small + h->w_off[l] : nullptr,
+                            h->params + h->b_off[l], h->act[l], last ? nullptr : h->act_small[l], B, h->sizes[l + 1],
+                            h->sizes[l], ODL_W_IN_OUT, last ? 0 : 1, h->precision, s);
+        if (rc)
+            return rc;
+        in = h->act[l], in_s = h->act_small[l];
+    }
+    const int C = h->sizes[h->L];
+    rc = softmax_ce_launch(h->act[h->L - 1], labels_are_int64 ? nullptr : static_cast<const int32_t *>(labels),
+                           labels_are_int64 ? static_cast<const int64_t *>(labels) : nullptr, B, C, h->loss, h->gbuf[0],
+                           h->row_loss, 1.0f, s);
+    if (rc)
+        return rc;
+    // low part of dlogits + bias gradient of the head in one pass
+    float *db = h->grads + h->b_off[h->L - 1];
+    ODL_CUDA_TRY(cudaMemsetAsync(db, 0, static_cast<size_t>(C) * 4, s));
+    return split_launch(h->gbuf[0], C, (int)B, C, nullptr, 0, nullptr, three(h) ? h->gbuf_small[0] : nullptr, C, db, s);
+}
+
+// Backward of layer `layer` (call for layer = L-1 ... 0): dW_layer into the flat gradient buffer and, for layer > 0,
+// the gradient w.r.t. the layer below's pre-activation together with that layer's bias gradient.
+int odl_mlp_backward_layer(void *handle, int layer, void *stream)
+{
+    Mlp *h = H(handle);
+    if (layer < 0 || layer >= h->L)
+    {
+        set_last_error("mlp: layer %d out of range", layer);
+        return kInvalidArgument;
+    }
+    cudaStream_t s   = ST(stream);
+    const int64_t B  = h->batch;
+    const int cur    = (h->L - 1 - layer) & 1;  // ping-pong: the head's gradient sits in gbuf[0]
+    const float *g   = h->gbuf[cur], *g_s = h->gbuf_small[cur];
+    const float *xin = layer == 0 ? h->cur_x : h->act[layer - 1];
+    const float *xin_s = layer == 0 ? h->x_small : h->act_small[layer - 1];
+    float *dx = nullptr, *dx_s = nullptr, *prev_db = nullptr;
+    const float *prev_y = nullptr;
+    if (layer > 0)
+    {
+        dx      = h->gbuf[cur ^ 1];
+        dx_s    = three(h) ? h->gbuf_small[cur ^ 1] : nullptr;
+        prev_y  = h->act[layer - 1];
+        prev_db = h->grads + h->b_off[layer - 1];
+    }
+    return linear_backward(xin, xin_s, h->params + h->w_off[layer], three(h) ? h->params_small + h->w_off[layer] : nullptr,
+                           g, g_s, nullptr, dx, dx_s, prev_y, prev_db, h->grads + h->w_off[layer], nullptr, B,
+                           h->sizes[layer + 1], h->sizes[layer], ODL_W_IN_OUT, h->precision, s);
+}
+
+// One fused update of every parameter.  grad_scale: 1/world_size after a summing all-reduce, else 1.
+int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream)
+{
+    Mlp *h = H(handle);
+    h->step_count += 1;
+    if (h->optimizer == 1)
+        return adam_launch(h->params, h->grads, h->m, h->v, h->params_small, h->total, h->step_count, h->lr, h->beta1,
+                           h->beta2, h->eps, h->hook_wd, grad_scale, ST(stream));
+    return sgd_launch(h->params, h->grads, h->m, h->params_small, h->total, h->lr, h->momentum, 0.0f, 0, h->hook_wd,
+                      grad_scale, ST(stream));
+}
+
+int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
+{
+    int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
+    if (rc)
+        return rc;
+    for (int l = H(handle)->L - 1; l >= 0; --l)
+        if ((rc = odl_mlp_backward_layer(handle, l, stream)))
+            return rc;
+    return odl_mlp_optimizer_step(handle, 1.0f, stream);
+}
+
+// Device pointer of the scalar loss of the last forward (read it after synchronising the stream).
+float *odl_mlp_loss_ptr(void *handle)
+{
+    return H(handle)->loss;
+}
+
+// Logits of the last forward: device pointer to [batch, sizes.back()].
+float *odl_mlp_logits_ptr(void *handle)
+{
+    Mlp *h = H(handle);
+    return h->act[h->L - 1];
+}
+
+// Contiguous gradient range [dW_layer, db_layer] (device pointer, element count) for the data-parallel all-reduce;
+// layer = -1 gives the whole flat gradient buffer.
+int odl_mlp_grad_bucket(void *handle, int layer, float **ptr, int64_t *count)
+{
+    Mlp *h = H(handle);
+    if (layer < -1 || layer >= h->L || !ptr || !count)
+    {
+        set_last_error("mlp: bad bucket request");
+        return kInvalidArgument;
+    }
+    if (layer == -1)
+    {
+        *ptr   = h->grads;
+        *count = h->total;
+        return kOk;
+    }
+    *ptr   = h->grads + h->w_off[layer];
+    *count = (layer + 1 < h->L ? h->w_off[layer + 1] : h->total) - h->w_off[layer];
+    return kOk;
+}
+
+}  // extern "C"

@@ -146,6 +146,7 @@ int split_launch(const float *src, int64_t ld_src, int rows, int cols, const flo
     SplitParams p{src, aux, dst_big, dst_small, colsum, ld_src, ld_aux, ld_dst, rows, cols};
     dim3 grid((cols + 127) / 128, (rows + kSplitRows - 1) / kSplitRows);
     split_kernel<<<grid, kSplitWarps * 32, 0, stream>>>(p);
+    ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {

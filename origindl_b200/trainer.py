@@ -1,0 +1,129 @@
+"""Host-side driver of the device-resident MLP training state (odl_mlp_* in include/odl_b200.h).
+
+Mirrors the reference's training loop (tests/example/mnist/mlp_mnist.cpp:176-437):
+
+    model = nn::MLP(sizes); optimizer = Adam(model, lr); optimizer.register_hook(WeightDecay(rate).hook())
+    y = model(x); loss = softmax_cross_entropy(y, t); optimizer.zero_grad(); loss.backward(); optimizer.step()
+
+Data parallelism (one process per GPU): every rank holds full parameter / optimizer replicas and its own slice of
+the batch.  After layer l's backward the rank's gradient bucket [dW_l, db_l] -- one contiguous range of the flat
+gradient buffer -- is summed across ranks with NCCL on a side stream while layers l-1 ... 0 keep computing; the
+optimizer then scales by 1/world_size inside its fused update.  torch supplies streams, events and the process
+group; all arithmetic is in libodl_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import capi
+
+
+class MLPTrainer:
+    def __init__(self, sizes, batch, optimizer="adam", lr=1e-3, momentum=0.0, hook_weight_decay=0.0,
+                 precision=capi.PRECISION_3XTF32, device=0, process_group=None, overlap=True):
+        capi.init(device)
+        self.sizes = [int(s) for s in sizes]
+        self.batch = int(batch)
+        self.n_layers = len(self.sizes) - 1
+        arr = (ctypes.c_int32 * len(self.sizes))(*self.sizes)
+        h = ctypes.c_void_p()
+        opt = {"sgd": 0, "adam": 1}[optimizer]
+        capi.call("odl_mlp_create", arr, len(self.sizes), self.batch, opt, lr, momentum, hook_weight_decay, precision,
+                  ctypes.byref(h))
+        self._h = h
+        self.pg = process_group
+        self.world = 1
+        self.overlap = overlap
+        self._buckets = None
+        if process_group is not None:
+            import torch.distributed as dist
+
+            self.world = dist.get_world_size(process_group)
+            self._comm_stream = torch.cuda.Stream()
+            self._buckets = [self._bucket_tensor(l) for l in range(self.n_layers)]
+        self._loss_view = self._view(capi.lib().odl_mlp_loss_ptr(self._h), 1)
+
+    # -- raw device memory of the library wrapped as torch tensors (no copy) so that NCCL can reduce it in place
+    @staticmethod
+    def _view(ptr: int, count: int) -> torch.Tensor:
+        class _Blob:
+            pass
+
+        b = _Blob()
+        b.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                      "strides": None}
+        return torch.as_tensor(b, device="cuda")
+
+    def _bucket_tensor(self, layer: int) -> torch.Tensor:
+        p, n = ctypes.c_void_p(), ctypes.c_int64()
+        capi.call("odl_mlp_grad_bucket", self._h, layer, ctypes.byref(p), ctypes.byref(n))
+        return self._view(p.value, n.value)
+
+    @property
+    def param_count(self) -> int:
+        return int(capi.lib().odl_mlp_param_count(self._h))
+
+    def set_params(self, packed: np.ndarray) -> None:
+        packed = np.ascontiguousarray(packed, np.float32)
+        assert packed.size == self.param_count
+        capi.call("odl_mlp_set_params", self._h, packed.ctypes.data, capi.stream_handle())
+
+    def get_params(self) -> np.ndarray:
+        out = np.empty(self.param_count, np.float32)
+        capi.call("odl_mlp_get_packed", self._h, 0, out.ctypes.data, capi.stream_handle())
+        return out
+
+    def get_grads(self) -> np.ndarray:
+        out = np.empty(self.param_count, np.float32)
+        capi.call("odl_mlp_get_packed", self._h, 1, out.ctypes.data, capi.stream_handle())
+        return out
+
+    def logits(self) -> torch.Tensor:
+        return self._view(capi.lib().odl_mlp_logits_ptr(self._h), self.batch * self.sizes[-1]).view(self.batch, -1)
+
+    def loss_tensor(self) -> torch.Tensor:
+        """0-dim view of the device loss of the last forward (no synchronisation)."""
+        return self._loss_view[0]
+
+    def train_step(self, x: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """One optimisation step on x[batch, sizes[0]] / labels[batch]; returns the device loss (a view)."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (self.batch, self.sizes[0])
+        assert labels.is_cuda and labels.is_contiguous() and labels.dtype in (torch.int32, torch.int64)
+        s = capi.stream_handle()
+        is64 = int(labels.dtype == torch.int64)
+        if self.pg is None:
+            capi.call("odl_mlp_train_step", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
+            return self._loss_view[0]
+        import torch.distributed as dist
+
+        compute = torch.cuda.current_stream()
+        capi.call("odl_mlp_forward_loss", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
+        for layer in range(self.n_layers - 1, -1, -1):
+            capi.call("odl_mlp_backward_layer", self._h, layer, s)
+            if self.overlap:
+                ev = torch.cuda.Event()
+                ev.record(compute)
+                self._comm_stream.wait_event(ev)
+                with torch.cuda.stream(self._comm_stream):
+                    dist.all_reduce(self._buckets[layer], op=dist.ReduceOp.SUM, group=self.pg)
+        if self.overlap:
+            compute.wait_stream(self._comm_stream)
+        else:
+            for layer in range(self.n_layers - 1, -1, -1):
+                dist.all_reduce(self._buckets[layer], op=dist.ReduceOp.SUM, group=self.pg)
+        capi.call("odl_mlp_optimizer_step", self._h, 1.0 / self.world, s)
+        return self._loss_view[0]
+
+    def close(self) -> None:
+        if self._h is not None:
+            capi.call("odl_mlp_destroy", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

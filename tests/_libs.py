@@ -115,3 +115,54 @@ def max_rel_err(a, b) -> float:
     b = np.asarray(b, np.float64)
     denom = np.abs(b).max()
     return float(np.abs(a - b).max() / (denom if denom > 0 else 1.0))
+
+
+# ---------------------------------------------------------------- MLP training composed from the oracle functions
+def oracle_mlp_train(sizes, params, xs, ts, steps, opt="adam", lr=1e-3, momentum=0.0, hook_wd=0.0, grad_hook=None):
+    """Train with the oracle's Linear / softmax-CE / optimizer functions, following nn::MLP + the reference loop.
+
+    params: packed [W_0 {in,out}, b_0, ...]; xs[n_batches, B, in], ts[n_batches, B].  `grad_hook(list_of_grads)` is
+    called after backward and before the optimizer (used by the data-parallel tests to all-reduce).  Returns
+    (losses, final packed params, last gradients as the optimizer left them)."""
+    orc = oracle()
+    sizes = [int(s) for s in sizes]
+    L = len(sizes) - 1
+    views, off = [], 0
+    params = params.copy()
+    for l in range(L):
+        nw, nb = sizes[l] * sizes[l + 1], sizes[l + 1]
+        views.append((off, nw, off + nw, nb))
+        off += nw + nb
+    m, v = np.zeros_like(params), np.zeros_like(params)
+    B = xs.shape[1]
+    losses = np.empty(steps, np.float32)
+    grads = np.zeros_like(params)
+    for s in range(steps):
+        x = np.ascontiguousarray(xs[s % xs.shape[0]])
+        t = np.ascontiguousarray(ts[s % ts.shape[0]])
+        acts = [x]
+        for l, (wo, nw, bo, nb) in enumerate(views):
+            y = np.empty((B, sizes[l + 1]), np.float32)
+            orc.oracle_linear_forward(acts[-1], params[wo:wo + nw], fptr(params[bo:bo + nb]), y, B, sizes[l + 1],
+                                      sizes[l], 1, int(l + 1 < L))
+            acts.append(y)
+        loss = ctypes.c_float()
+        g = np.empty_like(acts[-1])
+        assert orc.oracle_softmax_ce(acts[-1], t, B, sizes[-1], ctypes.byref(loss), fptr(g)) == 0
+        losses[s] = loss.value
+        grads = np.zeros_like(params)
+        for l in range(L - 1, -1, -1):
+            wo, nw, bo, nb = views[l]
+            dx = np.empty_like(acts[l]) if l > 0 else None
+            # the ReLU of layer l sits between its Linear and layer l+1: mask the incoming gradient with y_l > 0
+            relu = int(l + 1 < L)
+            orc.oracle_linear_backward(acts[l], params[wo:wo + nw], fptr(acts[l + 1]), g, fptr(dx),
+                                       fptr(grads[wo:wo + nw]), fptr(grads[bo:bo + nb]), B, sizes[l + 1], sizes[l], 1, relu)
+            g = dx
+        if grad_hook is not None:
+            grad_hook(grads)
+        if opt == "adam":
+            orc.oracle_adam_step(params, grads, m, v, params.size, s + 1, lr, 0.9, 0.999, 1e-8, hook_wd)
+        else:
+            orc.oracle_sgd_step(params, grads, fptr(m), params.size, lr, momentum, 0.0, 0, hook_wd)
+    return losses, params, grads

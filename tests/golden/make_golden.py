@@ -28,14 +28,72 @@ def c1_inputs(n_batches=4, B=512, sizes=(784, 1000, 1000, 10), seed=42):
     return params, x, t
 
 
+def stable_inputs(n_batches=4, B=256, sizes=(784, 256, 256, 10), seed=42):
+    """A well-conditioned 200-step configuration: MNIST-shaped inputs, labels from a fixed random linear teacher
+    (so the loss falls smoothly), trained with SGD lr 0.003 momentum 0.9."""
+    rng = np.random.default_rng(seed)
+    params = _libs.mlp_params(rng, sizes)
+    x = rng.uniform(0, 1, (n_batches, B, sizes[0])).astype(np.float32)
+    teacher = rng.standard_normal((sizes[0], sizes[-1])).astype(np.float32)
+    t = np.argmax((x - 0.5) @ teacher, axis=-1).astype(np.int32)
+    return params, x, t
+
+
+def mlp_curve_float64(sizes, params, xs, ts, steps, opt, lr, momentum=0.0, hook_wd=0.0):
+    """The same training step in float64 numpy (exact-arithmetic yardstick: how far does a run that makes NO fp32
+    rounding error drift from the reference's fp32 curve?)."""
+    sizes = [int(v) for v in sizes]
+    L = len(sizes) - 1
+    p = params.astype(np.float64)
+    views, off = [], 0
+    for l in range(L):
+        nw, nb = sizes[l] * sizes[l + 1], sizes[l + 1]
+        views.append((slice(off, off + nw), slice(off + nw, off + nw + nb)))
+        off += nw + nb
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    B = xs.shape[1]
+    losses = []
+    for s in range(steps):
+        x, t = xs[s % len(xs)].astype(np.float64), ts[s % len(ts)]
+        acts = [x]
+        for l, (ws, bs) in enumerate(views):
+            y = acts[-1] @ p[ws].reshape(sizes[l], sizes[l + 1]) + p[bs]
+            acts.append(np.maximum(y, 0) if l + 1 < L else y)
+        z = acts[-1] - acts[-1].max(1, keepdims=True)
+        pr = np.exp(z) / np.exp(z).sum(1, keepdims=True)
+        losses.append(-np.log(pr[np.arange(B), t] + 1e-8).sum() / B)
+        g = pr.copy()
+        g[np.arange(B), t] -= 1
+        g /= B
+        grads = np.zeros_like(p)
+        for l in range(L - 1, -1, -1):
+            ws, bs = views[l]
+            if l + 1 < L:
+                g = g * (acts[l + 1] > 0)
+            grads[ws] = (acts[l].T @ g).ravel()
+            grads[bs] = g.sum(0)
+            g = g @ p[ws].reshape(sizes[l], sizes[l + 1]).T
+        grads += hook_wd * p
+        if opt == "adam":
+            m = 0.9 * m + 0.1 * grads
+            v = 0.999 * v + 0.001 * grads * grads
+            p = p - lr * (m / (1 - 0.9 ** (s + 1))) / (np.sqrt(v / (1 - 0.999 ** (s + 1))) + 1e-8)
+        else:
+            m = momentum * m + grads
+            p = p - lr * m
+    return np.array(losses, np.float64)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--c1-steps", type=int, default=200)
+    ap.add_argument("--reuse", action="store_true", help="keep arrays already in the output file, add missing ones")
     args = ap.parse_args()
     ref = _libs.reference()
     if ref is None:
         raise SystemExit("reference library unavailable")
     out = {}
+    have = dict(np.load(OUT)) if (args.reuse and OUT.exists()) else {}
 
     # ---- Linear forward + backward, both weight layouts, with ReLU (N(0,1) inputs, b ~ N(0,0.1))
     for tag, (M, N, K) in {"lin_a": (96, 80, 72), "lin_b": (130, 33, 257)}.items():
@@ -101,7 +159,9 @@ def main():
         out.update({f"mlp_{tag}_losses": losses, f"mlp_{tag}_params": params, f"mlp_{tag}_lastgrads": grads})
 
     # ---- the MNIST-shaped configuration: loss curve of the reference over --c1-steps Adam steps (lr 1e-3, wd 1e-4)
-    if args.c1_steps > 0:
+    if "c1_losses" in have:
+        out.update({"c1_losses": have["c1_losses"], "c1_param_sample": have["c1_param_sample"]})
+    elif args.c1_steps > 0:
         sizes = np.array([784, 1000, 1000, 10], np.int32)
         params, x, t = c1_inputs()
         losses = np.empty(args.c1_steps, np.float32)
@@ -109,6 +169,22 @@ def main():
                                              None))
         # final parameters are 1.8 M floats; keep a strided sample (every 257th) for a cheap check
         out.update({"c1_losses": losses, "c1_param_sample": params[::257].copy()})
+    if "c1_losses" in out and "c1_losses_fp64" not in have:
+        params, x, t = c1_inputs()
+        out["c1_losses_fp64"] = mlp_curve_float64([784, 1000, 1000, 10], params, x, t, len(out["c1_losses"]), "adam", 1e-3,
+                                                  hook_wd=1e-4)
+    elif "c1_losses_fp64" in have:
+        out["c1_losses_fp64"] = have["c1_losses_fp64"]
+
+    # ---- the well-conditioned 200-step configuration (SGD momentum, teacher labels)
+    if "stable_losses" in have:
+        out.update({k: have[k] for k in ("stable_losses", "stable_param_sample")})
+    else:
+        sizes = np.array([784, 256, 256, 10], np.int32)
+        params, x, t = stable_inputs()
+        losses = np.empty(200, np.float32)
+        _libs.ref_check(ref.odlref_mlp_train(sizes, 4, params, x, t, 256, 4, 200, 0, 3e-3, 0.9, 0.0, losses, None))
+        out.update({"stable_losses": losses, "stable_param_sample": params[::101].copy()})
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 

@@ -1,0 +1,119 @@
+"""GPU: the device-resident MLP training step (odl_mlp_*) against the reference's own loss curves and parameters
+(golden vectors from the unmodified reference) and against the oracle at other sizes."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import _libs
+from _libs import max_rel_err
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def trainer_cls():
+    from origindl_b200 import capi
+    from origindl_b200.trainer import MLPTrainer
+
+    capi.init(0)
+    yield MLPTrainer
+    capi.device_status()
+
+
+def run(tr, xs, ts, steps):
+    xd, td = torch.from_numpy(xs).cuda(), torch.from_numpy(ts).cuda()
+    losses = []
+    for s in range(steps):
+        losses.append(tr.train_step(xd[s % xd.shape[0]], td[s % td.shape[0]]).item())
+    return np.array(losses, np.float32)
+
+
+@pytest.mark.parametrize("tag,kw", [("adam", dict(optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)),
+                                    ("sgd", dict(optimizer="sgd", lr=5e-2, momentum=0.9))])
+def test_small_mlp_tracks_reference(trainer_cls, tag, kw):
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    tr = trainer_cls(g["mlp_sizes"], 16, **kw)
+    tr.set_params(g["mlp_params0"])
+    losses = run(tr, g["mlp_x"], g["mlp_t"], 12)
+    assert np.abs(losses - g[f"mlp_{tag}_losses"]).max() <= 1e-5
+    assert max_rel_err(tr.get_params(), g[f"mlp_{tag}_params"]) <= 2e-5
+    # gradients of the last step as Parameter::grad() shows them after the hook ran
+    _, _, grads = _libs.oracle_mlp_train(g["mlp_sizes"], g["mlp_params0"], g["mlp_x"], g["mlp_t"], 12,
+                                         opt=tag, lr=kw["lr"], momentum=kw.get("momentum", 0.0),
+                                         hook_wd=kw.get("hook_weight_decay", 0.0))
+    assert max_rel_err(tr.get_grads(), grads) <= 1e-4
+    tr.close()
+
+
+def test_stable_200_step_curve_tracks_reference_within_1e3(trainer_cls):
+    """784-256-256-10, batch 256, teacher labels, SGD lr 3e-3 momentum 0.9: a well-conditioned run, where the
+    reference's 200-step fp32 loss curve is tracked within 1e-3 at every step."""
+    from golden.make_golden import stable_inputs
+
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    params, x, t = stable_inputs()
+    tr = trainer_cls([784, 256, 256, 10], 256, optimizer="sgd", lr=3e-3, momentum=0.9)
+    tr.set_params(params)
+    losses = run(tr, x, t, 200)
+    assert np.abs(losses - g["stable_losses"]).max() <= 1e-3
+    # parameters after 200 steps: a loose sanity bound (the stated tolerance is on the loss curve)
+    assert max_rel_err(tr.get_params()[::101], g["stable_param_sample"]) <= 1e-2
+    tr.close()
+
+
+def test_mnist_shaped_adam_curve_tracks_reference_like_exact_arithmetic(trainer_cls):
+    """784-1000-1000-10, batch 512, Adam lr 1e-3, weight decay 1e-4, random labels, seed 42 (the MNIST-shaped
+    benchmark configuration).  This run is chaotic: a float64 restatement of the very same step (no fp32 rounding at
+    all; golden `c1_losses_fp64`) leaves the 1e-3 band around the reference's curve after about a dozen steps.  So the
+    bar here is: inside 1e-3 while exact arithmetic is (first 10 steps), and over all 200 steps no further from the
+    reference than twice the drift of exact arithmetic."""
+    from golden.make_golden import c1_inputs
+
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    ref, f64 = g["c1_losses"], g["c1_losses_fp64"]
+    params, x, t = c1_inputs()
+    tr = trainer_cls([784, 1000, 1000, 10], 512, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+    tr.set_params(params)
+    losses = run(tr, x, t, len(ref))
+    dev = np.abs(losses - ref)
+    assert np.abs(f64[:10] - ref[:10]).max() <= 1e-3      # the yardstick itself is inside the band here
+    assert dev[:10].max() <= 1e-3
+    assert dev.max() <= max(1e-3, 2.0 * np.abs(f64 - ref).max())
+    assert losses[-1] < 0.5 * losses[0]                  # and it trains
+    tr.close()
+
+
+def test_tf32_mode_and_odd_widths(trainer_cls):
+    """Widths that are not multiples of 4 (staged through padded scratch) and the opt-in plain-TF32 mode."""
+    rng = np.random.default_rng(12)
+    sizes = [37, 50, 21, 7]
+    params = _libs.mlp_params(rng, sizes)
+    xs = rng.standard_normal((2, 24, 37)).astype(np.float32)
+    ts = rng.integers(0, 7, (2, 24)).astype(np.int32)
+    ref_losses, ref_params, _ = _libs.oracle_mlp_train(sizes, params, xs, ts, 6, opt="sgd", lr=0.05, momentum=0.9)
+    for precision, tol in ((0, 1e-5), (1, 5e-3)):
+        tr = trainer_cls(sizes, 24, optimizer="sgd", lr=0.05, momentum=0.9, precision=precision)
+        tr.set_params(params)
+        losses = run(tr, xs, ts, 6)
+        assert np.abs(losses - ref_losses).max() <= max(tol, 1e-5) * 10
+        assert max_rel_err(tr.get_params(), ref_params) <= tol * 10
+        tr.close()
+
+
+def test_int64_labels_and_logits_view(trainer_cls):
+    rng = np.random.default_rng(3)
+    sizes = [16, 32, 10]
+    tr = trainer_cls(sizes, 8)
+    params = _libs.mlp_params(rng, sizes)
+    tr.set_params(params)
+    x = torch.from_numpy(rng.standard_normal((8, 16)).astype(np.float32)).cuda()
+    t = torch.from_numpy(rng.integers(0, 10, 8)).cuda()          # int64
+    l64 = tr.train_step(x, t).item()
+    logits = tr.logits().clone()
+    tr.set_params(params)
+    l32 = tr.train_step(x, t.to(torch.int32)).item()
+    assert l64 == l32 and torch.equal(logits, tr.logits())
+    tr.close()
