@@ -519,3 +519,14 @@ extern "C" long long odl_launch_count(void)
 {
     return odl::g_launch_count;
 }
+
+namespace odl
+{
+extern int g_bk_override;
+}
+// Test hook: K elements per pipeline stage of the 256-wide GEMM tile (16 or 32; 0 = automatic).
+extern "C" int odl_debug_set_bk(int bk)
+{
+    odl::g_bk_override = bk;
+    return 0;
+}

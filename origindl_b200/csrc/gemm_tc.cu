@@ -39,7 +39,6 @@ namespace
 {
 
 constexpr int kBM          = 128;  // rows of D per CTA == TMEM lanes == UMMA M
-constexpr int kBK          = 32;   // fp32 elements per 128-byte swizzle row
 constexpr int kUmmaK       = 8;    // K per tcgen05.mma for kind::tf32
 constexpr int kEpiWarps    = 8;    // two warps per TMEM lane quarter, each owning half of the tile's columns
 constexpr int kThreads     = 64 + 32 * kEpiWarps;
@@ -49,11 +48,14 @@ constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kAuxBytes    = 1024;  // barriers, TMEM pointer, abort flag
 constexpr int kMaxStages   = 8;
 
-template <int BN>
+// BK: fp32 elements of K per pipeline stage: 32 (128-byte swizzle rows) or 16 (64-byte rows, twice as many stages
+// in flight for the same shared memory, which hides the load latency of the wide 3xTF32 stages).
+template <int BN, int BK>
 struct TileCfg
 {
-    static constexpr int a_bytes   = kBM * kBK * 4;
-    static constexpr int b_bytes   = BN * kBK * 4;
+    static constexpr int a_bytes   = kBM * BK * 4;
+    static constexpr int b_bytes   = BN * BK * 4;
+    static constexpr int mn_box    = 32 * BK * 4;  // bytes of one {32 mn, BK k} box of an MN-major operand
     __host__ __device__ static constexpr int stage_bytes(int terms) { return (a_bytes + b_bytes) * (terms == 3 ? 2 : 1); }
     __host__ __device__ static constexpr int stages(int terms)
     {
@@ -75,12 +77,12 @@ struct alignas(64) TmapPack
 // TMEM with truncation, which biases a long running sum towards zero by about 7.5e-9 * (chunk length in K) relative
 // to the largest result; summing short chunks in registers (round-to-nearest) keeps 3xTF32 at fp32-class accuracy
 // for any K.
-template <int BN>
+template <int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
                const int stages, const int chunk_kb)
 {
-    using Cfg = TileCfg<BN>;
+    using Cfg = TileCfg<BN, BK>;
     extern __shared__ uint8_t smem_raw[];
 
     // ---- carve shared memory (tiles need 1024-byte alignment for the 128-byte swizzle)
@@ -126,7 +128,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
     const int m0      = tile_m * kBM;
     const int n0      = tile_n * BN;
     const int kb_first = blockIdx.y * p.kb_per_split;  // split-K: this CTA reduces K-blocks [kb_first, kb_first + num_kb)
-    const int num_kb   = min((p.K + kBK - 1) / kBK - kb_first, p.kb_per_split);
+    const int num_kb   = min((p.K + BK - 1) / BK - kb_first, p.kb_per_split);
     const int nchunks  = (num_kb + chunk_kb - 1) / chunk_kb;
 
     // ---- one-time setup
@@ -175,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     break;
                 uint8_t *st = tiles + s * stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
-                const int k0 = (kb_first + kb) * kBK;
+                const int k0 = (kb_first + kb) * BK;
                 for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
                 {
                     uint8_t *sa           = st + t * Cfg::a_bytes;
@@ -188,7 +190,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     {
 #pragma unroll
                         for (int j = 0; j < kBM / 32; ++j)
-                            ptx::tma_load_2d(sa + j * 4096, ma, &full_bar[s], m0 + 32 * j, k0);
+                            ptx::tma_load_2d(sa + j * Cfg::mn_box, ma, &full_bar[s], m0 + 32 * j, k0);
                     }
                 }
                 uint8_t *sb0 = st + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
@@ -204,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     {
 #pragma unroll
                         for (int j = 0; j < BN / 32; ++j)
-                            ptx::tma_load_2d(sb + j * 4096, mb, &full_bar[s], n0 + 32 * j, k0);
+                            ptx::tma_load_2d(sb + j * Cfg::mn_box, mb, &full_bar[s], n0 + 32 * j, k0);
                     }
                 }
                 ++issued;
@@ -226,12 +228,15 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
             const uint32_t idesc  = ptx::make_idesc_tf32(kBM, BN, a_mn != 0, b_mn != 0);
             const uint32_t a_step = a_mn ? 1024u : 32u;  // bytes per K=8 step
             const uint32_t b_step = b_mn ? 1024u : 32u;
-            const uint32_t a_lbo  = a_mn ? 4096u : 16u;
-            const uint32_t b_lbo  = b_mn ? 4096u : 16u;
-            const uint32_t a_sbo  = a_mn ? 512u : 1024u;
-            const uint32_t b_sbo  = b_mn ? 512u : 1024u;
-            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
-            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            // K-major: 8-row groups of (BK*4)-byte rows; MN-major: 32-mn groups one box apart, 4-k groups 512 B apart
+            constexpr uint32_t k_sbo = 8u * BK * 4u;
+            constexpr uint32_t k_lay = BK == 32 ? ptx::kLayoutSw128 : ptx::kLayoutSw64;
+            const uint32_t a_lbo  = a_mn ? Cfg::mn_box : 16u;
+            const uint32_t b_lbo  = b_mn ? Cfg::mn_box : 16u;
+            const uint32_t a_sbo  = a_mn ? 512u : k_sbo;
+            const uint32_t b_sbo  = b_mn ? 512u : k_sbo;
+            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : k_lay;
+            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : k_lay;
             bool ok               = true;
             int kb                = 0;
             for (int c = 0; c < nchunks && ok; ++c)
@@ -261,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
                     const uint32_t sbs = sb + Cfg::b_bytes;
 #pragma unroll
-                    for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                    for (int kk = 0; kk < BK / kUmmaK; ++kk)
                     {
                         const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
                         const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
@@ -514,6 +519,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 }  // namespace
 extern int g_chunk_kb;
 extern int g_split_k;
+extern int g_bk_override;
 namespace
 {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -560,22 +566,21 @@ int make_tmap(CUtensorMap *out, const float *ptr, int64_t rows, int64_t cols, in
     return kOk;
 }
 
-template <int BN>
+template <int BN, int BK>
 int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int terms, cudaStream_t stream)
 {
-    using Cfg        = TileCfg<BN>;
+    using Cfg        = TileCfg<BN, BK>;
     const int stages = Cfg::stages(terms);
     const int smem   = Cfg::smem_bytes(terms);
-    static bool attr_set[64] = {};
+    static bool attr_set[64] = {};  // one flag per device for THIS instantiation
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
     if (!attr_set[dev])
     {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             TileCfg<BN>::smem_bytes(1) > TileCfg<BN>::smem_bytes(3)
-                                                 ? TileCfg<BN>::smem_bytes(1)
-                                                 : TileCfg<BN>::smem_bytes(3));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::smem_bytes(1) > Cfg::smem_bytes(3) ? Cfg::smem_bytes(1)
+                                                                                     : Cfg::smem_bytes(3));
         if (e != cudaSuccess)
         {
             set_last_error("cudaFuncSetAttribute(smem=%d) failed: %s", smem, cudaGetErrorString(e));
@@ -585,7 +590,7 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     }
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int num_kb   = (p.K + kBK - 1) / kBK;
+    const int num_kb   = (p.K + BK - 1) / BK;
     // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split adds its
     // partial tile into a zeroed D with atomics, so only the plain epilogue qualifies.
     GemmParams q = p;
@@ -610,15 +615,15 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
             return kCudaError;
         }
     }
-    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 2 : q.kb_per_split);
+    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 64 / BK : q.kb_per_split);
     if (chunk_kb > q.kb_per_split)
         chunk_kb = q.kb_per_split;
-    gemm_tc_kernel<BN><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb);
+    gemm_tc_kernel<BN, BK><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
-        set_last_error("gemm_tc_kernel<%d> launch failed: %s", BN, cudaGetErrorString(e));
+        set_last_error("gemm_tc_kernel<%d,%d> launch failed: %s", BN, BK, cudaGetErrorString(e));
         return kCudaError;
     }
     return kOk;
@@ -631,6 +636,8 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
 int g_chunk_kb = 0;
 // Test hook: 0 = automatic split-K, 1 = never split, n > 1 = force n splits where the epilogue allows it.
 int g_split_k = 0;
+// Test hook: K elements per pipeline stage of the 256-wide tile (16 or 32; 0 = automatic).
+int g_bk_override = 0;
 
 // A / B operands must already satisfy the tiled-load rules (16-byte aligned base, ld % 4 == 0); the callers in
 // linear.cu stage anything else through padded scratch.  a_mn / b_mn: 0 = K-major storage, 1 = MN-major storage.
@@ -672,9 +679,18 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
     std::memset(&tm, 0, sizeof(tm));
     int rc;
     // A: K-major -> matrix [M][K], box {32, 128};  MN-major -> matrix [K][M], box {32, 32}
+    // pipeline K-depth: BK = 32 everywhere.  BK = 16 (four 48 KB stages instead of two 96 KB ones for the 256-wide
+    // 3xTF32 tile) was measured 5-40 % slower on B200: the loads are bound by the number of 128-byte-or-narrower rows
+    // the TMA unit moves per cycle, not by bytes in flight, and halving the row width doubles the row count.
+    int bk = 32;
+    if (g_bk_override == 16 || g_bk_override == 32)
+        bk = g_bk_override;
+    if (bk == 16 && bn != 256)
+        bk = 32;
     auto mk = [&](CUtensorMap *m, const float *ptr, int64_t ld, int mn, int64_t extent_mn, int box_rows_kmajor) {
-        return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
-                  : make_tmap(m, ptr, extent_mn, p.K, ld, 32, box_rows_kmajor, CU_TENSOR_MAP_SWIZZLE_128B);
+        return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+                  : make_tmap(m, ptr, extent_mn, p.K, ld, bk, box_rows_kmajor,
+                              bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     };
     if ((rc = mk(&tm.a, A, lda, a_mn, p.M, kBM)))
         return rc;
@@ -690,11 +706,12 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
     switch (bn)
     {
         case 64:
-            return launch_bn<64>(tm, p, a_mn, b_mn, terms, stream);
+            return launch_bn<64, 32>(tm, p, a_mn, b_mn, terms, stream);
         case 128:
-            return launch_bn<128>(tm, p, a_mn, b_mn, terms, stream);
+            return launch_bn<128, 32>(tm, p, a_mn, b_mn, terms, stream);
         default:
-            return launch_bn<256>(tm, p, a_mn, b_mn, terms, stream);
+            return bk == 16 ? launch_bn<256, 16>(tm, p, a_mn, b_mn, terms, stream)
+                            : launch_bn<256, 32>(tm, p, a_mn, b_mn, terms, stream);
     }
 }
 

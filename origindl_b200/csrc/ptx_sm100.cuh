@@ -204,6 +204,7 @@ __device__ __forceinline__ void tmem_ld_wait()
 //   bits [61,64) layout: 2 = SWIZZLE_128B (16-byte chunks; K-major operands),
 //                        1 = SWIZZLE_128B with 32-byte chunks (the only layout MN-major 32-bit operands may use)
 constexpr uint32_t kLayoutSw128      = 2;
+constexpr uint32_t kLayoutSw64       = 4;  // 64-byte swizzle (16-byte chunks), K-major rows of 16 fp32
 constexpr uint32_t kLayoutSw128Base32 = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint32_t layout)

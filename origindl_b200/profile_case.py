@@ -1,0 +1,89 @@
+"""Small, self-terminating cases of each kernel of the library, sized for profiler captures.
+
+    python -m origindl_b200.profile_case gemm    --n 4096 [--precision 3xtf32|tf32] [--layout nt|nn|tn] [--iters 3]
+    python -m origindl_b200.profile_case split   --n 8192
+    python -m origindl_b200.profile_case adam    --n 67108864
+    python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
+    python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
+
+Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
+device, launches the kernel `--iters` times after one warm-up launch and prints the CUDA-event time per launch.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import capi, ops
+
+CONV_LAYERS = {1: (3, 16, 6, 2, 2, 320), 2: (16, 32, 3, 2, 1, 160), 3: (32, 32, 1, 1, 0, 80), 4: (64, 64, 3, 1, 1, 40)}
+
+
+def timed(fn, iters):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    capi.device_status()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv"])
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--cols", type=int, default=1024)
+    ap.add_argument("--layer", type=int, default=1)
+    ap.add_argument("--precision", default="3xtf32")
+    ap.add_argument("--layout", default="nt")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    capi.init(0)
+    torch.manual_seed(0)
+    prec = capi.PRECISION_3XTF32 if a.precision == "3xtf32" else capi.PRECISION_TF32
+    if a.case == "gemm":
+        n = a.n
+        ta, tb = {"nt": (False, True), "nn": (False, False), "tn": (True, False)}[a.layout]
+        A, B = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+        As, Bs = ops.split_tf32(A), ops.split_tf32(B)
+        ms = timed(lambda: ops.gemm(A, B, trans_a=ta, trans_b=tb, a_small=As, b_small=Bs, precision=prec), a.iters)
+        print(f"gemm {a.layout} {a.precision} n={n}: {ms:.4f} ms/launch, {2 * n ** 3 / ms / 1e9:.1f} TFLOP/s")
+    elif a.case == "split":
+        n = a.n
+        X = torch.randn(n, n, device="cuda")
+        ms = timed(lambda: ops.split_tf32(X), a.iters)
+        print(f"split n={n}: {ms:.4f} ms/launch, {8 * n * n / ms / 1e6:.1f} GB/s (4 B read + 4 B written per element)")
+    elif a.case == "adam":
+        n = a.n
+        p, g, m, v = (torch.randn(n, device="cuda") for _ in range(4))
+        v.abs_()
+        ps = torch.empty_like(p)
+        ms = timed(lambda: ops.adam_step(p, g, m, v, 3, hook_weight_decay=1e-4, p_small=ps), a.iters)
+        print(f"adam n={n}: {ms:.4f} ms/launch, {36 * n / ms / 1e6:.1f} GB/s (16 B read + 20 B written per parameter)")
+    elif a.case == "softmax":
+        x = torch.randn(a.rows, a.cols, device="cuda")
+        t = torch.randint(0, a.cols, (a.rows,), device="cuda", dtype=torch.int32)
+        ms = timed(lambda: ops.softmax_cross_entropy(x, t), a.iters)
+        print(f"softmax-CE {a.rows}x{a.cols}: {ms:.4f} ms per loss+gradient")
+    else:
+        C, OC, k, s, p, hw = CONV_LAYERS[a.layer]
+        x = torch.rand(16, C, hw, hw, device="cuda")
+        w = torch.randn(OC, C, k, k, device="cuda") * (2.0 / (C * k * k)) ** 0.5
+        b = torch.zeros(OC, device="cuda")
+        y = ops.conv2d_forward(x, w, b, s, p, precision=prec)
+        gy = torch.randn_like(y)
+        msf = timed(lambda: ops.conv2d_forward(x, w, b, s, p, precision=prec), a.iters)
+        msb = timed(lambda: ops.conv2d_backward(gy, x, w, s, p, precision=prec), a.iters)
+        ideal = 4 * (x.numel() + w.numel() + y.numel())
+        print(f"conv layer {a.layer} ({C}->{OC} k{k} s{s} p{p} on {hw}x{hw}, batch 16, {a.precision}): forward {msf:.4f} ms "
+              f"({ideal / msf / 1e6:.1f} GB/s of ideal traffic), backward {msb:.4f} ms")
+
+
+if __name__ == "__main__":
+    main()
