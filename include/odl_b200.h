@@ -141,6 +141,19 @@ int odl_sum_to_row(const float *g, float *out, int64_t M, int64_t N, void *strea
 int odl_softmax_cross_entropy(const float *logits, const void *labels, int labels_are_int64, int64_t B, int64_t C,
                               float *loss, float *dlogits, float grad_scale, void *stream);
 
+/* Same computation as odl_softmax_cross_entropy for callers that cannot allocate device memory once they are running
+ * (a host application that gave the whole GPU to its own pool at start-up; a latency-critical loop that cannot take
+ * the device-wide synchronisation of an allocation).  It has no counterpart in the reference.  The per-row scratch the
+ * loss needs lives in a fixed 256 KiB array inside the library image (held by every GPU that loads the library until
+ * the process exits) instead of the growable arena, so the call itself performs no allocation of any kind.
+ * Limits: B <= ODL_STATIC_SOFTMAX_MAX_ROWS, else ODL_ERR_TOO_LARGE.  The first call on a device resolves the array's
+ * device address (a symbol lookup, no allocation); make that first call before any stream capture.  All calls share
+ * the one array, which keeps the previous call's contents: nothing in it needs clearing (every call overwrites the
+ * rows it reads), but two calls that overlap on the GPU race on it -- keep them on one stream. */
+#define ODL_STATIC_SOFTMAX_MAX_ROWS 65536
+int odl_softmax_cross_entropy_static(const float *logits, const void *labels, int labels_are_int64, int64_t B, int64_t C,
+                                     float *loss, float *dlogits, float grad_scale, void *stream);
+
 /* ---- optimizers -------------------------------------------------------------------------------------------------- */
 
 /* One fused in-place Adam update of n contiguous parameters at step t (1-based), same operation order and fp32 rounding
