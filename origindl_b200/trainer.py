@@ -18,7 +18,7 @@ import ctypes
 import numpy as np
 import torch
 
-from . import capi
+from . import capi, dp
 
 
 class MLPTrainer:
@@ -101,7 +101,7 @@ class MLPTrainer:
 
         compute = torch.cuda.current_stream()
         capi.call("odl_mlp_forward_loss", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
-        for layer in range(self.n_layers - 1, -1, -1):
+        for layer in dp.reduce_order(self.n_layers):
             capi.call("odl_mlp_backward_layer", self._h, layer, s)
             if self.overlap:
                 ev = torch.cuda.Event()
