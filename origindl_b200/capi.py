@@ -44,6 +44,7 @@ _SIGNATURES = {
     "odl_split_tf32": [_P, _I64, _I64, _I64, _P, _I64, _P, _P, _I64, _P, _P],
     "odl_debug_set_split_k": [c_int],
     "odl_debug_set_bk": [c_int],
+    "odl_debug_set_pair_mode": [c_int],
     "odl_linear_forward": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, c_int, _P],
     "odl_linear_backward": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],
     "odl_linear_backward_chain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],

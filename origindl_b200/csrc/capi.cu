@@ -530,3 +530,10 @@ extern "C" int odl_debug_set_bk(int bk)
     odl::g_bk_override = bk;
     return 0;
 }
+
+// Test hook: 0 = pair (2-CTA) GEMM kernel where it pays, 1 = never, 2 = whenever the shape allows it.
+extern "C" int odl_debug_set_pair_mode(int mode)
+{
+    odl::g_pair_mode = mode;
+    return 0;
+}

@@ -28,9 +28,12 @@
 #include <cstring>
 #include <mutex>
 
+#include "gemm_epilogue.cuh"
 #include "gemm_tc.cuh"
 #include "host_util.h"
+#include "internal.h"
 #include "ptx_sm100.cuh"
+#include "tmap.h"
 
 namespace odl
 {
@@ -42,7 +45,6 @@ constexpr int kBM          = 128;  // rows of D per CTA == TMEM lanes == UMMA M
 constexpr int kUmmaK       = 8;    // K per tcgen05.mma for kind::tf32
 constexpr int kEpiWarps    = 8;    // two warps per TMEM lane quarter, each owning half of the tile's columns
 constexpr int kThreads     = 64 + 32 * kEpiWarps;
-constexpr int kStgLd       = 36;   // padded row length (floats) of the epilogue transpose slab
 constexpr int kGroupM      = 16;   // tile rasterisation: CTAs walk 16 row-tiles before moving to the next column-tile
 constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kAuxBytes    = 1024;  // barriers, TMEM pointer, abort flag
@@ -66,11 +68,6 @@ struct TileCfg
     __host__ __device__ static constexpr int smem_bytes(int terms) { return 1024 + kAuxBytes + stages(terms) * stage_bytes(terms); }
     static constexpr int tmem_cols  = 2 * BN;  // two accumulators: the MMAs fill one while the other is drained
     static constexpr int warp_cols  = BN / 2;  // columns of the tile owned by one epilogue warp
-};
-
-struct alignas(64) TmapPack
-{
-    CUtensorMap a, a_small, b, b_small;
 };
 
 // The accumulator is drained from TMEM into fp32 registers every `chunk_kb` K-blocks.  The tensor core adds into
@@ -338,167 +335,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
         {
             // The last acc_full has fired, so every MMA has completed and every tile load was consumed: the operand
             // ring is dead and its first bytes now serve as per-warp transpose slabs (disjoint between warps).
-            float *stg         = stg_all + e * 32 * kStgLd;
-            const int cg       = lane & 7;   // column group: columns 4cg..4cg+3 of the 32-column chunk
-            const int rr       = lane >> 3;  // row offset 0..3
-            const bool vec_d   = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
-            const bool vec_s   = (p.flags & kEpiSmall) && ((reinterpret_cast<uintptr_t>(p.D_small) & 15) == 0);
-            const bool vec_aux = (p.flags & kEpiMask) && ((p.ld_aux & 3) == 0) &&
-                                 ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
-            if (BN <= 128 && (p.flags & kEpiNCHW))
-            {
-                // Conv output (the launcher never pairs this flag with the 256-wide tile): lanes hold consecutive rows m = consecutive pixels of one image, so for a fixed column
-                // (output channel) a warp writes 32 consecutive floats of the NCHW tensor straight from registers.
-                const int m = m0 + 32 * q + lane;
-                if (m < p.M)
-                {
-                    const int img = m / p.ohw;
-                    const int r   = m - img * p.ohw;
-                    float *dimg   = p.D + (static_cast<size_t>(img) * p.N) * p.ohw + r;
-#pragma unroll
-                    for (int j = 0; j < (BN <= 128 ? Cfg::warp_cols : 1); ++j)
-                    {
-                        const int n = n0 + cw + j;
-                        if (n < p.N)
-                        {
-                            float v = acc[j];
-                            if (p.flags & kEpiBias)
-                                v += __ldg(p.bias + n);
-                            if (p.flags & kEpiRelu)
-                                v = v > 0.f ? v : 0.f;
-                            dimg[static_cast<size_t>(n) * p.ohw] = v;
-                        }
-                    }
-                }
-            }
-            else
-#pragma unroll
-            for (int j = 0; j < Cfg::warp_cols / 32; ++j)
-            {
-                const int c0 = cw + 32 * j;
-                if (n0 + c0 < p.N)
-                {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                    {
-                        float4 v = make_float4(acc[32 * j + 4 * i], acc[32 * j + 4 * i + 1], acc[32 * j + 4 * i + 2],
-                                               acc[32 * j + 4 * i + 3]);
-                        *reinterpret_cast<float4 *>(&stg[lane * kStgLd + 4 * i]) = v;
-                    }
-                    __syncwarp();
-
-                    const int n    = n0 + c0 + 4 * cg;
-                    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (p.flags & kEpiBias)
-                    {
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            if (n + jj < p.N)
-                                bias4[jj] = __ldg(p.bias + n + jj);
-                    }
-                    float csum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                    {
-                        const int row = rr + 4 * i;
-                        const int m   = m0 + 32 * q + row;
-                        float4 v4     = *reinterpret_cast<const float4 *>(&stg[row * kStgLd + 4 * cg]);
-                        float v[4]    = {v4.x, v4.y, v4.z, v4.w};
-                        if (m < p.M && n < p.N)
-                        {
-                            const bool full4 = (n + 3 < p.N);
-                            if (p.flags & kEpiBias)
-                            {
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj)
-                                    v[jj] += bias4[jj];
-                            }
-                            if (p.flags & kEpiRelu)
-                            {
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj)
-                                    v[jj] = v[jj] > 0.f ? v[jj] : 0.f;
-                            }
-                            if (p.flags & kEpiMask)
-                            {
-                                const float *ap = p.aux + static_cast<size_t>(m) * p.ld_aux + n;
-                                float a[4]      = {0.f, 0.f, 0.f, 0.f};
-                                if (vec_aux && full4)
-                                {
-                                    const float4 a4 = __ldg(reinterpret_cast<const float4 *>(ap));
-                                    a[0] = a4.x, a[1] = a4.y, a[2] = a4.z, a[3] = a4.w;
-                                }
-                                else
-                                {
-#pragma unroll
-                                    for (int jj = 0; jj < 4; ++jj)
-                                        if (n + jj < p.N)
-                                            a[jj] = __ldg(ap + jj);
-                                }
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj)
-                                    v[jj] = a[jj] > 0.f ? v[jj] : 0.f;
-                            }
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                if (n + jj < p.N)
-                                    csum[jj] += v[jj];
-                            float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
-                            if (p.flags & kEpiAtomic)
-                            {
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj)
-                                    if (n + jj < p.N)
-                                        atomicAdd(dp + jj, v[jj]);
-                            }
-                            else if (vec_d && full4)
-                            {
-                                *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
-                            }
-                            else
-                            {
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj)
-                                    if (n + jj < p.N)
-                                        dp[jj] = v[jj];
-                            }
-                            if (p.flags & kEpiSmall)
-                            {
-                                float *sp = p.D_small + static_cast<size_t>(m) * p.ldd + n;
-                                if (vec_d && vec_s && full4)
-                                {
-                                    *reinterpret_cast<float4 *>(sp) = make_float4(tf32_small(v[0]), tf32_small(v[1]),
-                                                                                  tf32_small(v[2]), tf32_small(v[3]));
-                                }
-                                else
-                                {
-#pragma unroll
-                                    for (int jj = 0; jj < 4; ++jj)
-                                        if (n + jj < p.N)
-                                            sp[jj] = tf32_small(v[jj]);
-                                }
-                            }
-                        }
-                    }
-                    if (p.flags & kEpiColsum)
-                    {
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                        {
-                            csum[jj] += __shfl_xor_sync(0xffffffffu, csum[jj], 8);
-                            csum[jj] += __shfl_xor_sync(0xffffffffu, csum[jj], 16);
-                        }
-                        if (rr == 0)
-                        {
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                if (n + jj < p.N)
-                                    atomicAdd(p.colsum + n + jj, csum[jj]);
-                        }
-                    }
-                    __syncwarp();
-                }
-            }
+            gemm_epilogue_store<BN, Cfg::warp_cols>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw, q, lane);
         }
         ptx::tc_fence_before_sync();
     }
@@ -540,6 +377,8 @@ EncodeTiledFn get_encode_fn()
     return fn;
 }
 
+}  // namespace
+
 // Tensor map over a row-major fp32 matrix with `rows` rows of `cols` contiguous elements (row pitch ld elements).
 int make_tmap(CUtensorMap *out, const float *ptr, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows,
               CUtensorMapSwizzle swizzle)
@@ -566,6 +405,8 @@ int make_tmap(CUtensorMap *out, const float *ptr, int64_t rows, int64_t cols, in
     return kOk;
 }
 
+namespace
+{
 template <int BN, int BK>
 int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int terms, cudaStream_t stream)
 {
@@ -675,6 +516,8 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         else
             bn = p.N > 128 ? 128 : (p.N > 64 ? 128 : 64);
     }
+    if (gemm_pair_eligible(p, bn, a_mn, b_mn))
+        return gemm_pair_launch(A, A_small, lda, a_mn, B, B_small, ldb, b_mn, p, terms, stream);
     TmapPack tm;
     std::memset(&tm, 0, sizeof(tm));
     int rc;

@@ -1,0 +1,437 @@
+// 2-CTA variant of the tcgen05 GEMM (tcgen05 cta_group::2): a pair of CTAs on neighbouring SMs computes one
+// 256 x BN tile of D.  Each CTA keeps its own 128 rows of A and HALF of the B tile in shared memory and its own 128
+// accumulator rows in TMEM; one thread of the pair's leader issues MMAs with M = 256 that read both CTAs' shared
+// memory.  Per SM this halves the B bytes the TMA unit has to land per MMA cycle -- the measured limiter of the 1-CTA
+// kernel -- and leaves room for a third 3xTF32 stage (64 KB per stage and CTA instead of 96 KB).
+//
+// Protocol inside a pair (cluster of 2; rank 0 = leader), all with plain mbarriers, no multicast of any kind:
+//   full[s]      lives in the leader; the leader's producer arms it with the bytes of BOTH CTAs, both producers' TMA
+//                loads report to it (the peer through the barrier's shared::cluster address);
+//   empty[s]     one per CTA; the leader's MMA thread commits to its own and to the peer's after the MMAs of stage s;
+//   acc_full[b]  one per CTA; committed to both when a chunk of K has been accumulated into TMEM buffer b;
+//   acc_empty[b] lives in the leader; the 8 epilogue warps of each CTA arrive on it after draining buffer b.
+// Everything else (operand layouts and descriptors, 3xTF32 terms, accumulator drains, epilogue) is the 1-CTA design.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "gemm_epilogue.cuh"
+#include "gemm_tc.cuh"
+#include "host_util.h"
+#include "internal.h"
+#include "ptx_sm100.cuh"
+#include "tmap.h"
+
+namespace odl
+{
+
+namespace
+{
+
+constexpr int kBM         = 128;  // rows of D per CTA
+constexpr int kBK         = 32;
+constexpr int kUmmaK      = 8;
+constexpr int kEpiWarps   = 8;
+constexpr int kThreads    = 64 + 32 * kEpiWarps;
+constexpr int kGroupM     = 8;    // rasterisation: 8 row-tiles of 256 per group
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kAuxBytes   = 1024;
+constexpr int kMaxStages  = 8;
+
+template <int BN>
+struct PairCfg
+{
+    static constexpr int a_bytes  = kBM * kBK * 4;
+    static constexpr int b_bytes  = (BN / 2) * kBK * 4;  // this CTA's half of the B tile
+    static constexpr int mn_box   = 32 * kBK * 4;
+    __host__ __device__ static constexpr int stage_bytes(int terms) { return (a_bytes + b_bytes) * (terms == 3 ? 2 : 1); }
+    __host__ __device__ static constexpr int stages(int terms)
+    {
+        int s = (kSmemBudget - 1024 - kAuxBytes) / stage_bytes(terms);
+        return s > kMaxStages ? kMaxStages : s;
+    }
+    __host__ __device__ static constexpr int smem_bytes(int terms) { return 1024 + kAuxBytes + stages(terms) * stage_bytes(terms); }
+    static constexpr int tmem_cols = 2 * BN;
+    static constexpr int warp_cols = BN / 2;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
+                const int stages, const int chunk_kb)
+{
+    using Cfg = PairCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int stage_bytes = Cfg::stage_bytes(terms);
+    uint8_t *tiles        = base;
+    float *stg_all        = reinterpret_cast<float *>(base);
+    uint8_t *aux_base     = base + stages * stage_bytes;
+    uint64_t *full_bar    = reinterpret_cast<uint64_t *>(aux_base);
+    uint64_t *empty_bar   = full_bar + kMaxStages;
+    uint64_t *acc_full    = empty_bar + kMaxStages;
+    uint64_t *acc_empty   = acc_full + 2;
+    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *early_out        = const_cast<int *>(abort_f) + 1;
+
+    const int warp      = threadIdx.x >> 5;
+    const int lane      = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader   = rank == 0;
+
+    if (threadIdx.x == 0)
+    {
+        *early_out = (leader && p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        *abort_f   = 0;
+    }
+    __syncthreads();
+    ptx::cluster_sync();
+    // A launch that follows a timed-out one does no work.  The LEADER reads the device flag and its peer takes the
+    // leader's answer, so both CTAs of a pair always agree (a pair that disagreed could wait for each other in the
+    // collective TMEM allocation); both still walk through every cluster barrier below.
+    const bool skip = ptx::ld_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(early_out), 0)) != 0;
+
+    // ---- tile coordinates: blockIdx.x = 2 * pair + rank
+    const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+    const int tiles_n = (p.N + BN - 1) / BN;
+    int tile_m, tile_n;
+    {
+        const int pair      = blockIdx.x >> 1;
+        const int per_group = kGroupM * tiles_n;
+        const int g         = pair / per_group;
+        const int first_m   = g * kGroupM;
+        const int gsz       = min(tiles_m - first_m, kGroupM);
+        const int local     = pair - g * per_group;
+        tile_m              = first_m + local % gsz;
+        tile_n              = local / gsz;
+    }
+    const int m0      = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;  // this CTA's rows of A and D
+    const int n0      = tile_n * BN;                                      // the pair's columns of D
+    const int nb0     = n0 + static_cast<int>(rank) * (BN / 2);           // this CTA's rows of the B tile
+    const int num_kb  = (p.K + kBK - 1) / kBK;
+    const int nchunks = (num_kb + chunk_kb - 1) / chunk_kb;
+
+    if (!skip)
+    {
+        if (warp == 0 && lane == 0)
+        {
+            ptx::prefetch_tmap(&tm.a);
+            ptx::prefetch_tmap(&tm.b);
+            if (terms == 3)
+            {
+                ptx::prefetch_tmap(&tm.a_small);
+                ptx::prefetch_tmap(&tm.b_small);
+            }
+            for (int s = 0; s < stages; ++s)
+            {
+                ptx::mbar_init(&full_bar[s], 1);
+                ptx::mbar_init(&empty_bar[s], 1);
+            }
+            for (int b = 0; b < 2; ++b)
+            {
+                ptx::mbar_init(&acc_full[b], 1);
+                ptx::mbar_init(&acc_empty[b], 2 * kEpiWarps);  // the epilogue warps of both CTAs
+            }
+            ptx::fence_mbar_init();
+        }
+        if (warp == 1)
+        {
+            ptx::tmem_alloc_pair(tmem_slot, Cfg::tmem_cols);
+            ptx::tmem_relinquish_pair();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // both CTAs' barriers exist before anyone signals across the pair
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = skip ? 0u : *tmem_slot;
+
+    if (skip)
+    {
+        // nothing
+    }
+    else if (warp == 0)
+    {
+        // ================================================================= TMA producer (both CTAs)
+        if (lane == 0)
+        {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb)
+            {
+                const int s       = kb % stages;
+                const uint32_t ph = (kb / stages) & 1;
+                if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
+                    break;
+                uint8_t *st = tiles + s * stage_bytes;
+                if (leader)
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * stage_bytes);
+                const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
+                const int k0       = kb * kBK;
+                for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
+                {
+                    uint8_t *sa           = st + t * Cfg::a_bytes;
+                    const CUtensorMap *ma = t ? &tm.a_small : &tm.a;
+                    if (!a_mn)
+                    {
+                        ptx::tma_load_2d_pair(sa, ma, bar, k0, m0);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int j = 0; j < kBM / 32; ++j)
+                            ptx::tma_load_2d_pair(sa + j * Cfg::mn_box, ma, bar, m0 + 32 * j, k0);
+                    }
+                }
+                uint8_t *sb0 = st + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
+                {
+                    uint8_t *sb           = sb0 + t * Cfg::b_bytes;
+                    const CUtensorMap *mb = t ? &tm.b_small : &tm.b;
+                    if (!b_mn)
+                    {
+                        ptx::tma_load_2d_pair(sb, mb, bar, k0, nb0);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_2d_pair(sb + j * Cfg::mn_box, mb, bar, nb0 + 32 * j, k0);
+                    }
+                }
+                ++issued;
+            }
+            if (*abort_f && leader)
+            {
+                const int first = issued > stages ? issued - stages : 0;
+                for (int kb = first; kb < issued; ++kb)
+                    ptx::mbar_wait(&full_bar[kb % stages], (kb / stages) & 1, nullptr);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ================================================================= MMA issuer (leader only)
+        if (lane == 0 && leader)
+        {
+            const uint32_t idesc  = ptx::make_idesc_tf32(2 * kBM, BN, a_mn != 0, b_mn != 0);
+            const uint32_t a_step = a_mn ? 1024u : 32u;
+            const uint32_t b_step = b_mn ? 1024u : 32u;
+            const uint32_t a_lbo  = a_mn ? Cfg::mn_box : 16u;
+            const uint32_t b_lbo  = b_mn ? Cfg::mn_box : 16u;
+            const uint32_t a_sbo  = a_mn ? 512u : 1024u;
+            const uint32_t b_sbo  = b_mn ? 512u : 1024u;
+            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            bool ok               = true;
+            int kb                = 0;
+            for (int c = 0; c < nchunks && ok; ++c)
+            {
+                const int buf         = c & 1;
+                const uint32_t use    = static_cast<uint32_t>(c >> 1);
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                if (!ptx::mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_f))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const int kb_end = min(kb + chunk_kb, num_kb);
+                for (bool first = true; kb < kb_end; ++kb)
+                {
+                    const int s       = kb % stages;
+                    const uint32_t ph = (kb / stages) & 1;
+                    if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                    const uint32_t sas = sa + Cfg::a_bytes;
+                    const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                    const uint32_t sbs = sb + Cfg::b_bytes;
+#pragma unroll
+                    for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                    {
+                        const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                        const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                        if (terms == 3)
+                        {
+                            const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
+                            const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32_ss_pair(tmem_d, das, db, idesc, first ? 0u : 1u);
+                            ptx::mma_tf32_ss_pair(tmem_d, da, dbs, idesc, 1);
+                            ptx::mma_tf32_ss_pair(tmem_d, da, db, idesc, 1);
+                        }
+                        else
+                        {
+                            ptx::mma_tf32_ss_pair(tmem_d, da, db, idesc, first ? 0u : 1u);
+                        }
+                        first = false;
+                    }
+                    // the stage is free in BOTH CTAs once these MMAs have read it
+                    const uint32_t eb = ptx::smem_u32(&empty_bar[s]);
+                    ptx::mma_commit_pair(ptx::map_to_cta(eb, 0));
+                    ptx::mma_commit_pair(ptx::map_to_cta(eb, 1));
+                }
+                if (ok)
+                {
+                    const uint32_t fb = ptx::smem_u32(&acc_full[buf]);
+                    ptx::mma_commit_pair(ptx::map_to_cta(fb, 0));
+                    ptx::mma_commit_pair(ptx::map_to_cta(fb, 1));
+                }
+            }
+        }
+    }
+    else
+    {
+        // ================================================================= accumulate + epilogue (warps 2..9, both CTAs)
+        const int e  = warp - 2;
+        const int q  = warp & 3;
+        const int h  = e >> 2;
+        const int cw = h * Cfg::warp_cols;
+        float acc[Cfg::warp_cols];
+        bool have = true;
+        for (int c = 0; c < nchunks; ++c)
+        {
+            const int buf      = c & 1;
+            const uint32_t use = static_cast<uint32_t>(c >> 1);
+            have = __all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], use & 1, abort_f));
+            if (!have)
+                break;
+            ptx::tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * BN + cw;
+#pragma unroll
+            for (int j = 0; j < Cfg::warp_cols / 32; ++j)
+            {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(taddr + 32 * j, r);
+                ptx::tmem_ld_wait();
+                if (c == 0)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        acc[32 * j + i] = __uint_as_float(r[i]);
+                }
+                else
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        acc[32 * j + i] += __uint_as_float(r[i]);
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty[buf]), 0));
+        }
+        if (have)
+            gemm_epilogue_store<256, Cfg::warp_cols>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw, q, lane);
+        ptx::tc_fence_before_sync();
+    }
+
+    // ---- teardown: nobody in the pair still uses TMEM or signals a barrier of the other CTA
+    __syncthreads();
+    ptx::cluster_sync();
+    if (!skip && warp == 1)
+    {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, Cfg::tmem_cols);
+    }
+    if (threadIdx.x == 0 && *abort_f && p.err != nullptr)
+        atomicExch(p.err, 1);
+}
+
+}  // namespace
+
+// Test hook: 0 = use the pair kernel where it pays (automatic), 1 = never, 2 = whenever the shape allows it.
+int g_pair_mode = 0;
+
+// True when gemm_tc_launch should hand this problem to the pair kernel.
+// Measured on B200 (8192^3): with an MN-major operand (many 4 KB boxes per stage) the pair kernel is 25-30 % faster
+// (3xTF32 182 -> 232 TFLOP/s, TF32 400 -> 500); with two K-major operands it is level in 3xTF32 and ~7 % slower in
+// plain TF32, so those stay on the 1-CTA kernel.
+bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn)
+{
+    if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiAtomic)))
+        return false;
+    if (g_pair_mode == 2)
+        return true;
+    const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
+    return pairs >= 74 && (a_mn || b_mn);  // at least one pair per two SMs
+}
+
+int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
+                     int64_t ldb, int b_mn, const GemmParams &p, int terms, cudaStream_t stream)
+{
+    constexpr int BN = 256;
+    using Cfg        = PairCfg<BN>;
+    TmapPack tm;
+    std::memset(&tm, 0, sizeof(tm));
+    int rc;
+    auto mk = [&](CUtensorMap *m, const float *ptr, int64_t ld, int mn, int64_t extent_mn, int box_rows_kmajor) {
+        return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, kBK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+                  : make_tmap(m, ptr, extent_mn, p.K, ld, kBK, box_rows_kmajor, CU_TENSOR_MAP_SWIZZLE_128B);
+    };
+    if ((rc = mk(&tm.a, A, lda, a_mn, p.M, kBM)))
+        return rc;
+    if ((rc = mk(&tm.b, B, ldb, b_mn, p.N, BN / 2)))
+        return rc;
+    if (terms == 3)
+    {
+        if ((rc = mk(&tm.a_small, A_small, lda, a_mn, p.M, kBM)))
+            return rc;
+        if ((rc = mk(&tm.b_small, B_small, ldb, b_mn, p.N, BN / 2)))
+            return rc;
+    }
+    const int stages = Cfg::stages(terms);
+    const int smem   = Cfg::smem_bytes(terms);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!attr_set[dev])
+    {
+        const int mx = Cfg::smem_bytes(1) > Cfg::smem_bytes(3) ? Cfg::smem_bytes(1) : Cfg::smem_bytes(3);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx);
+        if (e != cudaSuccess)
+        {
+            set_last_error("cudaFuncSetAttribute(pair kernel, smem=%d) failed: %s", mx, cudaGetErrorString(e));
+            return kCudaError;
+        }
+        attr_set[dev] = true;
+    }
+    GemmParams q   = p;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+    q.kb_per_split   = num_kb;
+    int chunk_kb     = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 64 / kBK : num_kb);
+    if (chunk_kb > num_kb)
+        chunk_kb = num_kb;
+    const int pairs = ((p.M + 2 * kBM - 1) / (2 * kBM)) * ((p.N + BN - 1) / BN);
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim          = dim3(2 * pairs, 1, 1);
+    cfg.blockDim         = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN>, tm, q, a_mn, b_mn, terms, stages, chunk_kb);
+    ++g_launch_count;
+    if (e != cudaSuccess)
+    {
+        set_last_error("gemm_tc2_kernel launch failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
+}  // namespace odl

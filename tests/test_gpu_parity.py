@@ -138,6 +138,40 @@ def test_gemm_split_k(ops, splits):
     assert max_rel_err(d, a.T.astype(np.float64) @ b.astype(np.float64)) <= 1e-5
 
 
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(129, 256, 32), (256, 300, 64), (300, 520, 100), (1024, 1024, 1024), (2048, 768, 515)])
+def test_gemm_cta_pair_kernel(ops, M, N, K, ta, tb, precision):
+    """The 2-CTA (cta_group::2) kernel, forced on shapes with ragged row / column / K tails, with the full epilogue."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(M + N + K + 2 * ta + tb)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    colsum = torch.zeros(N, device="cuda")
+    capi.call("odl_debug_set_pair_mode", 2)
+    capi.call("odl_debug_set_tile_n", 256)
+    try:
+        d, ds = ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True, mask_src=dev(mask),
+                         colsum=colsum, want_small=True, precision=precision)
+    finally:
+        capi.call("odl_debug_set_pair_mode", 0)
+        capi.call("odl_debug_set_tile_n", 0)
+    opa = a.T.astype(np.float64) if ta else a.astype(np.float64)
+    opb = b.T.astype(np.float64) if tb else b.astype(np.float64)
+    pre = opa @ opb + bias
+    ref = np.maximum(pre, 0) * (mask > 0)
+    # elements whose pre-activation is within the tolerance of zero may legitimately fall on either side of the ReLU
+    tol = TOL[precision] * np.abs(pre).max()
+    safe = np.abs(pre) > tol
+    assert np.abs(host(d) - ref)[safe].max() <= tol
+    assert np.abs(host(d) - ref).max() <= 2 * tol
+    assert max_rel_err(host(colsum), ref.sum(0)) <= 10 * TOL[precision]
+    assert torch.equal(ds, ops.split_tf32(d))
+
+
 def test_gemm_epilogues(ops):
     rng = np.random.default_rng(3)
     M, N, K = 200, 333, 150
