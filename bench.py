@@ -332,10 +332,12 @@ def run_ours(args):
         d = torch.empty((n, n), device=dev)
         s_ = capi.stream_handle()
         durations = []
+        layouts = [(0, 1), (0, 0), (1, 0)]  # forward (x.W^T), dX (g.W), dW (g^T.x): the three GEMMs of a Linear layer
         for i in range(3 + 3 * k):
+            ta, tb = layouts[i % 3]
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record()
-            capi.call("odl_gemm_ex", 0, 1, n, n, n, x.data_ptr(), xs_.data_ptr(), n, w.data_ptr(), ws_.data_ptr(), n,
+            capi.call("odl_gemm_ex", ta, tb, n, n, n, x.data_ptr(), xs_.data_ptr(), n, w.data_ptr(), ws_.data_ptr(), n,
                       d.data_ptr(), None, n, None, None, 0, None, 0, capi.PRECISION_3XTF32, s_)
             a1.record()
             durations.append((a0, a1))
@@ -348,7 +350,9 @@ def run_ours(args):
         line["linear_fwd_bwd"] = {"M": n, "N": n, "K": n, "ms": lin_ms, "tflops": lin_tflops,
                                   "frac_of_tf32_roofline_div3": lin_tflops / peak,
                                   "includes": "operand splits of x and W, fused bias+ReLU forward, mask/db pass, dX, dW"}
-        line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel<256> (3xTF32, M=N=K=8192)",
+        line["roofline"] = {"bound": "tensor",
+                            "kernel": "tcgen05 GEMM (gemm_tc_kernel<256,32> for K-major x K-major, gemm_tc2_kernel<256> "
+                                      "CTA pairs otherwise), 3xTF32, M=N=K=8192, mean over the forward / dX / dW layouts",
                             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                             "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
                             "traffic": GEMM_DRAM_TRAFFIC_BYTES}
@@ -365,9 +369,9 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one 8192^3 3xTF32 GEMM launch: scaled from the ncu capture summarised in
-# profiles/gemm_tc_3xtf32.md; None until that capture exists.
-GEMM_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one 8192^3 3xTF32 GEMM launch, mean of the three
+# layouts, from the one-pass ncu capture summarised in profiles/gemm_tc_3xtf32_n8192_dram.md (algorithmic: 1.34e9).
+GEMM_DRAM_TRAFFIC_BYTES = 4.85e9
 
 
 def main():
