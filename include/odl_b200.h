@@ -131,6 +131,19 @@ int odl_add_bias(const float *x, const float *b, float *y, int64_t M, int64_t N,
  * src/mat/origin/cuda/math/sum_to.cu:19-91), without its N <= 1024 launch limit (sum.cu:284-287). */
 int odl_sum_to_row(const float *g, float *out, int64_t M, int64_t N, void *stream);
 
+/* out = x (op) y for same-shape tensors: op 0 add, 1 subtract, 2 multiply.  Replaces origin::cuda::add / subtract /
+ * multiply (cuda_ops.cuh:57,:66,:75) as used by Add, Sub, Mul operators and by gradient accumulation. */
+int odl_binary(int op, const float *x, const float *y, float *out, int64_t n, void *stream);
+/* out = x * alpha (tensor times 0-dim scalar, src/operators/math/mul.cpp:113-117). */
+int odl_scale(const float *x, float alpha, float *out, int64_t n, void *stream);
+/* y += alpha * x with the product rounded first: add_inplace of a scaled tensor, i.e. the WeightDecay hook
+ * (include/origin/optim/hooks.h:52-64) and TensorImpl's gradient accumulation (src/core/tensor_impl.cpp:186-196). */
+int odl_axpy(float alpha, const float *x, float *y, int64_t n, void *stream);
+/* out[i] = value.  Replaces the factory kernels behind Tensor::zeros / ones / full (src/mat/origin/cuda/factory.cu). */
+int odl_fill(float *out, float value, int64_t n, void *stream);
+/* out[0] = sum of all elements, fixed order.  Replaces origin::cuda::sum with axis = -1 (cuda_ops.cuh:273). */
+int odl_sum_all(const float *x, float *out, int64_t n, void *stream);
+
 /* ---- loss ------------------------------------------------------------------------------------------------------- */
 
 /* loss[0] = -(1/B) sum_i log(softmax(logits)[i,t_i] + 1e-8) and/or dlogits = (softmax - onehot) * grad_scale / B, both

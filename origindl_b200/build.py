@@ -59,5 +59,25 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+def build_host_tests() -> Path:
+    """Compile the C++ test program of the host layer (host/origin.hpp) against the library: tests/cpp/build/."""
+    root = HERE.parent
+    src = root / "tests" / "cpp" / "test_host_api.cpp"
+    out_dir = root / "tests" / "cpp" / "build"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / "test_host_api"
+    deps = [src, HERE / "host" / "origin.hpp", root / "include" / "odl_b200.h"]
+    if exe.exists() and exe.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
+        return exe
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-I", str(root / "include"), "-I", str(HERE / "host"),
+           "-I", str(cuda / "include"), str(src), "-o", str(exe), "-L", str(HERE), "-lodl_b200", "-L", str(cuda / "lib64"),
+           "-lcudart_static", "-ldl", "-lrt", "-lpthread", f"-Wl,-rpath,{HERE}", "-Wl,-rpath,$ORIGIN/../../../origindl_b200"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the host-layer tests failed:\n" + r.stdout + r.stderr)
+    return exe
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))

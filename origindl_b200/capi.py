@@ -45,6 +45,11 @@ _SIGNATURES = {
     "odl_debug_set_split_k": [c_int],
     "odl_debug_set_bk": [c_int],
     "odl_debug_set_pair_mode": [c_int],
+    "odl_binary": [c_int, _P, _P, _P, _I64, _P],
+    "odl_scale": [_P, c_float, _P, _I64, _P],
+    "odl_axpy": [c_float, _P, _P, _I64, _P],
+    "odl_fill": [_P, c_float, _I64, _P],
+    "odl_sum_all": [_P, _P, _I64, _P],
     "odl_linear_forward": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, c_int, _P],
     "odl_linear_backward": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],
     "odl_linear_backward_chain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, c_int, c_int, _P],

@@ -1,0 +1,1139 @@
+// C++ host layer above the C ABI (include/odl_b200.h): the reference's operator-level interface for the dense hot
+// path, with the same names, argument meaning and error behaviour, running on one B200.
+//
+//   origin::Tensor / Parameter            include/origin/core/tensor.h:79-327, parameter.h:13-37
+//   origin::Operator forward()/backward() include/origin/core/operator.h:12-125 (tape: src/core/tensor_impl.cpp:78-278)
+//   origin::functional::mat_mul, relu, custom_linear, softmax_cross_entropy, conv2d, sum, broadcast_to, sum_to
+//   origin::nn::Module, Linear, MLP       src/nn/module.cpp, src/nn/layers/linear.cpp, src/nn/models/mlp.cpp
+//   origin::Optimizer, SGD, Adam, WeightDecay   src/optim/*.cpp, include/origin/optim/hooks.h
+//   origin::MemoryPool                    src/mat/origin/memory/memory_pool.cpp:37-176 (size-binned caching allocator)
+//
+// Differences that are deliberate: tensors of this layer live on the device only (fp32 data, int32/int64 labels);
+// nn::Linear and nn::MLP run the fused Linear(+ReLU) operator (one kernel forward, three backward) instead of
+// mat_mul + broadcast_to + add + relu; optimizers update parameters in place; the loss stays on the device until
+// item() is called.  Errors are std::invalid_argument / std::runtime_error, as the reference's THROW_* macros raise.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <memory>
+#include <queue>
+#include <random>
+#include <set>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "odl_b200.h"
+
+namespace origin
+{
+
+// ------------------------------------------------------------------------------------------------ errors
+inline void odl_check(int status)
+{
+    if (status == ODL_OK)
+        return;
+    const std::string msg = odl_last_error();
+    if (status == ODL_ERR_INVALID_ARGUMENT || status == ODL_ERR_MISALIGNED || status == ODL_ERR_TOO_LARGE)
+        throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
+}
+
+inline void cuda_check(cudaError_t e, const char *what)
+{
+    if (e != cudaSuccess)
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+inline void init(int device = 0)
+{
+    odl_check(odl_init(device));
+}
+
+// Surfaces asynchronous kernel errors (bounded-wait time-outs, out-of-range labels) as exceptions.
+inline void synchronize()
+{
+    odl_check(odl_device_status(nullptr));
+}
+
+// ------------------------------------------------------------------------------------------------ memory
+// Caching device allocator with the reference's bin rule: powers of two from 256 B below 512 KB, then 1 / 4 / 16 MB,
+// then multiples of 16 MB; freed blocks are kept for reuse until the cache exceeds its cap (512 MB by default).
+class MemoryPool
+{
+  public:
+    static MemoryPool &instance()
+    {
+        static MemoryPool p;
+        return p;
+    }
+    static size_t bin_size(size_t bytes)
+    {
+        if (bytes <= 256)
+            return 256;
+        if (bytes <= (512u << 10))
+        {
+            size_t b = 256;
+            while (b < bytes)
+                b <<= 1;
+            return b;
+        }
+        if (bytes <= (1u << 20))
+            return 1u << 20;
+        if (bytes <= (4u << 20))
+            return 4u << 20;
+        const size_t m16 = 16u << 20;
+        return (bytes + m16 - 1) / m16 * m16;
+    }
+    void *malloc(size_t bytes, size_t *granted)
+    {
+        const size_t b = bin_size(bytes);
+        *granted       = b;
+        auto &lst      = free_[b];
+        if (!lst.empty())
+        {
+            void *p = lst.back();
+            lst.pop_back();
+            cached_ -= b;
+            ++hits_;
+            return p;
+        }
+        void *p       = nullptr;
+        cudaError_t e = cudaMalloc(&p, b);
+        if (e != cudaSuccess)
+        {
+            release_cache();  // give cached blocks back and retry once
+            e = cudaMalloc(&p, b);
+        }
+        cuda_check(e, "MemoryPool: cudaMalloc");
+        ++misses_;
+        return p;
+    }
+    void free(void *p, size_t granted)
+    {
+        if (!p)
+            return;
+        if (cached_ + granted > cap_)
+        {
+            cudaFree(p);  // synchronises the device, so no kernel can still be using the block
+            return;
+        }
+        free_[granted].push_back(p);  // safe to hand out again: this layer issues everything on one stream
+        cached_ += granted;
+    }
+    void release_cache()
+    {
+        for (auto &kv : free_)
+            for (void *p : kv.second)
+                cudaFree(p);
+        free_.clear();
+        cached_ = 0;
+    }
+    void set_cache_cap(size_t bytes) { cap_ = bytes; }
+    size_t cached_bytes() const { return cached_; }
+    size_t hits() const { return hits_; }
+    size_t misses() const { return misses_; }
+    ~MemoryPool() { release_cache(); }
+
+  private:
+    std::map<size_t, std::vector<void *>> free_;
+    size_t cached_ = 0, cap_ = size_t(512) << 20, hits_ = 0, misses_ = 0;
+};
+
+struct Storage
+{
+    void *ptr      = nullptr;
+    size_t granted = 0;
+    explicit Storage(size_t bytes) { ptr = MemoryPool::instance().malloc(bytes == 0 ? 1 : bytes, &granted); }
+    ~Storage() { MemoryPool::instance().free(ptr, granted); }
+    Storage(const Storage &)            = delete;
+    Storage &operator=(const Storage &) = delete;
+};
+
+// ------------------------------------------------------------------------------------------------ shape / dtype
+class Shape
+{
+  public:
+    Shape() = default;
+    Shape(std::initializer_list<size_t> d) : d_(d) {}
+    explicit Shape(std::vector<size_t> d) : d_(std::move(d)) {}
+    size_t size() const { return d_.size(); }
+    size_t operator[](size_t i) const { return d_.at(i); }
+    size_t elements() const
+    {
+        size_t n = 1;
+        for (size_t v : d_)
+            n *= v;
+        return n;
+    }
+    bool operator==(const Shape &o) const { return d_ == o.d_; }
+    bool operator!=(const Shape &o) const { return d_ != o.d_; }
+    std::string to_string() const
+    {
+        std::ostringstream s;
+        s << "{";
+        for (size_t i = 0; i < d_.size(); ++i)
+            s << (i ? ", " : "") << d_[i];
+        s << "}";
+        return s.str();
+    }
+    const std::vector<size_t> &dims() const { return d_; }
+
+  private:
+    std::vector<size_t> d_;
+};
+
+enum class DataType
+{
+    kFloat32,
+    kInt32,
+    kInt64
+};
+inline size_t element_size(DataType t)
+{
+    return t == DataType::kInt64 ? 8 : 4;
+}
+template <typename T>
+struct DataTypeTraits;
+template <>
+struct DataTypeTraits<float>
+{
+    static constexpr DataType type = DataType::kFloat32;
+};
+template <>
+struct DataTypeTraits<int32_t>
+{
+    static constexpr DataType type = DataType::kInt32;
+};
+template <>
+struct DataTypeTraits<int64_t>
+{
+    static constexpr DataType type = DataType::kInt64;
+};
+
+struct TensorOptions
+{
+    DataType dtype_     = DataType::kFloat32;
+    bool requires_grad_ = false;
+    TensorOptions() = default;
+    TensorOptions(DataType t) : dtype_(t) {}
+    TensorOptions &requires_grad(bool r)
+    {
+        requires_grad_ = r;
+        return *this;
+    }
+};
+inline TensorOptions dtype(DataType t)
+{
+    return TensorOptions(t);
+}
+
+// ------------------------------------------------------------------------------------------------ tensor
+class Operator;
+class Tensor;
+
+struct TensorImpl
+{
+    Shape shape;
+    DataType dtype = DataType::kFloat32;
+    std::shared_ptr<Storage> storage;
+    bool requires_grad = false;
+    std::shared_ptr<TensorImpl> grad;
+    std::shared_ptr<Operator> creator;
+    int generation = 0;
+};
+
+class Tensor
+{
+  public:
+    Tensor() = default;
+    explicit Tensor(std::shared_ptr<TensorImpl> impl) : impl_(std::move(impl)) {}
+
+    template <typename T>
+    Tensor(const std::vector<T> &data, const Shape &shape, const TensorOptions &opt = TensorOptions(DataTypeTraits<T>::type))
+    {
+        if (data.size() != shape.elements())
+            throw std::invalid_argument("Data size (" + std::to_string(data.size()) + ") does not match shape elements (" +
+                                        std::to_string(shape.elements()) + ")");
+        if (opt.dtype_ != DataTypeTraits<T>::type)
+            throw std::invalid_argument("Tensor: data type of the values and of the options differ");
+        alloc(shape, opt);
+        cuda_check(cudaMemcpy(impl_->storage->ptr, data.data(), data.size() * sizeof(T), cudaMemcpyHostToDevice),
+                   "Tensor: host to device copy");
+    }
+    template <typename T>
+    Tensor(std::initializer_list<T> data, const Shape &shape, const TensorOptions &opt = TensorOptions(DataTypeTraits<T>::type))
+        : Tensor(std::vector<T>(data), shape, opt)
+    {
+    }
+
+    static Tensor empty(const Shape &shape, const TensorOptions &opt = TensorOptions())
+    {
+        Tensor t;
+        t.alloc(shape, opt);
+        return t;
+    }
+    static Tensor full(const Shape &shape, float value, const TensorOptions &opt = TensorOptions())
+    {
+        Tensor t = empty(shape, opt);
+        if (opt.dtype_ != DataType::kFloat32)
+            throw std::invalid_argument("Tensor::full: float32 only");
+        if (shape.elements())
+            odl_check(odl_fill(t.data_ptr<float>(), value, (int64_t)shape.elements(), nullptr));
+        return t;
+    }
+    static Tensor zeros(const Shape &shape, const TensorOptions &opt = TensorOptions()) { return full(shape, 0.0f, opt); }
+    static Tensor ones(const Shape &shape, const TensorOptions &opt = TensorOptions()) { return full(shape, 1.0f, opt); }
+    // Standard normal values from a HOST generator with a fixed seed sequence (the reference's randn cannot be seeded).
+    static Tensor randn(const Shape &shape, const TensorOptions &opt = TensorOptions(), uint64_t seed = 0)
+    {
+        static uint64_t counter = 0;
+        std::mt19937_64 gen(seed ? seed : 0x9E3779B97F4A7C15ull + (++counter));
+        std::normal_distribution<float> nd(0.0f, 1.0f);
+        std::vector<float> v(shape.elements());
+        for (auto &x : v)
+            x = nd(gen);
+        return Tensor(v, shape, opt);
+    }
+
+    bool defined() const { return impl_ != nullptr; }
+    const Shape &shape() const { return must()->shape; }
+    size_t ndim() const { return shape().size(); }
+    size_t elements() const { return shape().elements(); }
+    size_t numel() const { return elements(); }
+    DataType dtype() const { return must()->dtype; }
+    bool requires_grad() const { return must()->requires_grad; }
+    template <typename T>
+    T *data_ptr() const
+    {
+        return static_cast<T *>(must()->storage->ptr);
+    }
+    template <typename T>
+    std::vector<T> to_vector() const
+    {
+        if (DataTypeTraits<T>::type != dtype())
+            throw std::invalid_argument("to_vector: dtype mismatch");
+        std::vector<T> v(elements());
+        synchronize();
+        cuda_check(cudaMemcpy(v.data(), must()->storage->ptr, v.size() * sizeof(T), cudaMemcpyDeviceToHost), "to_vector");
+        return v;
+    }
+    template <typename T>
+    T item() const
+    {
+        if (elements() != 1)
+            throw std::runtime_error("item() requires a tensor with exactly one element, got shape " + shape().to_string());
+        return to_vector<T>()[0];
+    }
+    Tensor reshape(const Shape &s) const
+    {
+        if (s.elements() != elements())
+            throw std::invalid_argument("reshape: cannot reshape " + shape().to_string() + " to " + s.to_string());
+        auto impl           = std::make_shared<TensorImpl>(*must());
+        impl->shape         = s;
+        impl->grad          = nullptr;
+        impl->creator       = nullptr;
+        impl->requires_grad = false;
+        return Tensor(impl);
+    }
+    Tensor detach() const { return reshape(shape()); }
+    Tensor clone() const
+    {
+        Tensor t = empty(shape(), TensorOptions(dtype()));
+        cuda_check(cudaMemcpyAsync(t.must()->storage->ptr, must()->storage->ptr, elements() * element_size(dtype()),
+                                   cudaMemcpyDeviceToDevice, nullptr),
+                   "clone");
+        return t;
+    }
+
+    Tensor grad() const
+    {
+        if (!must()->grad)
+            throw std::runtime_error("grad(): tensor has no gradient");
+        return Tensor(must()->grad);
+    }
+    bool has_grad() const { return impl_ && impl_->grad != nullptr; }
+    void clear_grad() { must()->grad = nullptr; }
+    void accumulate_grad(const Tensor &g);
+    void backward();
+
+    std::shared_ptr<TensorImpl> impl() const { return impl_; }
+
+  protected:
+    void alloc(const Shape &shape, const TensorOptions &opt)
+    {
+        impl_                = std::make_shared<TensorImpl>();
+        impl_->shape         = shape;
+        impl_->dtype         = opt.dtype_;
+        impl_->requires_grad = opt.requires_grad_;
+        impl_->storage       = std::make_shared<Storage>(shape.elements() * element_size(opt.dtype_));
+    }
+    TensorImpl *must() const
+    {
+        if (!impl_)
+            throw std::runtime_error("operation on an undefined Tensor");
+        return impl_.get();
+    }
+    std::shared_ptr<TensorImpl> impl_;
+};
+
+class Parameter : public Tensor
+{
+  public:
+    Parameter() = default;
+    Parameter(const Tensor &t) : Tensor(t) {}
+};
+
+// ------------------------------------------------------------------------------------------------ operator + tape
+struct Config
+{
+    static bool &enable_backprop()
+    {
+        static bool v = true;
+        return v;
+    }
+};
+struct NoGradGuard  // include/origin/core/config.h: no_grad()
+{
+    bool prev;
+    NoGradGuard() : prev(Config::enable_backprop()) { Config::enable_backprop() = false; }
+    ~NoGradGuard() { Config::enable_backprop() = prev; }
+};
+
+class Operator : public std::enable_shared_from_this<Operator>
+{
+  public:
+    virtual ~Operator() = default;
+    virtual std::vector<Tensor> forward(const std::vector<Tensor> &xs)   = 0;
+    virtual std::vector<Tensor> backward(const std::vector<Tensor> &gys) = 0;
+
+    // Runs forward and, when any input requires a gradient, records the node on the tape
+    // (include/origin/core/operator.h:21-59, src/operators/operator.cpp:9-36).
+    std::vector<Tensor> operator()(const std::vector<Tensor> &xs)
+    {
+        std::vector<Tensor> ys = forward(xs);
+        bool any               = false;
+        for (const Tensor &x : xs)
+            any = any || (x.defined() && x.requires_grad());
+        if (Config::enable_backprop() && any)
+        {
+            inputs_     = xs;
+            generation_ = 0;
+            for (const Tensor &x : xs)
+                generation_ = std::max(generation_, x.impl()->generation);
+            for (Tensor &y : ys)
+            {
+                y.impl()->requires_grad = true;
+                y.impl()->creator       = shared_from_this();
+                y.impl()->generation    = generation_ + 1;
+                outputs_.push_back(y.impl());
+            }
+        }
+        return ys;
+    }
+    Tensor call1(const std::vector<Tensor> &xs) { return (*this)(xs)[0]; }
+
+    std::vector<Tensor> inputs_;
+    std::vector<std::weak_ptr<TensorImpl>> outputs_;
+    int generation_ = 0;
+};
+
+inline void Tensor::accumulate_grad(const Tensor &g)
+{
+    if (g.shape() != shape())
+        throw std::invalid_argument("accumulate_grad: gradient shape " + g.shape().to_string() + " != " + shape().to_string());
+    if (!must()->grad)
+        must()->grad = g.impl();  // the first gradient shares the produced tensor (src/core/tensor_impl.cpp:187-191)
+    else
+        odl_check(odl_binary(0, Tensor(must()->grad).data_ptr<float>(), g.data_ptr<float>(),
+                             Tensor(must()->grad).data_ptr<float>(), (int64_t)elements(), nullptr));
+}
+
+inline void Tensor::backward()
+{
+    if (!must()->grad)
+        must()->grad = Tensor::ones(shape()).impl();
+    auto cmp = [](const std::shared_ptr<Operator> &a, const std::shared_ptr<Operator> &b) {
+        return a->generation_ < b->generation_;
+    };
+    std::priority_queue<std::shared_ptr<Operator>, std::vector<std::shared_ptr<Operator>>, decltype(cmp)> todo(cmp);
+    std::set<Operator *> seen;
+    std::vector<std::shared_ptr<Operator>> visited;
+    auto push = [&](const std::shared_ptr<Operator> &f) {
+        if (f && seen.insert(f.get()).second)
+        {
+            todo.push(f);
+            visited.push_back(f);
+        }
+    };
+    push(must()->creator);
+    while (!todo.empty())
+    {
+        auto f = todo.top();
+        todo.pop();
+        std::vector<Tensor> gys;
+        for (auto &w : f->outputs_)
+        {
+            auto o = w.lock();
+            gys.push_back(o && o->grad ? Tensor(o->grad) : Tensor());
+        }
+        std::vector<Tensor> gxs = f->backward(gys);
+        if (gxs.size() != f->inputs_.size())
+            throw std::runtime_error("backward: operator returned " + std::to_string(gxs.size()) + " gradients for " +
+                                     std::to_string(f->inputs_.size()) + " inputs");
+        for (size_t i = 0; i < gxs.size(); ++i)
+        {
+            Tensor &x = f->inputs_[i];
+            if (!x.defined() || !x.requires_grad() || !gxs[i].defined())
+                continue;
+            x.accumulate_grad(gxs[i]);
+            push(x.impl()->creator);
+        }
+    }
+    // tear the graph down: intermediates lose their creator and gradient, leaves keep theirs (tensor_impl.cpp:205-277)
+    for (auto &f : visited)
+    {
+        for (auto &w : f->outputs_)
+            if (auto o = w.lock())
+            {
+                o->creator = nullptr;
+                if (o.get() != impl_.get())
+                    o->grad = nullptr;
+            }
+        f->inputs_.clear();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ operators
+namespace detail
+{
+inline int precision()
+{
+    static const int p = [] {
+        const char *e = std::getenv("ORIGIN_MATMUL_PRECISION");
+        return (e && std::string(e) == "tf32") ? ODL_PRECISION_TF32 : ODL_PRECISION_3XTF32;
+    }();
+    return p;
+}
+inline void need_f32(const Tensor &t, const char *who)
+{
+    if (t.dtype() != DataType::kFloat32)
+        throw std::invalid_argument(std::string(who) + ": float32 tensors only on this path");
+}
+inline int64_t i64(size_t v)
+{
+    return static_cast<int64_t>(v);
+}
+}  // namespace detail
+
+namespace functional
+{
+
+// y = x . w for 2-D, 3-D x 2-D and 3-D x 3-D operands (src/operators/math/mat_mul.cpp:12-182).
+class MatMul : public Operator
+{
+  public:
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 2)
+            throw std::runtime_error("MatMul operator requires exactly 2 inputs, but got " + std::to_string(xs.size()));
+        const Tensor &a = xs[0], &b = xs[1];
+        detail::need_f32(a, "mat_mul");
+        detail::need_f32(b, "mat_mul");
+        const Shape &as = a.shape(), &bs = b.shape();
+        if (as.size() == 2 && bs.size() == 2)
+        {
+            if (as[1] != bs[0])
+                throw std::invalid_argument("Matrix dimensions must be compatible for multiplication. A shape: " +
+                                            as.to_string() + ", B shape: " + bs.to_string());
+            Tensor y = Tensor::empty(Shape{as[0], bs[1]});
+            odl_check(odl_matmul(a.data_ptr<float>(), b.data_ptr<float>(), y.data_ptr<float>(), detail::i64(as[0]),
+                                 detail::i64(bs[1]), detail::i64(as[1]), 1, 0, detail::precision(), nullptr));
+            return {y};
+        }
+        if (as.size() == 3 && (bs.size() == 2 || bs.size() == 3))
+        {
+            const bool b3 = bs.size() == 3;
+            if ((b3 && (as[0] != bs[0] || as[2] != bs[1])) || (!b3 && as[2] != bs[0]))
+                throw std::invalid_argument("Matrix dimensions must be compatible for multiplication. A shape: " +
+                                            as.to_string() + ", B shape: " + bs.to_string());
+            const size_t n = b3 ? bs[2] : bs[1];
+            Tensor y       = Tensor::empty(Shape{as[0], as[1], n});
+            odl_check(odl_matmul(a.data_ptr<float>(), b.data_ptr<float>(), y.data_ptr<float>(), detail::i64(as[1]),
+                                 detail::i64(n), detail::i64(as[2]), detail::i64(as[0]), b3 ? 1 : 0, detail::precision(),
+                                 nullptr));
+            return {y};
+        }
+        throw std::invalid_argument("Matrix multiplication requires compatible dimensions. A shape: " + as.to_string() +
+                                    ", B shape: " + bs.to_string());
+    }
+    // gx = gy . w^T, gw = x^T . gy without materialised transposes (mat_mul.cpp:123-182)
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &x = inputs_[0], &w = inputs_[1], &gy = gys[0];
+        if (x.ndim() != 2 || w.ndim() != 2)
+            throw std::runtime_error("MatMul::backward: only the 2-D form is differentiated on this path");
+        const int64_t M = detail::i64(x.shape()[0]), K = detail::i64(x.shape()[1]), N = detail::i64(w.shape()[1]);
+        Tensor gx = Tensor::empty(x.shape()), gw = Tensor::empty(w.shape());
+        odl_check(odl_gemm_ex(0, 1, M, K, N, gy.data_ptr<float>(), nullptr, N, w.data_ptr<float>(), nullptr, N,
+                              gx.data_ptr<float>(), nullptr, K, nullptr, nullptr, 0, nullptr, 0, detail::precision(), nullptr));
+        odl_check(odl_gemm_ex(1, 0, K, N, M, x.data_ptr<float>(), nullptr, K, gy.data_ptr<float>(), nullptr, N,
+                              gw.data_ptr<float>(), nullptr, N, nullptr, nullptr, 0, nullptr, 0, detail::precision(), nullptr));
+        return {gx, gw};
+    }
+};
+
+// Same-shape element-wise add / subtract / multiply (src/operators/math/{add,sub,mul}.cpp).
+class Binary : public Operator
+{
+  public:
+    explicit Binary(int op) : op_(op) {}
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 2)
+            throw std::runtime_error("binary operator requires exactly 2 inputs");
+        if (xs[0].shape() != xs[1].shape())
+            throw std::invalid_argument("binary operator: shapes differ (" + xs[0].shape().to_string() + " vs " +
+                                        xs[1].shape().to_string() + "); broadcast_to the smaller operand first");
+        Tensor y = Tensor::empty(xs[0].shape());
+        odl_check(odl_binary(op_, xs[0].data_ptr<float>(), xs[1].data_ptr<float>(), y.data_ptr<float>(),
+                             detail::i64(y.elements()), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &gy = gys[0];
+        const int64_t n  = detail::i64(gy.elements());
+        if (op_ == 0)
+            return {gy, gy};
+        if (op_ == 1)
+        {
+            Tensor g1 = Tensor::empty(gy.shape());
+            odl_check(odl_scale(gy.data_ptr<float>(), -1.0f, g1.data_ptr<float>(), n, nullptr));
+            return {gy, g1};
+        }
+        Tensor g0 = Tensor::empty(gy.shape()), g1 = Tensor::empty(gy.shape());
+        odl_check(odl_binary(2, gy.data_ptr<float>(), inputs_[1].data_ptr<float>(), g0.data_ptr<float>(), n, nullptr));
+        odl_check(odl_binary(2, gy.data_ptr<float>(), inputs_[0].data_ptr<float>(), g1.data_ptr<float>(), n, nullptr));
+        return {g0, g1};
+    }
+
+  private:
+    int op_;
+};
+
+class Scale : public Operator  // tensor * scalar (src/operators/math/mul.cpp:113-117)
+{
+  public:
+    explicit Scale(float a) : a_(a) {}
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        Tensor y = Tensor::empty(xs[0].shape());
+        odl_check(odl_scale(xs[0].data_ptr<float>(), a_, y.data_ptr<float>(), detail::i64(y.elements()), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        Tensor g = Tensor::empty(gys[0].shape());
+        odl_check(odl_scale(gys[0].data_ptr<float>(), a_, g.data_ptr<float>(), detail::i64(g.elements()), nullptr));
+        return {g};
+    }
+
+  private:
+    float a_;
+};
+
+// {1,N} -> {M,N} (src/operators/math/broadcast_to.cpp:10-46); backward is sum_to.
+class BroadcastTo : public Operator
+{
+  public:
+    explicit BroadcastTo(Shape s) : shape_(std::move(s)) {}
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        const Tensor &x = xs[0];
+        if (x.shape() == shape_)
+            return {x};
+        if (shape_.size() != 2 || x.elements() != shape_[1])
+            throw std::invalid_argument("broadcast_to: only {1,N} or {N} -> {M,N} on this path, got " +
+                                        x.shape().to_string() + " -> " + shape_.to_string());
+        Tensor y = Tensor::zeros(shape_);
+        odl_check(odl_add_bias(y.data_ptr<float>(), x.data_ptr<float>(), y.data_ptr<float>(), detail::i64(shape_[0]),
+                               detail::i64(shape_[1]), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &x = inputs_[0];
+        if (x.shape() == shape_)
+            return {gys[0]};
+        Tensor g = Tensor::empty(x.shape());
+        odl_check(odl_sum_to_row(gys[0].data_ptr<float>(), g.data_ptr<float>(), detail::i64(shape_[0]),
+                                 detail::i64(shape_[1]), nullptr));
+        return {g};
+    }
+
+  private:
+    Shape shape_;
+};
+
+class Sum : public Operator  // sum of all elements -> 0-dim (src/operators/math/sum.cpp, axis = -1)
+{
+  public:
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        Tensor y = Tensor::empty(Shape{});
+        odl_check(odl_sum_all(xs[0].data_ptr<float>(), y.data_ptr<float>(), detail::i64(xs[0].elements()), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const float g = gys[0].item<float>();
+        return {Tensor::full(inputs_[0].shape(), g)};
+    }
+};
+
+class ReLU : public Operator  // src/operators/activation/relu.cpp:13-54
+{
+  public:
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 1)
+            throw std::runtime_error("ReLU operator requires exactly 1 input, but got " + std::to_string(xs.size()));
+        Tensor y = Tensor::empty(xs[0].shape());
+        odl_check(odl_relu_forward(xs[0].data_ptr<float>(), y.data_ptr<float>(), detail::i64(y.elements()), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        Tensor g = Tensor::empty(gys[0].shape());
+        odl_check(odl_relu_backward(gys[0].data_ptr<float>(), inputs_[0].data_ptr<float>(), g.data_ptr<float>(),
+                                    detail::i64(g.elements()), nullptr));
+        return {g};
+    }
+};
+
+// y = relu?(x . op(W) + b) as ONE kernel; backward = dX, dW, db with the ReLU mask and the column sums fused.
+// w_layout ODL_W_OUT_IN is LinearOp / custom_linear (src/operators/custom/linear.cpp), whose backward the reference
+// leaves unimplemented; ODL_W_IN_OUT is nn::Linear's weight (src/nn/layers/linear.cpp).
+class LinearOp : public Operator
+{
+  public:
+    LinearOp(int in_features, int out_features, bool use_bias, int w_layout = ODL_W_OUT_IN, bool relu = false)
+        : in_(in_features), out_(out_features), bias_(use_bias), layout_(w_layout), relu_(relu)
+    {
+    }
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != (bias_ ? 3u : 2u))
+            throw std::runtime_error("LinearOp requires " + std::to_string(bias_ ? 3 : 2) + " inputs, but got " +
+                                     std::to_string(xs.size()));
+        const Tensor &x = xs[0], &w = xs[1];
+        detail::need_f32(x, "custom_linear");
+        const size_t feat = x.ndim() >= 1 ? x.shape()[x.ndim() - 1] : 0;
+        if (x.ndim() < 2 && !(x.ndim() == 1))
+            throw std::invalid_argument("custom_linear: input must have at least 1 dimension");
+        const size_t rows = x.elements() / (feat ? feat : 1);
+        if ((int)feat != in_)
+            throw std::invalid_argument("custom_linear: input feature size " + std::to_string(feat) +
+                                        " does not match in_features " + std::to_string(in_));
+        const Shape want = layout_ == ODL_W_OUT_IN ? Shape{(size_t)out_, (size_t)in_} : Shape{(size_t)in_, (size_t)out_};
+        if (w.shape() != want)
+            throw std::invalid_argument("custom_linear: weight shape " + w.shape().to_string() + " != " + want.to_string());
+        if (bias_ && xs[2].elements() != (size_t)out_)
+            throw std::invalid_argument("custom_linear: bias size mismatch");
+        Tensor y = Tensor::empty(Shape{rows, (size_t)out_});
+        odl_check(odl_linear_forward(x.data_ptr<float>(), nullptr, w.data_ptr<float>(), nullptr,
+                                     bias_ ? xs[2].data_ptr<float>() : nullptr, y.data_ptr<float>(), nullptr,
+                                     detail::i64(rows), out_, in_, layout_, relu_ ? 1 : 0, detail::precision(), nullptr));
+        y_ = relu_ ? y.detach() : Tensor();
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &x = inputs_[0], &w = inputs_[1];
+        const int64_t rows = detail::i64(x.elements() / (size_t)in_);
+        Tensor gx = Tensor::empty(x.shape()), gw = Tensor::empty(w.shape());
+        Tensor gb = bias_ ? Tensor::empty(inputs_[2].shape()) : Tensor();
+        odl_check(odl_linear_backward(x.data_ptr<float>(), nullptr, w.data_ptr<float>(), nullptr, gys[0].data_ptr<float>(),
+                                      relu_ ? y_.data_ptr<float>() : nullptr, gx.data_ptr<float>(), gw.data_ptr<float>(),
+                                      bias_ ? gb.data_ptr<float>() : nullptr, rows, out_, in_, layout_, detail::precision(),
+                                      nullptr));
+        if (bias_)
+            return {gx, gw, gb};
+        return {gx, gw};
+    }
+
+  private:
+    int in_, out_;
+    bool bias_;
+    int layout_;
+    bool relu_;
+    Tensor y_;
+};
+
+// loss = -(1/N) sum log(softmax(x)[i, t_i] + 1e-8) kept on the device (src/operators/loss/softmax_cross_entropy.cpp).
+class SoftmaxCrossEntropy : public Operator
+{
+  public:
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 2)
+            throw std::runtime_error("SoftmaxCrossEntropy operator requires exactly 2 inputs (x and target), but got " +
+                                     std::to_string(xs.size()));
+        const Tensor &x = xs[0], &t = xs[1];
+        if (x.ndim() != 2)
+            throw std::invalid_argument("SoftmaxCrossEntropy expects x to be 2D (N, C), but got shape " + x.shape().to_string());
+        if (t.ndim() != 1)
+            throw std::invalid_argument("SoftmaxCrossEntropy expects target to be 1D (N,), but got shape " +
+                                        t.shape().to_string());
+        if (x.shape()[0] != t.shape()[0])
+            throw std::invalid_argument("SoftmaxCrossEntropy: batch size mismatch. x has " + std::to_string(x.shape()[0]) +
+                                        " samples, target has " + std::to_string(t.shape()[0]) + " samples");
+        if (t.dtype() == DataType::kFloat32)
+            throw std::invalid_argument("SoftmaxCrossEntropy: target must be int32 or int64");
+        Tensor loss = Tensor::empty(Shape{});
+        odl_check(odl_softmax_cross_entropy(x.data_ptr<float>(), t.data_ptr<void>(), t.dtype() == DataType::kInt64,
+                                            detail::i64(x.shape()[0]), detail::i64(x.shape()[1]), loss.data_ptr<float>(),
+                                            nullptr, 1.0f, nullptr));
+        synchronize();  // an out-of-range label throws here, where the reference throws from gather
+        return {loss};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &x = inputs_[0], &t = inputs_[1];
+        const float gy  = gys[0].item<float>();
+        Tensor gx       = Tensor::empty(x.shape());
+        odl_check(odl_softmax_cross_entropy(x.data_ptr<float>(), t.data_ptr<void>(), t.dtype() == DataType::kInt64,
+                                            detail::i64(x.shape()[0]), detail::i64(x.shape()[1]), nullptr,
+                                            gx.data_ptr<float>(), gy, nullptr));
+        return {gx, Tensor()};
+    }
+};
+
+class Conv2dOp : public Operator  // src/operators/conv/conv2d.cpp:14-89
+{
+  public:
+    Conv2dOp(int stride, int pad, bool use_bias, int gy_layout = 0)
+        : stride_(stride), pad_(pad), bias_(use_bias), gy_layout_(gy_layout)
+    {
+    }
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        const Tensor &x = xs[0], &w = xs[1];
+        if (x.ndim() != 4)
+            throw std::invalid_argument("conv2d: x must be 4D (N, C, H, W), but got shape " + x.shape().to_string());
+        if (w.ndim() != 4)
+            throw std::invalid_argument("conv2d: W must be 4D (OC, C, KH, KW), but got shape " + w.shape().to_string());
+        if (x.shape()[1] != w.shape()[1])
+            throw std::invalid_argument("conv2d: channel mismatch - x has " + std::to_string(x.shape()[1]) +
+                                        " channels, but W expects " + std::to_string(w.shape()[1]) + " channels");
+        const int64_t N = detail::i64(x.shape()[0]), C = detail::i64(x.shape()[1]), H = detail::i64(x.shape()[2]),
+                      W = detail::i64(x.shape()[3]), OC = detail::i64(w.shape()[0]);
+        const int KH = (int)w.shape()[2], KW = (int)w.shape()[3];
+        const int OH = (int)((H + 2 * pad_ - KH) / stride_ + 1), OW = (int)((W + 2 * pad_ - KW) / stride_ + 1);
+        if (OH <= 0 || OW <= 0)
+            throw std::invalid_argument("conv2d: invalid output size OH=" + std::to_string(OH) + ", OW=" + std::to_string(OW));
+        if (bias_ && (xs[2].ndim() != 1 || xs[2].shape()[0] != (size_t)OC))
+            throw std::invalid_argument("conv2d: b must be 1D with size " + std::to_string(OC));
+        Tensor y = Tensor::empty(Shape{(size_t)N, (size_t)OC, (size_t)OH, (size_t)OW});
+        odl_check(odl_conv2d_forward(x.data_ptr<float>(), w.data_ptr<float>(), bias_ ? xs[2].data_ptr<float>() : nullptr,
+                                     y.data_ptr<float>(), N, C, H, W, OC, KH, KW, stride_, pad_, 0, detail::precision(),
+                                     nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        const Tensor &x = inputs_[0], &w = inputs_[1];
+        Tensor gx = Tensor::empty(x.shape()), gw = Tensor::empty(w.shape());
+        Tensor gb = bias_ ? Tensor::empty(inputs_[2].shape()) : Tensor();
+        odl_check(odl_conv2d_backward(gys[0].data_ptr<float>(), x.data_ptr<float>(), w.data_ptr<float>(),
+                                      gx.data_ptr<float>(), gw.data_ptr<float>(), bias_ ? gb.data_ptr<float>() : nullptr,
+                                      detail::i64(x.shape()[0]), detail::i64(x.shape()[1]), detail::i64(x.shape()[2]),
+                                      detail::i64(x.shape()[3]), detail::i64(w.shape()[0]), (int)w.shape()[2],
+                                      (int)w.shape()[3], stride_, pad_, gy_layout_, detail::precision(), nullptr));
+        if (bias_)
+            return {gx, gw, gb};
+        return {gx, gw};
+    }
+
+  private:
+    int stride_, pad_;
+    bool bias_;
+    int gy_layout_;
+};
+
+// ---- free functions with the reference's names
+inline Tensor mat_mul(const Tensor &x, const Tensor &w) { return std::make_shared<MatMul>()->call1({x, w}); }
+inline Tensor relu(const Tensor &x) { return std::make_shared<ReLU>()->call1({x}); }
+inline Tensor sum(const Tensor &x) { return std::make_shared<Sum>()->call1({x}); }
+inline Tensor broadcast_to(const Tensor &x, const Shape &s) { return std::make_shared<BroadcastTo>(s)->call1({x}); }
+inline Tensor sum_to(const Tensor &x, const Shape &s)
+{
+    if (x.shape() == s)
+        return x;
+    if (x.ndim() != 2 || s.elements() != x.shape()[1])
+        throw std::invalid_argument("sum_to: only {M,N} -> {1,N} on this path");
+    Tensor y = Tensor::empty(s);
+    odl_check(odl_sum_to_row(x.data_ptr<float>(), y.data_ptr<float>(), detail::i64(x.shape()[0]), detail::i64(x.shape()[1]),
+                             nullptr));
+    return y;
+}
+inline Tensor custom_linear(const Tensor &x, const Tensor &weight, const Tensor &bias, int in_features, int out_features,
+                            bool use_bias)
+{
+    auto op = std::make_shared<LinearOp>(in_features, out_features, use_bias);
+    return use_bias ? op->call1({x, weight, bias}) : op->call1({x, weight});
+}
+inline Tensor custom_linear(const Tensor &x, const Tensor &weight, int in_features, int out_features)
+{
+    return std::make_shared<LinearOp>(in_features, out_features, false)->call1({x, weight});
+}
+inline Tensor softmax_cross_entropy(const Tensor &x, const Tensor &target)
+{
+    return std::make_shared<SoftmaxCrossEntropy>()->call1({x, target});
+}
+inline Tensor conv2d(const Tensor &x, const Tensor &W, const Tensor *b = nullptr, int stride = 1, int pad = 0)
+{
+    auto op = std::make_shared<Conv2dOp>(stride, pad, b != nullptr);
+    return b ? op->call1({x, W, *b}) : op->call1({x, W});
+}
+
+}  // namespace functional
+
+inline Tensor operator+(const Tensor &a, const Tensor &b) { return std::make_shared<functional::Binary>(0)->call1({a, b}); }
+inline Tensor operator-(const Tensor &a, const Tensor &b) { return std::make_shared<functional::Binary>(1)->call1({a, b}); }
+inline Tensor operator*(const Tensor &a, const Tensor &b) { return std::make_shared<functional::Binary>(2)->call1({a, b}); }
+inline Tensor operator*(const Tensor &a, float s) { return std::make_shared<functional::Scale>(s)->call1({a}); }
+
+// ------------------------------------------------------------------------------------------------ nn
+namespace nn
+{
+
+class Module
+{
+  public:
+    virtual ~Module() = default;
+    virtual Tensor forward(const Tensor &x) = 0;
+    Tensor operator()(const Tensor &x) { return forward(x); }
+    virtual std::vector<Parameter *> parameters()
+    {
+        std::vector<Parameter *> out;
+        for (auto &kv : params_)
+            out.push_back(kv.second);
+        for (auto &kv : modules_)
+            for (Parameter *p : kv.second->parameters())
+                out.push_back(p);
+        return out;
+    }
+    std::map<std::string, Parameter *> named_parameters(const std::string &prefix = "")
+    {
+        std::map<std::string, Parameter *> out;
+        for (auto &kv : params_)
+            out[prefix + kv.first] = kv.second;
+        for (auto &kv : modules_)
+            for (auto &sub : kv.second->named_parameters(prefix + kv.first + "."))
+                out[sub.first] = sub.second;
+        return out;
+    }
+    void zero_grad()
+    {
+        for (Parameter *p : parameters())
+            p->clear_grad();
+    }
+
+  protected:
+    void register_parameter(const std::string &name, Parameter &p) { params_.emplace_back(name, &p); }
+    void register_module(const std::string &name, std::unique_ptr<Module> m) { modules_.emplace_back(name, std::move(m)); }
+    std::vector<std::pair<std::string, Parameter *>> params_;
+    std::vector<std::pair<std::string, std::unique_ptr<Module>>> modules_;
+};
+
+// weight {in, out} = randn * sqrt(1/in), bias {1, out} = 0 (src/nn/layers/linear.cpp:39-62).
+class Linear : public Module
+{
+  public:
+    Linear(int in_features, int out_features, bool bias = true, bool fused_relu = false)
+        : in_(in_features), out_(out_features), use_bias_(bias), relu_(fused_relu)
+    {
+        if (in_features <= 0 || out_features <= 0)
+            throw std::invalid_argument("Linear: in_features and out_features must be positive");
+        Tensor w = Tensor::randn(Shape{(size_t)in_, (size_t)out_}, TensorOptions().requires_grad(true));
+        Tensor ws = Tensor::empty(w.shape(), TensorOptions().requires_grad(true));
+        odl_check(odl_scale(w.data_ptr<float>(), std::sqrt(1.0f / (float)in_), ws.data_ptr<float>(),
+                            detail::i64(w.elements()), nullptr));
+        weight_ = Parameter(ws);
+        register_parameter("weight", weight_);
+        if (use_bias_)
+        {
+            bias_ = Parameter(Tensor::zeros(Shape{1, (size_t)out_}, TensorOptions().requires_grad(true)));
+            register_parameter("bias", bias_);
+        }
+    }
+    Tensor forward(const Tensor &x) override
+    {
+        if (weight_.elements() == 0)
+            throw std::runtime_error("Weight is empty in forward! weight_.shape() = " + weight_.shape().to_string());
+        auto op = std::make_shared<functional::LinearOp>(in_, out_, use_bias_, ODL_W_IN_OUT, relu_);
+        return use_bias_ ? op->call1({x, weight_, bias_}) : op->call1({x, weight_});
+    }
+    Parameter *weight() { return &weight_; }
+    Parameter *bias() { return use_bias_ ? &bias_ : nullptr; }
+
+  private:
+    int in_, out_;
+    bool use_bias_, relu_;
+    Parameter weight_, bias_;
+};
+
+// Linear -> ReLU -> ... -> Linear, parameters named layer_i.weight / layer_i.bias (src/nn/models/mlp.cpp:11-61).
+class MLP : public Module
+{
+  public:
+    explicit MLP(const std::vector<int> &sizes)
+    {
+        if (sizes.size() < 2)
+            throw std::invalid_argument("MLP requires at least 2 layer sizes (input and output), but got " +
+                                        std::to_string(sizes.size()));
+        for (size_t i = 0; i + 1 < sizes.size(); ++i)
+        {
+            auto l = std::make_unique<Linear>(sizes[i], sizes[i + 1], true, /*fused_relu=*/i + 2 < sizes.size());
+            layers_.push_back(l.get());
+            register_module("layer_" + std::to_string(i), std::move(l));
+        }
+    }
+    Tensor forward(const Tensor &input) override
+    {
+        Tensor x = input;
+        for (Linear *l : layers_)
+            x = l->forward(x);
+        return x;
+    }
+
+  private:
+    std::vector<Linear *> layers_;
+};
+
+}  // namespace nn
+
+// ------------------------------------------------------------------------------------------------ optimizers
+class Optimizer
+{
+  public:
+    explicit Optimizer(nn::Module &target) : params_(target.parameters()) {}
+    virtual ~Optimizer() = default;
+    void register_hook(std::function<void(std::vector<Parameter *> &)> h) { hooks_.push_back(std::move(h)); }
+    void zero_grad()
+    {
+        for (Parameter *p : params_)
+            p->clear_grad();
+    }
+    // hooks first, then step_one per parameter that has a gradient (src/optim/optimizer.cpp:19-53)
+    void step()
+    {
+        std::vector<Parameter *> with_grad;
+        for (Parameter *p : params_)
+            if (p->has_grad())
+                with_grad.push_back(p);
+        for (auto &h : hooks_)
+            h(with_grad);
+        for (Parameter *p : with_grad)
+            step_one(*p);
+    }
+
+  protected:
+    virtual void step_one(Parameter &p) = 0;
+    std::vector<Parameter *> params_;
+    std::vector<std::function<void(std::vector<Parameter *> &)>> hooks_;
+};
+
+// grad += rate * param, in place on the gradient tensor (include/origin/optim/hooks.h:21-68).
+class WeightDecay
+{
+  public:
+    explicit WeightDecay(float rate = 1e-4f) : rate_(rate) {}
+    std::function<void(std::vector<Parameter *> &)> hook()
+    {
+        const float rate = rate_;
+        return [rate](std::vector<Parameter *> &params) {
+            for (Parameter *p : params)
+                if (p && p->has_grad())
+                    odl_check(odl_axpy(rate, p->data_ptr<float>(), p->grad().data_ptr<float>(), (int64_t)p->elements(),
+                                       nullptr));
+        };
+    }
+
+  private:
+    float rate_;
+};
+
+class SGD : public Optimizer  // src/optim/sgd.cpp:18-75, one fused in-place kernel per parameter
+{
+  public:
+    SGD(nn::Module &target, float lr, float momentum = 0.0f, float weight_decay = 0.0f, bool nesterov = false)
+        : Optimizer(target), lr_(lr), momentum_(momentum), wd_(weight_decay), nesterov_(nesterov)
+    {
+    }
+
+  protected:
+    void step_one(Parameter &p) override
+    {
+        float *buf = nullptr;
+        if (momentum_ > 0.0f)
+        {
+            auto it = buf_.find(p.impl().get());
+            if (it == buf_.end())
+                it = buf_.emplace(p.impl().get(), Tensor::zeros(p.shape())).first;
+            buf = it->second.data_ptr<float>();
+        }
+        odl_check(odl_sgd_step(p.data_ptr<float>(), p.grad().data_ptr<float>(), buf, nullptr, (int64_t)p.elements(), lr_,
+                               momentum_, wd_, nesterov_ ? 1 : 0, 0.0f, 1.0f, nullptr));
+    }
+
+  private:
+    float lr_, momentum_, wd_;
+    bool nesterov_;
+    std::unordered_map<TensorImpl *, Tensor> buf_;
+};
+
+class Adam : public Optimizer  // src/optim/adam.cpp:19-114
+{
+  public:
+    Adam(nn::Module &target, float lr = 1e-3f, float beta1 = 0.9f, float beta2 = 0.999f, float eps = 1e-8f)
+        : Optimizer(target), lr_(lr), b1_(beta1), b2_(beta2), eps_(eps)
+    {
+    }
+
+  protected:
+    void step_one(Parameter &p) override
+    {
+        TensorImpl *key = p.impl().get();
+        auto it         = state_.find(key);
+        if (it == state_.end())
+            it = state_.emplace(key, State{Tensor::zeros(p.shape()), Tensor::zeros(p.shape()), 0}).first;
+        State &s = it->second;
+        s.t += 1;
+        odl_check(odl_adam_step(p.data_ptr<float>(), p.grad().data_ptr<float>(), s.m.data_ptr<float>(),
+                                s.v.data_ptr<float>(), nullptr, (int64_t)p.elements(), s.t, lr_, b1_, b2_, eps_, 0.0f, 1.0f,
+                                nullptr));
+    }
+
+  private:
+    struct State
+    {
+        Tensor m, v;
+        int t;
+    };
+    float lr_, b1_, b2_, eps_;
+    std::unordered_map<TensorImpl *, State> state_;
+};
+
+}  // namespace origin

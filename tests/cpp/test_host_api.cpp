@@ -1,0 +1,311 @@
+// GPU test program for the C++ host layer (origindl_b200/host/origin.hpp).  The cases follow the reference's own
+// unit tests for this path -- same inputs, same expected values, same tolerances -- so that they read like
+// tests/unit_test/operator/test_{matmul,linear,relu,softmax_cross_entropy,conv2d,conv2d_transpose_output}.cpp,
+// tests/unit_test/optim/test_{adam,weight_decay}.cpp and tests/unit_test/autograd/test_linear_regression.cpp of the
+// reference, plus the cases the reference cannot run (LinearOp backward, fused MLP training, the memory pool).
+#include <cmath>
+#include <cstdio>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "origin.hpp"
+
+using namespace origin;
+namespace F = origin::functional;
+
+static int g_failed = 0, g_checks = 0;
+static const float kDefault = 1e-3f;  // TestTolerance::kDefault of the reference (tests/unit_test/common/test_utils.h)
+
+#define EXPECT_TRUE(c)                                                          \
+    do                                                                          \
+    {                                                                           \
+        ++g_checks;                                                             \
+        if (!(c))                                                               \
+        {                                                                       \
+            ++g_failed;                                                         \
+            std::printf("    FAILED %s:%d  %s\n", __FILE__, __LINE__, #c);      \
+        }                                                                       \
+    } while (0)
+#define EXPECT_NEAR(a, b, tol) EXPECT_TRUE(std::fabs((a) - (b)) <= (tol))
+#define EXPECT_THROW(stmt)                      \
+    do                                          \
+    {                                           \
+        bool thrown = false;                    \
+        try                                     \
+        {                                       \
+            stmt;                               \
+        }                                       \
+        catch (const std::exception &)          \
+        {                                       \
+            thrown = true;                      \
+        }                                       \
+        EXPECT_TRUE(thrown);                    \
+    } while (0)
+
+static void expect_tensor(const Tensor &t, const std::vector<float> &want, float tol = kDefault)
+{
+    auto v = t.to_vector<float>();
+    EXPECT_TRUE(v.size() == want.size());
+    for (size_t i = 0; i < v.size() && i < want.size(); ++i)
+        EXPECT_NEAR(v[i], want[i], tol);
+}
+
+static Tensor T(std::vector<float> v, Shape s, bool grad = false)
+{
+    return Tensor(v, s, dtype(DataType::kFloat32).requires_grad(grad));
+}
+
+// ---- test_matmul.cpp
+static void matmul_forward()
+{
+    expect_tensor(F::mat_mul(T({1, 2, 3, 4}, {2, 2}), T({5, 6, 7, 8}, {2, 2})), {19, 22, 43, 50});
+    EXPECT_NEAR(F::mat_mul(T({1, 2}, {1, 2}), T({3, 4}, {2, 1})).item<float>(), 11.0f, kDefault);
+    expect_tensor(F::mat_mul(T({1, 2, 3, 4, 5, 6}, {2, 3}), T({7, 8, 9, 10, 11, 12}, {3, 2})), {58, 64, 139, 154});
+    EXPECT_THROW(F::mat_mul(T({1, 2, 3, 4}, {2, 2}), T({1, 2, 3}, {3, 1})));  // dimension mismatch throws
+    // all-ones sweep incl. sizes that are no multiple of any tile (the reference's CUDA-only sweep)
+    for (size_t n : {16u, 31u, 127u, 512u})
+    {
+        auto y = F::mat_mul(Tensor::ones(Shape{n, n}), Tensor::ones(Shape{n, n})).to_vector<float>();
+        bool ok = true;
+        for (float v : y)
+            ok = ok && std::fabs(v - (float)n) <= kDefault;
+        EXPECT_TRUE(ok);
+    }
+    expect_tensor(F::mat_mul(Tensor::ones(Shape{1, 1000}), Tensor::ones(Shape{1000, 1})), {1000.0f});
+}
+static void matmul_backward()
+{
+    auto x = T({1, 2, 3, 4}, {2, 2}, true), w = T({5, 6, 7, 8}, {2, 2}, true);
+    auto y = F::mat_mul(x, w);
+    y.backward();
+    expect_tensor(x.grad(), {11, 15, 11, 15});
+    expect_tensor(w.grad(), {4, 4, 6, 6});
+}
+// ---- test_linear.cpp (+ the backward the reference does not have)
+static void linear_forward()
+{
+    auto y = F::custom_linear(T({1, 2, 3, 4, 5, 6}, {2, 3}), T({1, 0, 0, 0, 1, 0, 0, 0, 1, 1, 1, 1}, {4, 3}),
+                              T({0, 0, 0, 0}, {4}), 3, 4, true);
+    EXPECT_TRUE(y.shape() == (Shape{2, 4}));
+    expect_tensor(y, {1, 2, 3, 6, 4, 5, 6, 15});
+    expect_tensor(F::custom_linear(T({1, 2}, {1, 2}), T({1, 0, 0, 1}, {2, 2}), T({1, 2}, {2}), 2, 2, true), {2, 4});
+    expect_tensor(F::custom_linear(T({1, 2}, {1, 2}), T({1, 0, 0, 1}, {2, 2}), 2, 2), {1, 2});
+    EXPECT_THROW(F::custom_linear(T({1, 2, 3}, {1, 3}), T({1, 0, 0, 1}, {2, 2}), 2, 2));  // feature mismatch
+}
+static void linear_backward()
+{
+    // y = x.W^T + b, L = sum(y): dx = colsum(W) per row, dW = rows of colsum(x), db = M
+    auto x = T({1, 2, 3, 4, 5, 6}, {2, 3}, true), w = T({1, 0, 0, 0, 1, 0, 0, 0, 1, 1, 1, 1}, {4, 3}, true);
+    auto b = T({0, 0, 0, 0}, {4}, true);
+    auto y = F::custom_linear(x, w, b, 3, 4, true);
+    y.backward();
+    expect_tensor(x.grad(), {2, 2, 2, 2, 2, 2});
+    expect_tensor(w.grad(), {5, 7, 9, 5, 7, 9, 5, 7, 9, 5, 7, 9});
+    expect_tensor(b.grad(), {2, 2, 2, 2});
+}
+// ---- test_relu.cpp
+static void relu_cases()
+{
+    expect_tensor(F::relu(T({-1, 0, 1, 2}, {4})), {0, 0, 1, 2});
+    expect_tensor(F::relu(T({1, 2, 3}, {3})), {1, 2, 3});
+    auto x = T({-1, 0, 1, 2}, {4}, true);
+    auto y = F::relu(x);
+    y.backward();
+    expect_tensor(x.grad(), {0, 0, 1, 1});  // relu'(0) = 0
+}
+// ---- test_softmax_cross_entropy.cpp
+static void softmax_ce_cases()
+{
+    auto x = T({1, 1, 1}, {1, 3});
+    Tensor t(std::vector<int32_t>{1}, Shape{1}, dtype(DataType::kInt32));
+    EXPECT_NEAR(F::softmax_cross_entropy(x, t).item<float>(), std::log(3.0f), 0.01f);
+    // gradient = (p - onehot) / N
+    auto z = T({1, 2, 3, 1, 2, 3}, {2, 3}, true);
+    Tensor t2(std::vector<int32_t>{0, 2}, Shape{2}, dtype(DataType::kInt32));
+    auto loss = F::softmax_cross_entropy(z, t2);
+    loss.backward();
+    const float e1 = std::exp(1.f), e2 = std::exp(2.f), e3 = std::exp(3.f), s = e1 + e2 + e3;
+    expect_tensor(z.grad(), {(e1 / s - 1) / 2, e2 / s / 2, e3 / s / 2, e1 / s / 2, e2 / s / 2, (e3 / s - 1) / 2}, 0.01f);
+    Tensor bad(std::vector<int32_t>{5, 0}, Shape{2}, dtype(DataType::kInt32));
+    EXPECT_THROW(F::softmax_cross_entropy(z, bad));             // out-of-range index throws
+    Tensor t64(std::vector<int64_t>{0, 2}, Shape{2}, dtype(DataType::kInt64));
+    EXPECT_NEAR(F::softmax_cross_entropy(z, t64).item<float>(), loss.item<float>(), 1e-6f);
+    EXPECT_THROW(F::softmax_cross_entropy(T({1, 2, 3}, {3}), t));  // x must be 2-D
+}
+// ---- test_conv2d.cpp, test_conv2d_transpose_output.cpp
+static void conv2d_cases()
+{
+    auto x = T({1, 2, 3, 4, 5, 6, 7, 8, 9}, {1, 1, 3, 3});
+    expect_tensor(F::conv2d(x, T({1, 1, 1, 1}, {1, 1, 2, 2})), {12, 16, 24, 28});
+    auto b = T({1}, {1});
+    expect_tensor(F::conv2d(T({1, 2, 3, 4}, {1, 1, 2, 2}), T({1, 1, 1, 1}, {1, 1, 2, 2}), &b), {11});
+    auto y2 = F::conv2d(x, T({1, 1, 1, 1, 2, 2, 2, 2}, {2, 1, 2, 2}));
+    EXPECT_TRUE(y2.shape() == (Shape{1, 2, 2, 2}));
+    expect_tensor(y2, {12, 16, 24, 28, 24, 32, 48, 56});
+    // backward with gy = ones (as the reference's backward tests do): gW = sums of the input windows, gx = coverage
+    auto xg = T({1, 2, 3, 4, 5, 6, 7, 8, 9}, {1, 1, 3, 3}, true);
+    auto wg = T({1, 1, 1, 1}, {1, 1, 2, 2}, true);
+    auto yg = F::conv2d(xg, wg);
+    yg.backward();
+    expect_tensor(wg.grad(), {12, 16, 24, 28});
+    expect_tensor(xg.grad(), {1, 2, 1, 2, 4, 2, 1, 2, 1});
+    EXPECT_THROW(F::conv2d(T({1, 2, 3, 4}, {1, 1, 2, 2}), T({1, 1, 1, 1, 1, 1, 1, 1, 1}, {1, 1, 3, 3})));  // OH <= 0
+    EXPECT_THROW(F::conv2d(x, T({1, 1, 1, 1, 1, 1, 1, 1}, {1, 2, 2, 2})));                                 // channels
+}
+// ---- test_weight_decay.cpp, test_adam.cpp
+static void weight_decay_and_adam()
+{
+    nn::Linear lin(1, 1, false);
+    *lin.weight() = Parameter(T({1.0f}, {1, 1}, true));
+    SGD sgd(lin, 0.01f, 0.0f, 0.0f, false);
+    WeightDecay wd(0.1f);
+    auto x = T({1.0f}, {1, 1}), target = T({2.0f}, {1, 1});
+    auto y = lin(x);
+    auto loss = (y - target) * (y - target);
+    loss.backward();
+    const float before = lin.weight()->grad().item<float>();
+    EXPECT_NEAR(before, -2.0f, 1e-5f);
+    std::vector<Parameter *> ps = {lin.weight()};
+    wd.hook()(ps);
+    EXPECT_NEAR(lin.weight()->grad().item<float>(), before + 0.1f * 1.0f, 1e-5f);
+
+    nn::Linear lin2(1, 1, true);
+    *lin2.weight() = Parameter(T({1.0f}, {1, 1}, true));
+    Adam adam(lin2, 0.01f, 0.9f, 0.999f, 1e-8f);
+    float prev = 1.0f;
+    for (int s = 0; s < 3; ++s)  // MultipleSteps: the parameter keeps moving towards the target
+    {
+        adam.zero_grad();
+        auto yy = lin2(x);
+        auto l2 = (yy - target) * (yy - target);
+        l2.backward();
+        adam.step();
+        const float w = lin2.weight()->item<float>();
+        EXPECT_TRUE(w > prev);
+        prev = w;
+    }
+    EXPECT_NEAR(prev, 1.0f + 3 * 0.01f, 2e-3f);  // the first Adam steps move by ~lr each
+}
+// ---- autograd/test_linear_regression.cpp: 200 GD steps reach w = 2, b = 5 within 0.1
+static void linear_regression()
+{
+    const size_t n = 100;
+    std::vector<float> xs(n), ys(n);
+    std::mt19937 gen(0);
+    std::uniform_real_distribution<float> u(0.f, 1.f);
+    std::normal_distribution<float> noise(0.f, 0.05f);
+    for (size_t i = 0; i < n; ++i)
+    {
+        xs[i] = u(gen);
+        ys[i] = 2.0f * xs[i] + 5.0f + noise(gen);
+    }
+    auto x = T(xs, {n, 1}), y = T(ys, {n, 1});
+    auto w = T({0.0f}, {1, 1}, true), b = T({0.0f}, {1, 1}, true);
+    const float lr = 0.1f;
+    for (int it = 0; it < 200; ++it)
+    {
+        w.clear_grad();
+        b.clear_grad();
+        auto pred = F::mat_mul(x, w) + F::broadcast_to(b, Shape{n, 1});
+        auto diff = pred - y;
+        auto loss = F::sum(diff * diff) * (1.0f / n);
+        loss.backward();
+        odl_check(odl_axpy(-lr, w.grad().data_ptr<float>(), w.data_ptr<float>(), 1, nullptr));
+        odl_check(odl_axpy(-lr, b.grad().data_ptr<float>(), b.data_ptr<float>(), 1, nullptr));
+    }
+    EXPECT_NEAR(w.item<float>(), 2.0f, 0.1f);
+    EXPECT_NEAR(b.item<float>(), 5.0f, 0.1f);
+}
+// ---- nn::MLP training through the operator tape equals the composition of its parts
+static void mlp_training()
+{
+    nn::MLP model({8, 16, 4});
+    auto named = model.named_parameters("");
+    EXPECT_TRUE(named.size() == 4 && named.count("layer_0.weight") && named.count("layer_1.bias"));
+    EXPECT_TRUE(named.at("layer_0.weight")->shape() == (Shape{8, 16}) && named.at("layer_0.bias")->shape() == (Shape{1, 16}));
+    Adam opt(model, 1e-2f);
+    WeightDecay wd(1e-4f);
+    opt.register_hook(wd.hook());
+    std::mt19937 gen(3);
+    std::normal_distribution<float> nd;
+    std::vector<float> xv(32 * 8);
+    for (auto &v : xv)
+        v = nd(gen);
+    std::vector<int32_t> tv(32);
+    for (size_t i = 0; i < tv.size(); ++i)
+        tv[i] = (xv[i * 8] > 0) + 2 * (xv[i * 8 + 1] > 0);  // learnable labels
+    auto x = T(xv, {32, 8});
+    Tensor t(tv, Shape{32}, dtype(DataType::kInt32));
+    float first = 0, last = 0;
+    for (int s = 0; s < 60; ++s)
+    {
+        auto loss = F::softmax_cross_entropy(model(x), t);
+        if (s == 0)
+            first = loss.item<float>();
+        last = loss.item<float>();
+        opt.zero_grad();
+        loss.backward();
+        opt.step();
+    }
+    EXPECT_NEAR(first, std::log(4.0f), 0.8f);
+    EXPECT_TRUE(last < 0.5f * first);
+    {
+        NoGradGuard g;  // no tape is recorded under no_grad()
+        auto out = model(x);
+        EXPECT_TRUE(!out.impl()->creator);
+    }
+}
+// ---- memory pool: bins and reuse (src/mat/origin/memory/memory_pool.cpp)
+static void memory_pool()
+{
+    EXPECT_TRUE(MemoryPool::bin_size(1) == 256 && MemoryPool::bin_size(257) == 512 && MemoryPool::bin_size(300000) == 524288);
+    EXPECT_TRUE(MemoryPool::bin_size(600000) == (1u << 20) && MemoryPool::bin_size(3u << 20) == (4u << 20));
+    EXPECT_TRUE(MemoryPool::bin_size(17u << 20) == (32u << 20));
+    auto &pool        = MemoryPool::instance();
+    const size_t hits = pool.hits();
+    void *p1          = nullptr;
+    {
+        Tensor a = Tensor::zeros(Shape{1000});
+        p1       = a.data_ptr<float>();
+    }
+    Tensor b = Tensor::zeros(Shape{1000});
+    EXPECT_TRUE(b.data_ptr<float>() == p1 && pool.hits() > hits);  // the freed block was handed out again
+}
+
+int main()
+{
+    try
+    {
+        init(0);
+    }
+    catch (const std::exception &e)
+    {
+        std::printf("cannot initialise: %s\n", e.what());
+        return 2;
+    }
+    const std::vector<std::pair<const char *, std::function<void()>>> tests = {
+        {"matmul_forward", matmul_forward},   {"matmul_backward", matmul_backward},
+        {"linear_forward", linear_forward},   {"linear_backward", linear_backward},
+        {"relu", relu_cases},                 {"softmax_cross_entropy", softmax_ce_cases},
+        {"conv2d", conv2d_cases},             {"weight_decay_and_adam", weight_decay_and_adam},
+        {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
+        {"memory_pool", memory_pool}};
+    for (auto &t : tests)
+    {
+        const int before = g_failed;
+        try
+        {
+            t.second();
+            synchronize();
+        }
+        catch (const std::exception &e)
+        {
+            ++g_failed;
+            std::printf("    EXCEPTION in %s: %s\n", t.first, e.what());
+        }
+        std::printf("[%s] %s\n", g_failed == before ? "  OK  " : "FAILED", t.first);
+    }
+    std::printf("%d checks, %d failed\n", g_checks, g_failed);
+    return g_failed ? 1 : 0;
+}
