@@ -511,10 +511,10 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         const int64_t tiles128 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 127) / 128);
         if (p.N > 128 && tiles256 >= 148 && !(p.flags & kEpiNCHW))
             bn = 256;
-        else if (p.N > 64 && tiles128 >= 74)
+        else if (p.N > 64 && tiles128 >= 111)
             bn = 128;
         else
-            bn = p.N > 128 ? 128 : (p.N > 64 ? 128 : 64);
+            bn = 64;  // small problems are bound by the latency of one CTA's K loop: spread them over more SMs
     }
     if (gemm_pair_eligible(p, bn, a_mn, b_mn))
         return gemm_pair_launch(A, A_small, lda, a_mn, B, B_small, ldb, b_mn, p, terms, stream);
