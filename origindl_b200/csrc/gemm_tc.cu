@@ -509,8 +509,11 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         // widest tile that still fills the machine reasonably
         const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
         const int64_t tiles128 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 127) / 128);
+        const int64_t k_blocks = (p.K + 31) / 32;
         if (p.N > 128 && tiles256 >= 148 && !(p.flags & kEpiNCHW))
             bn = 256;
+        else if (p.N > 128 && p.flags == 0 && tiles256 * 2 <= 148 && k_blocks >= 64)
+            bn = 256;  // long reduction, few tiles, plain epilogue (dW of a skinny layer): wide tiles + split-K
         else if (p.N > 64 && tiles128 >= 111)
             bn = 128;
         else

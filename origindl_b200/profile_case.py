@@ -5,6 +5,7 @@
     python -m origindl_b200.profile_case adam    --n 67108864
     python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
     python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
+    python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
 
 Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
 device, launches the kernel `--iters` times after one warm-up launch and prints the CUDA-event time per launch.
@@ -35,8 +36,10 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv"])
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear"])
     ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--layer", type=int, default=1)
@@ -71,6 +74,30 @@ def main():
         t = torch.randint(0, a.cols, (a.rows,), device="cuda", dtype=torch.int32)
         ms = timed(lambda: ops.softmax_cross_entropy(x, t), a.iters)
         print(f"softmax-CE {a.rows}x{a.cols}: {ms:.4f} ms per loss+gradient")
+    elif a.case == "linear":
+        # Linear forward+backward, W [N,K]; forward, dX, dW and the dY preparation pass (mask + db + low part) timed apart
+        M, N, K = a.m, a.n, a.k
+        x, w = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda")
+        b, dy = 0.1 * torch.randn(N, device="cuda"), torch.randn(M, N, device="cuda")
+        y = ops.linear_forward(x, w, b, relu=True, precision=prec)
+        g = ops.relu_backward(dy, y)
+        three = prec == capi.PRECISION_3XTF32
+        xs, ws, gs = (ops.split_tf32(t) if three else None for t in (x, w, g))
+        t_split = timed(lambda: (ops.split_tf32(x), ops.split_tf32(w)), a.iters) if three else 0.0
+        t_fwd = timed(lambda: ops.linear_forward(x, w, b, relu=True, precision=prec, x_small=xs, w_small=ws), a.iters)
+        db = torch.zeros(N, device="cuda")
+        gbuf, gsm = torch.empty_like(dy), torch.empty_like(dy)
+        t_prep = timed(lambda: capi.call("odl_split_tf32", dy.data_ptr(), N, M, N, y.data_ptr(), N, gbuf.data_ptr(),
+                                         gsm.data_ptr() if three else None, N, db.data_ptr(), capi.stream_handle()), a.iters)
+        t_dx = timed(lambda: ops.gemm(g, w, a_small=gs, b_small=ws, precision=prec), a.iters)
+        t_dw = timed(lambda: ops.gemm(g, x, trans_a=True, a_small=gs, b_small=xs, precision=prec), a.iters)
+        t_all = timed(lambda: ops.linear_backward(x, w, dy, y, precision=prec, x_small=xs, w_small=ws), a.iters)
+        f = 2.0 * M * N * K / 1e9
+        tot = t_split + t_fwd + t_all
+        print(f"linear M={M} N={N} K={K} {a.precision}: split(x,W) {t_split:.3f} ms | fwd {t_fwd:.3f} ms {f / t_fwd:.0f} TF/s | "
+              f"dY pass (mask+db+low) {t_prep:.3f} ms {12.0 * M * N / t_prep / 1e6 if three else 8.0 * M * N / t_prep / 1e6:.0f} GB/s | "
+              f"dX {t_dx:.3f} ms {f / t_dx:.0f} TF/s | dW {t_dw:.3f} ms {f / t_dw:.0f} TF/s | backward call {t_all:.3f} ms | "
+              f"fwd+bwd {tot:.3f} ms = {3 * f / tot:.0f} TFLOP/s")
     else:
         C, OC, k, s, p, hw = CONV_LAYERS[a.layer]
         x = torch.rand(16, C, hw, hw, device="cuda")

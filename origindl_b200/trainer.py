@@ -117,6 +117,37 @@ class MLPTrainer:
         capi.call("odl_mlp_optimizer_step", self._h, 1.0 / self.world, s)
         return self._loss_view[0]
 
+    def capture(self, x: torch.Tensor, labels: torch.Tensor):
+        """Capture forward + loss + backward on the given STATIC input buffers into one CUDA graph and return a
+        function that runs one optimisation step: graph replay, then the optimizer launch (kept outside the graph
+        because Adam's bias corrections are host scalars that change every step).  The caller refills `x` / `labels`
+        in place between steps.  Two eager warm-up steps run first so that the scratch arena has its final size
+        before capture (allocation is not capturable).  Single-GPU only."""
+        if self.pg is not None:
+            raise NotImplementedError("graph capture of the data-parallel step is not implemented")
+        assert x.is_cuda and x.is_contiguous() and tuple(x.shape) == (self.batch, self.sizes[0])
+        is64 = int(labels.dtype == torch.int64)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.train_step(x, labels)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                s = capi.stream_handle()
+                capi.call("odl_mlp_forward_loss", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
+                for layer in dp.reduce_order(self.n_layers):
+                    capi.call("odl_mlp_backward_layer", self._h, layer, s)
+        torch.cuda.current_stream().wait_stream(side)
+
+        def step() -> torch.Tensor:
+            graph.replay()
+            capi.call("odl_mlp_optimizer_step", self._h, 1.0, capi.stream_handle())
+            return self._loss_view[0]
+
+        return step
+
     def close(self) -> None:
         if self._h is not None:
             capi.call("odl_mlp_destroy", self._h)

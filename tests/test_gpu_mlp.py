@@ -117,3 +117,23 @@ def test_int64_labels_and_logits_view(trainer_cls):
     l32 = tr.train_step(x, t.to(torch.int32)).item()
     assert l64 == l32 and torch.equal(logits, tr.logits())
     tr.close()
+
+
+def test_cuda_graph_step_equals_eager_step(trainer_cls):
+    """forward + loss + backward replayed from one CUDA graph (optimizer launched after it) trains like eager steps."""
+    rng = np.random.default_rng(31)
+    sizes = [64, 128, 96, 10]
+    params = _libs.mlp_params(rng, sizes)
+    x = torch.from_numpy(rng.standard_normal((32, 64)).astype(np.float32)).cuda()
+    t = torch.from_numpy(rng.integers(0, 10, 32).astype(np.int32)).cuda()
+    eager = trainer_cls(sizes, 32, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+    eager.set_params(params)
+    ref = [eager.train_step(x, t).item() for _ in range(8)]
+    graphed = trainer_cls(sizes, 32, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+    graphed.set_params(params)
+    step = graphed.capture(x, t)                 # runs two real warm-up steps eagerly
+    got = [step().item() for _ in range(6)]
+    assert np.abs(np.array(got) - np.array(ref[2:])).max() <= 1e-5
+    assert max_rel_err(graphed.get_params(), eager.get_params()) <= 1e-5
+    eager.close()
+    graphed.close()
