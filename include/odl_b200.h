@@ -113,7 +113,9 @@ int odl_linear_backward(const float *x, const float *x_small, const float *w, co
 
 /* Same, for a layer inside an MLP: the dx GEMM's epilogue already applies the PREVIOUS layer's ReLU mask
  * (prev_y[M,K] > 0), sums the previous layer's bias gradient prev_db[K] and emits dx_small, so the previous layer's
- * backward needs no preparation pass of its own (pass its y = NULL and db = NULL there and dx here as its dy).
+ * backward needs no preparation pass of its own (pass its y = NULL and db = NULL there, dx here as its dy and
+ * dx_small here as its dy_small).  dy_small is the 3xTF32 low part of dy when the caller already holds it (the
+ * dx_small of the layer above); NULL makes this call compute it.
  * No counterpart in the reference (it runs these as separate kernels). */
 int odl_linear_backward_chain(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
                               const float *y, float *dx, float *dx_small, const float *prev_y, float *prev_db, float *dw,
@@ -217,8 +219,15 @@ int64_t odl_mlp_param_count(void *handle);
 /* Install parameters from a packed HOST array [W_0 {in,out}, b_0 {1,out}, W_1, ...] (the order of
  * Module::named_parameters: layer_i.weight, layer_i.bias); resets the optimizer state. */
 int odl_mlp_set_params(void *handle, const float *host_packed, void *stream);
-/* Copy parameters (which = 0) or the gradients of the last backward (which = 1) to a packed HOST array. */
+/* Copy parameters (which = 0), the gradients of the last backward (1), the first-moment / momentum buffer (2) or
+ * Adam's second moment (3) to a packed HOST array. */
 int odl_mlp_get_packed(void *handle, int which, float *host_packed, void *stream);
+/* Restore optimizer state read with odl_mlp_get_packed(2 / 3) and odl_mlp_step_count (call after odl_mlp_set_params,
+ * which zeroes it).  The reference's checkpoint omits optimizer state (src/io/checkpoint.cpp:38-43: the optimizer.odl
+ * path is computed and never written); with it a resumed run continues the SAME trajectory. */
+int odl_mlp_set_optimizer_state(void *handle, const float *m_packed, const float *v_packed, int step_count, void *stream);
+/* Optimizer steps taken since odl_mlp_set_params (Adam's t, src/optim/adam.cpp:49-50). */
+int64_t odl_mlp_step_count(void *handle);
 /* model(x) and softmax_cross_entropy(y, t) for x[batch, sizes[0]] and labels[batch] on the device; also starts the
  * backward pass (d loss / d logits and the head's bias gradient). */
 int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);

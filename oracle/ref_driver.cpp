@@ -18,15 +18,19 @@
 //   functional::custom_linear      src/operators/custom/linear.cpp:123-144
 //   nn::MLP                        src/nn/models/mlp.cpp:11-61
 //   Adam / SGD / WeightDecay       src/optim/adam.cpp, src/optim/sgd.cpp, include/origin/optim/hooks.h
+//   save / load / load_checkpoint  src/io/model_io.cpp:114-273, src/io/checkpoint.cpp:15-226
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
 #include "origin/core/operator.h"
 #include "origin/core/parameter.h"
 #include "origin/core/tensor.h"
+#include "origin/io/checkpoint.h"
+#include "origin/io/model_io.h"
 #include "origin/nn/models/mlp.h"
 #include "origin/optim/adam.h"
 #include "origin/optim/hooks.h"
@@ -303,6 +307,106 @@ int odlref_optim_replay(float *p, const float *grads, int64_t n, int steps, int 
             optim->step();
         }
         dump(*lin.weight(), p);
+    });
+}
+
+// ---- .odl state-dict files and .ckpt checkpoint directories through the reference's own origin::save / origin::load
+//      (src/io/model_io.cpp:114-273, src/io/checkpoint.cpp:15-226).
+
+// Write n float32 tensors (names[i], rank ranks[i], dims flattened in `dims`, values data[i]) with origin::save.
+int odlref_save_state(const char *path, int n, const char **names, const int *ranks, const int64_t *dims,
+                      const float **data)
+{
+    return guarded([&] {
+        StateDict sd;
+        size_t d = 0;
+        for (int i = 0; i < n; ++i)
+        {
+            std::vector<size_t> shp(dims + d, dims + d + ranks[i]);
+            d += ranks[i];
+            Shape s(shp);
+            std::vector<float> v(data[i], data[i] + s.elements());
+            sd[names[i]] = Tensor(v, s, dtype(DataType::kFloat32));
+        }
+        save(sd, path);
+    });
+}
+
+// Names in a file read by origin::load, '\n'-separated, into buf (truncated to cap - 1 characters); *count = tensors.
+int odlref_load_state_names(const char *path, char *buf, int64_t cap, int *count)
+{
+    return guarded([&] {
+        StateDict sd = load(path);
+        std::string all;
+        for (auto &kv : sd)
+            all += kv.first + "\n";
+        *count = (int)sd.size();
+        std::snprintf(buf, (size_t)cap, "%s", all.c_str());
+    });
+}
+
+// One float32 tensor of a file read by origin::load: rank and dims (up to 8) always; values when out != NULL.
+int odlref_load_state_tensor(const char *path, const char *name, int *rank, int64_t *dims, float *out)
+{
+    return guarded([&] {
+        StateDict sd = load(path);
+        auto it      = sd.find(name);
+        if (it == sd.end())
+            throw std::runtime_error(std::string("no tensor named ") + name);
+        const Shape &s = it->second.shape();
+        *rank          = (int)s.size();
+        for (size_t i = 0; i < s.size() && i < 8; ++i)
+            dims[i] = (int64_t)s[i];
+        dump(it->second, out);
+    });
+}
+
+// origin::save(Checkpoint) of an MLP's state dict built from packed parameters (model.odl + metadata.json).
+int odlref_save_checkpoint(const char *path, const int *sizes, int n_sizes, const float *params, int epoch, int step,
+                           float loss, const char *optimizer_type, float lr, float beta1, float beta2, float eps)
+{
+    return guarded([&] {
+        std::vector<int> sz(sizes, sizes + n_sizes);
+        nn::MLP model(sz);
+        size_t off = 0;
+        for (int l = 0; l + 1 < n_sizes; ++l)
+        {
+            auto named = model.named_parameters("");
+            auto *w    = named.at("layer_" + std::to_string(l) + ".weight");
+            auto *b    = named.at("layer_" + std::to_string(l) + ".bias");
+            *w         = Parameter(make(params + off, {(size_t)sizes[l], (size_t)sizes[l + 1]}, true));
+            off += w->elements();
+            *b = Parameter(make(params + off, {1, (size_t)sizes[l + 1]}, true));
+            off += b->elements();
+        }
+        Checkpoint ck;
+        ck.model_state_dict          = model.state_dict();
+        ck.epoch                     = epoch;
+        ck.step                      = step;
+        ck.loss                      = loss;
+        ck.optimizer_type            = optimizer_type;
+        ck.optimizer_config["lr"]    = lr;
+        ck.optimizer_config["beta1"] = beta1;
+        ck.optimizer_config["beta2"] = beta2;
+        ck.optimizer_config["eps"]   = eps;
+        save(ck, path);
+    });
+}
+
+// origin::load_checkpoint: metadata fields and the number of tensors in the model state dict.
+int odlref_load_checkpoint_meta(const char *path, int *epoch, int *step, float *loss, char *optimizer_type, int64_t cap,
+                                float *cfg4, int *n_tensors)
+{
+    return guarded([&] {
+        Checkpoint ck = load_checkpoint(path);
+        *epoch        = ck.epoch;
+        *step         = ck.step;
+        *loss         = ck.loss;
+        std::snprintf(optimizer_type, (size_t)cap, "%s", ck.optimizer_type.c_str());
+        const char *keys[4] = {"lr", "beta1", "beta2", "eps"};
+        for (int i = 0; i < 4; ++i)
+            cfg4[i] = ck.optimizer_config.count(keys[i]) ? ck.optimizer_config.at(keys[i]) : -1.0f;
+        *n_tensors = (int)ck.model_state_dict.size();
     });
 }
 

@@ -142,10 +142,11 @@ _MLP_SIGNATURES = {
     "odl_mlp_optimizer_step": [_P, c_float, _P],
     "odl_mlp_train_step": [_P, _P, _P, c_int, _P],
     "odl_mlp_grad_bucket": [_P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)],
+    "odl_mlp_set_optimizer_state": [_P, _P, _P, c_int, _P],
 }
 _SIGNATURES.update(_MLP_SIGNATURES)
 _POINTER_RETURNS = {"odl_mlp_loss_ptr": [_P], "odl_mlp_logits_ptr": [_P]}
-_I64_RETURNS = {"odl_mlp_param_count": [_P], "odl_launch_count": []}
+_I64_RETURNS = {"odl_mlp_param_count": [_P], "odl_mlp_step_count": [_P], "odl_launch_count": []}
 
 
 def _declare_extra(L: ctypes.CDLL) -> None:

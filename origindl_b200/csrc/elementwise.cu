@@ -111,7 +111,20 @@ __global__ void add_bias_kernel(const float *__restrict__ x, const float *__rest
 }
 
 // ------------------------------------------------------------------------------------------------ softmax-CE
+// a / b for many a and one b: q = a * (1/b) followed by one residual correction.  With a correctly rounded 1/b this
+// yields the correctly rounded quotient (the value of a / b) except for rare operand pairs, where it is within one
+// ulp, at a third of the instructions of a division.
+__device__ __forceinline__ float div_by_common(float a, float b, float inv_b)
+{
+    const float q = a * inv_b;
+    const float r = fmaf(-q, b, a);
+    return fmaf(r, inv_b, q);
+}
+
 // One warp per row.  p = exp(x - max) / sum ; row_loss = log(p[t] + 1e-8) ; dlogits = (p - onehot) * scale.
+// Rows of up to 32 * kSmCache classes are read from global memory ONCE and kept in registers (each exponential is
+// computed once); longer rows fall back to re-reading.
+constexpr int kSmCache = 32;
 __global__ void __launch_bounds__(128) softmax_ce_kernel(const float *__restrict__ x, const int32_t *__restrict__ t32,
                                                          const int64_t *__restrict__ t64, int B, int C,
                                                          float *__restrict__ row_loss, float *__restrict__ dlogits,
@@ -121,19 +134,7 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float *__restrict
     const int row  = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= B)
         return;
-    const float *xr = x + static_cast<int64_t>(row) * C;
-    float mx        = -INFINITY;
-    for (int c = lane; c < C; c += 32)
-        mx = fmaxf(mx, xr[c]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-    for (int c = lane; c < C; c += 32)
-        sum += expf(xr[c] - mx);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float *xr     = x + static_cast<int64_t>(row) * C;
     const int64_t label = t32 ? static_cast<int64_t>(t32[row]) : t64[row];
     if (label < 0 || label >= C)
     {
@@ -141,6 +142,45 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float *__restrict
             atomicExch(err, 2);
         return;
     }
+    const bool cached = C <= 32 * kSmCache;
+    float v[kSmCache];
+    float mx = -INFINITY;
+    if (cached)
+    {
+#pragma unroll
+        for (int i = 0; i < kSmCache; ++i)
+        {
+            const int c = lane + 32 * i;
+            v[i]        = c < C ? xr[c] : -INFINITY;
+            mx          = fmaxf(mx, v[i]);
+        }
+    }
+    else
+    {
+        for (int c = lane; c < C; c += 32)
+            mx = fmaxf(mx, xr[c]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    if (cached)
+    {
+#pragma unroll
+        for (int i = 0; i < kSmCache; ++i)
+        {
+            v[i] = (lane + 32 * i) < C ? expf(v[i] - mx) : 0.f;
+            sum += v[i];
+        }
+    }
+    else
+    {
+        for (int c = lane; c < C; c += 32)
+            sum += expf(xr[c] - mx);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
     if (lane == 0 && row_loss)
     {
         const float pt = expf(xr[label] - mx) / sum;
@@ -148,11 +188,22 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float *__restrict
     }
     if (dlogits)
     {
-        float *dr = dlogits + static_cast<int64_t>(row) * C;
-        for (int c = lane; c < C; c += 32)
+        float *dr       = dlogits + static_cast<int64_t>(row) * C;
+        const float inv = 1.0f / sum;
+        if (cached)
         {
-            const float p = expf(xr[c] - mx) / sum;
-            dr[c]         = (p - (c == label ? 1.0f : 0.0f)) * scale;
+#pragma unroll
+            for (int i = 0; i < kSmCache; ++i)
+            {
+                const int c = lane + 32 * i;
+                if (c < C)
+                    dr[c] = (div_by_common(v[i], sum, inv) - (c == label ? 1.0f : 0.0f)) * scale;
+            }
+        }
+        else
+        {
+            for (int c = lane; c < C; c += 32)
+                dr[c] = (expf(xr[c] - mx) / sum - (c == label ? 1.0f : 0.0f)) * scale;
         }
     }
 }
@@ -313,45 +364,86 @@ struct ConvGeom
     int ld_col;   // ckk rounded up to a multiple of 4 (pad columns are written as zeros)
 };
 
-// col[(n*OH+oh)*OW+ow][(c*KH+kh)*KW+kw] = x[n,c,oh*S+kh-P,ow*S+kw-P] (0 outside).  One thread per 4 consecutive
-// columns of one row, rows fastest across blocks, so that every store is a coalesced float4; no padded image copy.
-__global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ col, float *__restrict__ col_small,
-                              ConvGeom g, int64_t rows)
+// col[(n*OH+oh)*OW+ow][(c*KH+kh)*KW+kw] = x[n,c,oh*S+kh-P,ow*S+kw-P] (0 outside); no padded image copy.
+// One warp per output row: the (n, oh, ow) decomposition is done once per row, each lane owns groups of 4 consecutive
+// columns (coalesced float4 stores) and decomposes its first column into (c, kh, kw) once, then steps kw / kh / c
+// incrementally -- the kernel was bound by integer division, not by HBM, when every element did its own div/mod.
+__global__ void __launch_bounds__(256) im2col_kernel(const float *__restrict__ x, float *__restrict__ col,
+                                                     float *__restrict__ col_small, ConvGeom g, int64_t rows)
 {
-    const int q4         = g.ld_col >> 2;
-    const int64_t total  = rows * q4;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    const int q4          = g.ld_col >> 2;
+    const int lane        = threadIdx.x & 31;
+    const int64_t warp0   = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int khw         = g.KH * g.KW;
+    for (int64_t row = warp0; row < rows; row += n_warps)
     {
-        const int64_t row = i / q4;
-        const int c4      = static_cast<int>(i - row * q4) * 4;
-        const int ow      = static_cast<int>(row % g.OW);
-        const int64_t t   = row / g.OW;
-        const int oh      = static_cast<int>(t % g.OH);
-        const int n       = static_cast<int>(t / g.OH);
-        float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
+        const int r32 = static_cast<int>(row);  // rows < 2^31 (checked by the launcher)
+        const int ow  = r32 % g.OW;
+        const int t   = r32 / g.OW;
+        const int oh  = t % g.OH;
+        const int n   = t / g.OH;
+        const int h0 = oh * g.S - g.P, w0 = ow * g.S - g.P;
+        const float *xn = x + static_cast<int64_t>(n) * g.C * g.H * g.W;
+        for (int q = lane; q < q4; q += 32)
         {
-            const int cidx = c4 + j;
-            float val      = 0.f;
-            if (cidx < g.ckk)
+            int cidx = q * 4;
+            int c    = cidx / khw;
+            int rem  = cidx - c * khw;
+            int kh   = rem / g.KW;
+            int kw   = rem - kh * g.KW;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
             {
-                const int kw = cidx % g.KW;
-                const int t2 = cidx / g.KW;
-                const int kh = t2 % g.KH;
-                const int c  = t2 / g.KH;
-                const int h  = oh * g.S + kh - g.P;
-                const int w  = ow * g.S + kw - g.P;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-                    val = __ldg(x + ((static_cast<int64_t>(n) * g.C + c) * g.H + h) * g.W + w);
+                float val = 0.f;
+                if (cidx + j < g.ckk)
+                {
+                    const int h = h0 + kh, w = w0 + kw;
+                    if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+                        val = __ldg(xn + (static_cast<int64_t>(c) * g.H + h) * g.W + w);
+                }
+                v[j] = val;
+                if (++kw == g.KW)
+                {
+                    kw = 0;
+                    if (++kh == g.KH)
+                    {
+                        kh = 0;
+                        ++c;
+                    }
+                }
             }
-            v[j] = val;
+            const int64_t o = row * q4 + q;
+            reinterpret_cast<float4 *>(col)[o] = make_float4(v[0], v[1], v[2], v[3]);
+            if (col_small)
+                reinterpret_cast<float4 *>(col_small)[o] =
+                    make_float4(tf32_small(v[0]), tf32_small(v[1]), tf32_small(v[2]), tf32_small(v[3]));
         }
-        reinterpret_cast<float4 *>(col)[i] = make_float4(v[0], v[1], v[2], v[3]);
-        if (col_small)
-            reinterpret_cast<float4 *>(col_small)[i] =
-                make_float4(tf32_small(v[0]), tf32_small(v[1]), tf32_small(v[2]), tf32_small(v[3]));
+    }
+}
+
+// Flat NCHW index -> (n, c, h, w); 32-bit division whenever the index allows it (64-bit division is ~10x slower).
+__device__ __forceinline__ void split_nchw_index(int64_t i, const ConvGeom &g, int &n, int &c, int &h, int &w)
+{
+    if (i <= 0x7fffffffLL)
+    {
+        unsigned u = static_cast<unsigned>(i);
+        w          = static_cast<int>(u % static_cast<unsigned>(g.W));
+        u /= static_cast<unsigned>(g.W);
+        h = static_cast<int>(u % static_cast<unsigned>(g.H));
+        u /= static_cast<unsigned>(g.H);
+        c = static_cast<int>(u % static_cast<unsigned>(g.C));
+        n = static_cast<int>(u / static_cast<unsigned>(g.C));
+    }
+    else
+    {
+        w         = static_cast<int>(i % g.W);
+        int64_t t = i / g.W;
+        h         = static_cast<int>(t % g.H);
+        t /= g.H;
+        c = static_cast<int>(t % g.C);
+        n = static_cast<int>(t / g.C);
     }
 }
 
@@ -365,27 +457,21 @@ __global__ void col2im_gather_kernel(const float *__restrict__ colT, int64_t ld_
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
     {
-        const int w     = static_cast<int>(i % g.W);
-        int64_t t       = i / g.W;
-        const int h     = static_cast<int>(t % g.H);
-        t /= g.H;
-        const int c = static_cast<int>(t % g.C);
-        const int n = static_cast<int>(t / g.C);
-        float acc   = 0.f;
-        for (int kh = 0; kh < g.KH; ++kh)
+        int n, c, h, w;
+        split_nchw_index(i, g, n, c, h, w);
+        float acc = 0.f;
+        // only taps with (h + P - kh) and (w + P - kw) divisible by the stride contribute: walk those directly
+        const int hp = h + g.P, wp = w + g.P;
+        const int kh0 = hp % g.S, kw0 = wp % g.S;
+        const int ow0 = (wp - kw0) / g.S;
+        int oh        = (hp - kh0) / g.S;
+        for (int kh = kh0; kh < g.KH && oh >= 0; kh += g.S, --oh)
         {
-            const int hh = h + g.P - kh;
-            if (hh < 0 || hh % g.S)
-                continue;
-            const int oh = hh / g.S;
             if (oh >= g.OH)
                 continue;
-            for (int kw = 0; kw < g.KW; ++kw)
+            int ow = ow0;
+            for (int kw = kw0; kw < g.KW && ow >= 0; kw += g.S, --ow)
             {
-                const int ww = w + g.P - kw;
-                if (ww < 0 || ww % g.S)
-                    continue;
-                const int ow = ww / g.S;
                 if (ow >= g.OW)
                     continue;
                 const int64_t r = (static_cast<int64_t>(n) * g.OH + oh) * g.OW + ow;
@@ -403,27 +489,21 @@ __global__ void col2im_rows_kernel(const float *__restrict__ col, float *__restr
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
     {
-        const int w = static_cast<int>(i % g.W);
-        int64_t t   = i / g.W;
-        const int h = static_cast<int>(t % g.H);
-        t /= g.H;
-        const int c = static_cast<int>(t % g.C);
-        const int n = static_cast<int>(t / g.C);
-        float acc   = 0.f;
-        for (int kh = 0; kh < g.KH; ++kh)
+        int n, c, h, w;
+        split_nchw_index(i, g, n, c, h, w);
+        float acc = 0.f;
+        // only taps with (h + P - kh) and (w + P - kw) divisible by the stride contribute: walk those directly
+        const int hp = h + g.P, wp = w + g.P;
+        const int kh0 = hp % g.S, kw0 = wp % g.S;
+        const int ow0 = (wp - kw0) / g.S;
+        int oh        = (hp - kh0) / g.S;
+        for (int kh = kh0; kh < g.KH && oh >= 0; kh += g.S, --oh)
         {
-            const int hh = h + g.P - kh;
-            if (hh < 0 || hh % g.S)
-                continue;
-            const int oh = hh / g.S;
             if (oh >= g.OH)
                 continue;
-            for (int kw = 0; kw < g.KW; ++kw)
+            int ow = ow0;
+            for (int kw = kw0; kw < g.KW && ow >= 0; kw += g.S, --ow)
             {
-                const int ww = w + g.P - kw;
-                if (ww < 0 || ww % g.S)
-                    continue;
-                const int ow = ww / g.S;
                 if (ow >= g.OW)
                     continue;
                 const int64_t r = (static_cast<int64_t>(n) * g.OH + oh) * g.OW + ow;
@@ -462,21 +542,17 @@ __global__ void __launch_bounds__(256) nchw_to_rows_kernel(const float *__restri
     }
 }
 
-// gb[oc] = sum over n, hw of gy[n][oc][hw]: grid (OC, slabs), block reduce, one atomic per block.
-__global__ void __launch_bounds__(256) channel_sum_kernel(const float *__restrict__ gy, float *__restrict__ gb, int N,
-                                                          int OC, int HW)
+// gb[oc] = sum over n, hw of gy[n][oc][hw]: grid (OC, N, slabs of one plane); every block streams a contiguous piece
+// of one (n, oc) plane (no per-element index arithmetic), reduces it and issues one atomic.
+__global__ void __launch_bounds__(256) channel_sum_kernel(const float *__restrict__ gy, float *__restrict__ gb, int OC,
+                                                          int HW)
 {
     __shared__ float red[256];
-    const int oc        = blockIdx.x;
-    const int64_t total = static_cast<int64_t>(N) * HW;
-    float s             = 0.f;
-    for (int64_t i = static_cast<int64_t>(blockIdx.y) * 256 + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.y) * 256)
-    {
-        const int n = static_cast<int>(i / HW);
-        const int r = static_cast<int>(i - static_cast<int64_t>(n) * HW);
-        s += __ldg(gy + (static_cast<int64_t>(n) * OC + oc) * HW + r);
-    }
+    const int oc = blockIdx.x, n = blockIdx.y;
+    const float *plane = gy + (static_cast<int64_t>(n) * OC + oc) * HW;
+    float s            = 0.f;
+    for (int i = blockIdx.z * 256 + threadIdx.x; i < HW; i += gridDim.z * 256)
+        s += __ldg(plane + i);
     red[threadIdx.x] = s;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1)
@@ -633,7 +709,12 @@ int im2col_launch(const float *x, float *col, float *col_small, int64_t N, int64
         return kInvalidArgument;
     }
     const int64_t rows = static_cast<int64_t>(g.N) * g.OH * g.OW;
-    im2col_kernel<<<grid_for(rows * (g.ld_col / 4), 256, 16), 256, 0, s>>>(x, col, col_small, g, rows);
+    if (rows > 0x7fffffff)
+    {
+        set_last_error("im2col: more than 2^31-1 output rows");
+        return kTooLarge;
+    }
+    im2col_kernel<<<grid_for(rows * 32, 256, 16), 256, 0, s>>>(x, col, col_small, g, rows);
     ODL_LAUNCH_CHECK("im2col_kernel");
     return kOk;
 }
@@ -675,14 +756,17 @@ int nchw_to_rows_launch(const float *src, float *dst, float *dst_small, int64_t 
 
 int channel_sum_launch(const float *gy, float *gb, int64_t N, int64_t OC, int64_t HW, cudaStream_t s)
 {
+    if (N > 65535 || OC > 0x7fffffff || HW > 0x7fffffff)
+    {
+        set_last_error("channel_sum: dimension out of range");
+        return kTooLarge;
+    }
     ODL_CUDA_TRY(cudaMemsetAsync(gb, 0, OC * sizeof(float), s));
-    int slabs = (int)((N * HW + 256 * 64 - 1) / (256 * 64));
-    if (slabs < 1)
-        slabs = 1;
-    if (slabs > 1024)
-        slabs = 1024;
-    dim3 grid((unsigned)OC, (unsigned)slabs);
-    channel_sum_kernel<<<grid, 256, 0, s>>>(gy, gb, (int)N, (int)OC, (int)HW);
+    int slabs = (int)((HW + 256 * 16 - 1) / (256 * 16));
+    if (slabs > 64)
+        slabs = 64;
+    dim3 grid((unsigned)OC, (unsigned)N, (unsigned)slabs);
+    channel_sum_kernel<<<grid, 256, 0, s>>>(gy, gb, (int)OC, (int)HW);
     ODL_LAUNCH_CHECK("channel_sum_kernel");
     return kOk;
 }

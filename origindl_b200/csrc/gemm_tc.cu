@@ -472,8 +472,8 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
 
 }  // namespace
 
-// Test hook: K-blocks (of 32) accumulated in TMEM between two drains into registers; 0 = default
-// (8, i.e. K = 256, for 3xTF32; the whole K for plain TF32).
+// Test hook: K-blocks accumulated in TMEM between two drains into registers; 0 = default
+// (64 K elements, i.e. 2 blocks of 32, for 3xTF32; the whole K for plain TF32).
 int g_chunk_kb = 0;
 // Test hook: 0 = automatic split-K, 1 = never split, n > 1 = force n splits where the epilogue allows it.
 int g_split_k = 0;

@@ -208,12 +208,18 @@ int odl_mlp_set_params(void *handle, const float *host_packed, void *stream)
     return kOk;
 }
 
-// which: 0 parameters, 1 gradients of the last backward (after the optimizer's hook, like Parameter::grad()).
+// which: 0 parameters, 1 gradients of the last backward (after the optimizer's hook, like Parameter::grad()),
+// 2 first-moment buffer (Adam m / SGD momentum buffer), 3 Adam's second moment.
 int odl_mlp_get_packed(void *handle, int which, float *host_packed, void *stream)
 {
     Mlp *h           = H(handle);
-    const float *src = which == 0 ? h->params : h->grads;
-    int64_t o        = 0;
+    const float *src = which == 0 ? h->params : which == 1 ? h->grads : which == 2 ? h->m : which == 3 ? h->v : nullptr;
+    if (!src || !host_packed)
+    {
+        set_last_error("mlp_get_packed: buffer %d does not exist for this optimizer", which);
+        return kInvalidArgument;
+    }
+    int64_t o = 0;
     for (int l = 0; l < h->L; ++l)
     {
         const int64_t nw = static_cast<int64_t>(h->sizes[l]) * h->sizes[l + 1], nb = h->sizes[l + 1];
@@ -224,6 +230,43 @@ int odl_mlp_get_packed(void *handle, int which, float *host_packed, void *stream
     }
     ODL_CUDA_TRY(cudaStreamSynchronize(ST(stream)));
     return kOk;
+}
+
+// Restore the optimizer state saved with odl_mlp_get_packed(2 / 3) and odl_mlp_step_count: packed HOST arrays in the
+// parameter order; v_packed is ignored (may be NULL) for SGD.  Call after odl_mlp_set_params, which zeroes the state.
+int odl_mlp_set_optimizer_state(void *handle, const float *m_packed, const float *v_packed, int step_count, void *stream)
+{
+    Mlp *h = H(handle);
+    if (!m_packed || step_count < 0 || (h->optimizer == 1 && !v_packed))
+    {
+        set_last_error("mlp_set_optimizer_state: invalid argument (step_count=%d)", step_count);
+        return kInvalidArgument;
+    }
+    const float *srcs[2] = {m_packed, h->optimizer == 1 ? v_packed : nullptr};
+    float *dsts[2]       = {h->m, h->v};
+    for (int k = 0; k < 2; ++k)
+    {
+        if (!srcs[k] || !dsts[k])
+            continue;
+        int64_t o = 0;
+        for (int l = 0; l < h->L; ++l)
+        {
+            const int64_t nw = static_cast<int64_t>(h->sizes[l]) * h->sizes[l + 1], nb = h->sizes[l + 1];
+            ODL_CUDA_TRY(cudaMemcpyAsync(dsts[k] + h->w_off[l], srcs[k] + o, nw * 4, cudaMemcpyHostToDevice, ST(stream)));
+            o += nw;
+            ODL_CUDA_TRY(cudaMemcpyAsync(dsts[k] + h->b_off[l], srcs[k] + o, nb * 4, cudaMemcpyHostToDevice, ST(stream)));
+            o += nb;
+        }
+    }
+    h->step_count = step_count;
+    ODL_CUDA_TRY(cudaStreamSynchronize(ST(stream)));
+    return kOk;
+}
+
+// Optimizer steps taken since the parameters were installed (Adam's t).
+int64_t odl_mlp_step_count(void *handle)
+{
+    return H(handle)->step_count;
 }
 
 // Forward through all layers, loss and d loss / d logits (scaled by grad_scale / batch), bias gradient of the head.

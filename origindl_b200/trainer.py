@@ -28,6 +28,7 @@ class MLPTrainer:
         self.sizes = [int(s) for s in sizes]
         self.batch = int(batch)
         self.n_layers = len(self.sizes) - 1
+        self.optimizer, self.lr = optimizer, float(lr)
         arr = (ctypes.c_int32 * len(self.sizes))(*self.sizes)
         h = ctypes.c_void_p()
         opt = {"sgd": 0, "adam": 1}[optimizer]
@@ -80,6 +81,93 @@ class MLPTrainer:
         out = np.empty(self.param_count, np.float32)
         capi.call("odl_mlp_get_packed", self._h, 1, out.ctypes.data, capi.stream_handle())
         return out
+
+    # -- state dict / checkpoint in the reference's formats (Module::state_dict, src/nn/module.cpp:118-128; origin::save
+    #    of a Checkpoint, src/io/checkpoint.cpp:15-75).  Names and shapes are those of nn::MLP: layer_i.weight {in,out},
+    #    layer_i.bias {1,out} (src/nn/models/mlp.cpp:21-34, src/nn/layers/linear.cpp:25-62).
+    def _named_shapes(self):
+        for i in range(self.n_layers):
+            yield f"layer_{i}.weight", (self.sizes[i], self.sizes[i + 1])
+            yield f"layer_{i}.bias", (1, self.sizes[i + 1])
+
+    def _unpack(self, packed: np.ndarray, prefix: str = "") -> dict:
+        out, o = {}, 0
+        for name, shape in self._named_shapes():
+            n = shape[0] * shape[1]
+            out[prefix + name] = packed[o:o + n].reshape(shape)
+            o += n
+        return out
+
+    def _pack(self, tensors: dict, prefix: str = "", strict: bool = True) -> np.ndarray:
+        packed = np.empty(self.param_count, np.float32) if strict else self.get_params()
+        o = 0
+        for name, shape in self._named_shapes():
+            n = shape[0] * shape[1]
+            t = tensors.get(prefix + name)
+            if t is None:
+                if strict:
+                    raise RuntimeError(f"Missing parameter '{prefix + name}' in state_dict (strict mode)")
+            else:
+                if tuple(t.shape) != shape:
+                    raise RuntimeError(f"Shape mismatch for parameter '{prefix + name}': expected {shape}, got {tuple(t.shape)}")
+                packed[o:o + n] = np.asarray(t, np.float32).reshape(-1)
+            o += n
+        return packed
+
+    def state_dict(self) -> dict:
+        return self._unpack(self.get_params())
+
+    def load_state_dict(self, state_dict: dict, strict: bool = True) -> None:
+        """Module::load_state_dict (src/nn/module.cpp:130-168): shape mismatches always raise; missing and unexpected
+        names raise in strict mode.  Installing parameters resets the optimizer state (load it afterwards)."""
+        if strict:
+            known = {n for n, _ in self._named_shapes()}
+            for key in state_dict:
+                if key not in known:
+                    raise RuntimeError(f"Unexpected parameter '{key}' in state_dict (strict mode)")
+        self.set_params(self._pack(state_dict, strict=strict))
+
+    def optimizer_state_dict(self) -> dict:
+        """m_<param>, v_<param> (Adam only) and step_<param>: the keys of Adam::state_dict (src/optim/adam.cpp:116-193)."""
+        buf = np.empty(self.param_count, np.float32)
+        capi.call("odl_mlp_get_packed", self._h, 2, buf.ctypes.data, capi.stream_handle())
+        out = self._unpack(buf.copy(), "m_")
+        if self.optimizer == "adam":
+            capi.call("odl_mlp_get_packed", self._h, 3, buf.ctypes.data, capi.stream_handle())
+            out.update(self._unpack(buf.copy(), "v_"))
+        step = int(capi.lib().odl_mlp_step_count(self._h))
+        for name, _ in self._named_shapes():
+            out["step_" + name] = np.array([step], np.int32)
+        return out
+
+    def load_optimizer_state_dict(self, state: dict) -> None:
+        m = self._pack(state, "m_")
+        v = self._pack(state, "v_") if self.optimizer == "adam" else None
+        steps = {int(np.asarray(state["step_" + n]).reshape(-1)[0]) for n, _ in self._named_shapes()}
+        if len(steps) != 1:
+            raise RuntimeError(f"optimizer state holds different step counts per parameter: {sorted(steps)}")
+        capi.call("odl_mlp_set_optimizer_state", self._h, m.ctypes.data, None if v is None else v.ctypes.data,
+                  steps.pop(), capi.stream_handle())
+
+    def save_checkpoint(self, filepath: str, epoch: int = -1, step: int = -1, loss: float = 0.0) -> str:
+        from . import odl_io
+
+        cfg = {"lr": self.lr}
+        if self.optimizer == "adam":
+            cfg.update(beta1=0.9, beta2=0.999, eps=1e-8)
+        ck = odl_io.Checkpoint(self.state_dict(), self.optimizer_state_dict(), epoch, step, loss,
+                               {"adam": "Adam", "sgd": "SGD"}[self.optimizer], cfg)
+        return odl_io.save_checkpoint(ck, filepath, (odl_io.DEVICE_CUDA, torch.cuda.current_device()))
+
+    def load_checkpoint(self, filepath: str):
+        """Restore parameters and, when the checkpoint holds it, the optimizer state; returns the Checkpoint."""
+        from . import odl_io
+
+        ck = odl_io.load_checkpoint(filepath)
+        self.load_state_dict(ck.model_state_dict)
+        if ck.optimizer_state_dict:
+            self.load_optimizer_state_dict(ck.optimizer_state_dict)
+        return ck
 
     def logits(self) -> torch.Tensor:
         return self._view(capi.lib().odl_mlp_logits_ptr(self._h), self.batch * self.sizes[-1]).view(self.batch, -1)

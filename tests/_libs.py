@@ -85,6 +85,15 @@ def reference():
         L.odlref_mlp_train.argtypes = [_I, c_int, _F, _F, _I, c_int64, c_int, c_int, c_int, c_float, c_float, c_float,
                                        _F, _FN]
         L.odlref_optim_replay.argtypes = [_F, _F, c_int64, c_int, c_int, c_float, c_float, c_float, c_int, c_float]
+        if hasattr(L, "odlref_save_state"):  # a prebuilt library may predate the state-dict entry points
+            cp, ip = ctypes.c_char_p, ctypes.POINTER(c_int)
+            L.odlref_save_state.argtypes = [cp, c_int, ctypes.POINTER(cp), _I, np.ctypeslib.ndpointer(np.int64, flags="C"),
+                                            ctypes.POINTER(ctypes.c_void_p)]
+            L.odlref_load_state_names.argtypes = [cp, cp, c_int64, ip]
+            L.odlref_load_state_tensor.argtypes = [cp, cp, ip, np.ctypeslib.ndpointer(np.int64, flags="C"), _FN]
+            L.odlref_save_checkpoint.argtypes = [cp, _I, c_int, _F, c_int, c_int, c_float, cp, c_float, c_float, c_float,
+                                                 c_float]
+            L.odlref_load_checkpoint_meta.argtypes = [cp, ip, ip, ctypes.POINTER(c_float), cp, c_int64, _F, ip]
         _reference = L
     return _reference
 
