@@ -244,6 +244,15 @@ float *odl_mlp_logits_ptr(void *handle);
 /* Contiguous device range [dW_layer, db_layer] of the flat gradient buffer (layer = -1: the whole buffer). */
 int odl_mlp_grad_bucket(void *handle, int layer, float **ptr, int64_t *count);
 
+/* ---- input pipeline --------------------------------------------------------------------------------------------- */
+
+/* Batch assembly from a data set resident in device memory: dst[i, 0:cols] = src[idx[i], 0:cols] and (when
+ * labels_dst != NULL) labels_dst[i] = labels_src[idx[i]], i < n_idx; idx, labels are int64 DEVICE arrays, 0 <= idx[i]
+ * < n_src (a violation writes zeros / -1 and is reported by odl_device_status).  Replaces the per-sample host loop of
+ * DataLoader::next (src/data/dataloader.cpp:38-139) followed by the host-to-device copy of the batch. */
+int odl_gather_rows(const float *src, int64_t ld_src, int64_t n_src, const int64_t *idx, int64_t n_idx, int64_t cols,
+                    float *dst, int64_t ld_dst, const int64_t *labels_src, int64_t *labels_dst, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -143,6 +143,7 @@ _MLP_SIGNATURES = {
     "odl_mlp_train_step": [_P, _P, _P, c_int, _P],
     "odl_mlp_grad_bucket": [_P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)],
     "odl_mlp_set_optimizer_state": [_P, _P, _P, c_int, _P],
+    "odl_gather_rows": [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _P, _P, _P],
 }
 _SIGNATURES.update(_MLP_SIGNATURES)
 _POINTER_RETURNS = {"odl_mlp_loss_ptr": [_P], "odl_mlp_logits_ptr": [_P]}

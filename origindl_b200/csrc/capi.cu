@@ -314,6 +314,11 @@ int odl_device_status(void *stream)
             set_last_error("softmax_cross_entropy: label out of range");
             return kInvalidArgument;
         }
+        if (flag == 3)
+        {
+            set_last_error("gather_rows: sample index out of range");
+            return kInvalidArgument;
+        }
         set_last_error("a kernel gave up on a bounded wait (pipeline barrier never completed)");
         return kKernelTimeout;
     }

@@ -7,6 +7,7 @@
 //   origin::nn::Module, Linear, MLP       src/nn/module.cpp, src/nn/layers/linear.cpp, src/nn/models/mlp.cpp
 //   origin::Optimizer, SGD, Adam, WeightDecay   src/optim/*.cpp, include/origin/optim/hooks.h
 //   origin::MemoryPool                    src/mat/origin/memory/memory_pool.cpp:37-176 (size-binned caching allocator)
+//   origin::save / load / Checkpoint / load_checkpoint   src/io/model_io.cpp:114-273, src/io/checkpoint.cpp:15-226
 //
 // Differences that are deliberate: tensors of this layer live on the device only (fp32 data, int32/int64 labels);
 // nn::Linear and nn::MLP run the fused Linear(+ReLU) operator (one kernel forward, three backward) instead of
@@ -17,9 +18,13 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <any>
+#include <cctype>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <filesystem>
+#include <fstream>
 #include <functional>
 #include <map>
 #include <memory>
@@ -949,6 +954,42 @@ class Module
         for (Parameter *p : parameters())
             p->clear_grad();
     }
+    // The parameters themselves (shared storage) keyed by dotted name (src/nn/module.cpp:118-128).
+    using StateDict = std::unordered_map<std::string, Tensor>;
+    virtual StateDict state_dict()
+    {
+        StateDict sd;
+        for (auto &kv : named_parameters())
+            sd[kv.first] = static_cast<const Tensor &>(*kv.second);
+        return sd;
+    }
+    // src/nn/module.cpp:130-168: a shape mismatch always throws; missing / unexpected names throw in strict mode.
+    // The parameter takes the VALUES of the loaded tensor (a device copy that requires grad).
+    virtual void load_state_dict(const StateDict &state_dict, bool strict = true)
+    {
+        std::set<std::string> loaded;
+        for (auto &kv : named_parameters())
+        {
+            auto it = state_dict.find(kv.first);
+            if (it != state_dict.end())
+            {
+                if (kv.second->shape() != it->second.shape())
+                    throw std::runtime_error("Shape mismatch for parameter '" + kv.first + "': expected " +
+                                             kv.second->shape().to_string() + ", got " + it->second.shape().to_string());
+                Tensor t              = it->second.clone();
+                t.impl()->requires_grad = true;
+                *kv.second            = Parameter(t);
+                loaded.insert(kv.first);
+            }
+            else if (strict)
+                throw std::runtime_error("Missing parameter '" + kv.first + "' in state_dict (strict mode)");
+        }
+        if (strict)
+            for (auto &kv : state_dict)
+                if (!loaded.count(kv.first))
+                    throw std::runtime_error("Unexpected parameter '" + kv.first + "' in state_dict (strict mode)");
+    }
+    void load(const std::string &filepath, bool strict = true);  // origin::load + load_state_dict (module.cpp:214-218)
 
   protected:
     void register_parameter(const std::string &name, Parameter &p) { params_.emplace_back(name, &p); }
@@ -1028,8 +1069,13 @@ class MLP : public Module
 class Optimizer
 {
   public:
-    explicit Optimizer(nn::Module &target) : params_(target.parameters()) {}
+    using State = std::unordered_map<std::string, std::any>;
+    explicit Optimizer(nn::Module &target) : target_(&target), params_(target.parameters()) {}
     virtual ~Optimizer() = default;
+    // Configuration scalars (float / bool), per-parameter buffers as a StateDict and, for Adam, the step counts
+    // (include/origin/optim/optimizer.h:66-80).
+    virtual State state_dict() = 0;
+    virtual void load_state_dict(const State &state) = 0;
     void register_hook(std::function<void(std::vector<Parameter *> &)> h) { hooks_.push_back(std::move(h)); }
     void zero_grad()
     {
@@ -1051,6 +1097,29 @@ class Optimizer
 
   protected:
     virtual void step_one(Parameter &p) = 0;
+    // buffers of `by_param` under "<prefix><parameter name>", the way the reference names them (adam.cpp:126-147)
+    template <typename Map, typename Get>
+    nn::Module::StateDict named_buffers(const Map &by_param, const std::string &prefix, Get get)
+    {
+        nn::Module::StateDict out;
+        for (auto &kv : target_->named_parameters())
+        {
+            auto it = by_param.find(kv.second);
+            if (it != by_param.end())
+                out[prefix + kv.first] = get(it->second);
+        }
+        return out;
+    }
+    template <typename T>
+    static bool fetch(const State &s, const char *key, T &out)
+    {
+        auto it = s.find(key);
+        if (it == s.end())
+            return false;
+        out = std::any_cast<T>(it->second);
+        return true;
+    }
+    nn::Module *target_;
     std::vector<Parameter *> params_;
     std::vector<std::function<void(std::vector<Parameter *> &)>> hooks_;
 };
@@ -1082,6 +1151,33 @@ class SGD : public Optimizer  // src/optim/sgd.cpp:18-75, one fused in-place ker
         : Optimizer(target), lr_(lr), momentum_(momentum), wd_(weight_decay), nesterov_(nesterov)
     {
     }
+    // lr, momentum, weight_decay, nesterov and "momentum_buffers" {momentum_<param>} (src/optim/sgd.cpp:77-115)
+    State state_dict() override
+    {
+        State st;
+        st["lr"]               = lr_;
+        st["momentum"]         = momentum_;
+        st["weight_decay"]     = wd_;
+        st["nesterov"]         = nesterov_;
+        st["momentum_buffers"] = named_buffers(buf_, "momentum_", [](const Tensor &t) { return t; });
+        return st;
+    }
+    void load_state_dict(const State &st) override
+    {
+        fetch(st, "lr", lr_);
+        fetch(st, "momentum", momentum_);
+        fetch(st, "weight_decay", wd_);
+        fetch(st, "nesterov", nesterov_);
+        nn::Module::StateDict bufs;
+        if (fetch(st, "momentum_buffers", bufs))
+        {
+            buf_.clear();
+            auto named = target_->named_parameters();
+            for (auto &kv : bufs)
+                if (kv.first.rfind("momentum_", 0) == 0 && named.count(kv.first.substr(9)))
+                    buf_[named[kv.first.substr(9)]] = kv.second.clone();
+        }
+    }
 
   protected:
     void step_one(Parameter &p) override
@@ -1089,9 +1185,9 @@ class SGD : public Optimizer  // src/optim/sgd.cpp:18-75, one fused in-place ker
         float *buf = nullptr;
         if (momentum_ > 0.0f)
         {
-            auto it = buf_.find(p.impl().get());
+            auto it = buf_.find(&p);
             if (it == buf_.end())
-                it = buf_.emplace(p.impl().get(), Tensor::zeros(p.shape())).first;
+                it = buf_.emplace(&p, Tensor::zeros(p.shape())).first;
             buf = it->second.data_ptr<float>();
         }
         odl_check(odl_sgd_step(p.data_ptr<float>(), p.grad().data_ptr<float>(), buf, nullptr, (int64_t)p.elements(), lr_,
@@ -1101,7 +1197,7 @@ class SGD : public Optimizer  // src/optim/sgd.cpp:18-75, one fused in-place ker
   private:
     float lr_, momentum_, wd_;
     bool nesterov_;
-    std::unordered_map<TensorImpl *, Tensor> buf_;
+    std::unordered_map<Parameter *, Tensor> buf_;
 };
 
 class Adam : public Optimizer  // src/optim/adam.cpp:19-114
@@ -1111,15 +1207,71 @@ class Adam : public Optimizer  // src/optim/adam.cpp:19-114
         : Optimizer(target), lr_(lr), b1_(beta1), b2_(beta2), eps_(eps)
     {
     }
+    // lr, beta1, beta2, eps, "m_buffers" {m_<param>}, "v_buffers" {v_<param>}, "step_counts" {step_<param>}
+    // (src/optim/adam.cpp:116-193)
+    State state_dict() override
+    {
+        State st;
+        st["lr"]        = lr_;
+        st["beta1"]     = b1_;
+        st["beta2"]     = b2_;
+        st["eps"]       = eps_;
+        st["m_buffers"] = named_buffers(state_, "m_", [](const PerParam &s) { return s.m; });
+        st["v_buffers"] = named_buffers(state_, "v_", [](const PerParam &s) { return s.v; });
+        std::unordered_map<std::string, int> steps;
+        for (auto &kv : target_->named_parameters())
+        {
+            auto it = state_.find(kv.second);
+            if (it != state_.end())
+                steps["step_" + kv.first] = it->second.t;
+        }
+        st["step_counts"] = steps;
+        return st;
+    }
+    void load_state_dict(const State &st) override  // src/optim/adam.cpp:195-277
+    {
+        fetch(st, "lr", lr_);
+        fetch(st, "beta1", b1_);
+        fetch(st, "beta2", b2_);
+        fetch(st, "eps", eps_);
+        auto named = target_->named_parameters();
+        nn::Module::StateDict m, v;
+        std::unordered_map<std::string, int> steps;
+        const bool has_m = fetch(st, "m_buffers", m), has_v = fetch(st, "v_buffers", v);
+        const bool has_t = fetch(st, "step_counts", steps);
+        if (has_m || has_v || has_t)
+            state_.clear();
+        auto slot = [&](const std::string &key, size_t prefix) -> PerParam * {
+            auto it = named.find(key.substr(prefix));
+            if (it == named.end())
+                return nullptr;
+            auto ins = state_.find(it->second);
+            if (ins == state_.end())
+                ins = state_.emplace(it->second, PerParam{Tensor::zeros(it->second->shape()),
+                                                          Tensor::zeros(it->second->shape()), 0}).first;
+            return &ins->second;
+        };
+        for (auto &kv : m)
+            if (kv.first.rfind("m_", 0) == 0)
+                if (PerParam *s = slot(kv.first, 2))
+                    s->m = kv.second.clone();
+        for (auto &kv : v)
+            if (kv.first.rfind("v_", 0) == 0)
+                if (PerParam *s = slot(kv.first, 2))
+                    s->v = kv.second.clone();
+        for (auto &kv : steps)
+            if (kv.first.rfind("step_", 0) == 0)
+                if (PerParam *s = slot(kv.first, 5))
+                    s->t = kv.second;
+    }
 
   protected:
     void step_one(Parameter &p) override
     {
-        TensorImpl *key = p.impl().get();
-        auto it         = state_.find(key);
+        auto it = state_.find(&p);
         if (it == state_.end())
-            it = state_.emplace(key, State{Tensor::zeros(p.shape()), Tensor::zeros(p.shape()), 0}).first;
-        State &s = it->second;
+            it = state_.emplace(&p, PerParam{Tensor::zeros(p.shape()), Tensor::zeros(p.shape()), 0}).first;
+        PerParam &s = it->second;
         s.t += 1;
         odl_check(odl_adam_step(p.data_ptr<float>(), p.grad().data_ptr<float>(), s.m.data_ptr<float>(),
                                 s.v.data_ptr<float>(), nullptr, (int64_t)p.elements(), s.t, lr_, b1_, b2_, eps_, 0.0f, 1.0f,
@@ -1127,13 +1279,287 @@ class Adam : public Optimizer  // src/optim/adam.cpp:19-114
     }
 
   private:
-    struct State
+    struct PerParam
     {
         Tensor m, v;
         int t;
     };
     float lr_, b1_, b2_, eps_;
-    std::unordered_map<TensorImpl *, State> state_;
+    std::unordered_map<Parameter *, PerParam> state_;
 };
+
+// ------------------------------------------------------------------------------------------------ .odl files, checkpoints
+// State-dict files in the reference's format (src/io/model_io.cpp:114-273), little endian, size_t = 8 bytes:
+//   u32 magic 0x4F444C00 | u32 version 1 | u64 count | per tensor: u64 name length, name | u64 rank, u64 dims[rank] |
+//   i32 dtype (reference enum: 0 float32, 3 int32) | i32 device type (1 = CUDA), i32 device index | raw values.
+// Tensors of this layer are float32 or int32/int64; like the reference, save() rejects what it cannot represent
+// (int64), and load() rejects float64 records, which have no tensor type here.
+using StateDict = nn::Module::StateDict;
+
+namespace detail
+{
+template <typename T>
+inline void put(std::ofstream &out, const T &v)
+{
+    out.write(reinterpret_cast<const char *>(&v), sizeof(T));
+}
+template <typename T>
+inline T get(std::ifstream &in, const char *what)
+{
+    T v;
+    in.read(reinterpret_cast<char *>(&v), sizeof(T));
+    if (in.fail())
+        throw std::runtime_error(std::string("Failed to read ") + what + " from file");
+    return v;
+}
+inline std::string checkpoint_dir(const std::string &filepath)
+{
+    return filepath.size() > 5 && filepath.substr(filepath.size() - 5) == ".ckpt" ? filepath.substr(0, filepath.size() - 5)
+                                                                                    : filepath;
+}
+}  // namespace detail
+
+inline void save(const StateDict &state_dict, const std::string &filepath)
+{
+    std::ofstream out(filepath, std::ios::binary);
+    if (!out.is_open())
+        throw std::runtime_error("Failed to open file for writing: " + filepath);
+    int device = 0;
+    cudaGetDevice(&device);
+    detail::put<uint32_t>(out, 0x4F444C00u);
+    detail::put<uint32_t>(out, 1u);
+    detail::put<uint64_t>(out, state_dict.size());
+    std::vector<std::string> names;
+    for (auto &kv : state_dict)
+        names.push_back(kv.first);
+    std::sort(names.begin(), names.end());  // the reference writes hash-map order; the order carries no meaning
+    for (const std::string &name : names)
+    {
+        const Tensor &t = state_dict.at(name);
+        detail::put<uint64_t>(out, name.size());
+        out.write(name.data(), (std::streamsize)name.size());
+        detail::put<uint64_t>(out, t.shape().size());
+        for (size_t d : t.shape().dims())
+            detail::put<uint64_t>(out, d);
+        if (t.dtype() != DataType::kFloat32 && t.dtype() != DataType::kInt32)
+            throw std::runtime_error("Unsupported dtype for saving: " + std::to_string(t.dtype() == DataType::kInt64 ? 4 : -1));
+        detail::put<int32_t>(out, t.dtype() == DataType::kFloat32 ? 0 : 3);
+        detail::put<int32_t>(out, 1);
+        detail::put<int32_t>(out, device);
+        if (t.dtype() == DataType::kFloat32)
+        {
+            auto v = t.to_vector<float>();
+            out.write(reinterpret_cast<const char *>(v.data()), (std::streamsize)(v.size() * sizeof(float)));
+        }
+        else
+        {
+            auto v = t.to_vector<int32_t>();
+            out.write(reinterpret_cast<const char *>(v.data()), (std::streamsize)(v.size() * sizeof(int32_t)));
+        }
+    }
+    out.close();
+    if (out.fail())
+        throw std::runtime_error("Failed to write to file: " + filepath);
+}
+
+inline StateDict load(const std::string &filepath)
+{
+    std::ifstream in(filepath, std::ios::binary);
+    if (!in.is_open())
+        throw std::runtime_error("Failed to open file for reading: " + filepath);
+    uint32_t magic = 0;
+    in.read(reinterpret_cast<char *>(&magic), sizeof(magic));
+    if (in.fail() || magic != 0x4F444C00u)
+        throw std::runtime_error("Invalid file format or corrupted file: " + filepath);
+    uint32_t version = 0;
+    in.read(reinterpret_cast<char *>(&version), sizeof(version));
+    if (in.fail() || version != 1)
+        throw std::runtime_error("Unsupported file version: " + std::to_string(version));
+    const uint64_t count = detail::get<uint64_t>(in, "parameter count");
+    StateDict sd;
+    for (uint64_t i = 0; i < count; ++i)
+    {
+        const uint64_t len = detail::get<uint64_t>(in, "string length");
+        std::string name(len, '\0');
+        in.read(&name[0], (std::streamsize)len);
+        if (in.fail())
+            throw std::runtime_error("Failed to read string data from file");
+        const uint64_t rank = detail::get<uint64_t>(in, "shape dimensions");
+        std::vector<size_t> dims(rank);
+        for (uint64_t d = 0; d < rank; ++d)
+            dims[d] = detail::get<uint64_t>(in, "shape dimension");
+        const int32_t code = detail::get<int32_t>(in, "dtype");
+        detail::get<int32_t>(in, "device");
+        detail::get<int32_t>(in, "device");  // tensors of this layer always live on the current CUDA device
+        Shape shape(dims);
+        if (code == 0)
+        {
+            std::vector<float> v(shape.elements());
+            in.read(reinterpret_cast<char *>(v.data()), (std::streamsize)(v.size() * sizeof(float)));
+            if (in.fail())
+                throw std::runtime_error("Failed to read tensor data for parameter '" + name + "'");
+            sd[name] = Tensor(v, shape);
+        }
+        else if (code == 3)
+        {
+            std::vector<int32_t> v(shape.elements());
+            in.read(reinterpret_cast<char *>(v.data()), (std::streamsize)(v.size() * sizeof(int32_t)));
+            if (in.fail())
+                throw std::runtime_error("Failed to read tensor data for parameter '" + name + "'");
+            sd[name] = Tensor(v, shape);
+        }
+        else
+            throw std::runtime_error("Unsupported dtype for loading: " + std::to_string(code));
+    }
+    return sd;
+}
+
+inline void nn::Module::load(const std::string &filepath, bool strict)
+{
+    load_state_dict(origin::load(filepath), strict);
+}
+
+// include/origin/io/checkpoint.h:13-25.  A checkpoint is a DIRECTORY (the path minus a trailing ".ckpt") with model.odl
+// and metadata.json written exactly as the reference writes them (src/io/checkpoint.cpp:15-75), plus optimizer.odl,
+// which the reference names and never writes: here it holds every StateDict found in optimizer_state_dict (the
+// m_/v_/momentum_ buffers) and the Adam step counts as int32 tensors of shape {1}, so that training resumes on the
+// same trajectory.  The reference's loader ignores the extra file.
+struct Checkpoint
+{
+    StateDict model_state_dict;
+    std::unordered_map<std::string, Optimizer::State> optimizer_state_dict;
+    int epoch  = -1;
+    int step   = -1;
+    float loss = 0.0f;
+    std::string optimizer_type;
+    std::unordered_map<std::string, float> optimizer_config;
+};
+
+inline void save(const Checkpoint &checkpoint, const std::string &filepath)
+{
+    namespace fs = std::filesystem;
+    const std::string dir = detail::checkpoint_dir(filepath);
+    try
+    {
+        fs::create_directories(dir);
+    }
+    catch (const std::exception &e)
+    {
+        throw std::runtime_error("Failed to create checkpoint directory '" + dir + "': " + e.what());
+    }
+    save(checkpoint.model_state_dict, dir + "/model.odl");
+    StateDict opt;
+    for (auto &named : checkpoint.optimizer_state_dict)
+        for (auto &kv : named.second)
+        {
+            if (kv.second.type() == typeid(StateDict))
+                for (auto &t : std::any_cast<const StateDict &>(kv.second))
+                    opt[t.first] = t.second;
+            else if (kv.second.type() == typeid(std::unordered_map<std::string, int>))
+                for (auto &t : std::any_cast<const std::unordered_map<std::string, int> &>(kv.second))
+                    opt[t.first] = Tensor(std::vector<int32_t>{t.second}, Shape{1});
+        }
+    if (!opt.empty())
+        save(opt, dir + "/optimizer.odl");
+    std::ofstream meta(dir + "/metadata.json");
+    if (!meta.is_open())
+        throw std::runtime_error("Failed to open metadata file for writing: " + dir + "/metadata.json");
+    meta << "{\n";
+    meta << "  \"format_version\": \"1.0\",\n";
+    meta << "  \"format_type\": \"origindl_checkpoint\",\n";
+    meta << "  \"epoch\": " << checkpoint.epoch << ",\n";
+    meta << "  \"step\": " << checkpoint.step << ",\n";
+    meta << "  \"loss\": " << checkpoint.loss << ",\n";
+    meta << "  \"optimizer_type\": \"" << checkpoint.optimizer_type << "\",\n";
+    meta << "  \"optimizer_config\": {\n";
+    bool first = true;
+    for (auto &kv : checkpoint.optimizer_config)
+    {
+        if (!first)
+            meta << ",\n";
+        meta << "    \"" << kv.first << "\": " << kv.second;
+        first = false;
+    }
+    meta << "\n  }\n";
+    meta << "}\n";
+}
+
+// src/io/checkpoint.cpp:77-226, including its line-oriented metadata parser.  When optimizer.odl exists its tensors
+// come back under optimizer_state_dict[<optimizer_type in lower case>] in the shape Optimizer::load_state_dict takes.
+inline Checkpoint load_checkpoint(const std::string &filepath)
+{
+    namespace fs = std::filesystem;
+    const std::string dir = detail::checkpoint_dir(filepath);
+    if (!fs::exists(dir) || !fs::is_directory(dir))
+        throw std::runtime_error("Checkpoint directory does not exist: " + dir);
+    Checkpoint ck;
+    if (!fs::exists(dir + "/model.odl"))
+        throw std::runtime_error("Model file not found in checkpoint: " + dir + "/model.odl");
+    ck.model_state_dict = load(dir + "/model.odl");
+    if (!fs::exists(dir + "/metadata.json"))
+        throw std::runtime_error("Metadata file not found in checkpoint: " + dir + "/metadata.json");
+    std::ifstream meta(dir + "/metadata.json");
+    if (!meta.is_open())
+        throw std::runtime_error("Failed to open metadata file: " + dir + "/metadata.json");
+    auto value_of = [](const std::string &line) {
+        std::string v = line.substr(line.find(':') + 1);
+        v.erase(0, v.find_first_not_of(" \t,"));
+        v.erase(v.find_last_not_of(" \t,") + 1);
+        return v;
+    };
+    std::string line;
+    while (std::getline(meta, line))
+    {
+        if (line.find(':') == std::string::npos)
+            continue;
+        if (line.find("\"epoch\"") != std::string::npos)
+            ck.epoch = std::atoi(value_of(line).c_str());
+        if (line.find("\"step\"") != std::string::npos)
+            ck.step = std::atoi(value_of(line).c_str());
+        if (line.find("\"loss\"") != std::string::npos)
+            ck.loss = (float)std::atof(value_of(line).c_str());
+        if (line.find("\"optimizer_type\"") != std::string::npos)
+        {
+            const std::string v = line.substr(line.find(':') + 1);
+            const size_t a = v.find('"'), b = v.find('"', a + 1);
+            if (a != std::string::npos && b != std::string::npos)
+                ck.optimizer_type = v.substr(a + 1, b - a - 1);
+        }
+        for (const char *key : {"lr", "beta1", "beta2", "eps"})
+            if (line.find(std::string("\"") + key + "\"") != std::string::npos)
+                ck.optimizer_config[key] = (float)std::atof(value_of(line).c_str());
+    }
+    if (fs::exists(dir + "/optimizer.odl"))
+    {
+        StateDict m, v, mom;
+        std::unordered_map<std::string, int> steps;
+        for (auto &kv : load(dir + "/optimizer.odl"))
+        {
+            if (kv.first.rfind("m_", 0) == 0 && kv.first.rfind("momentum_", 0) != 0)
+                m[kv.first] = kv.second;
+            else if (kv.first.rfind("v_", 0) == 0)
+                v[kv.first] = kv.second;
+            else if (kv.first.rfind("momentum_", 0) == 0)
+                mom[kv.first] = kv.second;
+            else if (kv.first.rfind("step_", 0) == 0)
+                steps[kv.first] = kv.second.to_vector<int32_t>()[0];
+        }
+        std::string key = ck.optimizer_type;
+        std::transform(key.begin(), key.end(), key.begin(), [](unsigned char c) { return (char)std::tolower(c); });
+        Optimizer::State st;
+        for (auto &kv : ck.optimizer_config)
+            st[kv.first] = kv.second;
+        if (!m.empty())
+            st["m_buffers"] = m;
+        if (!v.empty())
+            st["v_buffers"] = v;
+        if (!mom.empty())
+            st["momentum_buffers"] = mom;
+        if (!steps.empty())
+            st["step_counts"] = steps;
+        ck.optimizer_state_dict[key] = st;
+    }
+    return ck;
+}
 
 }  // namespace origin

@@ -6,6 +6,7 @@
     python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
     python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
     python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
+    python -m origindl_b200.profile_case checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
 
 Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
 device, launches the kernel `--iters` times after one warm-up launch and prints the CUDA-event time per launch.
@@ -36,13 +37,14 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear"])
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--layer", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--precision", default="3xtf32")
     ap.add_argument("--layout", default="nt")
     ap.add_argument("--iters", type=int, default=3)
@@ -50,7 +52,38 @@ def main():
     capi.init(0)
     torch.manual_seed(0)
     prec = capi.PRECISION_3XTF32 if a.precision == "3xtf32" else capi.PRECISION_TF32
-    if a.case == "gemm":
+    if a.case == "checkpoint":
+        import shutil
+        import tempfile
+        import time
+
+        import numpy as np
+
+        from .trainer import MLPTrainer
+
+        sizes = [a.n] * (a.layers + 1)
+        tr = MLPTrainer(sizes, 128)
+        tr.set_params(np.random.default_rng(0).standard_normal(tr.param_count).astype(np.float32) * 0.01)
+        x = torch.randn(128, a.n, device="cuda")
+        t = torch.randint(0, a.n, (128,), device="cuda", dtype=torch.int32)
+        tr.train_step(x, t)
+        torch.cuda.synchronize()
+        d = tempfile.mkdtemp(prefix="odl_ckpt_")
+        nbytes = 3 * 4 * tr.param_count  # parameters + both Adam moments
+        t0 = time.perf_counter()
+        tr.save_checkpoint(d + "/run.ckpt", epoch=1, step=1, loss=float(tr.loss_tensor()))
+        t1 = time.perf_counter()
+        tr2 = MLPTrainer(sizes, 128)
+        t2 = time.perf_counter()
+        tr2.load_checkpoint(d + "/run.ckpt")
+        torch.cuda.synchronize()
+        t3 = time.perf_counter()
+        same = bool(np.array_equal(tr.get_params(), tr2.get_params()))
+        shutil.rmtree(d)
+        print(f"checkpoint {len(sizes) - 1} x {a.n}^2 ({tr.param_count / 1e6:.1f} M parameters, {nbytes / 1e9:.2f} GB with Adam state): "
+              f"save {t1 - t0:.3f} s ({nbytes / (t1 - t0) / 1e9:.2f} GB/s), load {t3 - t2:.3f} s ({nbytes / (t3 - t2) / 1e9:.2f} GB/s), "
+              f"parameters identical after reload: {same}")
+    elif a.case == "gemm":
         n = a.n
         ta, tb = {"nt": (False, True), "nn": (False, False), "tn": (True, False)}[a.layout]
         A, B = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")

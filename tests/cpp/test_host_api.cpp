@@ -3,6 +3,8 @@
 // tests/unit_test/operator/test_{matmul,linear,relu,softmax_cross_entropy,conv2d,conv2d_transpose_output}.cpp,
 // tests/unit_test/optim/test_{adam,weight_decay}.cpp and tests/unit_test/autograd/test_linear_regression.cpp of the
 // reference, plus the cases the reference cannot run (LinearOp backward, fused MLP training, the memory pool).
+#include <unistd.h>
+
 #include <cmath>
 #include <cstdio>
 #include <functional>
@@ -256,6 +258,170 @@ static void mlp_training()
         EXPECT_TRUE(!out.impl()->creator);
     }
 }
+// ---- state dict, .odl files, checkpoints (tests/unit_test/io/test_checkpoint.cpp: SaveAndLoadCheckpoint,
+//      SaveAndLoadModelStateDict, OptimizerStateDict) plus what the reference cannot do: resume on the same trajectory
+static std::string g_golden_dir;  // tests/golden of this repository (argv[1]); empty = skip the fixture cases
+
+static float train_steps(nn::MLP &model, Optimizer &opt, const Tensor &x, const Tensor &t, int n)
+{
+    float last = 0.f;
+    for (int s = 0; s < n; ++s)
+    {
+        auto loss = F::softmax_cross_entropy(model(x), t);
+        last      = loss.item<float>();
+        opt.zero_grad();
+        loss.backward();
+        opt.step();
+    }
+    return last;
+}
+
+static void checkpoint_cases()
+{
+    namespace fs          = std::filesystem;
+    const std::string dir = (fs::temp_directory_path() / ("odl_host_test_" + std::to_string((long long)::getpid()))).string();
+    fs::create_directories(dir);
+    std::mt19937 gen(5);
+    std::normal_distribution<float> nd;
+    std::vector<float> xv(16 * 4);
+    for (auto &v : xv)
+        v = nd(gen);
+    std::vector<int32_t> tv(16);
+    for (size_t i = 0; i < tv.size(); ++i)
+        tv[i] = xv[i * 4] > 0;
+    auto x = T(xv, {16, 4});
+    Tensor t(tv, Shape{16}, dtype(DataType::kInt32));
+
+    // SaveAndLoadModelStateDict
+    {
+        nn::MLP model({3, 5, 2});
+        StateDict sd = model.state_dict();
+        EXPECT_TRUE(sd.size() == 4);
+        save(sd, dir + "/test_model.odl");
+        EXPECT_TRUE(fs::exists(dir + "/test_model.odl"));
+        StateDict back = load(dir + "/test_model.odl");
+        EXPECT_TRUE(back.size() == sd.size());
+        for (auto &kv : sd)
+        {
+            EXPECT_TRUE(back.count(kv.first) && back.at(kv.first).shape() == kv.second.shape());
+            EXPECT_TRUE(back.at(kv.first).to_vector<float>() == kv.second.to_vector<float>());
+        }
+        nn::MLP fresh({3, 5, 2});
+        fresh.load_state_dict(back);
+        auto probe = T({0.5f, -1.0f, 2.0f}, {1, 3});
+        EXPECT_TRUE(fresh(probe).to_vector<float>() == model(probe).to_vector<float>());
+        EXPECT_TRUE(fresh(probe).shape() == (Shape{1, 2}));
+        nn::MLP via_file({3, 5, 2});
+        via_file.load(dir + "/test_model.odl");
+        EXPECT_TRUE(via_file(probe).to_vector<float>() == model(probe).to_vector<float>());
+        // strictness (src/nn/module.cpp:130-168)
+        StateDict missing = back;
+        missing.erase("layer_1.bias");
+        EXPECT_THROW(fresh.load_state_dict(missing));
+        fresh.load_state_dict(missing, false);
+        StateDict extra = back;
+        extra["unknown"] = Tensor::zeros(Shape{1});
+        EXPECT_THROW(fresh.load_state_dict(extra));
+        StateDict wrong = back;
+        wrong["layer_0.weight"] = Tensor::zeros(Shape{5, 3});
+        EXPECT_THROW(fresh.load_state_dict(wrong, false));
+        EXPECT_THROW(load(dir + "/no_such_file.odl"));
+        {
+            std::ofstream bad(dir + "/bad.odl", std::ios::binary);
+            bad << "not an odl file";
+        }
+        EXPECT_THROW(load(dir + "/bad.odl"));
+    }
+    // OptimizerStateDict
+    {
+        nn::MLP model({2, 4, 1});
+        Adam optimizer(model, 0.01f, 0.9f, 0.999f, 1e-8f);
+        auto st = optimizer.state_dict();
+        EXPECT_TRUE(st.count("lr") && st.count("beta1") && st.count("beta2") && st.count("eps"));
+        EXPECT_TRUE(std::any_cast<float>(st.at("lr")) == 0.01f && std::any_cast<float>(st.at("beta1")) == 0.9f);
+        EXPECT_TRUE(std::any_cast<float>(st.at("beta2")) == 0.999f && std::any_cast<float>(st.at("eps")) == 1e-8f);
+        EXPECT_TRUE(std::any_cast<StateDict>(st.at("m_buffers")).empty());  // no step taken yet
+    }
+    // SaveAndLoadCheckpoint, and resuming: Adam moments and step counts travel, so the run continues bit for bit
+    {
+        nn::MLP model({4, 8, 2});
+        Adam optimizer(model, 0.001f);
+        train_steps(model, optimizer, x, t, 5);
+        Checkpoint ck;
+        ck.model_state_dict             = model.state_dict();
+        ck.optimizer_state_dict["adam"] = optimizer.state_dict();
+        ck.epoch                        = 5;
+        ck.step                         = 100;
+        ck.loss                         = 0.5f;
+        ck.optimizer_type               = "Adam";
+        ck.optimizer_config["lr"]       = 0.001f;
+        ck.optimizer_config["beta1"]    = 0.9f;
+        ck.optimizer_config["beta2"]    = 0.999f;
+        ck.optimizer_config["eps"]      = 1e-8f;
+        const std::string path          = dir + "/test_checkpoint.ckpt";
+        save(ck, path);
+        EXPECT_TRUE(fs::exists(dir + "/test_checkpoint") && fs::exists(dir + "/test_checkpoint/model.odl"));
+        EXPECT_TRUE(fs::exists(dir + "/test_checkpoint/metadata.json") && fs::exists(dir + "/test_checkpoint/optimizer.odl"));
+        Checkpoint back = load_checkpoint(path);
+        EXPECT_TRUE(back.epoch == 5 && back.step == 100 && back.loss == 0.5f && back.optimizer_type == "Adam");
+        EXPECT_NEAR(back.optimizer_config.at("lr"), 0.001f, 1e-9f);
+        EXPECT_NEAR(back.optimizer_config.at("beta1"), 0.9f, 1e-7f);
+        EXPECT_NEAR(back.optimizer_config.at("beta2"), 0.999f, 1e-7f);
+        EXPECT_NEAR(back.optimizer_config.at("eps"), 1e-8f, 1e-14f);
+        EXPECT_TRUE(back.model_state_dict.size() == ck.model_state_dict.size());
+        const float next_a = train_steps(model, optimizer, x, t, 4);
+
+        nn::MLP resumed({4, 8, 2});
+        resumed.load_state_dict(back.model_state_dict);
+        Adam optimizer_b(resumed, 0.5f);  // configuration comes from the checkpoint
+        EXPECT_TRUE(back.optimizer_state_dict.count("adam") == 1);
+        optimizer_b.load_state_dict(back.optimizer_state_dict.at("adam"));
+        auto steps = std::any_cast<std::unordered_map<std::string, int>>(optimizer_b.state_dict().at("step_counts"));
+        EXPECT_TRUE(steps.size() == 4 && steps.at("step_layer_0.weight") == 5);
+        const float next_b = train_steps(resumed, optimizer_b, x, t, 4);
+        EXPECT_TRUE(next_a == next_b);
+        for (auto &kv : model.state_dict())
+            EXPECT_TRUE(resumed.state_dict().at(kv.first).to_vector<float>() == kv.second.to_vector<float>());
+        EXPECT_THROW(load_checkpoint(dir + "/absent.ckpt"));
+    }
+    // SGD momentum buffers through the same path
+    {
+        nn::MLP model({4, 8, 2});
+        SGD optimizer(model, 0.05f, 0.9f);
+        train_steps(model, optimizer, x, t, 3);
+        Checkpoint ck;
+        ck.model_state_dict            = model.state_dict();
+        ck.optimizer_state_dict["sgd"] = optimizer.state_dict();
+        ck.optimizer_type              = "SGD";
+        ck.optimizer_config["lr"]      = 0.05f;
+        save(ck, dir + "/sgd.ckpt");
+        const float next_a = train_steps(model, optimizer, x, t, 3);
+        Checkpoint back    = load_checkpoint(dir + "/sgd.ckpt");
+        nn::MLP resumed({4, 8, 2});
+        resumed.load_state_dict(back.model_state_dict);
+        SGD optimizer_b(resumed, 0.05f, 0.9f);
+        optimizer_b.load_state_dict(back.optimizer_state_dict.at("sgd"));
+        EXPECT_TRUE(train_steps(resumed, optimizer_b, x, t, 3) == next_a);
+    }
+    // files written by the unmodified reference (tests/golden/make_odl_fixtures.py)
+    if (!g_golden_dir.empty())
+    {
+        StateDict sd = load(g_golden_dir + "/ref_state.odl");
+        EXPECT_TRUE(sd.size() == 4 && sd.at("conv.weight").shape() == (Shape{2, 3, 2, 2}) && sd.at("head.scale").shape() == (Shape{7}));
+        EXPECT_TRUE(sd.at("layer_0.weight").shape() == (Shape{3, 5}) && sd.at("layer_0.bias").shape() == (Shape{1, 5}));
+        Checkpoint ck = load_checkpoint(g_golden_dir + "/ref_checkpoint.ckpt");
+        EXPECT_TRUE(ck.epoch == 5 && ck.step == 100 && ck.loss == 0.5f && ck.optimizer_type == "Adam");
+        EXPECT_TRUE(ck.optimizer_state_dict.empty());  // the reference writes no optimizer.odl
+        nn::MLP model({4, 8, 2});
+        model.load_state_dict(ck.model_state_dict);
+        EXPECT_TRUE(model(x).shape() == (Shape{16, 2}));
+        // saved again by this layer, the file holds the same records (sorted by name here, hash order there)
+        save(ck.model_state_dict, dir + "/resaved.odl");
+        EXPECT_TRUE(fs::file_size(dir + "/resaved.odl") == fs::file_size(g_golden_dir + "/ref_checkpoint/model.odl"));
+    }
+    fs::remove_all(dir);
+}
+
 // ---- memory pool: bins and reuse (src/mat/origin/memory/memory_pool.cpp)
 static void memory_pool()
 {
@@ -273,8 +439,10 @@ static void memory_pool()
     EXPECT_TRUE(b.data_ptr<float>() == p1 && pool.hits() > hits);  // the freed block was handed out again
 }
 
-int main()
+int main(int argc, char **argv)
 {
+    if (argc > 1)
+        g_golden_dir = argv[1];
     try
     {
         init(0);
@@ -290,7 +458,7 @@ int main()
         {"relu", relu_cases},                 {"softmax_cross_entropy", softmax_ce_cases},
         {"conv2d", conv2d_cases},             {"weight_decay_and_adam", weight_decay_and_adam},
         {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
-        {"memory_pool", memory_pool}};
+        {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases}};
     for (auto &t : tests)
     {
         const int before = g_failed;

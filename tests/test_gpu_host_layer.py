@@ -16,7 +16,8 @@ def test_cpp_host_layer_program():
         build.build()
     if not exe.exists():
         exe = build.build_host_tests()
-    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    golden = Path(__file__).resolve().parent / "golden"
+    r = subprocess.run([str(exe), str(golden)], capture_output=True, text=True, timeout=600)
     print(r.stdout)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert "0 failed" in r.stdout
