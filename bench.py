@@ -240,41 +240,27 @@ def run_ours(args):
     ms_per_step = ms_total / args.steps
     value = world * PER_GPU_BATCH * args.steps / (ms_total / 1e3)
 
-    # ---- end to end: pinned host batches -> H2D on a copy stream (double buffered) -> step -> loss D2H
-    hx = [torch.randn((PER_GPU_BATCH, SIZES[0])).pin_memory() for _ in range(n_batches)]
-    ht = [torch.randint(0, SIZES[-1], (PER_GPU_BATCH,), dtype=torch.int32).pin_memory() for _ in range(n_batches)]
-    dbuf_x = [torch.empty((PER_GPU_BATCH, SIZES[0]), device=dev) for _ in range(2)]
-    dbuf_t = [torch.empty((PER_GPU_BATCH,), device=dev, dtype=torch.int32) for _ in range(2)]
-    copy_stream = torch.cuda.Stream()
+    # ---- end to end through the public API: host data set -> DataLoader (staged mode: page-locked data set, a worker
+    #      thread issuing the H2D copy of the following batches on a copy stream) -> train_step -> loss D2H
+    from origindl_b200.loader import DataLoader
+
+    e2e_batches = 4
+    hx = torch.randn((e2e_batches * PER_GPU_BATCH, SIZES[0]), generator=torch.Generator().manual_seed(2000 + rank))
+    ht = torch.randint(0, SIZES[-1], (e2e_batches * PER_GPU_BATCH,), generator=torch.Generator().manual_seed(3000 + rank))
+    loader = DataLoader(hx.numpy(), ht.numpy(), PER_GPU_BATCH, shuffle=False, resident=False, device=local)
     host_loss = torch.empty((1,), dtype=torch.float32).pin_memory()
-    compute = torch.cuda.current_stream()
-
-    consumed = [None, None]  # per slot: event recorded after the step that last read the slot
-
-    def stage(step):
-        slot = step % 2
-        with torch.cuda.stream(copy_stream):
-            if consumed[slot] is not None:
-                copy_stream.wait_event(consumed[slot])  # do not overwrite a batch that is still being read
-            dbuf_x[slot].copy_(hx[step % n_batches], non_blocking=True)
-            dbuf_t[slot].copy_(ht[step % n_batches], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(copy_stream)
-        return ev
 
     def e2e_loop(n_steps):
-        ev = stage(0)
-        for s in range(n_steps):
-            nxt = stage(s + 1) if s + 1 < n_steps else None  # next batch crosses PCIe while this step computes
-            compute.wait_event(ev)
-            lv = tr.train_step(dbuf_x[s % 2], dbuf_t[s % 2])
-            done = torch.cuda.Event()
-            done.record(compute)
-            consumed[s % 2] = done
+        h2d0 = loader.h2d_bytes
+        for _ in range(n_steps):
+            if not loader.has_next():
+                loader.reset()  # epoch boundary: the worker is already staging the next epoch
+            bx, bt = loader.next()
+            lv = tr.train_step(bx, bt)
+            loader.release()
             host_loss.copy_(lv.reshape(1), non_blocking=True)
-            ev = nxt
         torch.cuda.synchronize()
-        return float(host_loss.item())
+        return float(host_loss.item()), loader.h2d_bytes - h2d0
 
     e2e_loop(min(2, args.warmup))
     barrier()
@@ -284,9 +270,10 @@ def run_ours(args):
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
     e2e_value = world * PER_GPU_BATCH * args.steps / (e2e_ms / 1e3)
-    h2d = PER_GPU_BATCH * SIZES[0] * 4 + PER_GPU_BATCH * 4
+    h2d = PER_GPU_BATCH * SIZES[0] * 4 + PER_GPU_BATCH * 8  # fp32 inputs + int64 labels of one batch
+    loader.close()
     tr.close()
-    del xs, dbuf_x, hx
+    del xs, hx, loader
     torch.cuda.empty_cache()
 
     line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,

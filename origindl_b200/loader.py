@@ -9,7 +9,8 @@ src/data/dataloader.cpp:11-146):
 Semantics kept: samples are flattened to `features` values; batches follow the index list in order; the last batch of
 an epoch is short unless `drop_last`; next() past the end raises; integer labels come out as int64.  The reference
 seeds its shuffle from std::random_device (dataloader.cpp:29-31), so its order is not reproducible; here `seed` makes
-it so (None = from the OS, like the reference).
+it so (None = from the OS, like the reference): epoch e uses the e-th permutation drawn from that generator, in
+either mode.
 
 What differs is where the work happens.  The reference assembles each batch on the host one sample at a time and the
 training loop copies it to the device.  Here there are two modes:
@@ -17,10 +18,11 @@ training loop copies it to the device.  Here there are two modes:
 * resident (default when the data set fits `resident_limit_bytes`): inputs and labels are uploaded ONCE and stay in
   HBM (180 GB per B200 holds every data set of the reference's examples many times over); a batch is one row-gather
   kernel (odl_gather_rows) driven by the shuffled indices, which are uploaded once per epoch.
-* staged: the data set stays in host memory; a worker thread gathers the following batches into pinned staging
-  buffers (`depth` of them) and copies them with cudaMemcpyAsync on a copy stream while the current batch trains; the
-  compute stream waits on the copy's event, the worker on the event of the step that last read the buffer.  Without
-  shuffling, batches are contiguous row ranges and are copied straight from the (page-locked) data set.
+* staged: the data set stays in host memory; a worker thread gathers the following batches -- across epoch boundaries
+  -- into pinned staging buffers (`depth` of them) and copies them with cudaMemcpyAsync on a copy stream while the
+  current batch trains; the compute stream waits on the copy's event, the worker on the event of the step that last
+  read the buffer.  Without shuffling, batches are contiguous row ranges and are copied straight from the
+  (page-locked) data set.
 """
 from __future__ import annotations
 
@@ -49,26 +51,28 @@ class DataLoader:
         self.features = int(self.host_x.shape[1])
         self.batch_size, self.shuffle, self.drop_last = int(batch_size), bool(shuffle), bool(drop_last)
         self._rng = np.random.default_rng(seed)
+        self._orders, self._orders_lock, self._drawn = {}, threading.Lock(), 0
         capi.init(device)
         self.resident = (self.host_x.nbytes <= resident_limit_bytes) if resident is None else bool(resident)
-        self.h2d_bytes = 0  # bytes copied host -> device so far (the benchmark reports them per step)
+        self.h2d_bytes = 0  # bytes copied host -> device so far (a benchmark reports them per step)
+        self.epoch, self.current = 0, 0
+        self.indices = self._order_of(0)
         if self.resident:
             self._dev_x = torch.from_numpy(self.host_x).cuda()
             self._dev_t = torch.from_numpy(self.host_t).cuda()
             self.h2d_bytes += self.host_x.nbytes + self.host_t.nbytes
+            self._upload_indices()
         else:
             self._device = device
             self._copy_stream = torch.cuda.Stream()
             self._slots = [self._Slot(self.batch_size, self.features) for _ in range(max(2, depth))]
-            self._worker = None
-            self._pending_release = None
+            self._worker, self._pending_release = None, None
+            self._pinned_x = None
             if not self.shuffle and self.host_x.nbytes <= pin_limit_bytes:
                 # sequential batches are contiguous row ranges: page-lock the data set itself and copy from it directly
                 self._pinned_x = torch.from_numpy(self.host_x).pin_memory()
                 self._pinned_t = torch.from_numpy(self.host_t).pin_memory()
-            else:
-                self._pinned_x = None
-        self.reset()
+            self._start_worker()
 
     class _Slot:
         def __init__(self, batch, features):
@@ -81,18 +85,22 @@ class DataLoader:
             self.used = False
 
     # ---- index bookkeeping: DataLoader::reset_indices / has_next / next (dataloader.cpp:17-36, 141-146)
-    def reset(self) -> None:
-        if not self.resident:
-            self._stop_worker()
-        self.indices = np.arange(self.n, dtype=np.int64)
-        if self.shuffle:
-            self._rng.shuffle(self.indices)
-        self.current = 0
-        if self.resident:
-            self._dev_idx = torch.from_numpy(self.indices).cuda()
-            self.h2d_bytes += self.indices.nbytes
-        else:
-            self._start_worker()
+    def _order_of(self, epoch: int) -> np.ndarray:
+        """Index list of an epoch; permutations are drawn from the generator strictly in epoch order."""
+        with self._orders_lock:
+            while self._drawn <= epoch:
+                order = np.arange(self.n, dtype=np.int64)
+                if self.shuffle:
+                    self._rng.shuffle(order)
+                self._orders[self._drawn] = order
+                self._drawn += 1
+            for old in [e for e in self._orders if e < epoch - 1]:
+                del self._orders[old]
+            return self._orders[epoch]
+
+    def _upload_indices(self) -> None:
+        self._dev_idx = torch.from_numpy(self.indices).cuda()
+        self.h2d_bytes += self.indices.nbytes
 
     def _rows_at(self, cursor: int) -> int:
         rows = min(self.batch_size, self.n - cursor)
@@ -105,16 +113,31 @@ class DataLoader:
         return self.n // self.batch_size if self.drop_last else -(-self.n // self.batch_size)
 
     def __iter__(self):
-        self.reset()
+        if self.current:
+            self.reset()
         while self.has_next():
             yield self.next()
+
+    def reset(self) -> None:
+        """Start the next epoch (a new permutation when shuffling).  At an epoch boundary the staged mode carries on
+        without a pause: the worker has already begun staging the next epoch's first batches."""
+        finished = not self.has_next()
+        if not self.resident and not finished:
+            self._stop_worker()  # batches of the abandoned epoch are staged or in flight: drop them
+        self.epoch += 1
+        self.current = 0
+        self.indices = self._order_of(self.epoch)
+        if self.resident:
+            self._upload_indices()
+        elif not finished:
+            self._start_worker()
 
     # ---- staged mode: a worker thread fills pinned buffers and starts their copies ahead of the training loop
     def _start_worker(self) -> None:
         self._free, self._ready, self._stop = queue.Queue(), queue.Queue(), False
         for slot in self._slots:
             self._free.put(slot)
-        self._worker = threading.Thread(target=self._stage_epoch, args=(self.indices,), daemon=True)
+        self._worker = threading.Thread(target=self._stage_forever, args=(self.epoch,), daemon=True)
         self._worker.start()
 
     def _stop_worker(self) -> None:
@@ -123,38 +146,39 @@ class DataLoader:
         self._stop = True
         self._free.put(None)
         self._worker.join()
-        self._worker = None
-        self._pending_release = None
+        self._worker, self._pending_release = None, None
         torch.cuda.synchronize()  # nothing still reads or writes the slots
 
-    def _stage_epoch(self, indices: np.ndarray) -> None:
+    def _stage_forever(self, epoch: int) -> None:
         torch.cuda.set_device(self._device)
-        cursor = 0
         try:
             while not self._stop:
-                rows = self._rows_at(cursor)
-                if rows == 0:
-                    break
-                slot = self._free.get()
-                if slot is None or self._stop:
-                    break
-                if slot.used:
-                    slot.consumed.synchronize()
-                if self._pinned_x is not None:
-                    src_x, src_t = self._pinned_x[cursor:cursor + rows], self._pinned_t[cursor:cursor + rows]
-                else:
-                    ids = indices[cursor:cursor + rows]
-                    np.take(self.host_x, ids, axis=0, out=slot.pin_x.numpy()[:rows])
-                    np.take(self.host_t, ids, out=slot.pin_t.numpy()[:rows])
-                    src_x, src_t = slot.pin_x[:rows], slot.pin_t[:rows]
-                with torch.cuda.stream(self._copy_stream):
-                    slot.dev_x[:rows].copy_(src_x, non_blocking=True)
-                    slot.dev_t[:rows].copy_(src_t, non_blocking=True)
-                    slot.ready.record(self._copy_stream)
-                self.h2d_bytes += rows * (self.features * 4 + 8)
-                self._ready.put((slot, rows))
-                cursor += rows
-        except BaseException as e:  # surface the failure in next() instead of hanging it
+                indices, cursor = self._order_of(epoch), 0
+                while True:
+                    rows = self._rows_at(cursor)
+                    if rows == 0:
+                        break
+                    slot = self._free.get()
+                    if slot is None or self._stop:
+                        return
+                    if slot.used:
+                        slot.consumed.synchronize()
+                    if self._pinned_x is not None:
+                        src_x, src_t = self._pinned_x[cursor:cursor + rows], self._pinned_t[cursor:cursor + rows]
+                    else:
+                        ids = indices[cursor:cursor + rows]
+                        np.take(self.host_x, ids, axis=0, out=slot.pin_x.numpy()[:rows])
+                        np.take(self.host_t, ids, out=slot.pin_t.numpy()[:rows])
+                        src_x, src_t = slot.pin_x[:rows], slot.pin_t[:rows]
+                    with torch.cuda.stream(self._copy_stream):
+                        slot.dev_x[:rows].copy_(src_x, non_blocking=True)
+                        slot.dev_t[:rows].copy_(src_t, non_blocking=True)
+                        slot.ready.record(self._copy_stream)
+                    self.h2d_bytes += rows * (self.features * 4 + 8)
+                    self._ready.put((epoch, slot, rows))
+                    cursor += rows
+                epoch += 1
+        except BaseException as e:  # surface the failure in next() instead of leaving it waiting
             self._ready.put(e)
 
     def next(self):
@@ -174,8 +198,8 @@ class DataLoader:
         item = self._ready.get(timeout=600)
         if isinstance(item, BaseException):
             raise item
-        slot, got = item
-        assert got == rows
+        epoch, slot, got = item
+        assert epoch == self.epoch and got == rows, (epoch, self.epoch, got, rows)
         torch.cuda.current_stream().wait_event(slot.ready)
         self.current += rows
         self._pending_release = slot

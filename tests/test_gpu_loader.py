@@ -107,6 +107,21 @@ def test_shuffled_epochs_are_permutations_and_reproducible(capi, resident):
 
 
 @pytest.mark.parametrize("resident", [True, False])
+def test_reset_in_the_middle_of_an_epoch_starts_a_full_new_epoch(capi, resident):
+    from origindl_b200.loader import DataLoader
+
+    x, t = dataset(150, 8)
+    x[:, 0] = np.arange(150)
+    ld = DataLoader(x, t, 40, shuffle=True, seed=9, resident=resident)
+    first = ld.next()[0][:, 0].cpu().numpy().copy()
+    ld.reset()  # abandons the 110 samples not yet delivered
+    ids = np.concatenate([bx[:, 0].cpu().numpy() for bx, _ in ld]).astype(np.int64)
+    assert ids.size == 150 and np.array_equal(np.sort(ids), np.arange(150))
+    assert not np.array_equal(ids[:40], first)
+    ld.close()
+
+
+@pytest.mark.parametrize("resident", [True, False])
 def test_training_from_the_loader_equals_direct_feeding(capi, resident):
     from origindl_b200.loader import DataLoader
     from origindl_b200.trainer import MLPTrainer
