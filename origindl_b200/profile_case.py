@@ -6,6 +6,7 @@
     python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
     python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
     python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
+    python -m origindl_b200.profile_case gather  --rows 65536 --cols 1024       (batch assembly from a resident data set)
     python -m origindl_b200.profile_case checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
 
 Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
@@ -37,7 +38,7 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint"])
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint", "gather"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -83,6 +84,16 @@ def main():
         print(f"checkpoint {len(sizes) - 1} x {a.n}^2 ({tr.param_count / 1e6:.1f} M parameters, {nbytes / 1e9:.2f} GB with Adam state): "
               f"save {t1 - t0:.3f} s ({nbytes / (t1 - t0) / 1e9:.2f} GB/s), load {t3 - t2:.3f} s ({nbytes / (t3 - t2) / 1e9:.2f} GB/s), "
               f"parameters identical after reload: {same}")
+    elif a.case == "gather":
+        n_src = 4 * a.rows
+        src = torch.randn(n_src, a.cols, device="cuda")
+        lab = torch.randint(0, 10, (n_src,), device="cuda")
+        idx = torch.randperm(n_src, device="cuda")[:a.rows].contiguous()
+        dst, dl = torch.empty(a.rows, a.cols, device="cuda"), torch.empty(a.rows, dtype=torch.int64, device="cuda")
+        ms = timed(lambda: capi.call("odl_gather_rows", src.data_ptr(), a.cols, n_src, idx.data_ptr(), a.rows, a.cols,
+                                     dst.data_ptr(), a.cols, lab.data_ptr(), dl.data_ptr(), capi.stream_handle()), a.iters)
+        print(f"gather {a.rows} of {n_src} rows x {a.cols}: {ms:.4f} ms/launch, {8 * a.rows * a.cols / ms / 1e6:.1f} GB/s "
+              f"(4 B read + 4 B written per element)")
     elif a.case == "gemm":
         n = a.n
         ta, tb = {"nt": (False, True), "nn": (False, False), "tn": (True, False)}[a.layout]
