@@ -39,6 +39,11 @@ extern "C" {
 #define ODL_EPI_COLSUM 8  /* colsum[n] += v  (caller zeroes colsum)          */
 #define ODL_EPI_SMALL 16  /* also write D_small = tf32(v - trunc_tf32(v))    */
 
+/* activations fused after conv2d / BatchNorm */
+#define ODL_ACT_NONE 0
+#define ODL_ACT_RELU 1
+#define ODL_ACT_SILU 2
+
 /* weight layouts of the Linear entry points */
 #define ODL_W_OUT_IN 0 /* W is [out, in]: functional::custom_linear / LinearOp (include/origin/operators/custom/linear.h:13-15) */
 #define ODL_W_IN_OUT 1 /* W is {in, out}: nn::Linear (src/nn/layers/linear.cpp:39-48)                                       */
@@ -194,16 +199,53 @@ int odl_im2col(const float *x, float *col, int64_t N, int64_t C, int64_t H, int6
  * that needs no atomics. */
 int odl_col2im(const float *col, float *x, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int stride, int pad,
                void *stream);
-/* y[N,OC,OH,OW] = conv2d(x, w[OC,C,KH,KW]) + b, optional fused ReLU.  Replaces origin::cuda::conv2d (cuda_ops.cuh:363;
- * src/mat/origin/cuda/conv/conv2d.cu:563-678): im2col, one GEMM whose epilogue adds the bias and writes NCHW directly. */
+/* y[N,OC,OH,OW] = act(conv2d(x, w[OC,C,KH,KW]) + b), act = ODL_ACT_NONE / ODL_ACT_RELU / ODL_ACT_SILU.  Replaces
+ * origin::cuda::conv2d (cuda_ops.cuh:363; src/mat/origin/cuda/conv/conv2d.cu:563-678): im2col, one GEMM whose epilogue
+ * adds the bias, applies the activation and writes NCHW directly. */
 int odl_conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H,
-                       int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int relu, int precision, void *stream);
+                       int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int act, int precision, void *stream);
+/* The inference block conv -> BatchNorm2d (evaluation mode) -> ReLU / SiLU of the reference's CNN examples
+ * (tests/example/mnist/conv_mnist.cpp; the YOLOv5 Conv block) as ONE GEMM: y = act(scale[oc] * conv2d(x, w) + shift[oc])
+ * with scale / shift from odl_batch_norm_fold.  Replaces origin::cuda::conv2d + origin::cuda::batch_norm
+ * (src/mat/origin/cuda/normalization/batch_norm.cu) + relu / silu, i.e. three passes over the activation. */
+int odl_conv2d_bn_act_forward(const float *x, const float *w, const float *scale, const float *shift, float *y, int64_t N,
+                              int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int act,
+                              int precision, void *stream);
 /* gx, gw, gb for upstream gy[N,OC,OH,OW]; replaces origin::cuda::conv2d_backward (cuda_ops.cuh:376; conv2d.cu:680-765).
  * gy_layout 0: gy is permuted to [N*OH*OW, OC] (the gradient of the forward pass); 1: the NCHW buffer is
  * reinterpreted as [N*OH*OW, OC] exactly as the reference does (conv2d.cu:714).  gx, gw, gb may each be NULL. */
 int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N,
                         int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int gy_layout,
                         int precision, void *stream);
+
+/* ---- BatchNorm (+ activation), SiLU ---------------------------------------------------------------------------------- */
+
+/* y = act(gamma[c] * (x - mean[c]) / sqrt(var[c] + eps) + beta[c]) over x[N, C, HW] (HW = H*W; HW = 1 is the {N, C}
+ * form of BatchNorm1d).  Replaces cpu/cuda::batch_norm_forward (src/mat/origin/cpu/normalization/batch_norm.cpp:20-236,
+ * src/mat/origin/cuda/normalization/batch_norm.cu) and the activation that follows it.
+ * training != 0: mean / var are the batch mean and BIASED variance, written to save_mean / save_var[C] (required);
+ *   when running_mean / running_var are given they are updated in place the way nn::BatchNorm2d does after the
+ *   operator (src/nn/layers/batch_norm2d.cpp:66-83): running = momentum * running + (1 - momentum) * batch.
+ * training == 0: mean / var are running_mean / running_var (required; copied to save_* when those are given).
+ * The reference also materialises x_norm for backward; this library does not (backward recomputes it). */
+int odl_batch_norm_forward(const float *x, const float *gamma, const float *beta, float *running_mean,
+                           float *running_var, int training, float eps, float momentum, int64_t N, int64_t C, int64_t HW,
+                           int act, float *y, float *save_mean, float *save_var, void *stream);
+/* With g = gy * act'(z), z the pre-activation: dbeta = sum g, dgamma = sum g * x_norm,
+ * gx = gamma / std * (g - mean(g) - x_norm * mean(g * x_norm)) -- cpu::batch_norm_backward (batch_norm.cpp:252-415),
+ * which the reference applies whatever the mode of the forward pass; after a training-mode forward it is the exact
+ * gradient (there the reference's own operator throws, src/operators/normalization/batch_norm.cpp:78-92). */
+int odl_batch_norm_backward(const float *gy, const float *x, const float *gamma, const float *beta, const float *save_mean,
+                            const float *save_var, float eps, int64_t N, int64_t C, int64_t HW, int act, float *gx,
+                            float *dgamma, float *dbeta, void *stream);
+/* scale = gamma / sqrt(var + eps), shift = beta + scale * (bias - mean) (bias may be NULL): evaluation-mode BatchNorm
+ * as a per-channel affine map for odl_conv2d_bn_act_forward.  No counterpart in the reference. */
+int odl_batch_norm_fold(const float *gamma, const float *beta, const float *mean, const float *var, const float *bias,
+                        float eps, int64_t C, float *scale, float *shift, void *stream);
+/* y = x / (1 + exp(-x)); gx = gy * (s + x * s * (1 - s)), s = 1 / (1 + exp(-x)).  Replaces cpu/cuda::silu and
+ * silu_backward (src/mat/origin/cpu/activation/silu.cpp:48-92). */
+int odl_silu_forward(const float *x, float *y, int64_t n, void *stream);
+int odl_silu_backward(const float *gy, const float *x, float *gx, int64_t n, void *stream);
 
 /* ---- MLP training state (nn::MLP + loss + autograd + optimizer, device-resident) ----------------------------- */
 

@@ -406,3 +406,113 @@ void oracle_conv2d_backward(const float *gy, const float *x, const float *w, flo
     }
     free(gyf);
 }
+
+/* ---- BatchNorm (2-D {N,C}: HW = 1; 4-D {N,C,H,W}: HW = H*W) and SiLU -----------------------------------------------
+ * Follows cpu::batch_norm_forward (src/mat/origin/cpu/normalization/batch_norm.cpp:20-236): training statistics are
+ * two sequential passes per channel (mean, then the mean of squared differences -- the BIASED variance); in
+ * evaluation mode mean/var are copies of the running statistics; x_norm = (x - mean) / sqrt(var + eps);
+ * y = gamma * x_norm + beta. */
+void oracle_batch_norm_forward(const float *x, const float *gamma, const float *beta, const float *running_mean,
+                               const float *running_var, int training, float eps, int64_t N, int64_t C, int64_t HW,
+                               float *y, float *mean, float *var, float *x_norm)
+{
+    for (int64_t c = 0; c < C; ++c)
+    {
+        if (training)
+        {
+            float sum = 0.0f;
+            for (int64_t n = 0; n < N; ++n)
+                for (int64_t i = 0; i < HW; ++i)
+                    sum += x[(n * C + c) * HW + i];
+            const float count = (float)(N * HW);
+            mean[c]           = sum / count;
+            float sq          = 0.0f;
+            for (int64_t n = 0; n < N; ++n)
+                for (int64_t i = 0; i < HW; ++i)
+                {
+                    const float d = x[(n * C + c) * HW + i] - mean[c];
+                    sq += d * d;
+                }
+            var[c] = sq / count;
+        }
+        else
+        {
+            mean[c] = running_mean[c];
+            var[c]  = running_var[c];
+        }
+    }
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t c = 0; c < C; ++c)
+        {
+            const float sd = sqrtf(var[c] + eps);
+            for (int64_t i = 0; i < HW; ++i)
+            {
+                const int64_t idx = (n * C + c) * HW + i;
+                const float xn    = (x[idx] - mean[c]) / sd;
+                if (x_norm)
+                    x_norm[idx] = xn;
+                y[idx] = gamma[c] * xn + beta[c];
+            }
+        }
+}
+
+/* cpu::batch_norm_backward (batch_norm.cpp:252-415): dbeta = sum gy, dgamma = sum gy * x_norm,
+ * gx = (gamma / std) * (gy - mean(gy) - x_norm * mean(gy * x_norm)), whatever the mode of the forward pass. */
+void oracle_batch_norm_backward(const float *gy, const float *gamma, const float *saved_var, const float *x_norm,
+                                float eps, int64_t N, int64_t C, int64_t HW, float *gx, float *dgamma, float *dbeta)
+{
+    for (int64_t c = 0; c < C; ++c)
+    {
+        float sum_gy = 0.0f, sum_gx = 0.0f;
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t i = 0; i < HW; ++i)
+            {
+                const int64_t idx = (n * C + c) * HW + i;
+                sum_gy += gy[idx];
+                sum_gx += gy[idx] * x_norm[idx];
+            }
+        const float count = (float)(N * HW);
+        const float mg = sum_gy / count, mgx = sum_gx / count;
+        const float sd = sqrtf(saved_var[c] + eps);
+        dgamma[c]      = sum_gx;
+        dbeta[c]       = sum_gy;
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t i = 0; i < HW; ++i)
+            {
+                const int64_t idx = (n * C + c) * HW + i;
+                gx[idx]           = (gamma[c] / sd) * (gy[idx] - mg - x_norm[idx] * mgx);
+            }
+    }
+}
+
+/* nn::BatchNorm2d::forward's update after a training step (src/nn/layers/batch_norm2d.cpp:66-83):
+ * running = momentum * running + (1 - momentum) * current  -- momentum weighs the OLD value, default 0.1. */
+void oracle_batch_norm_update_running(float *running_mean, float *running_var, const float *mean, const float *var,
+                                      float momentum, int64_t C)
+{
+    for (int64_t c = 0; c < C; ++c)
+    {
+        running_mean[c] = momentum * running_mean[c] + (1.0f - momentum) * mean[c];
+        running_var[c]  = momentum * running_var[c] + (1.0f - momentum) * var[c];
+    }
+}
+
+/* cpu::silu / cpu::silu_backward (src/mat/origin/cpu/activation/silu.cpp:48-92). */
+void oracle_silu_forward(const float *x, float *y, int64_t n)
+{
+    for (int64_t i = 0; i < n; ++i)
+    {
+        const float s = 1.0f / (1.0f + expf(-x[i]));
+        y[i]          = x[i] * s;
+    }
+}
+
+void oracle_silu_backward(const float *gy, const float *x, float *gx, int64_t n)
+{
+    for (int64_t i = 0; i < n; ++i)
+    {
+        const float v = x[i];
+        const float s = 1.0f / (1.0f + expf(-v));
+        gx[i]         = gy[i] * (s + v * s * (1.0f - s));
+    }
+}

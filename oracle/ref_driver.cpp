@@ -31,6 +31,7 @@
 #include "origin/core/tensor.h"
 #include "origin/io/checkpoint.h"
 #include "origin/io/model_io.h"
+#include "origin/nn/layers/batch_norm2d.h"
 #include "origin/nn/models/mlp.h"
 #include "origin/optim/adam.h"
 #include "origin/optim/hooks.h"
@@ -307,6 +308,88 @@ int odlref_optim_replay(float *p, const float *grads, int64_t n, int steps, int 
             optim->step();
         }
         dump(*lin.weight(), p);
+    });
+}
+
+// ---- BatchNorm (+ ReLU / SiLU) through functional::BatchNorm, functional::relu / silu and nn::BatchNorm2d
+//      (src/operators/normalization/batch_norm.cpp:18-140, src/operators/activation/silu.cpp, src/nn/layers/batch_norm2d.cpp)
+
+// x is {N,C} when HW == 1 and {N,C,H,W} with H*W = HW otherwise (H = HW, W = 1 is used: the arithmetic only depends
+// on H*W).  act: 0 none, 1 relu, 2 silu.  dy != NULL runs backward of sum(out * dy).  mean / var receive the batch
+// statistics the operator returns in training mode.  x, gamma and beta always require grad: without that the operator
+// takes its inference path and reports zeros as the batch statistics (batch_norm.cpp:55-63).
+int odlref_batch_norm_fwd_bwd(const float *x, const float *gamma, const float *beta, const float *running_mean,
+                              const float *running_var, int training, float eps, int64_t N, int64_t C, int64_t HW,
+                              int act, const float *dy, float *y, float *mean, float *var, float *gx, float *dgamma,
+                              float *dbeta)
+{
+    return guarded([&] {
+        const bool four = HW > 1;
+        Shape xs        = four ? Shape{(size_t)N, (size_t)C, (size_t)HW, 1} : Shape{(size_t)N, (size_t)C};
+        std::vector<float> xv(x, x + N * C * HW);
+        Tensor X(xv, xs, dtype(DataType::kFloat32).requires_grad(true));
+        auto G  = make(gamma, {(size_t)C}, true);
+        auto B  = make(beta, {(size_t)C}, true);
+        auto RM = make(running_mean, {(size_t)C}, false);
+        auto RV = make(running_var, {(size_t)C}, false);
+        auto op = std::make_shared<F::BatchNorm>(training != 0, eps, 0.1f, four ? 4 : 2);
+        auto outs = (*op)({X, G, B, RM, RV});
+        Tensor out = outs[0];
+        if (training && outs.size() >= 3)
+        {
+            dump(outs[1], mean);
+            dump(outs[2], var);
+        }
+        if (act == 1)
+            out = F::relu(out);
+        else if (act == 2)
+            out = F::silu(out);
+        dump(out, y);
+        if (dy)
+        {
+            std::vector<float> dv(dy, dy + N * C * HW);
+            Tensor DY(dv, xs, dtype(DataType::kFloat32));
+            auto L = F::sum(out * DY);
+            L.backward();
+            dump(X.grad(), gx);
+            dump(G.grad(), dgamma);
+            dump(B.grad(), dbeta);
+        }
+    });
+}
+
+// nn::BatchNorm2d: `steps` training-mode forwards over xs[steps][N,C,H*W] (updating the running statistics), then one
+// evaluation-mode forward of probe[N,C,H*W] -> y.
+int odlref_batch_norm2d_layer(const float *xs, int steps, const float *probe, int64_t N, int64_t C, int64_t HW, float eps,
+                              float momentum, float *y)
+{
+    return guarded([&] {
+        nn::BatchNorm2d bn((int)C, eps, momentum);
+        Shape s{(size_t)N, (size_t)C, (size_t)HW, 1};
+        bn.train();
+        for (int k = 0; k < steps; ++k)
+        {
+            std::vector<float> v(xs + (size_t)k * N * C * HW, xs + (size_t)(k + 1) * N * C * HW);
+            bn.forward(Tensor(v, s, dtype(DataType::kFloat32)));
+        }
+        bn.eval();
+        std::vector<float> pv(probe, probe + N * C * HW);
+        dump(bn.forward(Tensor(pv, s, dtype(DataType::kFloat32))), y);
+    });
+}
+
+int odlref_silu_fwd_bwd(const float *x, const float *dy, int64_t n, float *y, float *gx)
+{
+    return guarded([&] {
+        auto X   = make(x, {(size_t)n}, dy != nullptr);
+        auto out = F::silu(X);
+        dump(out, y);
+        if (dy)
+        {
+            auto L = F::sum(out * make(dy, {(size_t)n}, false));
+            L.backward();
+            dump(X.grad(), gx);
+        }
     });
 }
 

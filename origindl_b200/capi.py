@@ -18,6 +18,7 @@ PRECISION_3XTF32 = 0
 PRECISION_TF32 = 1
 EPI_BIAS, EPI_RELU, EPI_MASK, EPI_COLSUM, EPI_SMALL = 1, 2, 4, 8, 16
 W_OUT_IN, W_IN_OUT = 0, 1
+ACT_NONE, ACT_RELU, ACT_SILU = 0, 1, 2
 
 _lib = None
 
@@ -143,6 +144,13 @@ _MLP_SIGNATURES = {
     "odl_mlp_train_step": [_P, _P, _P, c_int, _P],
     "odl_mlp_grad_bucket": [_P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)],
     "odl_mlp_set_optimizer_state": [_P, _P, _P, c_int, _P],
+    "odl_batch_norm_forward": [_P, _P, _P, _P, _P, c_int, c_float, c_float, _I64, _I64, _I64, c_int, _P, _P, _P, _P],
+    "odl_batch_norm_backward": [_P, _P, _P, _P, _P, _P, c_float, _I64, _I64, _I64, c_int, _P, _P, _P, _P],
+    "odl_batch_norm_fold": [_P, _P, _P, _P, _P, c_float, _I64, _P, _P, _P],
+    "odl_silu_forward": [_P, _P, _I64, _P],
+    "odl_silu_backward": [_P, _P, _P, _I64, _P],
+    "odl_conv2d_bn_act_forward": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, _P],
     "odl_gather_rows": [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _P, _P, _P],
 }
 _SIGNATURES.update(_MLP_SIGNATURES)

@@ -182,7 +182,7 @@ size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t
 int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
                   int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
                   const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
-                  cudaStream_t stream, bool reset_arena, int ohw)
+                  cudaStream_t stream, bool reset_arena, int ohw, const float *scale)
 {
     if (!is_ready())
     {
@@ -206,7 +206,8 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
         return kInvalidArgument;
     }
     if (((flags & kEpiBias) && !bias) || ((flags & kEpiMask) && !mask_src) || ((flags & kEpiColsum) && !colsum) ||
-        ((flags & kEpiSmall) && !D_small))
+        ((flags & kEpiSmall) && !D_small) || ((flags & kEpiScale) && !scale) ||
+        ((flags & (kEpiScale | kEpiSilu)) && !(flags & kEpiNCHW)))
     {
         set_last_error("gemm: epilogue flag 0x%x set without its pointer", flags);
         return kInvalidArgument;
@@ -238,6 +239,7 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
     p.D       = D;
     p.D_small = D_small;
     p.bias    = bias;
+    p.scale   = scale;
     p.aux     = mask_src;
     p.colsum  = colsum;
     p.err     = device_error_flag();
@@ -509,6 +511,18 @@ int odl_conv2d_forward(const float *x, const float *w, const float *b, float *y,
                        int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int relu, int precision, void *stream)
 {
     return conv2d_forward(x, w, b, y, N, C, H, W, OC, KH, KW, stride, pad, relu, precision, ST(stream));
+}
+
+int odl_conv2d_bn_act_forward(const float *x, const float *w, const float *scale, const float *shift, float *y, int64_t N,
+                              int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int stride, int pad, int act,
+                              int precision, void *stream)
+{
+    if (!scale || !shift)
+    {
+        set_last_error("conv2d_bn_act_forward: scale and shift are required (see odl_batch_norm_fold)");
+        return kInvalidArgument;
+    }
+    return conv2d_forward(x, w, shift, y, N, C, H, W, OC, KH, KW, stride, pad, act, precision, ST(stream), scale);
 }
 
 int odl_conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N,

@@ -149,16 +149,16 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
 }
 
 int conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H, int64_t W,
-                   int64_t OC, int KH, int KW, int S, int P, int relu, int precision, cudaStream_t stream)
+                   int64_t OC, int KH, int KW, int S, int P, int act, int precision, cudaStream_t stream, const float *scale)
 {
     if (!is_ready())
     {
         set_last_error("odl_init has not been called");
         return kNotInitialized;
     }
-    if (!x || !w || !y || OC <= 0)
+    if (!x || !w || !y || OC <= 0 || act < 0 || act > 2)
     {
-        set_last_error("conv2d: null buffer");
+        set_last_error("conv2d: null buffer or unknown activation %d", act);
         return kInvalidArgument;
     }
     const int OH = conv_out_size(H, KH, S, P), OW = conv_out_size(W, KW, S, P);
@@ -187,11 +187,15 @@ int conv2d_forward(const float *x, const float *w, const float *b, float *y, int
     int flags = kEpiNCHW;
     if (b)
         flags |= kEpiBias;
-    if (relu)
+    if (act == 1)
         flags |= kEpiRelu;
+    if (act == 2)
+        flags |= kEpiSilu;
+    if (scale)
+        flags |= kEpiScale;
     // y_flat[rows, OC] = col[rows, ckk] . W[OC, ckk]^T, written straight into NCHW by the epilogue
     return gemm_dispatch(0, 1, rows, OC, ckk, col, col_s, ldcol, w, nullptr, ckk, y, nullptr, OC, b, nullptr, 0, nullptr, flags,
-                         precision, stream, false, OH * OW);
+                         precision, stream, false, OH * OW, scale);
 }
 
 int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N, int64_t C,

@@ -43,10 +43,14 @@ __device__ __forceinline__ void gemm_epilogue_store(const GemmParams &p, float (
                     if (n < p.N)
                     {
                         float v = acc[j];
+                        if (p.flags & kEpiScale)
+                            v = __fmul_rn(v, __ldg(p.scale + n));
                         if (p.flags & kEpiBias)
-                            v += __ldg(p.bias + n);
+                            v = __fadd_rn(v, __ldg(p.bias + n));
                         if (p.flags & kEpiRelu)
                             v = v > 0.f ? v : 0.f;
+                        if (p.flags & kEpiSilu)
+                            v = __fmul_rn(v, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))));
                         dimg[static_cast<size_t>(n) * p.ohw] = v;
                     }
                 }

@@ -33,6 +33,8 @@ enum EpiFlags : int
     kEpiSmall  = 16,
     kEpiNCHW   = 32,  // D is [M/ohw][N][ohw] (conv output): row m = img*ohw + r goes to D[(img*N + n)*ohw + r]
     kEpiAtomic = 64,  // split-K: partial tiles are added to a zeroed D with fp32 atomics (set by the launcher)
+    kEpiScale  = 128,  // v *= scale[n] before the bias (folded evaluation-mode BatchNorm); kEpiNCHW stores only
+    kEpiSilu   = 256,  // v = v / (1 + exp(-v)) after bias / ReLU; kEpiNCHW stores only
 };
 
 struct GemmParams
@@ -40,6 +42,7 @@ struct GemmParams
     float *D;
     float *D_small;
     const float *bias;
+    const float *scale;  // kEpiScale: per-column factor
     const float *aux;
     float *colsum;
     int *err;  // device int: non-zero once any CTA gave up on a wait

@@ -36,7 +36,7 @@ int split_launch(const float *src, int64_t ld_src, int rows, int cols, const flo
 int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, const float *A_small,
                   int64_t lda, const float *B, const float *B_small, int64_t ldb, float *D, float *D_small, int64_t ldd,
                   const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
-                  cudaStream_t stream, bool reset_arena, int ohw = 0);
+                  cudaStream_t stream, bool reset_arena, int ohw = 0, const float *scale = nullptr);
 
 int relu_forward_launch(const float *x, float *y, float *y_small, int64_t n, cudaStream_t s);
 int relu_backward_launch(const float *gy, const float *ref, float *gx, int64_t n, cudaStream_t s);
@@ -63,7 +63,8 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
                     const float *y, float *dx, float *dx_small, const float *dx_mask_src, float *dx_colsum, float *dw,
                     float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream);
 int conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H, int64_t W,
-                   int64_t OC, int KH, int KW, int S, int P, int relu, int precision, cudaStream_t stream);
+                   int64_t OC, int KH, int KW, int S, int P, int act, int precision, cudaStream_t stream,
+                   const float *scale = nullptr);
 int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, float *gw, float *gb, int64_t N, int64_t C,
                     int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int mode, int precision,
                     cudaStream_t stream);

@@ -5,6 +5,7 @@
 //   origin::Operator forward()/backward() include/origin/core/operator.h:12-125 (tape: src/core/tensor_impl.cpp:78-278)
 //   origin::functional::mat_mul, relu, custom_linear, softmax_cross_entropy, conv2d, sum, broadcast_to, sum_to
 //   origin::nn::Module, Linear, MLP       src/nn/module.cpp, src/nn/layers/linear.cpp, src/nn/models/mlp.cpp
+//   functional::batch_norm, silu; nn::BatchNorm2d   src/operators/normalization/batch_norm.cpp, src/nn/layers/batch_norm2d.cpp
 //   origin::Optimizer, SGD, Adam, WeightDecay   src/optim/*.cpp, include/origin/optim/hooks.h
 //   origin::MemoryPool                    src/mat/origin/memory/memory_pool.cpp:37-176 (size-binned caching allocator)
 //   origin::save / load / Checkpoint / load_checkpoint   src/io/model_io.cpp:114-273, src/io/checkpoint.cpp:15-226
@@ -726,6 +727,92 @@ class ReLU : public Operator  // src/operators/activation/relu.cpp:13-54
     }
 };
 
+class SiLU : public Operator  // src/operators/activation/silu.cpp
+{
+  public:
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 1)
+            throw std::runtime_error("SiLU operator requires exactly 1 input, but got " + std::to_string(xs.size()));
+        Tensor y = Tensor::empty(xs[0].shape());
+        odl_check(odl_silu_forward(xs[0].data_ptr<float>(), y.data_ptr<float>(), detail::i64(y.elements()), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        Tensor g = Tensor::empty(gys[0].shape());
+        odl_check(odl_silu_backward(gys[0].data_ptr<float>(), inputs_[0].data_ptr<float>(), g.data_ptr<float>(),
+                                    detail::i64(g.elements()), nullptr));
+        return {g};
+    }
+};
+
+// Inputs (x, gamma, beta, running_mean, running_var), x {N,C} (num_dims 2) or {N,C,H,W} (num_dims 4)
+// (src/operators/normalization/batch_norm.cpp:18-118).  Differences from the reference operator, all deliberate:
+// one output (the batch statistics are read with mean() / var()), so that backward also works after a TRAINING-mode
+// forward -- the reference returns three outputs there and its own backward then throws; no x_norm tensor is kept;
+// `act` fuses a ReLU / SiLU; `update_running` applies nn::BatchNorm2d's running-statistics rule inside the kernel.
+class BatchNorm : public Operator
+{
+  public:
+    BatchNorm(bool training, float eps, float momentum, int num_dims, int act = ODL_ACT_NONE, bool update_running = false)
+        : training_(training), eps_(eps), momentum_(momentum), num_dims_(num_dims), act_(act), update_(update_running)
+    {
+    }
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 5)
+            throw std::runtime_error("BatchNorm operator requires exactly 5 inputs (x, gamma, beta, running_mean, "
+                                     "running_var), but got " + std::to_string(xs.size()));
+        const Tensor &x = xs[0];
+        if (num_dims_ != 2 && num_dims_ != 4)
+            throw std::invalid_argument("batch_norm: num_dims must be 2 or 4, but got " + std::to_string(num_dims_));
+        if (x.ndim() != (size_t)num_dims_)
+            throw std::invalid_argument("batch_norm: x must have " + std::to_string(num_dims_) +
+                                        " dimensions, but got shape " + x.shape().to_string());
+        const size_t C = x.shape()[1];
+        for (int i = 1; i < 5; ++i)
+            if (xs[i].shape() != Shape{C})
+                throw std::invalid_argument("batch_norm: gamma, beta, running_mean, running_var must have shape (" +
+                                            std::to_string(C) + ")");
+        detail::need_f32(x, "batch_norm");
+        const int64_t hw = num_dims_ == 4 ? detail::i64(x.shape()[2] * x.shape()[3]) : 1;
+        Tensor y = Tensor::empty(x.shape());
+        mean_    = Tensor::empty(Shape{C});
+        var_     = Tensor::empty(Shape{C});
+        const bool pass_running = !training_ || update_;
+        odl_check(odl_batch_norm_forward(x.data_ptr<float>(), xs[1].data_ptr<float>(), xs[2].data_ptr<float>(),
+                                         pass_running ? xs[3].data_ptr<float>() : nullptr,
+                                         pass_running ? xs[4].data_ptr<float>() : nullptr, training_ ? 1 : 0, eps_, momentum_,
+                                         detail::i64(x.shape()[0]), detail::i64(C), hw, act_, y.data_ptr<float>(),
+                                         mean_.data_ptr<float>(), var_.data_ptr<float>(), nullptr));
+        return {y};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override
+    {
+        if (gys.size() != 1)
+            throw std::runtime_error("BatchNorm backward requires exactly 1 gradient, but got " + std::to_string(gys.size()));
+        const Tensor &x = inputs_[0];
+        const size_t C  = x.shape()[1];
+        const int64_t hw = num_dims_ == 4 ? detail::i64(x.shape()[2] * x.shape()[3]) : 1;
+        Tensor gx = Tensor::empty(x.shape()), dgamma = Tensor::empty(Shape{C}), dbeta = Tensor::empty(Shape{C});
+        odl_check(odl_batch_norm_backward(gys[0].data_ptr<float>(), x.data_ptr<float>(), inputs_[1].data_ptr<float>(),
+                                          inputs_[2].data_ptr<float>(), mean_.data_ptr<float>(), var_.data_ptr<float>(), eps_,
+                                          detail::i64(x.shape()[0]), detail::i64(C), hw, act_, gx.data_ptr<float>(),
+                                          dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), nullptr));
+        return {gx, dgamma, dbeta, Tensor(), Tensor()};
+    }
+    const Tensor &mean() const { return mean_; }  // statistics the last forward normalised with
+    const Tensor &var() const { return var_; }
+
+  private:
+    bool training_;
+    float eps_, momentum_;
+    int num_dims_, act_;
+    bool update_;
+    Tensor mean_, var_;
+};
+
 // y = relu?(x . op(W) + b) as ONE kernel; backward = dX, dW, db with the ReLU mask and the column sums fused.
 // w_layout ODL_W_OUT_IN is LinearOp / custom_linear (src/operators/custom/linear.cpp), whose backward the reference
 // leaves unimplemented; ODL_W_IN_OUT is nn::Linear's weight (src/nn/layers/linear.cpp).
@@ -879,6 +966,13 @@ class Conv2dOp : public Operator  // src/operators/conv/conv2d.cpp:14-89
 // ---- free functions with the reference's names
 inline Tensor mat_mul(const Tensor &x, const Tensor &w) { return std::make_shared<MatMul>()->call1({x, w}); }
 inline Tensor relu(const Tensor &x) { return std::make_shared<ReLU>()->call1({x}); }
+inline Tensor silu(const Tensor &x) { return std::make_shared<SiLU>()->call1({x}); }
+inline Tensor batch_norm(const Tensor &x, const Tensor &gamma, const Tensor &beta, const Tensor &running_mean,
+                         const Tensor &running_var, bool training, float eps = 1e-5f, float momentum = 0.1f,
+                         int num_dims = 4)
+{
+    return std::make_shared<BatchNorm>(training, eps, momentum, num_dims)->call1({x, gamma, beta, running_mean, running_var});
+}
 inline Tensor sum(const Tensor &x) { return std::make_shared<Sum>()->call1({x}); }
 inline Tensor broadcast_to(const Tensor &x, const Shape &s) { return std::make_shared<BroadcastTo>(s)->call1({x}); }
 inline Tensor sum_to(const Tensor &x, const Shape &s)
@@ -990,12 +1084,22 @@ class Module
                     throw std::runtime_error("Unexpected parameter '" + kv.first + "' in state_dict (strict mode)");
     }
     void load(const std::string &filepath, bool strict = true);  // origin::load + load_state_dict (module.cpp:214-218)
+    // training / evaluation mode, propagated to the sub-modules (include/origin/nn/module.h:131-143)
+    void train(bool mode = true)
+    {
+        training_ = mode;
+        for (auto &kv : modules_)
+            kv.second->train(mode);
+    }
+    void eval() { train(false); }
+    bool is_training() const { return training_; }
 
   protected:
     void register_parameter(const std::string &name, Parameter &p) { params_.emplace_back(name, &p); }
     void register_module(const std::string &name, std::unique_ptr<Module> m) { modules_.emplace_back(name, std::move(m)); }
     std::vector<std::pair<std::string, Parameter *>> params_;
     std::vector<std::pair<std::string, std::unique_ptr<Module>>> modules_;
+    bool training_ = true;
 };
 
 // weight {in, out} = randn * sqrt(1/in), bias {1, out} = 0 (src/nn/layers/linear.cpp:39-62).
@@ -1036,6 +1140,50 @@ class Linear : public Module
 };
 
 // Linear -> ReLU -> ... -> Linear, parameters named layer_i.weight / layer_i.bias (src/nn/models/mlp.cpp:11-61).
+// gamma = 1, beta = 0 (parameters "weight", "bias"), running_mean = 0, running_var = 1; in training mode the running
+// statistics follow running = momentum * running + (1 - momentum) * batch (src/nn/layers/batch_norm2d.cpp:12-83),
+// applied by the statistics kernel itself instead of four device-to-host copies.  `act` fuses the ReLU / SiLU that
+// follows the layer in the reference's CNN blocks.
+class BatchNorm2d : public Module
+{
+  public:
+    explicit BatchNorm2d(int num_features, float eps = 1e-5f, float momentum = 0.1f, int act = ODL_ACT_NONE)
+        : num_features_(num_features), eps_(eps), momentum_(momentum), act_(act)
+    {
+        if (num_features <= 0)
+            throw std::invalid_argument("BatchNorm2d: num_features must be positive, but got " + std::to_string(num_features));
+        const Shape s{(size_t)num_features};
+        gamma_        = Parameter(Tensor::ones(s, TensorOptions().requires_grad(true)));
+        beta_         = Parameter(Tensor::zeros(s, TensorOptions().requires_grad(true)));
+        running_mean_ = Tensor::zeros(s);
+        running_var_  = Tensor::ones(s);
+        register_parameter("weight", gamma_);
+        register_parameter("bias", beta_);
+    }
+    Tensor forward(const Tensor &input) override
+    {
+        if (input.ndim() != 4)
+            throw std::runtime_error("BatchNorm2d forward: input must be 4D (N, C, H, W), but got shape " +
+                                     input.shape().to_string());
+        if (input.shape()[1] != (size_t)num_features_)
+            throw std::runtime_error("BatchNorm2d forward: input feature size " + std::to_string(input.shape()[1]) +
+                                     " does not match num_features " + std::to_string(num_features_));
+        auto op = std::make_shared<functional::BatchNorm>(is_training(), eps_, momentum_, 4, act_, is_training());
+        return op->call1({input, gamma_, beta_, running_mean_, running_var_});
+    }
+    Parameter *weight() { return &gamma_; }
+    Parameter *bias() { return &beta_; }
+    const Tensor &running_mean() const { return running_mean_; }
+    const Tensor &running_var() const { return running_var_; }
+
+  private:
+    int num_features_;
+    float eps_, momentum_;
+    int act_;
+    Parameter gamma_, beta_;
+    Tensor running_mean_, running_var_;
+};
+
 class MLP : public Module
 {
   public:

@@ -219,3 +219,75 @@ def conv2d_backward(gy, x, w, stride=1, pad=0, gy_layout=0, need_gb=True, precis
     capi.call("odl_conv2d_backward", _p(gy), _p(x), _p(w), _p(gx), _p(gw), _p(gb), N, C, H, W, OC, KH, KW, stride, pad,
               gy_layout, precision, _s())
     return gx, gw, gb
+
+
+# ---- BatchNorm (+ activation), SiLU, conv -> BatchNorm -> activation -------------------------------------------------
+def _bn_dims(x):
+    if x.dim() == 2:
+        return x.shape[0], x.shape[1], 1
+    if x.dim() == 4:
+        return x.shape[0], x.shape[1], x.shape[2] * x.shape[3]
+    raise ValueError(f"batch_norm: x must have 2 or 4 dimensions, but got shape {tuple(x.shape)}")
+
+
+def batch_norm_forward(x, gamma, beta, running_mean=None, running_var=None, training=True, eps=1e-5, momentum=0.1,
+                       act=capi.ACT_NONE):
+    """Returns (y, save_mean, save_var).  Training mode updates running_mean / running_var in place when given (the
+    reference layer's rule: running = momentum * running + (1 - momentum) * batch)."""
+    _chk(x, gamma, beta, running_mean, running_var)
+    N, C, HW = _bn_dims(x)
+    for t in (gamma, beta, running_mean, running_var):
+        if t is not None and tuple(t.shape) != (C,):
+            raise ValueError(f"batch_norm: gamma, beta, running_mean, running_var must have shape ({C})")
+    y = torch.empty_like(x)
+    mean, var = torch.empty(C, device=x.device), torch.empty(C, device=x.device)
+    capi.call("odl_batch_norm_forward", _p(x), _p(gamma), _p(beta), _p(running_mean), _p(running_var), int(training), eps,
+              momentum, N, C, HW, act, _p(y), _p(mean), _p(var), _s())
+    return y, mean, var
+
+
+def batch_norm_backward(gy, x, gamma, beta, save_mean, save_var, eps=1e-5, act=capi.ACT_NONE):
+    """Returns (gx, dgamma, dbeta) for the statistics the forward pass used."""
+    _chk(gy, x, gamma, beta, save_mean, save_var)
+    N, C, HW = _bn_dims(x)
+    gx, dg, db = torch.empty_like(x), torch.empty(C, device=x.device), torch.empty(C, device=x.device)
+    capi.call("odl_batch_norm_backward", _p(gy), _p(x), _p(gamma), _p(beta), _p(save_mean), _p(save_var), eps, N, C, HW,
+              act, _p(gx), _p(dg), _p(db), _s())
+    return gx, dg, db
+
+
+def batch_norm_fold(gamma, beta, mean, var, bias=None, eps=1e-5):
+    """(scale, shift) of evaluation-mode BatchNorm applied to conv(x) + bias."""
+    _chk(gamma, beta, mean, var, bias)
+    C = gamma.numel()
+    scale, shift = torch.empty(C, device=gamma.device), torch.empty(C, device=gamma.device)
+    capi.call("odl_batch_norm_fold", _p(gamma), _p(beta), _p(mean), _p(var), _p(bias), eps, C, _p(scale), _p(shift), _s())
+    return scale, shift
+
+
+def silu(x):
+    _chk(x)
+    y = torch.empty_like(x)
+    capi.call("odl_silu_forward", _p(x), _p(y), x.numel(), _s())
+    return y
+
+
+def silu_backward(gy, x):
+    _chk(gy, x)
+    gx = torch.empty_like(x)
+    capi.call("odl_silu_backward", _p(gy), _p(x), _p(gx), x.numel(), _s())
+    return gx
+
+
+def conv2d_bn_act_forward(x, w, scale, shift, stride=1, pad=0, act=capi.ACT_RELU, precision=PRECISION_3XTF32):
+    """act(scale[oc] * conv2d(x, w) + shift[oc]) in one GEMM (scale / shift from batch_norm_fold)."""
+    _chk(x, w, scale, shift)
+    N, C, H, W = x.shape
+    OC, C2, KH, KW = w.shape
+    if C != C2:
+        raise ValueError(f"conv2d: channel mismatch - x has {C} channels, but W expects {C2} channels")
+    OH, OW = conv_out_size(H, KH, stride, pad), conv_out_size(W, KW, stride, pad)
+    y = torch.empty((N, OC, OH, OW), device=x.device, dtype=torch.float32)
+    capi.call("odl_conv2d_bn_act_forward", _p(x), _p(w), _p(scale), _p(shift), _p(y), N, C, H, W, OC, KH, KW, stride, pad,
+              act, precision, _s())
+    return y

@@ -6,6 +6,7 @@
     python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
     python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
     python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
+    python -m origindl_b200.profile_case batchnorm --n 64 --cols 64 --rows 25600   (N x C x HW, training fwd + bwd, fused SiLU)
     python -m origindl_b200.profile_case gather  --rows 65536 --cols 1024       (batch assembly from a resident data set)
     python -m origindl_b200.profile_case checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
 
@@ -38,7 +39,7 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint", "gather"])
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint", "gather", "batchnorm"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -84,6 +85,19 @@ def main():
         print(f"checkpoint {len(sizes) - 1} x {a.n}^2 ({tr.param_count / 1e6:.1f} M parameters, {nbytes / 1e9:.2f} GB with Adam state): "
               f"save {t1 - t0:.3f} s ({nbytes / (t1 - t0) / 1e9:.2f} GB/s), load {t3 - t2:.3f} s ({nbytes / (t3 - t2) / 1e9:.2f} GB/s), "
               f"parameters identical after reload: {same}")
+    elif a.case == "batchnorm":
+        N, C, HW = a.n, a.cols, a.rows
+        x, dy = torch.randn(N, C, HW, 1, device="cuda"), torch.randn(N, C, HW, 1, device="cuda")
+        gamma, beta = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda")
+        rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+        _, mean, var = ops.batch_norm_forward(x, gamma, beta, rm, rv, act=capi.ACT_SILU)
+        nb = 4.0 * x.numel()
+        t_f = timed(lambda: ops.batch_norm_forward(x, gamma, beta, rm, rv, act=capi.ACT_SILU), a.iters)
+        t_e = timed(lambda: ops.batch_norm_forward(x, gamma, beta, rm, rv, training=False, act=capi.ACT_SILU), a.iters)
+        t_b = timed(lambda: ops.batch_norm_backward(dy, x, gamma, beta, mean, var, act=capi.ACT_SILU), a.iters)
+        print(f"batchnorm+silu {N}x{C}x{HW} ({nb / 1e6:.0f} MB per tensor): training forward {t_f:.4f} ms "
+              f"({3 * nb / t_f / 1e6:.0f} GB/s: 2 reads + 1 write), evaluation forward {t_e:.4f} ms ({2 * nb / t_e / 1e6:.0f} GB/s), "
+              f"backward {t_b:.4f} ms ({5 * nb / t_b / 1e6:.0f} GB/s: 4 reads + 1 write)")
     elif a.case == "gather":
         n_src = 4 * a.rows
         src = torch.randn(n_src, a.cols, device="cuda")

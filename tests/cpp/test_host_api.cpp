@@ -258,6 +258,82 @@ static void mlp_training()
         EXPECT_TRUE(!out.impl()->creator);
     }
 }
+// ---- tests/unit_test/operator/test_batch_norm.cpp, tests/unit_test/nn/test_batch_norm.cpp (same inputs; the reference
+//      only checks shapes and finiteness there -- the values below are the closed forms) and silu
+static void batch_norm_cases()
+{
+    const float eps = 1e-5f;
+    // BatchNorm1dForwardTraining: x = [[1,2,3],[4,5,6]] -> mean [2.5,3.5,4.5], biased var 2.25
+    auto x1 = T({1, 2, 3, 4, 5, 6}, {2, 3}, true);
+    auto g1 = T({1, 1, 1}, {3}, true), b1 = T({0, 0, 0}, {3}, true), rm1 = T({0, 0, 0}, {3}), rv1 = T({1, 1, 1}, {3});
+    auto y1 = F::batch_norm(x1, g1, b1, rm1, rv1, true, eps, 0.1f, 2);
+    EXPECT_TRUE(y1.shape() == (Shape{2, 3}));
+    const float n1 = 1.5f / std::sqrt(2.25f + eps);
+    expect_tensor(y1, {-n1, -n1, -n1, n1, n1, n1}, 1e-6f);
+    expect_tensor(rm1, {0, 0, 0});  // the functional form leaves the running statistics alone
+    // BatchNorm1dForwardEval: running statistics (0, 1)
+    auto y1e = F::batch_norm(x1, g1, b1, rm1, rv1, false, eps, 0.1f, 2);
+    const float k = 1.0f / std::sqrt(1.0f + eps);
+    expect_tensor(y1e, {1 * k, 2 * k, 3 * k, 4 * k, 5 * k, 6 * k}, 1e-6f);
+    // BatchNorm1dWithGammaBeta: gamma [2, 3], beta [1, -1]
+    auto y1g = F::batch_norm(T({1, 2, 3, 4}, {2, 2}), T({2, 3}, {2}), T({1, -1}, {2}), T({0, 0}, {2}), T({1, 1}, {2}), true,
+                             eps, 0.1f, 2);
+    const float n2 = 1.0f / std::sqrt(1.0f + eps);
+    expect_tensor(y1g, {1 - 2 * n2, -1 - 3 * n2, 1 + 2 * n2, -1 + 3 * n2}, 1e-6f);
+    // BatchNorm2dForwardTraining: {2,2,2,2}, channel c of image n holds n*8 + c*4 + {1,2,3,4}
+    std::vector<float> xv(16);
+    for (int i = 0; i < 16; ++i)
+        xv[i] = (float)(i + 1);
+    auto x2 = T(xv, {2, 2, 2, 2}, true);
+    auto g2 = T({1, 1}, {2}, true), b2 = T({0, 0}, {2}, true);
+    auto op = std::make_shared<F::BatchNorm>(true, eps, 0.1f, 4);
+    auto y2 = op->call1({x2, g2, b2, T({0, 0}, {2}), T({1, 1}, {2})});
+    EXPECT_TRUE(y2.shape() == (Shape{2, 2, 2, 2}));
+    expect_tensor(op->mean(), {6.5f, 10.5f}, 1e-6f);    // mean of {1..4, 9..12} and of {5..8, 13..16}
+    expect_tensor(op->var(), {17.25f, 17.25f}, 1e-5f);
+    EXPECT_NEAR(y2.to_vector<float>()[0], (1.0f - 6.5f) / std::sqrt(17.25f + eps), 1e-6f);
+    // backward after a TRAINING forward (the reference's operator throws here): sum(gx) = 0 per channel,
+    // dbeta = sum(gy), dgamma = sum(gy * x_norm)
+    auto w2 = T({1, -2, 3, 0.5f, 2, 1, -1, 4, 0, 1, 1, -3, 2, 2, -1, 0.25f}, {2, 2, 2, 2});
+    F::sum(y2 * w2).backward();
+    auto gx = x2.grad().to_vector<float>();
+    EXPECT_NEAR(gx[0] + gx[1] + gx[2] + gx[3] + gx[8] + gx[9] + gx[10] + gx[11], 0.0f, 1e-5f);
+    expect_tensor(b2.grad(), {1 - 2 + 3 + 0.5f + 0 + 1 + 1 - 3, 2 + 1 - 1 + 4 + 2 + 2 - 1 + 0.25f}, 1e-5f);
+    auto yv = y2.to_vector<float>(), wv = w2.to_vector<float>();
+    float dg0 = 0.f;
+    for (int i : {0, 1, 2, 3, 8, 9, 10, 11})
+        dg0 += yv[i] * wv[i];
+    EXPECT_NEAR(g2.grad().to_vector<float>()[0], dg0, 1e-5f);
+    // invalid inputs (src/mat/origin/cpu/normalization/batch_norm.cpp:29-45)
+    EXPECT_THROW(F::batch_norm(x2, g2, b2, T({0, 0}, {2}), T({1, 1}, {2}), true, eps, 0.1f, 2));
+    EXPECT_THROW(F::batch_norm(x2, g1, b2, T({0, 0}, {2}), T({1, 1}, {2}), true, eps, 0.1f, 4));
+    EXPECT_THROW(F::batch_norm(x1, g1, b1, rm1, rv1, true, eps, 0.1f, 3));
+    // nn::BatchNorm2d: BasicForward / EvalMode and the running-statistics rule
+    nn::BatchNorm2d bn(2, eps, 0.1f);
+    EXPECT_TRUE(bn.is_training());
+    auto yb = bn(x2.detach());
+    EXPECT_TRUE(yb.shape() == (Shape{2, 2, 2, 2}));
+    expect_tensor(bn.running_mean(), {0.9f * 6.5f, 0.9f * 10.5f}, 1e-5f);  // 0.1 * 0 + 0.9 * batch mean
+    expect_tensor(bn.running_var(), {0.1f + 0.9f * 17.25f, 0.1f + 0.9f * 17.25f}, 1e-4f);
+    bn.eval();
+    EXPECT_TRUE(!bn.is_training());
+    auto ye = bn(x2.detach());
+    EXPECT_NEAR(ye.to_vector<float>()[0], (1.0f - 5.85f) / std::sqrt(15.625f + eps), 1e-5f);
+    expect_tensor(bn.running_mean(), {0.9f * 6.5f, 0.9f * 10.5f}, 1e-5f);  // unchanged in evaluation mode
+    EXPECT_TRUE(bn.named_parameters("").count("weight") && bn.named_parameters("").count("bias"));
+    EXPECT_THROW(bn(x1.detach()));
+    EXPECT_THROW(nn::BatchNorm2d(0));
+    // fused activation: BatchNorm2d(act = SiLU) == silu(BatchNorm2d)
+    nn::BatchNorm2d fused(2, eps, 0.1f, ODL_ACT_SILU), plain(2, eps, 0.1f);
+    EXPECT_TRUE(fused(x2.detach()).to_vector<float>() == F::silu(plain(x2.detach())).to_vector<float>());
+    // silu values and gradient: silu(0) = 0, silu(1) = 0.7310586, silu'(0) = 0.5
+    auto xs = T({0, 1, -1, 4}, {4}, true);
+    auto ys = F::silu(xs);
+    expect_tensor(ys, {0.0f, 0.7310586f, -0.2689414f, 3.9280552f}, 1e-6f);
+    F::sum(ys).backward();
+    expect_tensor(xs.grad(), {0.5f, 0.9276706f, 0.0723295f, 1.0526646f}, 1e-6f);
+}
+
 // ---- state dict, .odl files, checkpoints (tests/unit_test/io/test_checkpoint.cpp: SaveAndLoadCheckpoint,
 //      SaveAndLoadModelStateDict, OptimizerStateDict) plus what the reference cannot do: resume on the same trajectory
 static std::string g_golden_dir;  // tests/golden of this repository (argv[1]); empty = skip the fixture cases
@@ -458,7 +534,8 @@ int main(int argc, char **argv)
         {"relu", relu_cases},                 {"softmax_cross_entropy", softmax_ce_cases},
         {"conv2d", conv2d_cases},             {"weight_decay_and_adam", weight_decay_and_adam},
         {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
-        {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases}};
+        {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases},
+        {"batch_norm_silu", batch_norm_cases}};
     for (auto &t : tests)
     {
         const int before = g_failed;

@@ -1,0 +1,181 @@
+"""GPU: BatchNorm (+ReLU / SiLU) forward / backward, SiLU, and the fused conv -> BatchNorm(eval) -> activation GEMM,
+through the C ABI, against golden outputs of the unmodified reference (tests/golden/reference_bn_vectors.npz) and the
+oracle on other shapes.
+
+Tolerances (max|a-b| / max|ref|): evaluation-mode forward without SiLU is the same fp32 operation sequence as the
+reference -> bit-exact; batch statistics are reduced in double instead of one sequential fp32 accumulator -> 2e-6;
+SiLU uses the device expf -> 2e-6; backward 1e-5; the fused conv block inherits the 3xTF32 GEMM's 1e-5."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import _libs
+from _libs import max_rel_err
+from golden import make_bn_golden as mk
+from test_oracle_batch_norm import oracle_bn
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden" / "reference_bn_vectors.npz"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from origindl_b200 import capi, ops
+
+    capi.init(0)
+    yield ops
+    capi.device_status()
+
+
+def dev(inp):
+    return {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in inp.items()}
+
+
+def shaped(t, name):
+    """The {N, C} form for HW == 1, else {N, C, H, W} with H * W = HW."""
+    n, c, hw = mk.CASES[name] if isinstance(name, str) else name
+    return t.reshape(n, c) if hw == 1 else t.reshape(n, c, hw, 1)
+
+
+@pytest.mark.parametrize("name", list(mk.CASES))
+@pytest.mark.parametrize("act_name", list(mk.ACTS))
+def test_matches_golden_reference_outputs(ops, name, act_name):
+    g, inp, act = np.load(GOLDEN), mk.case_inputs(name), mk.ACTS[act_name]
+    d = dev(inp)
+    x, dy = shaped(d["x"], name), shaped(d["dy"], name)
+    # training mode: batch statistics, running statistics updated in place
+    rm, rv = d["running_mean"].clone(), d["running_var"].clone()
+    y, mean, var = ops.batch_norm_forward(x, d["gamma"], d["beta"], rm, rv, training=True, eps=mk.EPS, momentum=0.1, act=act)
+    key = f"{name}/train/{act_name}"
+    assert max_rel_err(mean.cpu().numpy(), g[key + "/mean"]) <= 2e-6
+    assert max_rel_err(var.cpu().numpy(), g[key + "/var"]) <= 2e-6
+    assert max_rel_err(y.cpu().numpy().reshape(inp["x"].shape), g[key + "/y"]) <= 2e-6
+    want_rm = np.float32(0.1) * inp["running_mean"] + np.float32(0.9) * g[key + "/mean"]
+    want_rv = np.float32(0.1) * inp["running_var"] + np.float32(0.9) * g[key + "/var"]
+    assert max_rel_err(rm.cpu().numpy(), want_rm) <= 2e-6 and max_rel_err(rv.cpu().numpy(), want_rv) <= 2e-6
+    # evaluation mode: the reference's forward and its backward
+    key = f"{name}/eval/{act_name}"
+    y, mean, var = ops.batch_norm_forward(x, d["gamma"], d["beta"], d["running_mean"], d["running_var"], training=False,
+                                          eps=mk.EPS, act=act)
+    got = y.cpu().numpy().reshape(inp["x"].shape)
+    if act == 2:
+        assert max_rel_err(got, g[key + "/y"]) <= 2e-6
+    else:
+        assert np.array_equal(got, g[key + "/y"])
+    assert np.array_equal(mean.cpu().numpy(), inp["running_mean"]) and np.array_equal(var.cpu().numpy(), inp["running_var"])
+    gx, dg, db = ops.batch_norm_backward(dy, x, d["gamma"], d["beta"], mean, var, eps=mk.EPS, act=act)
+    assert max_rel_err(gx.cpu().numpy().reshape(inp["x"].shape), g[key + "/gx"]) <= 1e-5
+    assert max_rel_err(dg.cpu().numpy(), g[key + "/dgamma"]) <= 1e-5
+    assert max_rel_err(db.cpu().numpy(), g[key + "/dbeta"]) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(16, 16, 160 * 160), (3, 5, 1001), (70000, 3, 1), (2, 300, 17), (1, 1, 1)])
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_training_forward_and_backward_match_the_oracle(ops, shape, act):
+    """Other shapes (a conv layer-1 output, ragged planes, BatchNorm1d with many rows, many channels) against the
+    oracle, whose training-mode backward is the reference's formula on the batch statistics."""
+    n, c, hw = shape
+    if n * c * hw > 2_000_000 and act == 2:
+        pytest.skip("one large case per activation family is enough for the CPU checker")
+    rng = np.random.default_rng(n + c + hw + act)
+    inp = {"x": (rng.standard_normal(shape) * 1.3 + rng.standard_normal((1, c, 1))).astype(np.float32),
+           "gamma": (1 + 0.3 * rng.standard_normal(c)).astype(np.float32), "beta": (0.2 * rng.standard_normal(c)).astype(np.float32),
+           "running_mean": np.zeros(c, np.float32), "running_var": np.ones(c, np.float32),
+           "dy": rng.standard_normal(shape).astype(np.float32)}
+    want = oracle_bn(inp, True, act, True)
+    d = dev(inp)
+    x, dy = shaped(d["x"], shape), shaped(d["dy"], shape)
+    y, mean, var = ops.batch_norm_forward(x, d["gamma"], d["beta"], None, None, training=True, eps=mk.EPS, act=act)
+    # the oracle's sequential fp32 sums drift with the element count; the device sums are double
+    tol = 2e-6 if n * hw < 100000 else 2e-5
+    x64 = inp["x"].astype(np.float64)
+    assert max_rel_err(mean.cpu().numpy(), x64.mean(axis=(0, 2))) <= 2e-7 + 1e-7
+    assert max_rel_err(var.cpu().numpy(), x64.var(axis=(0, 2))) <= 1e-6 if n * hw > 1 else True
+    assert max_rel_err(y.cpu().numpy().reshape(shape), want["y"]) <= tol * 5
+    gx, dg, db = ops.batch_norm_backward(dy, x, d["gamma"], d["beta"], mean, var, eps=mk.EPS, act=act)
+    tol_b = 5e-5 if n * hw < 100000 else 5e-4  # at 409600 elements per channel the ORACLE's fp32 running sums drift
+    if n * hw > 1:
+        assert max_rel_err(gx.cpu().numpy().reshape(shape), want["gx"]) <= tol_b
+        assert max_rel_err(dg.cpu().numpy(), want["dgamma"]) <= tol_b
+    assert max_rel_err(db.cpu().numpy(), want["dbeta"]) <= tol_b
+    if n * hw >= 100000:  # ... so at that size the gradient is also checked against float64 directly
+        dy64, ga64 = inp["dy"].astype(np.float64), inp["gamma"].astype(np.float64)
+        m64, v64 = x64.mean(axis=(0, 2), keepdims=True), x64.var(axis=(0, 2), keepdims=True)
+        xn = (x64 - m64) / np.sqrt(v64 + mk.EPS)
+        z = xn * ga64[None, :, None] + inp["beta"].astype(np.float64)[None, :, None]
+        if act == 1:
+            g64 = dy64 * (z > 0)
+        elif act == 2:
+            sg = 1 / (1 + np.exp(-z))
+            g64 = dy64 * (sg + z * sg * (1 - sg))
+        else:
+            g64 = dy64
+        gx64 = ga64[None, :, None] / np.sqrt(v64 + mk.EPS) * (g64 - g64.mean(axis=(0, 2), keepdims=True)
+                                                               - xn * (g64 * xn).mean(axis=(0, 2), keepdims=True))
+        assert max_rel_err(gx.cpu().numpy().reshape(shape), gx64) <= 1e-5
+        assert max_rel_err(dg.cpu().numpy(), (g64 * xn).sum(axis=(0, 2))) <= 1e-5
+
+
+def test_running_statistics_follow_the_layer(ops):
+    g, inp = np.load(GOLDEN), mk.layer_inputs()
+    steps, n, c, hw = inp["xs"].shape
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    gamma, beta = torch.ones(c, device="cuda"), torch.zeros(c, device="cuda")
+    for k in range(steps):
+        ops.batch_norm_forward(torch.from_numpy(inp["xs"][k]).cuda().reshape(n, c, hw, 1), gamma, beta, rm, rv, training=True,
+                               eps=mk.EPS, momentum=inp["momentum"])
+    y, _, _ = ops.batch_norm_forward(torch.from_numpy(inp["probe"]).cuda().reshape(n, c, hw, 1), gamma, beta, rm, rv,
+                                     training=False, eps=mk.EPS)
+    assert max_rel_err(y.cpu().numpy().reshape(n, c, hw), g["layer/y"]) <= 2e-6
+
+
+def test_silu_matches_golden(ops):
+    g, inp = np.load(GOLDEN), mk.silu_inputs()
+    x, dy = torch.from_numpy(inp["x"]).cuda(), torch.from_numpy(inp["dy"]).cuda()
+    assert max_rel_err(ops.silu(x).cpu().numpy(), g["silu/y"]) <= 2e-6
+    assert max_rel_err(ops.silu_backward(dy, x).cpu().numpy(), g["silu/gx"]) <= 2e-6
+
+
+def test_invalid_arguments(ops):
+    from origindl_b200 import capi
+
+    x = torch.randn(4, 3, 5, 5, device="cuda")
+    ones = torch.ones(3, device="cuda")
+    with pytest.raises(ValueError, match="2 or 4 dimensions"):
+        ops.batch_norm_forward(x.reshape(4, 3, 25), ones, ones)
+    with pytest.raises(ValueError, match="must have shape"):
+        ops.batch_norm_forward(x, torch.ones(4, device="cuda"), ones)
+    with pytest.raises(capi.OdlError):
+        ops.batch_norm_forward(x, ones, ones, None, None, training=False)  # evaluation mode needs running statistics
+    with pytest.raises(capi.OdlError):
+        ops.batch_norm_forward(x, ones, ones, act=7)
+
+
+@pytest.mark.parametrize("act", [1, 2])
+@pytest.mark.parametrize("geom", [(2, 3, 20, 20, 16, 6, 2, 2), (2, 16, 12, 12, 32, 3, 1, 1), (1, 8, 9, 9, 5, 1, 1, 0)])
+def test_conv_bn_act_block_is_one_gemm(ops, act, geom):
+    """conv2d + bias -> BatchNorm2d (evaluation mode) -> ReLU / SiLU against the oracle's three separate steps."""
+    N, C, H, W, OC, k, s, p = geom
+    rng = np.random.default_rng(sum(geom) + act)
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * (2.0 / (C * k * k)) ** 0.5).astype(np.float32)
+    b = (0.1 * rng.standard_normal(OC)).astype(np.float32)
+    L = _libs.oracle()
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    conv = np.empty((N, OC, OH, OW), np.float32)
+    L.oracle_conv2d_forward(x, w, _libs.fptr(b), conv, N, C, H, W, OC, k, k, s, p)
+    inp = {"x": conv.reshape(N, OC, OH * OW), "gamma": (1 + 0.3 * rng.standard_normal(OC)).astype(np.float32),
+           "beta": (0.2 * rng.standard_normal(OC)).astype(np.float32), "running_mean": (0.3 * rng.standard_normal(OC)).astype(np.float32),
+           "running_var": (0.5 + rng.random(OC)).astype(np.float32), "dy": np.zeros((N, OC, OH * OW), np.float32)}
+    want = oracle_bn(inp, False, act, False)["y"].reshape(N, OC, OH, OW)
+    d = dev({"x": x, "w": w, "b": b, **{k_: inp[k_] for k_ in ("gamma", "beta", "running_mean", "running_var")}})
+    scale, shift = ops.batch_norm_fold(d["gamma"], d["beta"], d["running_mean"], d["running_var"], d["b"], eps=mk.EPS)
+    got = ops.conv2d_bn_act_forward(d["x"], d["w"], scale, shift, stride=s, pad=p, act=act)
+    assert max_rel_err(got.cpu().numpy(), want) <= 1e-5
+    # the plain conv with a fused SiLU / ReLU too
+    plain = ops.conv2d_forward(d["x"], d["w"], d["b"], stride=s, pad=p, relu=act)
+    z = conv.astype(np.float64)
+    ref = np.maximum(z, 0) if act == 1 else z / (1 + np.exp(-z))
+    assert max_rel_err(plain.cpu().numpy(), ref) <= 1e-5
