@@ -50,6 +50,7 @@ def main():
     ap.add_argument("--precision", default="3xtf32")
     ap.add_argument("--layout", default="nt")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
     a = ap.parse_args()
     capi.init(0)
     torch.manual_seed(0)
@@ -115,6 +116,13 @@ def main():
         As, Bs = ops.split_tf32(A), ops.split_tf32(B)
         ms = timed(lambda: ops.gemm(A, B, trans_a=ta, trans_b=tb, a_small=As, b_small=Bs, precision=prec), a.iters)
         print(f"gemm {a.layout} {a.precision} n={n}: {ms:.4f} ms/launch, {2 * n ** 3 / ms / 1e9:.1f} TFLOP/s")
+        if a.yardstick:
+            # context only: the vendor library's single-pass TF32 and fp32 GEMMs on the same operands
+            At, Bt = (A.t() if ta else A), (B.t() if tb else B)
+            for name, flag in (("TF32", True), ("fp32", False)):
+                torch.backends.cuda.matmul.allow_tf32 = flag
+                t = timed(lambda: torch.matmul(At, Bt), a.iters)
+                print(f"  yardstick torch.matmul {name}: {t:.4f} ms, {2 * n ** 3 / t / 1e9:.1f} TFLOP/s")
     elif a.case == "split":
         n = a.n
         X = torch.randn(n, n, device="cuda")
