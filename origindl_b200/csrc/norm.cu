@@ -30,7 +30,7 @@ struct BnGeom
 {
     int N, C, HW;
     int chunks;     // slabs per (n, c) plane (4-D form) or row slabs (2-D form)
-    int chunk_len;  // elements of a plane per slab / rows per slab
+    int chunk_len;  // elements of a plane per slab / rows per slab (a multiple of 4 in the 4-D form)
 };
 
 // Pre-activation -> activation and its derivative (act: 0 none, 1 relu, 2 silu), the reference's formulas.
@@ -108,7 +108,45 @@ __device__ __forceinline__ void block_sum2(double &a, double &b)
     }
 }
 
+// One block's elements, V at a time (V = 4: float4 loads / stores; the launcher guarantees 16-byte alignment of every
+// group then).  body(offset, lane values...) is written out per kernel below through these two helpers.
+template <int V>
+__device__ __forceinline__ void load_vec(const float *__restrict__ p, float (&v)[V])
+{
+    if (V == 4)
+    {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+    else
+        v[0] = __ldg(p);
+}
+template <int V>
+__device__ __forceinline__ void store_vec(float *__restrict__ p, const float (&v)[V])
+{
+    if (V == 4)
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else
+        p[0] = v[0];
+}
+
+// Finishes a channel once its last block has added its partial sums: returns true in exactly one thread of the grid
+// per channel, with the totals in (s, q).
+__device__ __forceinline__ bool channel_done(double *acc, unsigned *done, int c, double &s, double &q)
+{
+    atomicAdd(acc + 2 * c, s);
+    atomicAdd(acc + 2 * c + 1, q);
+    __threadfence();
+    if (atomicAdd(done + c, 1u) != gridDim.y - 1)
+        return false;
+    __threadfence();
+    s = atomicAdd(acc + 2 * c, 0.0);
+    q = atomicAdd(acc + 2 * c + 1, 0.0);
+    return true;
+}
+
 // ---- forward, training: per-channel sum and sum of squares; the last block of a channel finishes the statistics
+template <int V>
 __global__ void __launch_bounds__(kThreads) bn_stats_kernel(const float *__restrict__ x, BnGeom g, double *__restrict__ acc,
                                                             unsigned *__restrict__ done, float *__restrict__ save_mean,
                                                             float *__restrict__ save_var, float *__restrict__ running_mean,
@@ -116,41 +154,40 @@ __global__ void __launch_bounds__(kThreads) bn_stats_kernel(const float *__restr
 {
     const Range r = block_range(g);
     double s = 0.0, q = 0.0;
-    for (int i = r.i0 + threadIdx.x; i < r.i1; i += kThreads)
+    for (int i = r.i0 + V * threadIdx.x; i < r.i1; i += V * kThreads)
     {
-        const double v = static_cast<double>(__ldg(x + r.base + i * r.step));
-        s += v;
-        q += v * v;
+        float v[V];
+        load_vec<V>(x + r.base + i * r.step, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+        {
+            const double d = static_cast<double>(v[j]);
+            s += d;
+            q += d * d;
+        }
     }
     block_sum2(s, q);
-    if (threadIdx.x == 0)
+    const int c = blockIdx.x;
+    if (threadIdx.x == 0 && channel_done(acc, done, c, s, q))
     {
-        const int c = blockIdx.x;
-        atomicAdd(acc + 2 * c, s);
-        atomicAdd(acc + 2 * c + 1, q);
-        __threadfence();
-        if (atomicAdd(done + c, 1u) == gridDim.y - 1)
+        const double count = static_cast<double>(g.N) * g.HW;
+        const double mean  = s / count;
+        double var         = q / count - mean * mean;
+        var                = var > 0.0 ? var : 0.0;
+        const float mf = static_cast<float>(mean), vf = static_cast<float>(var);
+        save_mean[c] = mf;
+        save_var[c]  = vf;
+        if (running_mean)  // nn::BatchNorm2d: momentum weighs the OLD value (src/nn/layers/batch_norm2d.cpp:76-79)
         {
-            __threadfence();
-            const double count = static_cast<double>(g.N) * g.HW;
-            const double sum = atomicAdd(acc + 2 * c, 0.0), sq = atomicAdd(acc + 2 * c + 1, 0.0);
-            const double mean = sum / count;
-            double var        = sq / count - mean * mean;
-            var               = var > 0.0 ? var : 0.0;
-            const float mf = static_cast<float>(mean), vf = static_cast<float>(var);
-            save_mean[c] = mf;
-            save_var[c]  = vf;
-            if (running_mean)  // nn::BatchNorm2d: momentum weighs the OLD value (src/nn/layers/batch_norm2d.cpp:76-79)
-            {
-                const float keep = __fsub_rn(1.0f, momentum);
-                running_mean[c]  = __fadd_rn(__fmul_rn(momentum, running_mean[c]), __fmul_rn(keep, mf));
-                running_var[c]   = __fadd_rn(__fmul_rn(momentum, running_var[c]), __fmul_rn(keep, vf));
-            }
+            const float keep = __fsub_rn(1.0f, momentum);
+            running_mean[c]  = __fadd_rn(__fmul_rn(momentum, running_mean[c]), __fmul_rn(keep, mf));
+            running_var[c]   = __fadd_rn(__fmul_rn(momentum, running_var[c]), __fmul_rn(keep, vf));
         }
     }
 }
 
-// ---- forward: y = act(gamma * (x - mean) / sqrt(var + eps) + beta)
+// ---- forward: y = act(gamma * (x - mean) / sqrt(var + eps) + beta), the reference's operation sequence
+template <int V>
 __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const float *__restrict__ x, BnGeom g,
                                                             const float *__restrict__ gamma, const float *__restrict__ beta,
                                                             const float *__restrict__ mean, const float *__restrict__ var,
@@ -159,16 +196,21 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const float *__restr
     const Range r = block_range(g);
     const int c   = blockIdx.x;
     const float m = mean[c], sd = __fsqrt_rn(__fadd_rn(var[c], eps)), ga = gamma[c], be = beta[c];
-    for (int i = r.i0 + threadIdx.x; i < r.i1; i += kThreads)
+    for (int i = r.i0 + V * threadIdx.x; i < r.i1; i += V * kThreads)
     {
         const int64_t o = r.base + i * r.step;
-        const float xn  = __fdiv_rn(__fsub_rn(__ldg(x + o), m), sd);
-        y[o]            = act_forward(__fadd_rn(__fmul_rn(ga, xn), be), act);
+        float v[V];
+        load_vec<V>(x + o, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+            v[j] = act_forward(__fadd_rn(__fmul_rn(ga, __fdiv_rn(__fsub_rn(v[j], m), sd)), be), act);
+        store_vec<V>(y + o, v);
     }
 }
 
 // ---- backward: g = gy * act'(z); per-channel sum g and sum g * x_norm; the last block writes dgamma, dbeta and the
-//      two means the second pass needs
+//      two means the second pass needs.  (x - mean) * (1 / std) here: no bit-level claim is made for gradients.
+template <int V>
 __global__ void __launch_bounds__(kThreads)
     bn_bwd_stats_kernel(const float *__restrict__ gy, const float *__restrict__ x, BnGeom g, const float *__restrict__ gamma,
                         const float *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ var,
@@ -177,37 +219,37 @@ __global__ void __launch_bounds__(kThreads)
 {
     const Range r = block_range(g);
     const int c   = blockIdx.x;
-    const float m = mean[c], sd = __fsqrt_rn(__fadd_rn(var[c], eps)), ga = gamma[c], be = beta[c];
+    const float m = mean[c], rsd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var[c], eps))), ga = gamma[c], be = beta[c];
     double s = 0.0, q = 0.0;
-    for (int i = r.i0 + threadIdx.x; i < r.i1; i += kThreads)
+    for (int i = r.i0 + V * threadIdx.x; i < r.i1; i += V * kThreads)
     {
         const int64_t o = r.base + i * r.step;
-        const float xn  = __fdiv_rn(__fsub_rn(__ldg(x + o), m), sd);
-        const float gv  = act_backward(__ldg(gy + o), __fadd_rn(__fmul_rn(ga, xn), be), act);
-        s += static_cast<double>(gv);
-        q += static_cast<double>(__fmul_rn(gv, xn));
+        float xv[V], gv[V];
+        load_vec<V>(x + o, xv);
+        load_vec<V>(gy + o, gv);
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+        {
+            const float xn = __fmul_rn(__fsub_rn(xv[j], m), rsd);
+            const float t  = act_backward(gv[j], __fadd_rn(__fmul_rn(ga, xn), be), act);
+            s += static_cast<double>(t);
+            q += static_cast<double>(__fmul_rn(t, xn));
+        }
     }
     block_sum2(s, q);
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0 && channel_done(acc, done, c, s, q))
     {
-        atomicAdd(acc + 2 * c, s);
-        atomicAdd(acc + 2 * c + 1, q);
-        __threadfence();
-        if (atomicAdd(done + c, 1u) == gridDim.y - 1)
-        {
-            __threadfence();
-            const float sum_g = static_cast<float>(atomicAdd(acc + 2 * c, 0.0));
-            const float sum_q = static_cast<float>(atomicAdd(acc + 2 * c + 1, 0.0));
-            const float count = static_cast<float>(static_cast<int64_t>(g.N) * g.HW);
-            dbeta[c]          = sum_g;
-            dgamma[c]         = sum_q;
-            means[2 * c]      = __fdiv_rn(sum_g, count);
-            means[2 * c + 1]  = __fdiv_rn(sum_q, count);
-        }
+        const float sum_g = static_cast<float>(s), sum_q = static_cast<float>(q);
+        const float count = static_cast<float>(static_cast<int64_t>(g.N) * g.HW);
+        dbeta[c]          = sum_g;
+        dgamma[c]         = sum_q;
+        means[2 * c]      = __fdiv_rn(sum_g, count);
+        means[2 * c + 1]  = __fdiv_rn(sum_q, count);
     }
 }
 
 // ---- backward: gx = (gamma / std) * (g - mean(g) - x_norm * mean(g * x_norm))
+template <int V>
 __global__ void __launch_bounds__(kThreads)
     bn_bwd_apply_kernel(const float *__restrict__ gy, const float *__restrict__ x, BnGeom g, const float *__restrict__ gamma,
                         const float *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ var,
@@ -215,14 +257,22 @@ __global__ void __launch_bounds__(kThreads)
 {
     const Range r = block_range(g);
     const int c   = blockIdx.x;
-    const float m = mean[c], sd = __fsqrt_rn(__fadd_rn(var[c], eps)), ga = gamma[c], be = beta[c];
+    const float m = mean[c], sd = __fsqrt_rn(__fadd_rn(var[c], eps)), rsd = __fdiv_rn(1.0f, sd), ga = gamma[c], be = beta[c];
     const float k = __fdiv_rn(ga, sd), mg = means[2 * c], mq = means[2 * c + 1];
-    for (int i = r.i0 + threadIdx.x; i < r.i1; i += kThreads)
+    for (int i = r.i0 + V * threadIdx.x; i < r.i1; i += V * kThreads)
     {
         const int64_t o = r.base + i * r.step;
-        const float xn  = __fdiv_rn(__fsub_rn(__ldg(x + o), m), sd);
-        const float gv  = act_backward(__ldg(gy + o), __fadd_rn(__fmul_rn(ga, xn), be), act);
-        gx[o]           = __fmul_rn(k, __fsub_rn(__fsub_rn(gv, mg), __fmul_rn(xn, mq)));
+        float xv[V], gv[V];
+        load_vec<V>(x + o, xv);
+        load_vec<V>(gy + o, gv);
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+        {
+            const float xn = __fmul_rn(__fsub_rn(xv[j], m), rsd);
+            const float t  = act_backward(gv[j], __fadd_rn(__fmul_rn(ga, xn), be), act);
+            gv[j]          = __fmul_rn(k, __fsub_rn(__fsub_rn(t, mg), __fmul_rn(xn, mq)));
+        }
+        store_vec<V>(gx + o, gv);
     }
 }
 
@@ -266,6 +316,12 @@ int check_launch(const char *name)
     return kOk;
 }
 
+// float4 access needs planes that start and end on 16-byte boundaries.
+bool vec4_ok(const BnGeom &g, const void *a, const void *b)
+{
+    return g.HW > 1 && (g.HW & 3) == 0 && !(reinterpret_cast<uintptr_t>(a) & 15) && !(reinterpret_cast<uintptr_t>(b) & 15);
+}
+
 // Slabs: enough blocks for about four waves of 148 SMs, at least 1024 elements per block.
 int make_geom(int64_t N, int64_t C, int64_t HW, BnGeom *g, dim3 *grid)
 {
@@ -295,6 +351,7 @@ int make_geom(int64_t N, int64_t C, int64_t HW, BnGeom *g, dim3 *grid)
         int64_t len = (HW + chunks - 1) / chunks;
         if (len < 1024)
             len = 1024;
+        len = (len + 3) & ~int64_t(3);
         g->chunk_len = (int)len;
         g->chunks    = (int)((HW + len - 1) / len);
         per_channel  = N * g->chunks;
@@ -303,7 +360,7 @@ int make_geom(int64_t N, int64_t C, int64_t HW, BnGeom *g, dim3 *grid)
     {
         // fewer, longer slabs: the y dimension of a grid holds 65535 blocks
         const int64_t shrink = (per_channel + 65534) / 65535;
-        g->chunk_len *= (int)shrink;
+        g->chunk_len *= (int)shrink;  // stays a multiple of 4
         g->chunks   = (int)(((HW == 1 ? N : HW) + g->chunk_len - 1) / g->chunk_len);
         per_channel = HW == 1 ? g->chunks : N * g->chunks;
         if (per_channel > 65535)
@@ -350,7 +407,12 @@ int odl_batch_norm_forward(const float *x, const float *gamma, const float *beta
         unsigned *done = static_cast<unsigned *>(arena_alloc(sizeof(unsigned) * C));
         ODL_CUDA_TRY(cudaMemsetAsync(acc, 0, acc_bytes, s));
         ODL_CUDA_TRY(cudaMemsetAsync(done, 0, sizeof(unsigned) * C, s));
-        bn_stats_kernel<<<grid, kThreads, 0, s>>>(x, g, acc, done, save_mean, save_var, running_mean, running_var, momentum);
+        if (vec4_ok(g, x, x))
+            bn_stats_kernel<4><<<grid, kThreads, 0, s>>>(x, g, acc, done, save_mean, save_var, running_mean, running_var,
+                                                         momentum);
+        else
+            bn_stats_kernel<1><<<grid, kThreads, 0, s>>>(x, g, acc, done, save_mean, save_var, running_mean, running_var,
+                                                         momentum);
         if ((rc = check_launch("bn_stats_kernel")))
             return rc;
         mean = save_mean, var = save_var;
@@ -360,7 +422,10 @@ int odl_batch_norm_forward(const float *x, const float *gamma, const float *beta
         ODL_CUDA_TRY(cudaMemcpyAsync(save_mean, running_mean, sizeof(float) * C, cudaMemcpyDeviceToDevice, s));
         ODL_CUDA_TRY(cudaMemcpyAsync(save_var, running_var, sizeof(float) * C, cudaMemcpyDeviceToDevice, s));
     }
-    bn_apply_kernel<<<grid, kThreads, 0, s>>>(x, g, gamma, beta, mean, var, eps, act, y);
+    if (vec4_ok(g, x, y))
+        bn_apply_kernel<4><<<grid, kThreads, 0, s>>>(x, g, gamma, beta, mean, var, eps, act, y);
+    else
+        bn_apply_kernel<1><<<grid, kThreads, 0, s>>>(x, g, gamma, beta, mean, var, eps, act, y);
     return check_launch("bn_apply_kernel");
 }
 
@@ -388,11 +453,19 @@ int odl_batch_norm_backward(const float *gy, const float *x, const float *gamma,
     float *means   = static_cast<float *>(arena_alloc(sizeof(float) * 2 * C));
     ODL_CUDA_TRY(cudaMemsetAsync(acc, 0, acc_bytes, s));
     ODL_CUDA_TRY(cudaMemsetAsync(done, 0, sizeof(unsigned) * C, s));
-    bn_bwd_stats_kernel<<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, acc, done, dgamma,
-                                                  dbeta, means);
+    const bool v4 = vec4_ok(g, x, gy) && vec4_ok(g, x, gx);
+    if (v4)
+        bn_bwd_stats_kernel<4><<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, acc, done,
+                                                         dgamma, dbeta, means);
+    else
+        bn_bwd_stats_kernel<1><<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, acc, done,
+                                                         dgamma, dbeta, means);
     if ((rc = check_launch("bn_bwd_stats_kernel")))
         return rc;
-    bn_bwd_apply_kernel<<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, means, gx);
+    if (v4)
+        bn_bwd_apply_kernel<4><<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, means, gx);
+    else
+        bn_bwd_apply_kernel<1><<<grid, kThreads, 0, s>>>(gy, x, g, gamma, beta, save_mean, save_var, eps, act, means, gx);
     return check_launch("bn_bwd_apply_kernel");
 }
 

@@ -50,7 +50,7 @@ def save(state_dict: dict[str, np.ndarray], filepath: str, device: tuple[int, in
             out.write(struct.pack("<Q", t.ndim))
             out.write(struct.pack(f"<{t.ndim}Q", *t.shape))
             out.write(struct.pack("<iii", DTYPE_CODES[t.dtype], device[0], device[1]))
-            out.write(t.tobytes())
+            out.write(memoryview(t.reshape(-1)).cast("B"))  # no intermediate copy of the values
 
 
 def load(filepath: str, with_devices: bool = False):
@@ -85,9 +85,10 @@ def load(filepath: str, with_devices: bool = False):
             if code not in CODE_DTYPES:
                 raise OdlFormatError(f"Unsupported dtype for loading: {code}")
             dt = CODE_DTYPES[code]
-            nbytes = int(np.prod(shape, dtype=np.int64)) * dt.itemsize if rank else dt.itemsize
-            data = take(nbytes, f"tensor data for parameter '{name}'")
-            tensors[name] = np.frombuffer(data, dtype=dt).reshape(shape).copy()
+            arr = np.empty(shape, dtype=dt)
+            if f.readinto(memoryview(arr.reshape(-1)).cast("B")) != arr.nbytes:
+                raise OdlFormatError(f"Failed to read tensor data for parameter '{name}' from file")
+            tensors[name] = arr
             devices[name] = (dev_type, dev_index)
     return (tensors, devices) if with_devices else tensors
 

@@ -95,18 +95,23 @@ def test_training_forward_and_backward_match_the_oracle(ops, shape, act):
     assert max_rel_err(var.cpu().numpy(), x64.var(axis=(0, 2))) <= 1e-6 if n * hw > 1 else True
     assert max_rel_err(y.cpu().numpy().reshape(shape), want["y"]) <= tol * 5
     gx, dg, db = ops.batch_norm_backward(dy, x, d["gamma"], d["beta"], mean, var, eps=mk.EPS, act=act)
-    tol_b = 5e-5 if n * hw < 100000 else 5e-4  # at 409600 elements per channel the ORACLE's fp32 running sums drift
-    if n * hw > 1:
+    big = n * hw >= 100000
+    # At 409600 elements per channel the ORACLE's single fp32 accumulators drift (its mean is off by ~1e-5), which with a
+    # ReLU also moves elements across the kink; there the oracle comparison is loose and skipped for the ReLU gradient,
+    # and the float64 check below is the sharp one.
+    tol_b = 5e-4 if big else 5e-5
+    if n * hw > 1 and not (big and act == 1):
         assert max_rel_err(gx.cpu().numpy().reshape(shape), want["gx"]) <= tol_b
         assert max_rel_err(dg.cpu().numpy(), want["dgamma"]) <= tol_b
-    assert max_rel_err(db.cpu().numpy(), want["dbeta"]) <= tol_b
-    if n * hw >= 100000:  # ... so at that size the gradient is also checked against float64 directly
+        assert max_rel_err(db.cpu().numpy(), want["dbeta"]) <= tol_b
+    if big:
         dy64, ga64 = inp["dy"].astype(np.float64), inp["gamma"].astype(np.float64)
         m64, v64 = x64.mean(axis=(0, 2), keepdims=True), x64.var(axis=(0, 2), keepdims=True)
         xn = (x64 - m64) / np.sqrt(v64 + mk.EPS)
         z = xn * ga64[None, :, None] + inp["beta"].astype(np.float64)[None, :, None]
         if act == 1:
-            g64 = dy64 * (z > 0)
+            # the ReLU mask of the device's own forward (backward recomputes the same fp32 pre-activation)
+            g64 = dy64 * (y.cpu().numpy().reshape(shape) > 0)
         elif act == 2:
             sg = 1 / (1 + np.exp(-z))
             g64 = dy64 * (sg + z * sg * (1 - sg))
@@ -116,6 +121,7 @@ def test_training_forward_and_backward_match_the_oracle(ops, shape, act):
                                                                - xn * (g64 * xn).mean(axis=(0, 2), keepdims=True))
         assert max_rel_err(gx.cpu().numpy().reshape(shape), gx64) <= 1e-5
         assert max_rel_err(dg.cpu().numpy(), (g64 * xn).sum(axis=(0, 2))) <= 1e-5
+        assert max_rel_err(db.cpu().numpy(), g64.sum(axis=(0, 2))) <= 1e-5
 
 
 def test_running_statistics_follow_the_layer(ops):
