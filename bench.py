@@ -157,8 +157,8 @@ def run_reference(args):
 
 
 def workload_config(n):
-    return {"workload": "data-parallel MLP training (BASELINE config 5 at 8192 samples per GPU) + Linear fwd+bwd "
-                        "M=N=K=8192 (BASELINE config 2)",
+    return {"workload": "data-parallel MLP training (benchmark config 5: five 8192-wide layers + 1024 classes, 8192 samples "
+                        "per GPU) + Linear fwd+bwd M=N=K=8192 (benchmark config 2)",
             "layers": SIZES, "per_gpu_batch": PER_GPU_BATCH, "global_batch": PER_GPU_BATCH * n, "optimizer": "adam",
             "precision": "3xTF32", "parallelism": f"dp{n}", "l2": "inputs (2 x 256 MiB per rank) larger than L2"}
 
