@@ -287,8 +287,9 @@ def run_ours(args):
     if clocks is not None:
         line["clocks"] = clocks
 
-    # ---- N = 1 extras: Linear fwd+bwd at 8192^3, roofline of the GEMM, CPU baseline
-    if world == 1:
+    # ---- rank 0 extras: Linear fwd+bwd at 8192^3 and the roofline of the GEMM (every N; the other ranks wait at the
+    #      barrier below, so the kernel is timed on a GPU that runs nothing else); CPU baseline at N = 1 only
+    if rank == 0:
         peaks = measured_peaks()
         n = LIN
         x = torch.randn((n, n), device=dev, generator=g)
@@ -343,16 +344,19 @@ def run_ours(args):
                             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                             "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
                             "traffic": GEMM_DRAM_TRAFFIC_BYTES}
-        try:
-            cb = time_reference_cpu(4, 1)
-        except Exception as ex:  # the checker must never take the measured arm down
-            cb = {"error": repr(ex)}
+        cb = None
+        if world == 1:
+            try:
+                cb = time_reference_cpu(4, 1)
+            except Exception as ex:  # the checker must never take the measured arm down
+                cb = {"error": repr(ex)}
         if cb is not None:
             cb.pop("seconds", None)
             line["cpu_baseline"] = cb
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        barrier()
         dist.destroy_process_group()
 
 
