@@ -168,9 +168,38 @@ int conv2d_forward(const float *x, const float *w, const float *b, float *y, int
                        (long long)W);
         return kInvalidArgument;
     }
+    if (precision != ODL_PRECISION_3XTF32 && precision != ODL_PRECISION_TF32)
+    {
+        set_last_error("conv2d: unknown precision %d", precision);
+        return kInvalidArgument;
+    }
     const int terms     = precision == ODL_PRECISION_3XTF32 ? 3 : 1;
     const int64_t rows  = N * OH * OW;
     const int64_t ckk   = C * KH * KW;
+    if (conv_igemm_eligible(N, C, H, W, OC, KH, KW, OH, OW))
+    {
+        // implicit GEMM: no column matrix; only the (small) weight matrix is prepared -- padded to a pitch of 4 floats
+        // when needed and split into its 3xTF32 low part
+        const int64_t ldw = pad4(ckk);
+        const bool w_ok   = ldw == ckk && !(reinterpret_cast<uintptr_t>(w) & 15);
+        const size_t wb   = a256(static_cast<size_t>(OC) * ldw * 4);
+        arena_reset();
+        int rc = arena_reserve(2 * wb);
+        if (rc)
+            return rc;
+        float *w_big   = w_ok ? nullptr : static_cast<float *>(arena_alloc(wb));
+        float *w_small = terms == 3 ? static_cast<float *>(arena_alloc(wb)) : nullptr;
+        if ((!w_ok && !w_big) || (terms == 3 && !w_small))
+            return kCudaError;
+        if (w_big || w_small)
+        {
+            rc = split_launch(w, ckk, (int)OC, (int)ckk, nullptr, 0, w_big, w_small, ldw, nullptr, stream);
+            if (rc)
+                return rc;
+        }
+        return conv_igemm_launch(x, w_big ? w_big : w, w_small, ldw, b, scale, y, N, C, H, W, OC, KH, KW, S, P, OH, OW, act,
+                                 terms, stream);
+    }
     const int64_t ldcol = pad4(ckk);
     const size_t colb   = a256(static_cast<size_t>(rows) * ldcol * 4);
     arena_reset();

@@ -50,6 +50,8 @@ def main():
     ap.add_argument("--precision", default="3xtf32")
     ap.add_argument("--layout", default="nt")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--explicit", action="store_true", help="conv: force the im2col + GEMM forward path")
+    ap.add_argument("--batch", type=int, default=16, help="conv: images per batch")
     ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
     a = ap.parse_args()
     capi.init(0)
@@ -166,7 +168,8 @@ def main():
               f"fwd+bwd {tot:.3f} ms = {3 * f / tot:.0f} TFLOP/s")
     else:
         C, OC, k, s, p, hw = CONV_LAYERS[a.layer]
-        x = torch.rand(16, C, hw, hw, device="cuda")
+        capi.lib().odl_debug_set_conv_mode(1 if a.explicit else 0)
+        x = torch.rand(a.batch, C, hw, hw, device="cuda")
         w = torch.randn(OC, C, k, k, device="cuda") * (2.0 / (C * k * k)) ** 0.5
         b = torch.zeros(OC, device="cuda")
         y = ops.conv2d_forward(x, w, b, s, p, precision=prec)
@@ -174,7 +177,8 @@ def main():
         msf = timed(lambda: ops.conv2d_forward(x, w, b, s, p, precision=prec), a.iters)
         msb = timed(lambda: ops.conv2d_backward(gy, x, w, s, p, precision=prec), a.iters)
         ideal = 4 * (x.numel() + w.numel() + y.numel())
-        print(f"conv layer {a.layer} ({C}->{OC} k{k} s{s} p{p} on {hw}x{hw}, batch 16, {a.precision}): forward {msf:.4f} ms "
+        print(f"conv layer {a.layer} ({C}->{OC} k{k} s{s} p{p} on {hw}x{hw}, batch {a.batch}, {a.precision}, "
+              f"{'im2col + GEMM' if a.explicit else 'implicit GEMM'} forward): forward {msf:.4f} ms "
               f"({ideal / msf / 1e6:.1f} GB/s of ideal traffic), backward {msb:.4f} ms")
 
 

@@ -357,6 +357,45 @@ def test_conv2d_vs_oracle(ops, orc, N, C, H, W, OC, k, s, p):
         assert max_rel_err(host(gb), db_o) <= 1e-5
 
 
+IGEMM_CASES = CONV_CASES + [(3, 3, 33, 29, 16, 6, 2, 2),      # ragged pixel count, K = 108 (not a multiple of 32)
+                            (2, 5, 11, 13, 70, 3, 1, 1),      # K = 45 (not a multiple of 4: padded weights), 64 < OC
+                            (1, 8, 14, 14, 130, 3, 2, 0),     # OC > 128: two column tiles
+                            (1, 128, 6, 6, 32, 3, 1, 1),      # K = 1152, the longest reduction of the implicit path
+                            (1, 130, 6, 6, 8, 3, 1, 1)]       # K = 1170: falls back to the explicit path
+
+
+@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES)
+@pytest.mark.parametrize("precision", ["3xtf32", "tf32"])
+def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k, s, p, precision):
+    """The forward pass has two implementations -- implicit GEMM (tiles of the column matrix gathered in shared memory) and
+    im2col + GEMM; both against the oracle, with and without bias, with the fused activations."""
+    from origindl_b200 import capi
+
+    prec, tol = (capi.PRECISION_3XTF32, 1e-5) if precision == "3xtf32" else (capi.PRECISION_TF32, 5e-3)
+    rng = np.random.default_rng(N * 7 + C + H + OC + k)
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = (0.1 * rng.standard_normal(OC)).astype(np.float32)
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    y_o, y_nb = np.empty((N, OC, OH, OW), np.float32), np.empty((N, OC, OH, OW), np.float32)
+    orc.oracle_conv2d_forward(x, w, fptr(b), y_o, N, C, H, W, OC, k, k, s, p)
+    orc.oracle_conv2d_forward(x, w, None, y_nb, N, C, H, W, OC, k, k, s, p)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    try:
+        for mode in (0, 1):
+            capi.lib().odl_debug_set_conv_mode(mode)
+            assert max_rel_err(host(ops.conv2d_forward(xd, wd, bd, s, p, precision=prec)), y_o) <= tol
+            assert max_rel_err(host(ops.conv2d_forward(xd, wd, None, s, p, precision=prec)), y_nb) <= tol
+            relu = host(ops.conv2d_forward(xd, wd, bd, s, p, relu=1, precision=prec))
+            assert max_rel_err(relu, np.maximum(y_o, 0)) <= tol
+            silu = host(ops.conv2d_forward(xd, wd, bd, s, p, relu=2, precision=prec))
+            z = y_o.astype(np.float64)
+            assert max_rel_err(silu, z / (1 + np.exp(-z))) <= tol
+    finally:
+        capi.lib().odl_debug_set_conv_mode(0)
+    capi.device_status()
+
+
 def test_conv2d_golden_vectors_from_reference(ops):
     g = np.load(GOLDEN / "reference_vectors.npz")
     N, C, H, W, OC, k, s, p = (int(v) for v in g["conv_cfg"])
