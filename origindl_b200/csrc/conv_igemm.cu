@@ -38,6 +38,8 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads  = 64 + 32 * kEpiWarps;
 constexpr int kStages   = 2;
 constexpr int kAuxBytes = 256;
+constexpr int kMaxK     = 1152;                  // longest reduction C*KH*KW the kernel takes
+constexpr int kTabBytes = (kMaxK + 32) * 8;      // per-k lookup table {offset, kh << 16 | kw}, padded to a K-block
 
 struct IgemmGeom
 {
@@ -52,7 +54,7 @@ struct IgemmCfg
     static constexpr int a_bytes     = kBM * kBK * 4;
     static constexpr int b_bytes     = BN * kBK * 4;
     static constexpr int stage_bytes = 2 * (a_bytes + b_bytes);  // A, A_small, B, B_small
-    static constexpr int smem_bytes  = 1024 + kStages * stage_bytes + kAuxBytes;
+    static constexpr int smem_bytes  = 1024 + kStages * stage_bytes + kAuxBytes + kTabBytes;
     static constexpr int tmem_cols   = BN < 32 ? 32 : BN;
     static constexpr int warp_cols   = BN / 2;
 };
@@ -74,6 +76,7 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
     int *early_out        = const_cast<int *>(abort_f) + 1;
+    int2 *ktab            = reinterpret_cast<int2 *>(base + kStages * Cfg::stage_bytes + kAuxBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -92,6 +95,20 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
     const int m0 = tile_m * kBM, n0 = tile_n * BN;
     const int num_kb = (g.ckk + kBK - 1) / kBK;
 
+    // Per-k table, built once per CTA: x[n, c, h0 + kh, w0 + kw] sits at pix_off + ktab[k].x with
+    // ktab[k].x = (c * H + kh) * W + kw; ktab[k].y = kh << 16 | kw serves the bounds checks of border pixels.
+    // Entries past C*KH*KW (the padding of the last K-block) are marked with y = -1.
+    for (int k = threadIdx.x; k < num_kb * kBK; k += kThreads)
+    {
+        int2 e = make_int2(0, -1);
+        if (k < g.ckk)
+        {
+            const int khw = g.KH * g.KW;
+            const int c = k / khw, rm = k - c * khw, kh = rm / g.KW, kw = rm - kh * g.KW;
+            e = make_int2((c * g.H + kh) * g.W + kw, (kh << 16) | kw);
+        }
+        ktab[k] = e;
+    }
     if (warp == 0 && lane == 0)
     {
         ptx::prefetch_tmap(&tm.b);
@@ -125,7 +142,7 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             for (int kb = 0; kb < num_kb; ++kb)
             {
                 const int s = kb % kStages;
-                if (!ptx::mbar_wait(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_f))
+                if (!ptx::mbar_wait_quiet(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_f))
                     break;
                 uint8_t *sb = tiles + s * Cfg::stage_bytes + 2 * Cfg::a_bytes;
                 ptx::mbar_arrive_expect_tx(&b_full[s], Cfg::b_bytes * (terms == 3 ? 2 : 1));
@@ -138,7 +155,7 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             {
                 const int first = issued > kStages ? issued - kStages : 0;
                 for (int kb = first; kb < issued; ++kb)
-                    ptx::mbar_wait(&b_full[kb % kStages], (kb / kStages) & 1, nullptr);
+                    ptx::mbar_wait_quiet(&b_full[kb % kStages], (kb / kStages) & 1, nullptr);
             }
         }
     }
@@ -153,7 +170,7 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             {
                 const int s       = kb % kStages;
                 const uint32_t ph = (kb / kStages) & 1;
-                if (!ptx::mbar_wait(&a_full[s], ph, abort_f) || !ptx::mbar_wait(&b_full[s], ph, abort_f))
+                if (!ptx::mbar_wait_quiet(&a_full[s], ph, abort_f) || !ptx::mbar_wait_quiet(&b_full[s], ph, abort_f))
                 {
                     ok = false;
                     break;
@@ -206,54 +223,60 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             n           = t / g.OH;
         }
         const int h0 = oh * g.S - g.P, w0 = ow * g.S - g.P;
-        const float *xn = x + static_cast<int64_t>(n) * g.C * g.H * g.W;
-        const int khw   = g.KH * g.KW;
-        bool have       = true;
+        // 32-bit element offsets (the launcher keeps x below 2^31 elements)
+        const int pix_off = (n * g.C * g.H + h0) * g.W + w0;
+        // pixels whose whole window lies inside the image need no bounds checks
+        const bool interior = row_ok && h0 >= 0 && h0 + g.KH <= g.H && w0 >= 0 && w0 + g.KW <= g.W;
+        bool have           = true;
+        // The 16 values of K-block kb are loaded into registers one K-block ahead of the stores: the loads need no
+        // barrier (x is read-only), so their latency overlaps the previous block's stores, fence and hand-over.
+        auto gather = [&](int kb, float (&v)[16]) {
+            const int2 *tab = ktab + kb * kBK + 16 * h;  // this thread's 16 consecutive k (same for the whole warp)
+            if (interior)
+            {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                {
+                    const int2 e = tab[i];
+                    v[i]         = e.y >= 0 ? __ldg(x + pix_off + e.x) : 0.f;
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                {
+                    const int2 e  = tab[i];
+                    const int hh  = h0 + (e.y >> 16), ww = w0 + (e.y & 0xffff);
+                    const bool in = row_ok && e.y >= 0 && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W;
+                    v[i]          = in ? __ldg(x + pix_off + e.x) : 0.f;
+                }
+            }
+        };
+        float v[16], v_next[16];
+        gather(0, v_next);
         for (int kb = 0; kb < num_kb; ++kb)
         {
             const int s = kb % kStages;
-            have        = __all_sync(0xffffffffu, ptx::mbar_wait(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_f));
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                v[i] = v_next[i];
+            if (kb + 1 < num_kb)
+                gather(kb + 1, v_next);
+            have = __all_sync(0xffffffffu, ptx::mbar_wait_quiet(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_f));
             if (!have)
                 break;
-            // this thread's 16 consecutive k of the K-block: k = kb*32 + 16*h + i
-            int k  = kb * kBK + 16 * h;
-            int c  = k / khw;
-            int rm = k - c * khw;
-            int kh = rm / g.KW;
-            int kw = rm - kh * g.KW;
             uint8_t *row_big   = tiles + s * Cfg::stage_bytes + r * 128;
             uint8_t *row_small = row_big + Cfg::a_bytes;
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4)
             {
-                float v[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    float val = 0.f;
-                    if (row_ok && k < g.ckk)
-                    {
-                        const int hh = h0 + kh, ww = w0 + kw;
-                        if (hh >= 0 && hh < g.H && ww >= 0 && ww < g.W)
-                            val = __ldg(xn + (static_cast<int64_t>(c) * g.H + hh) * g.W + ww);
-                    }
-                    v[i] = val;
-                    ++k;
-                    if (++kw == g.KW)
-                    {
-                        kw = 0;
-                        if (++kh == g.KH)
-                        {
-                            kh = 0;
-                            ++c;
-                        }
-                    }
-                }
                 const int chunk = ((4 * h + j4) ^ (r & 7)) * 16;  // 128-byte swizzle: chunk index XOR row-in-atom
-                *reinterpret_cast<float4 *>(row_big + chunk) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4 *>(row_big + chunk) = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
                 if (terms == 3)
                     *reinterpret_cast<float4 *>(row_small + chunk) =
-                        make_float4(tf32_small(v[0]), tf32_small(v[1]), tf32_small(v[2]), tf32_small(v[3]));
+                        make_float4(tf32_small(v[4 * j4]), tf32_small(v[4 * j4 + 1]), tf32_small(v[4 * j4 + 2]),
+                                    tf32_small(v[4 * j4 + 3]));
             }
             ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
             __syncwarp();
@@ -261,7 +284,7 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
                 ptx::mbar_arrive(&a_full[s]);
         }
         if (have)
-            have = __all_sync(0xffffffffu, ptx::mbar_wait(acc_full, 0, abort_f));
+            have = __all_sync(0xffffffffu, ptx::mbar_wait_quiet(acc_full, 0, abort_f));
         if (have)
         {
             ptx::tc_fence_after_sync();
@@ -331,7 +354,7 @@ int g_conv_mode = 0;
 bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW)
 {
     const int64_t ckk = C * KH * KW, rows = N * OH * OW;
-    return g_conv_mode != 1 && ckk <= 1152 && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 40);
+    return g_conv_mode != 1 && ckk <= 1152 && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
 }
 
 // w_big / w_small: the weights as a K-major [OC][ldw] matrix (ldw a multiple of 4, 16-byte aligned) and its low part.

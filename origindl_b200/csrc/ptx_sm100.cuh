@@ -77,6 +77,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 
+// try_wait with an explicit suspend-time hint: the thread may sleep in hardware until the phase completes or the hint
+// (nanoseconds) runs out, instead of returning after the short default limit.  For waits of warps that share an SM
+// with instruction-bound work, where a polling loop would take the issue slots that work needs.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait for long waits on a busy SM: suspends in hardware (20 us per try) and sleeps between tries.
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
+{
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = globaltimer_ns();
+    while (true)
+    {
+        if (mbar_try_wait_hint(bar, parity, 20000u))
+            return true;
+        __nanosleep(64);
+        if (abort_flag && *abort_flag)
+            return false;
+        if (globaltimer_ns() - t0 > ODL_WAIT_NS)
+        {
+            if (abort_flag)
+                *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
 // Bounded wait.  `abort_flag` (shared memory, may be null) lets one role's time-out release the others.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {
