@@ -258,8 +258,9 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     const size_t gyb    = a256(static_cast<size_t>(rows) * pad4(OC) * 4);
     const size_t ctb    = a256(static_cast<size_t>(ckk) * ldt * 4);
     arena_reset();
-    int rc = arena_reserve((gw ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx ? ctb : 0) + 2 * operand_worst(rows, OC) +
-                           operand_worst(OC, ckk));
+    const bool dx_direct = gx && conv_dx_direct_eligible(N, C, H, W, OC, KH, KW, S);
+    int rc = arena_reserve((gw ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct ? ctb : 0) +
+                           2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
     if (gb)
@@ -267,6 +268,14 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
         rc = channel_sum_launch(gy, gb, N, OC, hw, stream);
         if (rc)
             return rc;
+    }
+    // Input gradient of a conv with few products per output: direct fp32 kernel, no column-gradient matrix
+    if (dx_direct)
+    {
+        rc = conv_dx_direct_launch(gy, w, gx, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        if (rc)
+            return rc;
+        gx = nullptr;
     }
     if (!gw && !gx)
         return kOk;

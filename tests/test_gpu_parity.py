@@ -396,6 +396,36 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
     capi.device_status()
 
 
+@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES + [(2, 6, 17, 15, 12, 5, 3, 2), (1, 2, 9, 9, 3, 4, 2, 1)])
+def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
+    """gx has two implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
+    BIT-EXACT against the oracle) and GEMM + gather col2im (3xTF32, 1e-5).  Both gradient layouts."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(N * 11 + C + H + OC + k + s)
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    dy = rng.standard_normal((N, OC, OH, OW)).astype(np.float32)
+    direct = OC * (-(-k // s)) ** 2 <= 256
+    try:
+        for layout in (0, 1):
+            dx_o = np.empty_like(x)
+            orc.oracle_conv2d_backward(dy, x, w, fptr(dx_o), None, None, N, C, H, W, OC, k, k, s, p, layout)
+            capi.lib().odl_debug_set_conv_mode(0)
+            gx, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+            if direct:
+                assert np.array_equal(host(gx), dx_o)
+            else:
+                assert max_rel_err(host(gx), dx_o) <= 1e-5
+            capi.lib().odl_debug_set_conv_mode(1)
+            gx, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+            assert max_rel_err(host(gx), dx_o) <= 1e-5
+    finally:
+        capi.lib().odl_debug_set_conv_mode(0)
+    capi.device_status()
+
+
 def test_conv2d_golden_vectors_from_reference(ops):
     g = np.load(GOLDEN / "reference_vectors.npz")
     N, C, H, W, OC, k, s, p = (int(v) for v in g["conv_cfg"])
