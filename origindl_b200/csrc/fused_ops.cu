@@ -259,7 +259,8 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     const size_t ctb    = a256(static_cast<size_t>(ckk) * ldt * 4);
     arena_reset();
     const bool dx_direct = gx && conv_dx_direct_eligible(N, C, H, W, OC, KH, KW, S);
-    int rc = arena_reserve((gw ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct ? ctb : 0) +
+    const bool dw_direct = gw && conv_dw_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW);
+    int rc = arena_reserve((gw && !dw_direct ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct ? ctb : 0) +
                            2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
@@ -276,6 +277,14 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
         if (rc)
             return rc;
         gx = nullptr;
+    }
+    // Weight gradient of a small conv: direct fp32 kernel, the column matrix only ever exists tile-wise in shared memory
+    if (gw && conv_dw_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW))
+    {
+        rc = conv_dw_direct_launch(x, gy, gw, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        if (rc)
+            return rc;
+        gw = nullptr;
     }
     if (!gw && !gx)
         return kOk;

@@ -398,8 +398,9 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
 
 @pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES + [(2, 6, 17, 15, 12, 5, 3, 2), (1, 2, 9, 9, 3, 4, 2, 1)])
 def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
-    """gx has two implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
-    BIT-EXACT against the oracle) and GEMM + gather col2im (3xTF32, 1e-5).  Both gradient layouts."""
+    """gx and gw each have two implementations.  gx: a direct fp32 kernel (few products per output; the reference's summation order, so
+    BIT-EXACT against the oracle) and GEMM + gather col2im (3xTF32, 1e-5); gw: a direct fp32 kernel for small layers and im2col +
+    split-K GEMM.  Both gradient layouts."""
     from origindl_b200 import capi
 
     rng = np.random.default_rng(N * 11 + C + H + OC + k + s)
@@ -410,17 +411,18 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
     direct = OC * (-(-k // s)) ** 2 <= 256
     try:
         for layout in (0, 1):
-            dx_o = np.empty_like(x)
-            orc.oracle_conv2d_backward(dy, x, w, fptr(dx_o), None, None, N, C, H, W, OC, k, k, s, p, layout)
+            dx_o, dw_o = np.empty_like(x), np.empty_like(w)
+            orc.oracle_conv2d_backward(dy, x, w, fptr(dx_o), fptr(dw_o), None, N, C, H, W, OC, k, k, s, p, layout)
             capi.lib().odl_debug_set_conv_mode(0)
-            gx, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+            gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
             if direct:
                 assert np.array_equal(host(gx), dx_o)
             else:
                 assert max_rel_err(host(gx), dx_o) <= 1e-5
+            assert max_rel_err(host(gw), dw_o) <= 1e-5  # direct fp32 kernel when OC <= 32 and C*KH*KW <= 256
             capi.lib().odl_debug_set_conv_mode(1)
-            gx, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
-            assert max_rel_err(host(gx), dx_o) <= 1e-5
+            gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+            assert max_rel_err(host(gx), dx_o) <= 1e-5 and max_rel_err(host(gw), dw_o) <= 1e-5
     finally:
         capi.lib().odl_debug_set_conv_mode(0)
     capi.device_status()
