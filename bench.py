@@ -34,7 +34,8 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "MLP train samples/s @1/2/4/8 B200; Linear fwd+bwd TFLOP/s vs TF32 peak"
 SIZES = [8192, 8192, 8192, 8192, 8192, 1024]
-PER_GPU_BATCH = 8192
+PER_GPU_BATCH = 8192  # weak scaling (default); --global-batch B switches to strong scaling with B / N samples per GPU
+SCALING = "weak"
 LR = 1e-3
 LIN = 8192  # M = N = K of the Linear forward+backward leg
 
@@ -149,7 +150,7 @@ def run_reference(args):
         return
     line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": "samples/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * res["seconds"] / steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": SCALING, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args.gpus),
             "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": res["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -157,10 +158,10 @@ def run_reference(args):
 
 
 def workload_config(n):
-    return {"workload": "data-parallel MLP training (benchmark config 5: five 8192-wide layers + 1024 classes, 8192 samples "
-                        "per GPU) + Linear fwd+bwd M=N=K=8192 (benchmark config 2)",
+    return {"workload": f"data-parallel MLP training (benchmark config 5: five 8192-wide layers + 1024 classes, {PER_GPU_BATCH} "
+                        "samples per GPU) + Linear fwd+bwd M=N=K=8192 (benchmark config 2)",
             "layers": SIZES, "per_gpu_batch": PER_GPU_BATCH, "global_batch": PER_GPU_BATCH * n, "optimizer": "adam",
-            "precision": "3xTF32", "parallelism": f"dp{n}", "l2": "inputs (2 x 256 MiB per rank) larger than L2"}
+            "precision": "3xTF32", "parallelism": f"dp{n}", "l2": f"inputs (2 x {PER_GPU_BATCH * SIZES[0] * 4 >> 20} MiB per rank) larger than L2"}
 
 
 # ------------------------------------------------------------------------------------------------ our arm
@@ -244,7 +245,7 @@ def run_ours(args):
     #      thread issuing the H2D copy of the following batches on a copy stream) -> train_step -> loss D2H
     from origindl_b200.loader import DataLoader
 
-    e2e_batches = 4
+    e2e_batches = 4 if PER_GPU_BATCH <= 8192 else 2
     hx = torch.randn((e2e_batches * PER_GPU_BATCH, SIZES[0]), generator=torch.Generator().manual_seed(2000 + rank))
     ht = torch.randint(0, SIZES[-1], (e2e_batches * PER_GPU_BATCH,), generator=torch.Generator().manual_seed(3000 + rank))
     loader = DataLoader(hx.numpy(), ht.numpy(), PER_GPU_BATCH, shuffle=False, resident=False, device=local)
@@ -277,7 +278,7 @@ def run_ours(args):
     torch.cuda.empty_cache()
 
     line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": SCALING,
             "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)", "data": "synthetic",
             "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world,
@@ -371,7 +372,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="strong scaling: fix the global batch (e.g. 65536) and give every rank global / N samples; "
+                         "default 0 = weak scaling with 8192 samples per GPU")
     args = ap.parse_args()
+    if args.global_batch:
+        global PER_GPU_BATCH, SCALING
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if args.global_batch % world:
+            raise SystemExit(f"--global-batch {args.global_batch} is not divisible by {world} ranks")
+        PER_GPU_BATCH, SCALING = args.global_batch // world, "strong"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
