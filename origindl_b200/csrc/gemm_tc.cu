@@ -519,7 +519,7 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         else
             bn = 64;  // small problems are bound by the latency of one CTA's K loop: spread them over more SMs
     }
-    if (gemm_pair_eligible(p, bn, a_mn, b_mn))
+    if (gemm_pair_eligible(p, bn, a_mn, b_mn, terms))
         return gemm_pair_launch(A, A_small, lda, a_mn, B, B_small, ldb, b_mn, p, terms, stream);
     TmapPack tm;
     std::memset(&tm, 0, sizeof(tm));

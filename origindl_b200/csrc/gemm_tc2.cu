@@ -351,17 +351,19 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
 int g_pair_mode = 0;
 
 // True when gemm_tc_launch should hand this problem to the pair kernel.
-// Measured on B200 (8192^3): with an MN-major operand (many 4 KB boxes per stage) the pair kernel is 25-30 % faster
-// (3xTF32 182 -> 232 TFLOP/s, TF32 400 -> 500); with two K-major operands it is level in 3xTF32 and ~7 % slower in
-// plain TF32, so those stay on the 1-CTA kernel.
-bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn)
+// Measured on B200 at 8192^3 with the two kernels alternated inside one run (the GPU sits at its power cap during long
+// runs, so numbers taken minutes apart differ by up to 8 %): 3xTF32 is faster on pairs in every layout (K-major x
+// K-major 203 -> 225 TFLOP/s, with an MN-major operand 181 -> 225): the 1-CTA kernel saturates its SM's shared-memory
+// bandwidth (240 KB per K-block against 160 KB per CTA of a pair).  Plain TF32 gains only with an MN-major operand
+// (420 -> 505; many 4 KB boxes per stage) and loses with two K-major operands (529 -> 486), which stay on one CTA.
+bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms)
 {
     if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiAtomic)))
         return false;
     if (g_pair_mode == 2)
         return true;
     const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
-    return pairs >= 74 && (a_mn || b_mn);  // at least one pair per two SMs
+    return pairs >= 74 && (terms == 3 || a_mn || b_mn);  // at least one pair per two SMs
 }
 
 int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
