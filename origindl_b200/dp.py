@@ -16,6 +16,16 @@ def shard_rows(global_batch: int, rank: int, world: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+def shard_epoch_order(order, rank: int, world: int):
+    """The samples of one epoch that `rank` trains on: every rank draws the SAME permutation `order` (same seed) and
+    takes the positions rank, rank + world, ... of it, after trimming the tail so that all ranks get equally many
+    samples (a data-parallel step needs every rank to have a batch).  Together the shards cover each kept sample once."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a world of {world}")
+    keep = (len(order) // world) * world
+    return order[:keep][rank::world]
+
+
 def layer_buckets_packed(sizes) -> list[tuple[int, int]]:
     """(offset, count) of [dW_l, db_l] for every layer in the PACKED parameter order
     [W_0 {in,out}, b_0, W_1, b_1, ...] (Module::named_parameters order)."""

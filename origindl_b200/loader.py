@@ -10,7 +10,8 @@ Semantics kept: samples are flattened to `features` values; batches follow the i
 an epoch is short unless `drop_last`; next() past the end raises; integer labels come out as int64.  The reference
 seeds its shuffle from std::random_device (dataloader.cpp:29-31), so its order is not reproducible; here `seed` makes
 it so (None = from the OS, like the reference): epoch e uses the e-th permutation drawn from that generator, in
-either mode.
+either mode.  For data-parallel training `shard=(rank, world)` gives every rank the positions rank, rank + world, ... of
+the epoch's (common) permutation.
 
 What differs is where the work happens.  The reference assembles each batch on the host one sample at a time and the
 training loop copies it to the device.  Here there are two modes:
@@ -32,13 +33,13 @@ import threading
 import numpy as np
 import torch
 
-from . import capi
+from . import capi, dp
 
 
 class DataLoader:
     def __init__(self, inputs, labels, batch_size: int, shuffle: bool = True, seed: int | None = None,
                  drop_last: bool = False, resident: bool | None = None, resident_limit_bytes: int = 64 << 30,
-                 depth: int = 3, pin_limit_bytes: int = 16 << 30, device: int = 0):
+                 depth: int = 3, pin_limit_bytes: int = 16 << 30, device: int = 0, shard: tuple[int, int] | None = None):
         inputs = np.asarray(inputs, np.float32)
         self.n = int(inputs.shape[0])
         if self.n == 0 or batch_size <= 0:
@@ -51,6 +52,10 @@ class DataLoader:
         self.features = int(self.host_x.shape[1])
         self.batch_size, self.shuffle, self.drop_last = int(batch_size), bool(shuffle), bool(drop_last)
         self._rng = np.random.default_rng(seed)
+        # data parallel: shard = (rank, world); every rank must pass the same seed so that all draw the same permutation
+        self.shard = shard
+        if shard is not None and (seed is None and shuffle):
+            raise ValueError("DataLoader: a sharded, shuffled loader needs an explicit seed shared by all ranks")
         self._orders, self._orders_lock, self._drawn = {}, threading.Lock(), 0
         capi.init(device)
         self.resident = (self.host_x.nbytes <= resident_limit_bytes) if resident is None else bool(resident)
@@ -68,7 +73,7 @@ class DataLoader:
             self._slots = [self._Slot(self.batch_size, self.features) for _ in range(max(2, depth))]
             self._worker, self._pending_release = None, None
             self._pinned_x = None
-            if not self.shuffle and self.host_x.nbytes <= pin_limit_bytes:
+            if not self.shuffle and self.shard is None and self.host_x.nbytes <= pin_limit_bytes:
                 # sequential batches are contiguous row ranges: page-lock the data set itself and copy from it directly
                 self._pinned_x = torch.from_numpy(self.host_x).pin_memory()
                 self._pinned_t = torch.from_numpy(self.host_t).pin_memory()
@@ -92,6 +97,8 @@ class DataLoader:
                 order = np.arange(self.n, dtype=np.int64)
                 if self.shuffle:
                     self._rng.shuffle(order)
+                if self.shard is not None:
+                    order = np.ascontiguousarray(dp.shard_epoch_order(order, *self.shard))
                 self._orders[self._drawn] = order
                 self._drawn += 1
             for old in [e for e in self._orders if e < epoch - 1]:
@@ -103,14 +110,15 @@ class DataLoader:
         self.h2d_bytes += self.indices.nbytes
 
     def _rows_at(self, cursor: int) -> int:
-        rows = min(self.batch_size, self.n - cursor)
+        rows = min(self.batch_size, len(self.indices) - cursor)
         return 0 if rows <= 0 or (self.drop_last and rows < self.batch_size) else rows
 
     def has_next(self) -> bool:
         return self._rows_at(self.current) > 0
 
     def __len__(self) -> int:
-        return self.n // self.batch_size if self.drop_last else -(-self.n // self.batch_size)
+        n = len(self.indices)
+        return n // self.batch_size if self.drop_last else -(-n // self.batch_size)
 
     def __iter__(self):
         if self.current:

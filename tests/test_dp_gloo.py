@@ -76,3 +76,20 @@ def test_plan_helpers():
     b = dp.layer_buckets_packed([784, 1000, 1000, 10])
     assert b[0] == (0, 785000) and b[-1][0] + b[-1][1] == 784 * 1000 + 1000 + 1000 * 1000 + 1000 + 10010
     assert dp.reduce_order(3) == [2, 1, 0]
+
+
+def test_epoch_order_shards_cover_the_epoch_once():
+    """DataLoader(shard=(rank, world)): all ranks draw the same permutation and take interleaved positions of it."""
+    import numpy as np
+
+    from origindl_b200 import dp
+
+    order = np.random.default_rng(3).permutation(103)
+    shards = [dp.shard_epoch_order(order, r, 4) for r in range(4)]
+    assert all(len(s) == 25 for s in shards)                       # 103 -> 100 kept, equally many per rank
+    assert np.array_equal(np.sort(np.concatenate(shards)), np.sort(order[:100]))
+    assert np.array_equal(shards[1], order[1:100:4])
+    import pytest
+
+    with pytest.raises(ValueError):
+        dp.shard_epoch_order(order, 4, 4)

@@ -143,3 +143,30 @@ def test_training_from_the_loader_equals_direct_feeding(capi, resident):
         ld.release()
     assert got == want
     ld.close(), direct.close(), fed.close()
+
+
+@pytest.mark.parametrize("resident", [True, False])
+@pytest.mark.parametrize("shuffle", [True, False])
+def test_sharded_loaders_partition_every_epoch(capi, resident, shuffle):
+    """shard=(rank, world): the ranks' loaders (same seed) deliver disjoint samples that together cover the epoch, with
+    equally many batches per rank."""
+    from origindl_b200.loader import DataLoader
+
+    x, t = dataset(210, 8)
+    x[:, 0] = np.arange(210)
+    world = 4
+    loaders = [DataLoader(x, t, 16, shuffle=shuffle, seed=21, resident=resident, shard=(r, world)) for r in range(world)]
+    assert len({len(ld) for ld in loaders}) == 1
+    for epoch in range(2):
+        seen = []
+        for ld in loaders:
+            ids = np.concatenate([bx[:, 0].cpu().numpy() for bx, _ in ld]).astype(np.int64)
+            assert ids.size == 208 // world
+            seen.append(ids)
+        allids = np.concatenate(seen)
+        assert np.unique(allids).size == 208 and allids.max() < 210
+    if shuffle:
+        with pytest.raises(ValueError, match="explicit seed"):
+            DataLoader(x, t, 16, shuffle=True, shard=(0, 2))
+    for ld in loaders:
+        ld.close()
