@@ -550,6 +550,17 @@ extern "C" int odl_debug_set_bk(int bk)
     return 0;
 }
 
+namespace odl
+{
+extern int g_slabs;
+}
+// Test hook: K-slabs per pipeline stage of the 1-CTA kernel in plain TF32 (0 = automatic, 1 or 2).
+extern "C" int odl_debug_set_slabs(int n)
+{
+    odl::g_slabs = n;
+    return 0;
+}
+
 // Test hook: 0 = pair (2-CTA) GEMM kernel where it pays, 1 = never, 2 = whenever the shape allows it.
 extern "C" int odl_debug_set_pair_mode(int mode)
 {

@@ -77,14 +77,17 @@ struct TileCfg
 template <int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
-               const int stages, const int chunk_kb)
+               const int stages, const int chunk_kb, const int slabs)
 {
     using Cfg = TileCfg<BN, BK>;
     extern __shared__ uint8_t smem_raw[];
 
     // ---- carve shared memory (tiles need 1024-byte alignment for the 128-byte swizzle)
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int stage_bytes = Cfg::stage_bytes(terms);
+    // A stage holds `slabs` K-slabs of BK elements each (2 in plain TF32 on the wide tile: twice the MMAs per stage
+    // release, which is what bounds that mode); a "K-block" below is one stage, BK * slabs elements of K.
+    const int slab_bytes  = Cfg::stage_bytes(terms);
+    const int stage_bytes = slab_bytes * slabs;
     uint8_t *tiles        = base;
     float *stg_all        = reinterpret_cast<float *>(base);  // reused after the last MMA has read the ring
     uint8_t *aux_base     = base + stages * stage_bytes;
@@ -125,7 +128,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
     const int m0      = tile_m * kBM;
     const int n0      = tile_n * BN;
     const int kb_first = blockIdx.y * p.kb_per_split;  // split-K: this CTA reduces K-blocks [kb_first, kb_first + num_kb)
-    const int num_kb   = min((p.K + BK - 1) / BK - kb_first, p.kb_per_split);
+    const int num_kb   = min((p.K + BK * slabs - 1) / (BK * slabs) - kb_first, p.kb_per_split);
     const int nchunks  = (num_kb + chunk_kb - 1) / chunk_kb;
 
     // ---- one-time setup
@@ -172,9 +175,11 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                 const uint32_t ph = (kb / stages) & 1;
                 if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
                     break;
-                uint8_t *st = tiles + s * stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
-                const int k0 = (kb_first + kb) * BK;
+                for (int sl = 0; sl < slabs; ++sl)
+                {
+                uint8_t *st  = tiles + s * stage_bytes + sl * slab_bytes;
+                const int k0 = ((kb_first + kb) * slabs + sl) * BK;
                 for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
                 {
                     uint8_t *sa           = st + t * Cfg::a_bytes;
@@ -205,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                         for (int j = 0; j < BN / 32; ++j)
                             ptx::tma_load_2d(sb + j * Cfg::mn_box, mb, &full_bar[s], n0 + 32 * j, k0);
                     }
+                }
                 }
                 ++issued;
             }
@@ -258,7 +264,9 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                    for (int sl = 0; sl < slabs; ++sl)
+                    {
+                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes + sl * slab_bytes);
                     const uint32_t sas = sa + Cfg::a_bytes;
                     const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
                     const uint32_t sbs = sb + Cfg::b_bytes;
@@ -281,6 +289,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                             ptx::mma_tf32_ss(tmem_d, da, db, idesc, first ? 0u : 1u);
                         }
                         first = false;
+                    }
                     }
                     ptx::mma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
                 }
@@ -357,6 +366,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 extern int g_chunk_kb;
 extern int g_split_k;
 extern int g_bk_override;
+extern int g_slabs;
 namespace
 {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -411,7 +421,11 @@ template <int BN, int BK>
 int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int terms, cudaStream_t stream)
 {
     using Cfg        = TileCfg<BN, BK>;
-    const int stages = Cfg::stages(terms);
+    // plain TF32 on the wide tile: two K-slabs per stage when the reduction is long enough to fill the ring
+    int slabs = (terms == 1 && BN == 256 && BK == 32 && p.K >= 8 * BK) ? 2 : 1;
+    if (g_slabs == 1 || g_slabs == 2)
+        slabs = (terms == 1 && BK == 32) ? g_slabs : 1;
+    const int stages = Cfg::stages(terms) / slabs;
     const int smem   = Cfg::smem_bytes(terms);
     static bool attr_set[64] = {};  // one flag per device for THIS instantiation
     int dev = 0;
@@ -431,12 +445,12 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     }
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int num_kb   = (p.K + BK - 1) / BK;
+    const int num_kb   = (p.K + BK * slabs - 1) / (BK * slabs);  // in stages
     // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split adds its
     // partial tile into a zeroed D with atomics, so only the plain epilogue qualifies.
     GemmParams q = p;
     int splits   = 1;
-    if (g_split_k != 1 && p.flags == 0 && tiles_m * tiles_n * 2 <= 148 && num_kb >= 32)
+    if (g_split_k != 1 && p.flags == 0 && tiles_m * tiles_n * 2 <= 148 && num_kb * slabs >= 32)
     {
         splits = g_split_k > 1 ? g_split_k : 148 / (tiles_m * tiles_n);
         if (splits > num_kb / 8)
@@ -456,10 +470,10 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
             return kCudaError;
         }
     }
-    int chunk_kb       = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 64 / BK : q.kb_per_split);
+    int chunk_kb       = g_chunk_kb > 0 ? (g_chunk_kb + slabs - 1) / slabs : (terms == 3 ? 64 / BK : q.kb_per_split);
     if (chunk_kb > q.kb_per_split)
         chunk_kb = q.kb_per_split;
-    gemm_tc_kernel<BN, BK><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb);
+    gemm_tc_kernel<BN, BK><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb, slabs);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
@@ -475,6 +489,8 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
 // Test hook: K-blocks accumulated in TMEM between two drains into registers; 0 = default
 // (64 K elements, i.e. 2 blocks of 32, for 3xTF32; the whole K for plain TF32).
 int g_chunk_kb = 0;
+// Test hook: K-slabs of 32 per pipeline stage in plain TF32 (0 = automatic, 1 or 2).
+int g_slabs = 0;
 // Test hook: 0 = automatic split-K, 1 = never split, n > 1 = force n splits where the epilogue allows it.
 int g_split_k = 0;
 // Test hook: K elements per pipeline stage of the 256-wide tile (16 or 32; 0 = automatic).

@@ -59,12 +59,14 @@ struct PairCfg
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
-                const int stages, const int chunk_kb)
+                const int stages, const int chunk_kb, const int slabs)
 {
     using Cfg = PairCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int stage_bytes = Cfg::stage_bytes(terms);
+    // `slabs` K-slabs of kBK elements per stage (2 in plain TF32: twice the MMAs per stage release)
+    const int slab_bytes  = Cfg::stage_bytes(terms);
+    const int stage_bytes = slab_bytes * slabs;
     uint8_t *tiles        = base;
     float *stg_all        = reinterpret_cast<float *>(base);
     uint8_t *aux_base     = base + stages * stage_bytes;
@@ -110,7 +112,7 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
     const int m0      = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;  // this CTA's rows of A and D
     const int n0      = tile_n * BN;                                      // the pair's columns of D
     const int nb0     = n0 + static_cast<int>(rank) * (BN / 2);           // this CTA's rows of the B tile
-    const int num_kb  = (p.K + kBK - 1) / kBK;
+    const int num_kb  = (p.K + kBK * slabs - 1) / (kBK * slabs);  // stages
     const int nchunks = (num_kb + chunk_kb - 1) / chunk_kb;
 
     if (!skip)
@@ -164,11 +166,13 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                 const uint32_t ph = (kb / stages) & 1;
                 if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
                     break;
-                uint8_t *st = tiles + s * stage_bytes;
                 if (leader)
                     ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * stage_bytes);
                 const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
-                const int k0       = kb * kBK;
+                for (int sl = 0; sl < slabs; ++sl)
+                {
+                uint8_t *st  = tiles + s * stage_bytes + sl * slab_bytes;
+                const int k0 = (kb * slabs + sl) * kBK;
                 for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
                 {
                     uint8_t *sa           = st + t * Cfg::a_bytes;
@@ -199,6 +203,7 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                         for (int j = 0; j < BN / 64; ++j)
                             ptx::tma_load_2d_pair(sb + j * Cfg::mn_box, mb, bar, nb0 + 32 * j, k0);
                     }
+                }
                 }
                 ++issued;
             }
@@ -248,7 +253,9 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                    for (int sl = 0; sl < slabs; ++sl)
+                    {
+                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes + sl * slab_bytes);
                     const uint32_t sas = sa + Cfg::a_bytes;
                     const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
                     const uint32_t sbs = sb + Cfg::b_bytes;
@@ -270,6 +277,7 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                             ptx::mma_tf32_ss_pair(tmem_d, da, db, idesc, first ? 0u : 1u);
                         }
                         first = false;
+                    }
                     }
                     // the stage is free in BOTH CTAs once these MMAs have read it
                     const uint32_t eb = ptx::smem_u32(&empty_bar[s]);
@@ -349,21 +357,24 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
 
 // Test hook: 0 = use the pair kernel where it pays (automatic), 1 = never, 2 = whenever the shape allows it.
 int g_pair_mode = 0;
+extern int g_slabs;
 
-// True when gemm_tc_launch should hand this problem to the pair kernel.
-// Measured on B200 at 8192^3 with the two kernels alternated inside one run (the GPU sits at its power cap during long
-// runs, so numbers taken minutes apart differ by up to 8 %): 3xTF32 is faster on pairs in every layout (K-major x
-// K-major 203 -> 225 TFLOP/s, with an MN-major operand 181 -> 225): the 1-CTA kernel saturates its SM's shared-memory
-// bandwidth (240 KB per K-block against 160 KB per CTA of a pair).  Plain TF32 gains only with an MN-major operand
-// (420 -> 505; many 4 KB boxes per stage) and loses with two K-major operands (529 -> 486), which stay on one CTA.
+// True when gemm_tc_launch should hand this problem to the pair kernel: whenever there is at least one pair per two SMs.
+// Measured on B200 at 8192^3 with the kernels alternated inside one run (the GPU sits at its power cap during long
+// runs, so numbers taken minutes apart differ by up to 8 %), TFLOP/s, 1-CTA -> pairs:
+//   3xTF32: K-major x K-major 203 -> 225, with an MN-major operand 181 -> 225 (the 1-CTA kernel saturates its SM's
+//           shared-memory bandwidth: 240 KB per K-block against 160 KB per CTA of a pair);
+//   TF32 with two K-slabs per stage: K-major x K-major 533 -> 652, MN-major B 443 -> 583, both MN-major 399 -> 506
+//           (with one slab per stage the pair kernel was the slower one for K-major operands: 473).
 bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms)
 {
+    (void)a_mn, (void)b_mn, (void)terms;
     if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiAtomic)))
         return false;
     if (g_pair_mode == 2)
         return true;
     const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
-    return pairs >= 74 && (terms == 3 || a_mn || b_mn);  // at least one pair per two SMs
+    return pairs >= 74;
 }
 
 int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
@@ -389,7 +400,10 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         if ((rc = mk(&tm.b_small, B_small, ldb, b_mn, p.N, BN / 2)))
             return rc;
     }
-    const int stages = Cfg::stages(terms);
+    int slabs = (terms == 1 && p.K >= 8 * kBK) ? 2 : 1;
+    if (g_slabs == 1 || g_slabs == 2)
+        slabs = terms == 1 ? g_slabs : 1;
+    const int stages = Cfg::stages(terms) / slabs;
     const int smem   = Cfg::smem_bytes(terms);
     static bool attr_set[64] = {};
     int dev = 0;
@@ -407,9 +421,9 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         attr_set[dev] = true;
     }
     GemmParams q   = p;
-    const int num_kb = (p.K + kBK - 1) / kBK;
+    const int num_kb = (p.K + kBK * slabs - 1) / (kBK * slabs);
     q.kb_per_split   = num_kb;
-    int chunk_kb     = g_chunk_kb > 0 ? g_chunk_kb : (terms == 3 ? 64 / kBK : num_kb);
+    int chunk_kb     = g_chunk_kb > 0 ? (g_chunk_kb + slabs - 1) / slabs : (terms == 3 ? 64 / kBK : num_kb);
     if (chunk_kb > num_kb)
         chunk_kb = num_kb;
     const int pairs = ((p.M + 2 * kBM - 1) / (2 * kBM)) * ((p.N + BN - 1) / BN);
@@ -426,7 +440,7 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
     attr[0].val.clusterDim.z = 1;
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN>, tm, q, a_mn, b_mn, terms, stages, chunk_kb);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN>, tm, q, a_mn, b_mn, terms, stages, chunk_kb, slabs);
     ++g_launch_count;
     if (e != cudaSuccess)
     {
