@@ -280,15 +280,11 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                     }
                     }
                     // the stage is free in BOTH CTAs once these MMAs have read it
-                    const uint32_t eb = ptx::smem_u32(&empty_bar[s]);
-                    ptx::mma_commit_pair(ptx::map_to_cta(eb, 0));
-                    ptx::mma_commit_pair(ptx::map_to_cta(eb, 1));
+                    ptx::mma_commit_pair_both(&empty_bar[s]);
                 }
                 if (ok)
                 {
-                    const uint32_t fb = ptx::smem_u32(&acc_full[buf]);
-                    ptx::mma_commit_pair(ptx::map_to_cta(fb, 0));
-                    ptx::mma_commit_pair(ptx::map_to_cta(fb, 1));
+                    ptx::mma_commit_pair_both(&acc_full[buf]);
                 }
             }
         }

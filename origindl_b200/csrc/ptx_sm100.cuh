@@ -353,5 +353,17 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr)
                  : "memory");
 }
 
+// The same, signalling the barrier at this shared-memory offset in BOTH CTAs of the pair with one instruction (the
+// commit form with a CTA mask; it signals barriers only and moves no data).  One commit instead of two per stage
+// release matters: every commit costs the tensor pipe on the order of a hundred idle cycles.
+__device__ __forceinline__ void mma_commit_pair_both(uint64_t *bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"(mask)
+                 : "memory");
+}
+
 }  // namespace ptx
 }  // namespace odl
