@@ -8,6 +8,7 @@
     python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
     python -m origindl_b200.profile_case batchnorm --n 64 --cols 64 --rows 25600   (N x C x HW, training fwd + bwd, fused SiLU)
     python -m origindl_b200.profile_case gather  --rows 65536 --cols 1024       (batch assembly from a resident data set)
+    python -m origindl_b200.profile_case mlp --sizes 4096,4096,4096,4096,4096,4096,4096,1000 --batch 8192 --optimizer sgd --iters 10
     python -m origindl_b200.profile_case checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
 
 Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
@@ -39,7 +40,7 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint", "gather", "batchnorm"])
+    ap.add_argument("case", choices=["gemm", "split", "adam", "softmax", "conv", "linear", "checkpoint", "gather", "batchnorm", "mlp"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -52,6 +53,8 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--explicit", action="store_true", help="conv: force the im2col + GEMM forward path")
     ap.add_argument("--batch", type=int, default=16, help="conv: images per batch")
+    ap.add_argument("--sizes", default="4096,4096,4096,4096,4096,4096,4096,1000", help="mlp: layer widths")
+    ap.add_argument("--optimizer", default="sgd", help="mlp: sgd (momentum 0.9) or adam")
     ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
     a = ap.parse_args()
     capi.init(0)
@@ -88,6 +91,28 @@ def main():
         print(f"checkpoint {len(sizes) - 1} x {a.n}^2 ({tr.param_count / 1e6:.1f} M parameters, {nbytes / 1e9:.2f} GB with Adam state): "
               f"save {t1 - t0:.3f} s ({nbytes / (t1 - t0) / 1e9:.2f} GB/s), load {t3 - t2:.3f} s ({nbytes / (t3 - t2) / 1e9:.2f} GB/s), "
               f"parameters identical after reload: {same}")
+    elif a.case == "mlp":
+        import numpy as np
+
+        from .trainer import MLPTrainer
+
+        sizes = [int(v) for v in a.sizes.split(",")]
+        kw = dict(optimizer="sgd", lr=1e-2, momentum=0.9) if a.optimizer == "sgd" else dict(optimizer="adam", lr=1e-3)
+        tr = MLPTrainer(sizes, a.batch, precision=prec, **kw)
+        rng, parts = np.random.default_rng(0), []
+        for i, o in zip(sizes[:-1], sizes[1:]):  # Kaiming-uniform weights {in,out}, zero biases
+            parts += [rng.uniform(-np.sqrt(6.0 / i), np.sqrt(6.0 / i), i * o).astype(np.float32), np.zeros(o, np.float32)]
+        tr.set_params(np.concatenate(parts))
+        x = torch.randn(a.batch, sizes[0], device="cuda")
+        t = torch.randint(0, sizes[-1], (a.batch,), device="cuda", dtype=torch.int32)
+        for _ in range(2):
+            tr.train_step(x, t)
+        ms = timed(lambda: tr.train_step(x, t), a.iters)
+        flops = 6.0 * a.batch * sum(i * o for i, o in zip(sizes[:-1], sizes[1:])) - 2.0 * a.batch * sizes[0] * sizes[1]
+        print(f"mlp {a.sizes} batch {a.batch} {a.optimizer} {a.precision}: {ms:.3f} ms per training step, "
+              f"{a.batch / ms * 1e3:.0f} samples/s, {flops / ms / 1e9:.1f} TFLOP/s (no dX for the first layer), "
+              f"loss {float(tr.loss_tensor()):.4f}")
+        tr.close()
     elif a.case == "batchnorm":
         N, C, HW = a.n, a.cols, a.rows
         x, dy = torch.randn(N, C, HW, 1, device="cuda"), torch.randn(N, C, HW, 1, device="cuda")
