@@ -241,7 +241,16 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
     p.bias    = bias;
     p.scale   = scale;
     p.aux     = mask_src;
-    p.colsum  = colsum;
+    p.colsum    = nullptr;
+    p.ld_colsum = 0;
+    const int slabs = static_cast<int>((M + 127) / 128) * 4;  // 32-row slabs of whole 128-row tiles
+    if (flags & kEpiColsum)
+    {
+        p.ld_colsum = static_cast<int>(pad4(N));
+        p.colsum    = colsum_partial_scratch(slabs, p.ld_colsum);
+        if (!p.colsum)
+            return kCudaError;
+    }
     p.err     = device_error_flag();
     p.M       = (int)M;
     p.N       = (int)N;
@@ -253,7 +262,10 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
     p.kb_per_split = 0;
     const int a_mn = transA ? 1 : 0;
     const int b_mn = transB ? 0 : 1;
-    return gemm_tc_launch(pa.big, pa.small, pa.ld, a_mn, pb.big, pb.small, pb.ld, b_mn, p, terms, g_bn_override, stream);
+    rc = gemm_tc_launch(pa.big, pa.small, pa.ld, a_mn, pb.big, pb.small, pb.ld, b_mn, p, terms, g_bn_override, stream);
+    if (rc == kOk && (flags & kEpiColsum))
+        rc = colsum_finish_launch(p.colsum, slabs, p.ld_colsum, (int)N, colsum, stream);
+    return rc;
 }
 
 int g_bn_override = 0;

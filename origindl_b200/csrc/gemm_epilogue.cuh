@@ -1,7 +1,7 @@
 // Epilogue of the tcgen05 GEMM kernels, shared by the 1-CTA and the 2-CTA variants: takes one warp's accumulator
 // slice out of registers (WARP_COLS columns of 32 rows), transposes it through a padded shared-memory slab and applies
-//   + bias[n] -> ReLU -> ReLU-mask (aux > 0) -> column sums -> store D (+ low TF32 part), or the NCHW scatter store
-// of conv outputs, or the atomic accumulation of split-K partial tiles, with coalesced 128-bit global accesses.
+//   + bias[n] -> ReLU -> ReLU-mask (aux > 0) -> per-slab column sums -> store D (+ low TF32 part), or the NCHW scatter store
+// of conv outputs, or the store of a split-K partial tile into its slice, with coalesced 128-bit global accesses.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -129,14 +129,9 @@ __device__ __forceinline__ void gemm_epilogue_store(const GemmParams &p, float (
                             if (n + jj < p.N)
                                 csum[jj] += v[jj];
                         float *dp = p.D + static_cast<size_t>(m) * p.ldd + n;
-                        if (p.flags & kEpiAtomic)
-                        {
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                if (n + jj < p.N)
-                                    atomicAdd(dp + jj, v[jj]);
-                        }
-                        else if (vec_d && full4)
+                        if (p.flags & kEpiSplitK)
+                            dp += static_cast<size_t>(blockIdx.y) * p.M * p.ldd;  // this split's slice of the scratch
+                        if (vec_d && full4)
                         {
                             *reinterpret_cast<float4 *>(dp) = make_float4(v[0], v[1], v[2], v[3]);
                         }
@@ -175,10 +170,11 @@ __device__ __forceinline__ void gemm_epilogue_store(const GemmParams &p, float (
                     }
                     if (rr == 0)
                     {
+                        float *cp = p.colsum + static_cast<size_t>((m0 >> 5) + q) * p.ld_colsum + n;
 #pragma unroll
                         for (int jj = 0; jj < 4; ++jj)
                             if (n + jj < p.N)
-                                atomicAdd(p.colsum + n + jj, csum[jj]);
+                                cp[jj] = csum[jj];
                     }
                 }
                 __syncwarp();

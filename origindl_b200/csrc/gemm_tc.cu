@@ -366,6 +366,24 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
 extern int g_chunk_kb;
 extern int g_split_k;
 extern int g_bk_override;
+// Second pass of split-K: D[m][n] = sum over splits z (ascending) of slices[z][m][n].
+__global__ void __launch_bounds__(256) splitk_sum_kernel(const float *__restrict__ slices, int splits, int M, int N, int lds,
+                                                         float *__restrict__ D, int ldd)
+{
+    const int64_t total  = static_cast<int64_t>(M) * N;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const size_t slice   = static_cast<size_t>(M) * lds;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    {
+        const int m = static_cast<int>(i / N), n = static_cast<int>(i - static_cast<int64_t>(m) * N);
+        const float *sp = slices + static_cast<size_t>(m) * lds + n;
+        float s         = __ldcg(sp);
+        for (int z = 1; z < splits; ++z)
+            s += __ldcg(sp + z * slice);
+        D[static_cast<size_t>(m) * ldd + n] = s;
+    }
+}
+
 extern int g_slabs;
 namespace
 {
@@ -446,8 +464,9 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_kb   = (p.K + BK * slabs - 1) / (BK * slabs);  // in stages
-    // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split adds its
-    // partial tile into a zeroed D with atomics, so only the plain epilogue qualifies.
+    // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split stores its
+    // partial tile into its own slice of a scratch buffer and a second pass adds the slices in order, so only the
+    // plain epilogue qualifies.
     GemmParams q = p;
     int splits   = 1;
     if (g_split_k != 1 && p.flags == 0 && tiles_m * tiles_n * 2 <= 148 && num_kb * slabs >= 32)
@@ -462,13 +481,11 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     splits         = (num_kb + q.kb_per_split - 1) / q.kb_per_split;
     if (splits > 1)
     {
-        q.flags |= kEpiAtomic;
-        cudaError_t e = cudaMemset2DAsync(q.D, static_cast<size_t>(q.ldd) * 4, 0, static_cast<size_t>(q.N) * 4, q.M, stream);
-        if (e != cudaSuccess)
-        {
-            set_last_error("gemm split-K: clearing D failed: %s", cudaGetErrorString(e));
+        q.flags |= kEpiSplitK;
+        q.ldd = (p.N + 3) & ~3;
+        q.D   = colsum_partial_scratch(splits * p.M, q.ldd);
+        if (!q.D)
             return kCudaError;
-        }
     }
     int chunk_kb       = g_chunk_kb > 0 ? (g_chunk_kb + slabs - 1) / slabs : (terms == 3 ? 64 / BK : q.kb_per_split);
     if (chunk_kb > q.kb_per_split)
@@ -480,6 +497,18 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     {
         set_last_error("gemm_tc_kernel<%d,%d> launch failed: %s", BN, BK, cudaGetErrorString(e));
         return kCudaError;
+    }
+    if (splits > 1)
+    {
+        const int64_t total = static_cast<int64_t>(p.M) * p.N;
+        splitk_sum_kernel<<<static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 8)), 256, 0, stream>>>(
+            q.D, splits, p.M, p.N, q.ldd, p.D, p.ldd);
+        ++g_launch_count;
+        if ((e = cudaGetLastError()) != cudaSuccess)
+        {
+            set_last_error("splitk_sum_kernel launch failed: %s", cudaGetErrorString(e));
+            return kCudaError;
+        }
     }
     return kOk;
 }

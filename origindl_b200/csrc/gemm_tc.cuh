@@ -22,7 +22,8 @@ enum Status : int
 //   v += bias[n]            (kEpiBias)
 //   v  = v > 0 ? v : 0      (kEpiRelu)
 //   v  = aux[m,n] > 0 ? v:0 (kEpiMask)   -- ReLU backward with the forward OUTPUT (or pre-activation) as aux
-//   colsum[n] += v          (kEpiColsum) -- fp32 atomics, one per column per 32-row slab
+//   colsum[slab][n] = sum of v over the 32 rows of slab m/32   (kEpiColsum) -- plain stores of per-slab partial
+//                             sums; the launcher adds them up in slab order afterwards (same bits every run)
 //   D[m,n] = v ; D_small[m,n] = tf32(v - trunc_tf32(v))   (kEpiSmall) -- low part for the 3xTF32 split
 enum EpiFlags : int
 {
@@ -32,7 +33,8 @@ enum EpiFlags : int
     kEpiColsum = 8,
     kEpiSmall  = 16,
     kEpiNCHW   = 32,  // D is [M/ohw][N][ohw] (conv output): row m = img*ohw + r goes to D[(img*N + n)*ohw + r]
-    kEpiAtomic = 64,  // split-K: partial tiles are added to a zeroed D with fp32 atomics (set by the launcher)
+    kEpiSplitK = 64,  // split-K (set by the launcher): the CTAs of split z store their partial tile into slice z of a
+                      // scratch D [splits][M][ldd]; a second pass adds the slices in order (same bits every run)
     kEpiScale  = 128,  // v *= scale[n] before the bias (folded evaluation-mode BatchNorm); kEpiNCHW stores only
     kEpiSilu   = 256,  // v = v / (1 + exp(-v)) after bias / ReLU; kEpiNCHW stores only
 };
@@ -44,7 +46,8 @@ struct GemmParams
     const float *bias;
     const float *scale;  // kEpiScale: per-column factor
     const float *aux;
-    float *colsum;
+    float *colsum;     // kEpiColsum: [ceil(M/128)*4][ld_colsum] per-slab partial column sums (scratch)
+    int ld_colsum;
     int *err;  // device int: non-zero once any CTA gave up on a wait
     int M, N, K;
     int ldd, ld_aux;

@@ -365,7 +365,7 @@ extern int g_slabs;
 bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms)
 {
     (void)a_mn, (void)b_mn, (void)terms;
-    if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiAtomic)))
+    if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiSplitK)))
         return false;
     if (g_pair_mode == 2)
         return true;

@@ -30,6 +30,10 @@ extern int g_split_k;
 int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
                    int64_t ldb, int b_mn, const GemmParams &p, int terms, int bn_hint, cudaStream_t stream);
 
+// Column sums of a GEMM epilogue (kEpiColsum): scratch for the per-slab partial sums (nullptr on allocation failure) and
+// the pass that adds them, in a fixed order, to colsum[0..n_cols).
+float *colsum_partial_scratch(int slabs, int64_t pitch);
+int colsum_finish_launch(const float *partial, int slabs, int64_t pitch, int n_cols, float *colsum, cudaStream_t stream);
 int split_launch(const float *src, int64_t ld_src, int rows, int cols, const float *aux, int64_t ld_aux, float *dst_big,
                  float *dst_small, int64_t ld_dst, float *colsum, cudaStream_t stream);
 

@@ -2,7 +2,9 @@
 //   v = src[r,c]                                  (optionally v = aux[r,c] > 0 ? v : 0  -- ReLU backward mask)
 //   dst_big[r,c]   = v                            (optional: a 16-byte-aligned, padded copy for the tiled loads)
 //   dst_small[r,c] = tf32(v - trunc_tf32(v))      (optional: low part of the 3xTF32 split)
-//   colsum[c]     += sum_r v                      (optional: bias gradient, fp32 atomics per 64-row slab)
+//   colsum[c]     += sum_r v                      (optional: bias gradient; per-slab partial sums are combined in a
+//                                                  fixed order by the last block of a column group, so the result
+//                                                  does not depend on block scheduling: same bits every run)
 // Rows are walked by warps, columns by lanes in 128-bit groups, so every global access is a coalesced float4
 // whenever pointer and pitch allow it; ragged edges and unaligned pitches fall back to scalar accesses.
 #include <cuda_runtime.h>
@@ -17,7 +19,7 @@ namespace
 {
 
 constexpr int kSplitWarps = 8;
-constexpr int kSplitRows  = 64;  // rows per block
+constexpr int kSplitRows  = 64;  // rows per block (256 for tall matrices: fewer slabs for the column sums' last step)
 
 struct SplitParams
 {
@@ -26,8 +28,11 @@ struct SplitParams
     float *dst_big;
     float *dst_small;
     float *colsum;
+    float *partial;    // [gridDim.y][gridDim.x * 128] per-slab column sums (only with colsum)
+    unsigned *done;    // [gridDim.x] slabs finished per column group; left at zero by the launch
     int64_t ld_src, ld_aux, ld_dst;
     int rows, cols;
+    int rows_per_block;
 };
 
 __global__ void __launch_bounds__(kSplitWarps * 32) split_kernel(const SplitParams p)
@@ -36,8 +41,8 @@ __global__ void __launch_bounds__(kSplitWarps * 32) split_kernel(const SplitPara
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int c    = (blockIdx.x * 32 + lane) * 4;
-    const int r0   = blockIdx.y * kSplitRows;
-    const int r1   = min(r0 + kSplitRows, p.rows);
+    const int r0   = blockIdx.y * p.rows_per_block;
+    const int r1   = min(r0 + p.rows_per_block, p.rows);
 
     const bool vec_src = ((p.ld_src & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
     const bool vec_aux = p.aux && ((p.ld_aux & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
@@ -116,7 +121,46 @@ __global__ void __launch_bounds__(kSplitWarps * 32) split_kernel(const SplitPara
         for (int j = 0; j < 4; ++j)
             red[warp][lane * 4 + j] = cs[j];
         __syncthreads();
-        if (warp == 0 && c < p.cols)
+        const int64_t pitch = static_cast<int64_t>(gridDim.x) * 128;
+        if (warp == 0)
+        {
+            float4 s4;
+            float *sp = &s4.x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < kSplitWarps; ++w)
+                    s += red[w][lane * 4 + j];
+                sp[j] = s;
+            }
+            *reinterpret_cast<float4 *>(p.partial + blockIdx.y * pitch + blockIdx.x * 128 + lane * 4) = s4;
+            __threadfence();
+        }
+        // the last block of this column group to finish adds up all slabs, always in slab order
+        __shared__ bool last;
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            __threadfence();
+            last = atomicAdd(p.done + blockIdx.x, 1u) == gridDim.y - 1;
+        }
+        __syncthreads();
+        if (!last)
+            return;
+        __threadfence();
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int y = warp; y < static_cast<int>(gridDim.y); y += kSplitWarps)
+        {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(p.partial + y * pitch + blockIdx.x * 128 + lane * 4));
+            acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
+        }
+        red[warp][lane * 4 + 0] = acc.x, red[warp][lane * 4 + 1] = acc.y;
+        red[warp][lane * 4 + 2] = acc.z, red[warp][lane * 4 + 3] = acc.w;
+        __syncthreads();
+        if (warp == 0)
         {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -126,15 +170,94 @@ __global__ void __launch_bounds__(kSplitWarps * 32) split_kernel(const SplitPara
                 for (int w = 0; w < kSplitWarps; ++w)
                     s += red[w][lane * 4 + j];
                 if (c + j < p.cols)
-                    atomicAdd(p.colsum + c + j, s);
+                    p.colsum[c + j] += s;
             }
         }
+        if (threadIdx.x == 0)
+            p.done[blockIdx.x] = 0;
     }
 }
 
 }  // namespace
 
-// colsum (if given) must be zeroed by the caller; this pass only adds to it.
+namespace
+{
+// Scratch of the column sums: grown on demand (the device is drained first, like the scratch arena), never shrunk.
+float *g_partial        = nullptr;
+size_t g_partial_floats = 0;
+unsigned *g_done        = nullptr;
+size_t g_done_count     = 0;
+
+int colsum_scratch(size_t floats, size_t groups)
+{
+    if (floats > g_partial_floats || groups > g_done_count)
+    {
+        if (cudaDeviceSynchronize() != cudaSuccess)
+            return kCudaError;
+        cudaFree(g_partial);
+        cudaFree(g_done);
+        g_partial = nullptr, g_done = nullptr, g_partial_floats = 0, g_done_count = 0;
+        floats = floats + (floats >> 2);
+        groups = groups < 1024 ? 1024 : 2 * groups;
+        if (cudaMalloc(&g_partial, floats * 4) != cudaSuccess || cudaMalloc(&g_done, groups * 4) != cudaSuccess ||
+            cudaMemset(g_done, 0, groups * 4) != cudaSuccess)
+        {
+            set_last_error("split: cannot allocate %zu bytes of column-sum scratch", floats * 4 + groups * 4);
+            return kCudaError;
+        }
+        g_partial_floats = floats, g_done_count = groups;
+    }
+    return kOk;
+}
+}  // namespace
+
+// Second half of the GEMM epilogue's column sums: colsum[n] += sum over slabs of partial[slab][n], slabs taken in a
+// fixed order (8 interleaved chains, then the chains in order).
+namespace
+{
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float *__restrict__ partial, int slabs, int64_t pitch,
+                                                            int n_cols, float *__restrict__ colsum)
+{
+    __shared__ float red[8][33];
+    const int lane = threadIdx.x & 31, chain = threadIdx.x >> 5;
+    const int n = blockIdx.x * 32 + lane;
+    float s     = 0.f;
+    if (n < n_cols)
+#pragma unroll 8
+        for (int y = chain; y < slabs; y += 8)
+            s += __ldcg(partial + y * pitch + n);
+    red[chain][lane] = s;
+    __syncthreads();
+    if (chain == 0 && n < n_cols)
+    {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+            t += red[w][lane];
+        colsum[n] += t;
+    }
+}
+}  // namespace
+
+float *colsum_partial_scratch(int slabs, int64_t pitch)
+{
+    return colsum_scratch(static_cast<size_t>(slabs) * pitch, 1) == kOk ? g_partial : nullptr;
+}
+
+int colsum_finish_launch(const float *partial, int slabs, int64_t pitch, int n_cols, float *colsum, cudaStream_t stream)
+{
+    colsum_finish_kernel<<<(n_cols + 31) / 32, 256, 0, stream>>>(partial, slabs, pitch, n_cols, colsum);
+    ++g_launch_count;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("colsum_finish_kernel launch failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
+// colsum (if given) must be initialised by the caller (zeros for a plain sum); this pass adds to it.
 int split_launch(const float *src, int64_t ld_src, int rows, int cols, const float *aux, int64_t ld_aux, float *dst_big,
                  float *dst_small, int64_t ld_dst, float *colsum, cudaStream_t stream)
 {
@@ -143,8 +266,16 @@ int split_launch(const float *src, int64_t ld_src, int rows, int cols, const flo
         set_last_error("split: invalid argument (rows=%d cols=%d)", rows, cols);
         return kInvalidArgument;
     }
-    SplitParams p{src, aux, dst_big, dst_small, colsum, ld_src, ld_aux, ld_dst, rows, cols};
-    dim3 grid((cols + 127) / 128, (rows + kSplitRows - 1) / kSplitRows);
+    const int gx  = (cols + 127) / 128;
+    const int rpb = (colsum && rows >= 32768 && static_cast<int64_t>(gx) * (rows / (4 * kSplitRows)) >= 148 * 8) ? 4 * kSplitRows : kSplitRows;
+    dim3 grid(gx, (rows + rpb - 1) / rpb);
+    if (colsum)
+    {
+        const int rc = colsum_scratch(static_cast<size_t>(grid.x) * 128 * grid.y, grid.x);
+        if (rc)
+            return rc;
+    }
+    SplitParams p{src, aux, dst_big, dst_small, colsum, g_partial, g_done, ld_src, ld_aux, ld_dst, rows, cols, rpb};
     split_kernel<<<grid, kSplitWarps * 32, 0, stream>>>(p);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();

@@ -137,3 +137,47 @@ def test_cuda_graph_step_equals_eager_step(trainer_cls):
     assert max_rel_err(graphed.get_params(), eager.get_params()) <= 1e-5
     eager.close()
     graphed.close()
+
+
+def test_training_and_reductions_are_reproducible_bit_for_bit(trainer_cls):
+    """Same inputs, same bits: bias gradients (column sums in the dY pass and in the dX GEMM's epilogue) and split-K
+    GEMMs add their partial sums in a fixed order, as the reference's sequential CPU loops do -- no floating-point
+    atomics on this path."""
+    from origindl_b200 import ops
+
+    rng = np.random.default_rng(8)
+    sizes, batch = [200, 384, 256, 10], 512
+    params = _libs.mlp_params(rng, sizes)
+    xs = rng.standard_normal((2, batch, sizes[0])).astype(np.float32)
+    ts = rng.integers(0, 10, (2, batch)).astype(np.int32)
+    runs = []
+    for _ in range(3):
+        tr = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+        tr.set_params(params)
+        losses = run(tr, xs, ts, 6)
+        runs.append((losses, tr.get_grads(), tr.get_params()))
+        tr.close()
+    for other in runs[1:]:
+        for a, b in zip(runs[0], other):
+            assert np.array_equal(a, b)
+    # split-K (few output tiles, long reduction) and the masked column sums of Linear's backward, each run three times
+    a, b = torch.randn(256, 16384, device="cuda"), torch.randn(192, 16384, device="cuda")
+    outs = [ops.gemm(a, b, trans_b=True).clone() for _ in range(3)]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ref = a.double() @ b.double().t()
+    assert ((outs[0].double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
+    x, w = torch.randn(4096, 300, device="cuda"), torch.randn(520, 300, device="cuda")
+    y, dy = torch.randn(4096, 520, device="cuda"), torch.randn(4096, 520, device="cuda")
+    grads = [[t.clone() for t in ops.linear_backward(x, w, dy, y=y)] for _ in range(3)]
+    for other in grads[1:]:
+        assert all(torch.equal(p, q) for p, q in zip(grads[0], other))
+    # column sums taken in a GEMM's epilogue (ragged M and N)
+    a, b = torch.randn(1000, 264, device="cuda"), torch.randn(264, 300, device="cuda")
+    sums = []
+    for _ in range(3):
+        cs = torch.zeros(300, device="cuda")
+        d = ops.gemm(a, b, colsum=cs)
+        sums.append(cs)
+    assert torch.equal(sums[0], sums[1]) and torch.equal(sums[0], sums[2])
+    want = (a.double() @ b.double()).sum(0)
+    assert ((sums[0].double() - want).abs().max() / want.abs().max()).item() <= 1e-5
