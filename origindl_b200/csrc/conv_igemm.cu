@@ -387,6 +387,55 @@ int conv_igemm_launch(const float *x, const float *w_big, const float *w_small, 
     return bn == 64 ? launch_igemm<64>(tm, x, g, p, terms, stream) : launch_igemm<128>(tm, x, g, p, terms, stream);
 }
 
+// ---- input gradient of a stride-1 convolution as a convolution: gx = conv(gy, Wf, pad K-1-P) with
+//      Wf[c][oc][kh][kw] = W[oc][c][KH-1-kh][KW-1-kw].  This kernel writes Wf as the K-major [C][ldf] matrix the implicit
+//      GEMM reads (pitch ldf >= OC*KH*KW, padding zeroed) together with its 3xTF32 low part.
+namespace
+{
+__global__ void __launch_bounds__(256) conv_weight_flip_kernel(const float *__restrict__ w, float *__restrict__ wf,
+                                                               float *__restrict__ wf_small, int OC, int C, int KH, int KW,
+                                                               int ldf)
+{
+    const int c = blockIdx.y, kk = KH * KW;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < ldf; j += gridDim.x * blockDim.x)
+    {
+        float v = 0.f;
+        if (j < OC * kk)
+        {
+            const int oc = j / kk, t = j - oc * kk;
+            v = __ldg(w + (static_cast<size_t>(oc) * C + c) * kk + (kk - 1 - t));  // both kernel axes reversed
+        }
+        wf[static_cast<size_t>(c) * ldf + j] = v;
+        if (wf_small)
+            wf_small[static_cast<size_t>(c) * ldf + j] = tf32_small(v);
+    }
+}
+}  // namespace
+
+bool conv_dx_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int OH,
+                            int OW)
+{
+    return S == 1 && KH == KW && P <= KH - 1 && conv_igemm_eligible(N, OC, OH, OW, C, KH, KW, (int)H, (int)W);
+}
+
+// wf / wf_small: scratch of C * pad4(OC*KH*KW) floats each (wf_small may be null in plain TF32).
+int conv_dx_igemm_launch(const float *gy, const float *w, float *wf, float *wf_small, float *gx, int64_t N, int64_t C,
+                         int64_t H, int64_t W, int64_t OC, int KH, int KW, int P, int OH, int OW, int terms, cudaStream_t stream)
+{
+    const int ldf = static_cast<int>((OC * KH * KW + 3) & ~int64_t(3));
+    conv_weight_flip_kernel<<<dim3((ldf + 255) / 256, (unsigned)C), 256, 0, stream>>>(w, wf, wf_small, (int)OC, (int)C, KH,
+                                                                                       KW, ldf);
+    ++g_launch_count;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("conv_weight_flip_kernel launch failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return conv_igemm_launch(gy, wf, wf_small, ldf, nullptr, nullptr, gx, N, OC, OH, OW, C, KH, KW, 1, KH - 1 - P, (int)H,
+                             (int)W, 0, terms, stream);
+}
+
 }  // namespace odl
 
 extern "C" int odl_debug_set_conv_mode(int mode)

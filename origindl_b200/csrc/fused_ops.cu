@@ -260,7 +260,10 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     arena_reset();
     const bool dx_direct = gx && conv_dx_direct_eligible(N, C, H, W, OC, KH, KW, S);
     const bool dw_direct = gw && conv_dw_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW);
-    int rc = arena_reserve((gw && !dw_direct ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct ? ctb : 0) +
+    // stride 1, the correct gradient layout: gx is itself a convolution of gy (no column-gradient matrix, no col2im)
+    const bool dx_igemm = gx && !dx_direct && mode == 0 && conv_dx_igemm_eligible(N, C, H, W, OC, KH, KW, S, P, OH, OW);
+    const size_t wfb    = a256(static_cast<size_t>(C) * pad4(OC * KH * KW) * 4);
+    int rc = arena_reserve((dx_igemm ? 2 * wfb : 0) + (gw && !dw_direct ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct && !dx_igemm ? ctb : 0) +
                            2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
@@ -274,6 +277,17 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     if (dx_direct)
     {
         rc = conv_dx_direct_launch(gy, w, gx, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        if (rc)
+            return rc;
+        gx = nullptr;
+    }
+    if (dx_igemm)
+    {
+        float *wf   = static_cast<float *>(arena_alloc(wfb));
+        float *wf_s = terms == 3 ? static_cast<float *>(arena_alloc(wfb)) : nullptr;
+        if (!wf || (terms == 3 && !wf_s))
+            return kCudaError;
+        rc = conv_dx_igemm_launch(gy, w, wf, wf_s, gx, N, C, H, W, OC, KH, KW, P, OH, OW, terms, stream);
         if (rc)
             return rc;
         gx = nullptr;

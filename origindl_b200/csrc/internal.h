@@ -73,6 +73,11 @@ bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
 int conv_igemm_launch(const float *x, const float *w_big, const float *w_small, int64_t ldw, const float *bias,
                       const float *scale, float *y, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW,
                       int S, int P, int OH, int OW, int act, int terms, cudaStream_t stream);
+// Input gradient of a stride-1 convolution through the same implicit GEMM (flipped, transposed weights).
+bool conv_dx_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int OH,
+                            int OW);
+int conv_dx_igemm_launch(const float *gy, const float *w, float *wf, float *wf_small, float *gx, int64_t N, int64_t C,
+                         int64_t H, int64_t W, int64_t OC, int KH, int KW, int P, int OH, int OW, int terms, cudaStream_t stream);
 bool conv_dw_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
 int conv_dw_direct_launch(const float *x, const float *gy, float *gw, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
                           int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream);

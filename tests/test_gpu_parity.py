@@ -396,11 +396,15 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
     capi.device_status()
 
 
-@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES + [(2, 6, 17, 15, 12, 5, 3, 2), (1, 2, 9, 9, 3, 4, 2, 1)])
+@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES + [(2, 6, 17, 15, 12, 5, 3, 2), (1, 2, 9, 9, 3, 4, 2, 1),
+                                                            (1, 20, 9, 9, 300, 1, 1, 0),   # 1x1, 300 products per gx element
+                                                            (2, 40, 8, 10, 48, 3, 1, 0),   # stride 1 without padding
+                                                            (1, 40, 8, 8, 40, 3, 1, 2)])   # stride 1, pad = k - 1
 def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
-    """gx and gw each have two implementations.  gx: a direct fp32 kernel (few products per output; the reference's summation order, so
-    BIT-EXACT against the oracle) and GEMM + gather col2im (3xTF32, 1e-5); gw: a direct fp32 kernel for small layers and im2col +
-    split-K GEMM.  Both gradient layouts."""
+    """gx has three implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
+    BIT-EXACT against the oracle); for stride 1 in the correct gradient layout the implicit-GEMM convolution of gy with the
+    flipped, transposed weights; and GEMM + gather col2im (both 3xTF32, 1e-5).  gw: a direct fp32 kernel for small layers
+    and im2col + split-K GEMM.  Both gradient layouts, with the implicit paths on and forced off."""
     from origindl_b200 import capi
 
     rng = np.random.default_rng(N * 11 + C + H + OC + k + s)
