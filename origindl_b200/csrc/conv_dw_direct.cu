@@ -154,7 +154,7 @@ extern int g_conv_mode;
 
 bool conv_dw_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW)
 {
-    return g_conv_mode != 1 && OC <= 32 && C * KH * KW <= 256 && N * OH * OW < (int64_t(1) << 31) - 256 &&
+    return g_conv_mode != 1 && g_conv_mode != 2 && OC <= 32 && C * KH * KW <= 256 && N * OH * OW < (int64_t(1) << 31) - 256 &&
            N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
 }
 

@@ -263,7 +263,12 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     // stride 1, the correct gradient layout: gx is itself a convolution of gy (no column-gradient matrix, no col2im)
     const bool dx_igemm = gx && !dx_direct && mode == 0 && conv_dx_igemm_eligible(N, C, H, W, OC, KH, KW, S, P, OH, OW);
     const size_t wfb    = a256(static_cast<size_t>(C) * pad4(OC * KH * KW) * 4);
-    int rc = arena_reserve((dx_igemm ? 2 * wfb : 0) + (gw && !dw_direct ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct && !dx_igemm ? ctb : 0) +
+    // weight gradient without a column matrix (the correct gradient layout only: gy must be a real NCHW tensor)
+    const bool dw_igemm = gw && !dw_direct && mode == 0 && !(reinterpret_cast<uintptr_t>(gy) & 15) &&
+                          conv_dw_igemm_eligible(N, C, H, W, OC, KH, KW, OH, OW);
+    const size_t gysb = a256(static_cast<size_t>(rows) * OC * 4);
+    const size_t slb  = dw_igemm ? a256(conv_dw_igemm_scratch(N, C, OC, KH, KW, OH, OW) * 4) : 0;
+    int rc = arena_reserve((dx_igemm ? 2 * wfb : 0) + (dw_igemm ? gysb + slb : 0) + (gw && !dw_direct && !dw_igemm ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct && !dx_igemm ? ctb : 0) +
                            2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
@@ -296,6 +301,23 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     if (gw && conv_dw_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW))
     {
         rc = conv_dw_direct_launch(x, gy, gw, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        if (rc)
+            return rc;
+        gw = nullptr;
+    }
+    if (dw_igemm)
+    {
+        float *gys = terms == 3 ? static_cast<float *>(arena_alloc(gysb)) : nullptr;
+        float *sl  = static_cast<float *>(arena_alloc(slb));
+        if ((terms == 3 && !gys) || !sl)
+            return kCudaError;
+        if (gys)
+        {
+            rc = split_launch(gy, hw, (int)(N * OC), (int)hw, nullptr, 0, nullptr, gys, hw, nullptr, stream);
+            if (rc)
+                return rc;
+        }
+        rc = conv_dw_igemm_launch(x, gy, gys, sl, gw, N, C, H, W, OC, KH, KW, S, P, OH, OW, terms, stream);
         if (rc)
             return rc;
         gw = nullptr;

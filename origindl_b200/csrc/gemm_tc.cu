@@ -24,6 +24,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -384,6 +385,21 @@ __global__ void __launch_bounds__(256) splitk_sum_kernel(const float *__restrict
     }
 }
 
+int splitk_sum_launch(const float *slices, int splits, int M, int N, int lds, float *D, int ldd, cudaStream_t stream)
+{
+    const int64_t total = static_cast<int64_t>(M) * N;
+    splitk_sum_kernel<<<static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 8)), 256, 0, stream>>>(
+        slices, splits, M, N, lds, D, ldd);
+    ++g_launch_count;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("splitk_sum_kernel launch failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
 extern int g_slabs;
 namespace
 {
@@ -499,17 +515,7 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
         return kCudaError;
     }
     if (splits > 1)
-    {
-        const int64_t total = static_cast<int64_t>(p.M) * p.N;
-        splitk_sum_kernel<<<static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 8)), 256, 0, stream>>>(
-            q.D, splits, p.M, p.N, q.ldd, p.D, p.ldd);
-        ++g_launch_count;
-        if ((e = cudaGetLastError()) != cudaSuccess)
-        {
-            set_last_error("splitk_sum_kernel launch failed: %s", cudaGetErrorString(e));
-            return kCudaError;
-        }
-    }
+        return splitk_sum_launch(q.D, splits, p.M, p.N, q.ldd, p.D, p.ldd, stream);
     return kOk;
 }
 

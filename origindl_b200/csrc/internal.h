@@ -78,6 +78,14 @@ bool conv_dx_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t 
                             int OW);
 int conv_dx_igemm_launch(const float *gy, const float *w, float *wf, float *wf_small, float *gx, int64_t N, int64_t C,
                          int64_t H, int64_t W, int64_t OC, int KH, int KW, int P, int OH, int OW, int terms, cudaStream_t stream);
+// D[m][n] = sum over z (ascending) of slices[z][m][n]; slices are [splits][M][lds].
+int splitk_sum_launch(const float *slices, int splits, int M, int N, int lds, float *D, int ldd, cudaStream_t stream);
+// Weight gradient through an implicit GEMM (no column matrix): see conv_dw_igemm.cu.
+bool conv_dw_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
+size_t conv_dw_igemm_scratch(int64_t N, int64_t C, int64_t OC, int KH, int KW, int OH, int OW);
+int conv_dw_igemm_launch(const float *x, const float *gy, const float *gy_small, float *slices, float *gw, int64_t N,
+                         int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int OH, int OW, int terms,
+                         cudaStream_t stream);
 bool conv_dw_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
 int conv_dw_direct_launch(const float *x, const float *gy, float *gw, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
                           int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream);

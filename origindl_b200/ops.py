@@ -209,12 +209,15 @@ def conv2d_forward(x, w, b=None, stride=1, pad=0, relu=False, precision=PRECISIO
     return y
 
 
-def conv2d_backward(gy, x, w, stride=1, pad=0, gy_layout=0, need_gb=True, precision=PRECISION_3XTF32):
-    """Returns (gx, gw, gb).  gy_layout 0: true gradient; 1: the reference's reinterpretation of gy."""
+def conv2d_backward(gy, x, w, stride=1, pad=0, gy_layout=0, need_gb=True, precision=PRECISION_3XTF32, need_gx=True,
+                    need_gw=True):
+    """Returns (gx, gw, gb); a gradient that is not asked for is None and is not computed.  gy_layout 0: true gradient;
+    1: the reference's reinterpretation of gy."""
     _chk(gy, x, w)
     N, C, H, W = x.shape
     OC, _, KH, KW = w.shape
-    gx, gw = torch.empty_like(x), torch.empty_like(w)
+    gx = torch.empty_like(x) if need_gx else None
+    gw = torch.empty_like(w) if need_gw else None
     gb = torch.empty((OC,), device=x.device, dtype=torch.float32) if need_gb else None
     capi.call("odl_conv2d_backward", _p(gy), _p(x), _p(w), _p(gx), _p(gw), _p(gb), N, C, H, W, OC, KH, KW, stride, pad,
               gy_layout, precision, _s())

@@ -53,6 +53,7 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--explicit", action="store_true", help="conv: force the im2col + GEMM forward path")
     ap.add_argument("--batch", type=int, default=16, help="conv: images per batch")
+    ap.add_argument("--conv-mode", type=int, default=0, help="conv: 2 = implicit-GEMM weight gradient also for small layers")
     ap.add_argument("--sizes", default="4096,4096,4096,4096,4096,4096,4096,1000", help="mlp: layer widths")
     ap.add_argument("--optimizer", default="sgd", help="mlp: sgd (momentum 0.9) or adam")
     ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
@@ -193,7 +194,7 @@ def main():
               f"fwd+bwd {tot:.3f} ms = {3 * f / tot:.0f} TFLOP/s")
     else:
         C, OC, k, s, p, hw = CONV_LAYERS[a.layer]
-        capi.lib().odl_debug_set_conv_mode(1 if a.explicit else 0)
+        capi.lib().odl_debug_set_conv_mode(1 if a.explicit else a.conv_mode)
         x = torch.rand(a.batch, C, hw, hw, device="cuda")
         w = torch.randn(OC, C, k, k, device="cuda") * (2.0 / (C * k * k)) ** 0.5
         b = torch.zeros(OC, device="cuda")
@@ -201,10 +202,13 @@ def main():
         gy = torch.randn_like(y)
         msf = timed(lambda: ops.conv2d_forward(x, w, b, s, p, precision=prec), a.iters)
         msb = timed(lambda: ops.conv2d_backward(gy, x, w, s, p, precision=prec), a.iters)
+        parts = [timed(lambda kw=kw: ops.conv2d_backward(gy, x, w, s, p, precision=prec, **kw), a.iters)
+                 for kw in (dict(need_gw=False, need_gb=False), dict(need_gx=False, need_gb=False), dict(need_gx=False, need_gw=False))]
         ideal = 4 * (x.numel() + w.numel() + y.numel())
         print(f"conv layer {a.layer} ({C}->{OC} k{k} s{s} p{p} on {hw}x{hw}, batch {a.batch}, {a.precision}, "
               f"{'im2col + GEMM' if a.explicit else 'implicit GEMM'} forward): forward {msf:.4f} ms "
-              f"({ideal / msf / 1e6:.1f} GB/s of ideal traffic), backward {msb:.4f} ms")
+              f"({ideal / msf / 1e6:.1f} GB/s of ideal traffic), backward {msb:.4f} ms "
+              f"(gx {parts[0]:.4f}, gw {parts[1]:.4f}, gb {parts[2]:.4f} when asked for alone)")
 
 
 if __name__ == "__main__":

@@ -399,12 +399,15 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
 @pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES + [(2, 6, 17, 15, 12, 5, 3, 2), (1, 2, 9, 9, 3, 4, 2, 1),
                                                             (1, 20, 9, 9, 300, 1, 1, 0),   # 1x1, 300 products per gx element
                                                             (2, 40, 8, 10, 48, 3, 1, 0),   # stride 1 without padding
-                                                            (1, 40, 8, 8, 40, 3, 1, 2)])   # stride 1, pad = k - 1
+                                                            (1, 40, 8, 8, 40, 3, 1, 2),    # stride 1, pad = k - 1
+                                                            (3, 3, 40, 36, 16, 6, 2, 2),   # gw over 3 images x 12 pixel blocks
+                                                            (2, 24, 16, 16, 200, 3, 1, 1)])  # two output-channel tiles, 216 k-rows
 def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
     """gx has three implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
     BIT-EXACT against the oracle); for stride 1 in the correct gradient layout the implicit-GEMM convolution of gy with the
-    flipped, transposed weights; and GEMM + gather col2im (both 3xTF32, 1e-5).  gw: a direct fp32 kernel for small layers
-    and im2col + split-K GEMM.  Both gradient layouts, with the implicit paths on and forced off."""
+    flipped, transposed weights; and GEMM + gather col2im (both 3xTF32, 1e-5).  gw: a direct fp32 kernel for small layers,
+    the implicit GEMM over pixels (correct layout, OH*OW a multiple of 4) and im2col + split-K GEMM.  Both gradient
+    layouts, with the implicit paths on and forced off."""
     from origindl_b200 import capi
 
     rng = np.random.default_rng(N * 11 + C + H + OC + k + s)
@@ -424,9 +427,10 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
             else:
                 assert max_rel_err(host(gx), dx_o) <= 1e-5
             assert max_rel_err(host(gw), dw_o) <= 1e-5  # direct fp32 kernel when OC <= 32 and C*KH*KW <= 256
-            capi.lib().odl_debug_set_conv_mode(1)
-            gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
-            assert max_rel_err(host(gx), dx_o) <= 1e-5 and max_rel_err(host(gw), dw_o) <= 1e-5
+            for conv_mode in (2, 1):  # 2: small layers through the implicit-GEMM gw kernel too; 1: explicit paths only
+                capi.lib().odl_debug_set_conv_mode(conv_mode)
+                gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+                assert max_rel_err(host(gx), dx_o) <= 1e-5 and max_rel_err(host(gw), dw_o) <= 1e-5
     finally:
         capi.lib().odl_debug_set_conv_mode(0)
     capi.device_status()
