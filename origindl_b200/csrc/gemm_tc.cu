@@ -49,6 +49,8 @@ constexpr int kThreads     = 64 + 32 * kEpiWarps;
 constexpr int kGroupM      = 16;   // tile rasterisation: CTAs walk 16 row-tiles before moving to the next column-tile
 constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kAuxBytes    = 1024;  // barriers, TMEM pointer, abort flag
+constexpr int kPartOffset  = 40960; // split-K partial sums of cluster ranks 1.. start here in rank 0's ring (after the
+                                    // epilogue's transpose slabs: 8 warps x 32 x 36 floats)
 constexpr int kMaxStages   = 8;
 
 // BK: fp32 elements of K per pipeline stage: 32 (128-byte swizzle rows) or 16 (64-byte rows, twice as many stages
@@ -78,7 +80,7 @@ struct TileCfg
 template <int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn, const int terms,
-               const int stages, const int chunk_kb, const int slabs)
+               const int stages, const int chunk_kb, const int slabs, const int cluster_k)
 {
     using Cfg = TileCfg<BN, BK>;
     extern __shared__ uint8_t smem_raw[];
@@ -106,7 +108,9 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
     // ---- a launch that follows a timed-out one does nothing
     if (threadIdx.x == 0)
     {
-        *early_out = (p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        // (the CTAs of a split-K cluster meet at cluster barriers below, so none of them may leave early on its own
+        // reading of the flag; their waits are bounded all the same)
+        *early_out = (cluster_k == 1 && p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
         *abort_f   = 0;
     }
     __syncthreads();
@@ -223,6 +227,12 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     ptx::mbar_wait(&full_bar[kb % stages], (kb / stages) & 1, nullptr);
             }
         }
+        if (cluster_k > 1)
+        {
+            __syncwarp();
+            ptx::cluster_sync();
+            ptx::cluster_sync();
+        }
     }
     else if (warp == 1)
     {
@@ -298,6 +308,12 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     ptx::mma_commit(&acc_full[buf]);  // this chunk's accumulator is complete
             }
         }
+        if (cluster_k > 1)
+        {
+            __syncwarp();
+            ptx::cluster_sync();
+            ptx::cluster_sync();
+        }
     }
     else
     {
@@ -340,6 +356,47 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
             __syncwarp();
             if (lane == 0)
                 ptx::mbar_arrive(&acc_empty[buf]);
+        }
+        if (nchunks <= 0)
+        {
+#pragma unroll
+            for (int i = 0; i < Cfg::warp_cols; ++i)
+                acc[i] = 0.f;
+        }
+        if (cluster_k > 1)
+        {
+            // Split-K inside a thread-block cluster: the cluster_k CTAs along gridDim.y hold partial sums of the same
+            // tile in registers.  Ranks 1.. write theirs into rank 0's (dead) operand ring through distributed shared
+            // memory; rank 0 adds them in rank order -- the same bits every run -- and runs the normal epilogue, so
+            // every epilogue flag works with this kind of split.  Layout [rank-1][warp][column][lane]: consecutive
+            // lanes write consecutive words.
+            __syncwarp();
+            ptx::cluster_sync();  // every CTA of the cluster is past its last MMA: all operand rings are dead
+            const uint32_t rank = ptx::cluster_ctarank();
+            float *part         = stg_all + kPartOffset / 4;
+            if (rank != 0 && have)
+            {
+                const uint32_t dst = ptx::map_to_cta(
+                    ptx::smem_u32(part + (static_cast<size_t>(rank - 1) * kEpiWarps + e) * Cfg::warp_cols * 32), 0);
+#pragma unroll
+                for (int i = 0; i < Cfg::warp_cols; ++i)
+                    ptx::st_shared_cluster_f32(dst + (i * 32 + lane) * 4, acc[i]);
+            }
+            ptx::cluster_sync();  // release / acquire: the partial sums are visible to rank 0
+            if (rank == 0)
+            {
+                for (int r = 1; r < cluster_k; ++r)
+                {
+                    const float *src = part + (static_cast<size_t>(r - 1) * kEpiWarps + e) * Cfg::warp_cols * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < Cfg::warp_cols; ++i)
+                        acc[i] += src[i * 32];
+                }
+            }
+            else
+            {
+                have = false;  // only rank 0 stores the tile
+            }
         }
         if (have)
         {
@@ -480,21 +537,47 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_kb   = (p.K + BK * slabs - 1) / (BK * slabs);  // in stages
-    // Split-K when the output has too few tiles to fill 148 SMs and the reduction is long: every split stores its
-    // partial tile into its own slice of a scratch buffer and a second pass adds the slices in order, so only the
-    // plain epilogue qualifies.
+    // Split-K when the output has too few tiles to fill 148 SMs.  Two forms:
+    //  * inside a thread-block cluster of 2 or 4 CTAs along K (partial tiles combined through distributed shared
+    //    memory in rank order by the CTA that then runs the epilogue): any epilogue, no scratch, no second launch --
+    //    what small-batch layers need, whose CTAs are bound by how fast ONE SM can stream its K range;
+    //  * across more CTAs than a cluster's staging area holds (long reductions into tiny outputs, plain epilogue
+    //    only): every split stores its partial tile into a slice of a scratch buffer, a second pass adds the slices.
+    // Both add in a fixed order.  g_split_k (test hook): 1 = never split, n > 1 = n slices, -n = cluster of n.
     GemmParams q = p;
-    int splits   = 1;
-    if (g_split_k != 1 && p.flags == 0 && tiles_m * tiles_n * 2 <= 148 && num_kb * slabs >= 32)
+    int splits = 1, cluster_k = 1;
+    const int tiles = tiles_m * tiles_n;
+    // rank 0 stages (cluster_k - 1) partial tiles of 128 x BN floats behind the transpose slabs of its dead operand ring
+    const int ring       = stages * Cfg::stage_bytes(terms) * slabs;
+    const int max_cluster = ring >= kPartOffset + 3 * kBM * BN * 4 ? 4 : (ring >= kPartOffset + kBM * BN * 4 ? 2 : 1);
+    if (g_split_k != 1 && tiles * 2 <= 148)
     {
-        splits = g_split_k > 1 ? g_split_k : 148 / (tiles_m * tiles_n);
-        if (splits > num_kb / 8)
-            splits = num_kb / 8;
-        if (splits < 1)
-            splits = 1;
+        int want = g_split_k > 1 ? g_split_k : 148 / tiles;
+        if (g_split_k == 0 && want > num_kb / 4)
+            want = num_kb / 4;  // at least four K-blocks per split
+        const bool slices_ok = p.flags == 0 && num_kb * slabs >= 32;
+        if (g_split_k < 0)
+            cluster_k = -g_split_k <= max_cluster ? -g_split_k : max_cluster;
+        else if (g_split_k > 1 || (slices_ok && want > max_cluster))
+        {
+            splits = want;
+            if (g_split_k == 0 && splits > num_kb / 8)
+                splits = num_kb / 8;
+            if (splits < 1)
+                splits = 1;
+        }
+        else if (want >= 2)
+            cluster_k = (want >= 4 && max_cluster >= 4) ? 4 : (max_cluster >= 2 ? 2 : 1);
     }
-    q.kb_per_split = (num_kb + splits - 1) / splits;
-    splits         = (num_kb + q.kb_per_split - 1) / q.kb_per_split;
+    if (cluster_k > 1)
+    {
+        q.kb_per_split = (num_kb + cluster_k - 1) / cluster_k;
+    }
+    else
+    {
+        q.kb_per_split = (num_kb + splits - 1) / splits;
+        splits         = (num_kb + q.kb_per_split - 1) / q.kb_per_split;
+    }
     if (splits > 1)
     {
         q.flags |= kEpiSplitK;
@@ -506,9 +589,21 @@ int launch_bn(const TmapPack &tm, const GemmParams &p, int a_mn, int b_mn, int t
     int chunk_kb       = g_chunk_kb > 0 ? (g_chunk_kb + slabs - 1) / slabs : (terms == 3 ? 64 / BK : q.kb_per_split);
     if (chunk_kb > q.kb_per_split)
         chunk_kb = q.kb_per_split;
-    gemm_tc_kernel<BN, BK><<<dim3(tiles_m * tiles_n, splits), kThreads, smem, stream>>>(tm, q, a_mn, b_mn, terms, stages, chunk_kb, slabs);
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim          = dim3(tiles, cluster_k > 1 ? cluster_k : splits, 1);
+    cfg.blockDim         = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_k;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = cluster_k > 1 ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK>, tm, q, a_mn, b_mn, terms, stages, chunk_kb, slabs, cluster_k);
     ++g_launch_count;
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
         set_last_error("gemm_tc_kernel<%d,%d> launch failed: %s", BN, BK, cudaGetErrorString(e));

@@ -290,6 +290,11 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
     return v;
 }
 
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ void cluster_sync()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -138,6 +138,44 @@ def test_gemm_split_k(ops, splits):
     assert max_rel_err(d, a.T.astype(np.float64) @ b.astype(np.float64)) <= 1e-5
 
 
+@pytest.mark.parametrize("cluster", [2, 4, 0])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(512, 1000, 784), (200, 70, 1000), (130, 300, 96), (512, 10, 1000)])
+def test_gemm_split_k_inside_a_cluster(ops, M, N, K, ta, tb, bn, cluster):
+    """Split-K across the CTAs of a thread-block cluster (partial tiles combined through distributed shared memory by the
+    CTA that runs the epilogue): every epilogue flag at once, all operand layouts, all tile widths (a cluster of 4 falls
+    back to 2 where the staging area of the wider tiles holds only one partial tile), K ranges that leave the last rank
+    short or empty, and the automatic choice (0).  Same bits on every run."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(M + N + K + 2 * ta + tb + bn)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    bias = rng.standard_normal(N, dtype=np.float32)
+    aux = rng.standard_normal((M, N), dtype=np.float32)
+    ref = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64) + bias
+    ref = np.where(aux > 0, np.maximum(ref, 0), 0)
+    capi.call("odl_debug_set_split_k", -cluster)
+    capi.call("odl_debug_set_tile_n", bn)
+    try:
+        outs = []
+        for _ in range(2):
+            cs = torch.zeros(N, device="cuda")
+            d, d_small = ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True,
+                                  mask_src=dev(aux), colsum=cs, want_small=True)
+            outs.append((d, d_small, cs))
+    finally:
+        capi.call("odl_debug_set_split_k", 0)
+        capi.call("odl_debug_set_tile_n", 0)
+    capi.device_status()
+    d, d_small, cs = outs[0]
+    assert max_rel_err(host(d), ref) <= 1e-5
+    assert max_rel_err(host(cs), ref.sum(0)) <= 1e-5
+    assert torch.equal(d_small, ops.split_tf32(d))
+    assert all(torch.equal(x, y) for x, y in zip(outs[0], outs[1]))
+
+
 @pytest.mark.parametrize("precision", [0, 1])
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(129, 256, 32), (256, 300, 64), (300, 520, 100), (1024, 1024, 1024), (2048, 768, 515)])
