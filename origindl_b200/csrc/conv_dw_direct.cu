@@ -7,8 +7,8 @@
 // reads them back in a split-K GEMM whose 16 x 108 output uses a fraction of one tensor-core tile, and needs gy
 // re-laid out as rows.  Here a block stages PIX pixels of gy and of col in shared memory (col gathered from x through a
 // per-block table k -> offset, like the implicit-GEMM forward) and every thread keeps a 4 x KT register tile of
-// (oc, k) sums in plain fp32 FMAs; blocks walk the pixels grid-stride and add their partial sums into gw with one
-// atomic per output.  The work is N*OH*OW * OC * C*KH*KW FMAs (0.7 G for that layer) on the CUDA cores.
+// (oc, k) sums in plain fp32 FMAs; blocks walk the pixels grid-stride, store their partial gw into their own slice of
+// a scratch buffer, and a second pass adds the slices in a fixed order (same bits every run).  The work is N*OH*OW * OC * C*KH*KW FMAs (0.7 G for that layer) on the CUDA cores.
 //
 // gy_layout 0: gy_rows is the permuted NCHW gradient (the true gradient); 1: the NCHW buffer reinterpreted as
 // [N*OH*OW, OC] as the reference does.  Summation order differs from the reference's single accumulator (as it does in
@@ -37,7 +37,7 @@ constexpr int kOcPad = 32;  // gy staging pitch: 4 oc per thread x 8 thread rows
 // KT: k values per thread (the block covers 32 * KT columns of col); PIX pixels staged per iteration.
 template <int KT, int PIX>
 __global__ void __launch_bounds__(256) conv_dw_direct_kernel(const float *__restrict__ x, const float *__restrict__ gy,
-                                                             float *__restrict__ gw, const DwGeom g, const int layout)
+                                                             float *__restrict__ slices, const DwGeom g, const int layout)
 {
     constexpr int KP  = 32 * KT;
     constexpr int KPP = KP + 1;      // odd pitches: the staging threads write down a column without bank conflicts
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(256) conv_dw_direct_kernel(const float *__rest
         {
             const int oc = ty + 8 * i, k = tx + 32 * j;
             if (oc < g.OC && k < g.ckk)
-                atomicAdd(gw + static_cast<int64_t>(oc) * g.ckk + k, acc[i][j]);
+                slices[(static_cast<int64_t>(blockIdx.x) * g.OC + oc) * g.ckk + k] = acc[i][j];
         }
 }
 
@@ -138,7 +138,11 @@ int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int l
     const size_t smem  = sizeof(float) * (PIX * (KP + 1 + kOcPad + 1) + 2) + sizeof(int2) * KP;
     const int chunks   = (g.rows + PIX - 1) / PIX;
     const int blocks   = chunks < 148 * 4 ? chunks : 148 * 4;
-    conv_dw_direct_kernel<KT, PIX><<<blocks, 256, smem, stream>>>(x, gy, gw, g, layout);
+    const int64_t out  = static_cast<int64_t>(g.OC) * g.ckk;
+    float *slices      = colsum_partial_scratch(blocks, out);
+    if (!slices)
+        return kCudaError;
+    conv_dw_direct_kernel<KT, PIX><<<blocks, 256, smem, stream>>>(x, gy, slices, g, layout);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
@@ -146,7 +150,7 @@ int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int l
         set_last_error("conv_dw_direct_kernel<%d,%d> launch failed: %s", KT, PIX, cudaGetErrorString(e));
         return kCudaError;
     }
-    return kOk;
+    return colsum_finish_launch(slices, blocks, out, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
 }
 }  // namespace
 

@@ -11,7 +11,9 @@
 //
 // One CTA = 128 output pixels x BN output channels; warp 0 lane 0: TMA producer of the weight tiles; warp 1 lane 0: MMA
 // issuer (TMEM accumulator, all of K in one pass: the truncating accumulation costs about 7.5e-9 * K relative error,
-// so the launcher keeps K = C*KH*KW <= 1152 here and sends longer reductions to the explicit path); warps 2..9:
+// so one CTA takes at most 1152 of K; for 1152 < K <= 2304 -- 256 channels x 3 x 3 -- the launcher starts clusters of
+// two CTAs that split K, the second handing its partial tile to the first through distributed shared memory; longer
+// reductions go to the explicit path); warps 2..9:
 // gather, then epilogue (bias / folded BatchNorm scale / ReLU / SiLU, NCHW store).  Two 48 KB (BN = 64) stages per CTA
 // so that two CTAs share an SM and one's prologue and epilogue overlap the other's main loop.  Every wait is bounded.
 #include <cuda.h>
@@ -38,7 +40,9 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads  = 64 + 32 * kEpiWarps;
 constexpr int kStages   = 2;
 constexpr int kAuxBytes = 256;
-constexpr int kMaxK     = 1152;                  // longest reduction C*KH*KW the kernel takes
+constexpr int kMaxK     = 1152;                  // longest reduction one CTA takes (a cluster of two CTAs: twice that)
+constexpr int kPartOffset = 40960;               // where rank 1's partial tile lands in rank 0's dead operand ring (after
+                                                 // the epilogue's transpose slabs: 8 warps x 32 x 36 floats)
 constexpr int kTabBytes = (kMaxK + 32) * 8;      // per-k lookup table {offset, kh << 16 | kw}, padded to a K-block
 
 struct IgemmGeom
@@ -62,7 +66,7 @@ struct IgemmCfg
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 2)
 conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__ x, const IgemmGeom g, const GemmParams p,
-                  const int terms)
+                  const int terms, const int cluster_k)
 {
     using Cfg = IgemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -82,7 +86,8 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
     const int lane = threadIdx.x & 31;
     if (threadIdx.x == 0)
     {
-        *early_out = (p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        // (the two CTAs of a K-splitting cluster meet at cluster barriers: neither may leave early on its own)
+        *early_out = (cluster_k == 1 && p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
         *abort_f   = 0;
     }
     __syncthreads();
@@ -93,21 +98,26 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
     const int tile_m  = blockIdx.x / tiles_n;
     const int tile_n  = blockIdx.x - tile_m * tiles_n;
     const int m0 = tile_m * kBM, n0 = tile_n * BN;
-    const int num_kb = (g.ckk + kBK - 1) / kBK;
+    // K-blocks [kb0, kb0 + num_kb) of the reduction belong to this CTA (all of them unless a cluster splits K)
+    const int total_kb = (g.ckk + kBK - 1) / kBK;
+    const int kb_per   = (total_kb + cluster_k - 1) / cluster_k;
+    const int kb0      = blockIdx.y * kb_per;
+    const int num_kb   = max(0, min(kb_per, total_kb - kb0));
 
     // Per-k table, built once per CTA: x[n, c, h0 + kh, w0 + kw] sits at pix_off + ktab[k].x with
     // ktab[k].x = (c * H + kh) * W + kw; ktab[k].y = kh << 16 | kw serves the bounds checks of border pixels.
     // Entries past C*KH*KW (the padding of the last K-block) are marked with y = -1.
-    for (int k = threadIdx.x; k < num_kb * kBK; k += kThreads)
+    for (int kl = threadIdx.x; kl < num_kb * kBK; kl += kThreads)
     {
-        int2 e = make_int2(0, -1);
+        int2 e      = make_int2(0, -1);
+        const int k = kb0 * kBK + kl;
         if (k < g.ckk)
         {
             const int khw = g.KH * g.KW;
             const int c = k / khw, rm = k - c * khw, kh = rm / g.KW, kw = rm - kh * g.KW;
             e = make_int2((c * g.H + kh) * g.W + kw, (kh << 16) | kw);
         }
-        ktab[k] = e;
+        ktab[kl] = e;
     }
     if (warp == 0 && lane == 0)
     {
@@ -146,9 +156,9 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
                     break;
                 uint8_t *sb = tiles + s * Cfg::stage_bytes + 2 * Cfg::a_bytes;
                 ptx::mbar_arrive_expect_tx(&b_full[s], Cfg::b_bytes * (terms == 3 ? 2 : 1));
-                ptx::tma_load_2d(sb, &tm.b, &b_full[s], kb * kBK, n0);
+                ptx::tma_load_2d(sb, &tm.b, &b_full[s], (kb0 + kb) * kBK, n0);
                 if (terms == 3)
-                    ptx::tma_load_2d(sb + Cfg::b_bytes, &tm.b_small, &b_full[s], kb * kBK, n0);
+                    ptx::tma_load_2d(sb + Cfg::b_bytes, &tm.b_small, &b_full[s], (kb0 + kb) * kBK, n0);
                 ++issued;
             }
             if (*abort_f)
@@ -157,6 +167,12 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
                 for (int kb = first; kb < issued; ++kb)
                     ptx::mbar_wait_quiet(&b_full[kb % kStages], (kb / kStages) & 1, nullptr);
             }
+        }
+        if (cluster_k > 1)
+        {
+            __syncwarp();
+            ptx::cluster_sync();
+            ptx::cluster_sync();
         }
     }
     else if (warp == 1)
@@ -203,6 +219,12 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             }
             if (ok)
                 ptx::mma_commit(acc_full);
+        }
+        if (cluster_k > 1)
+        {
+            __syncwarp();
+            ptx::cluster_sync();
+            ptx::cluster_sync();
         }
     }
     else
@@ -254,7 +276,8 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             }
         };
         float v[16], v_next[16];
-        gather(0, v_next);
+        if (num_kb > 0)
+            gather(0, v_next);
         for (int kb = 0; kb < num_kb; ++kb)
         {
             const int s = kb % kStages;
@@ -283,13 +306,16 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             if (lane == 0)
                 ptx::mbar_arrive(&a_full[s]);
         }
-        if (have)
+        if (have && num_kb > 0)
             have = __all_sync(0xffffffffu, ptx::mbar_wait_quiet(acc_full, 0, abort_f));
-        if (have)
+        const int cw = h * Cfg::warp_cols;
+        float acc[Cfg::warp_cols];
+#pragma unroll
+        for (int i = 0; i < Cfg::warp_cols; ++i)
+            acc[i] = 0.f;
+        if (have && num_kb > 0)
         {
             ptx::tc_fence_after_sync();
-            const int cw = h * Cfg::warp_cols;
-            float acc[Cfg::warp_cols];
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + cw;
 #pragma unroll
             for (int j = 0; j < Cfg::warp_cols / 32; ++j)
@@ -301,8 +327,36 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
                 for (int i = 0; i < 32; ++i)
                     acc[32 * j + i] = __uint_as_float(rr[i]);
             }
-            gemm_epilogue_store<BN, Cfg::warp_cols>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw, q, lane);
         }
+        if (cluster_k > 1)
+        {
+            // K split over the two CTAs of the cluster: rank 1 writes its partial tile into rank 0's dead operand ring
+            // (layout [warp][column][lane]), rank 0 adds it and runs the epilogue.
+            __syncwarp();
+            ptx::cluster_sync();  // both CTAs are past their last MMA
+            const uint32_t rank = ptx::cluster_ctarank();
+            float *part         = stg_all + kPartOffset / 4 + static_cast<size_t>(e) * Cfg::warp_cols * 32;
+            if (rank != 0 && have)
+            {
+                const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(part), 0);
+#pragma unroll
+                for (int i = 0; i < Cfg::warp_cols; ++i)
+                    ptx::st_shared_cluster_f32(dst + (i * 32 + lane) * 4, acc[i]);
+            }
+            ptx::cluster_sync();
+            if (rank == 0)
+            {
+#pragma unroll
+                for (int i = 0; i < Cfg::warp_cols; ++i)
+                    acc[i] += part[i * 32 + lane];
+            }
+            else
+            {
+                have = false;
+            }
+        }
+        if (have)
+            gemm_epilogue_store<BN, Cfg::warp_cols>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw, q, lane);
         ptx::tc_fence_before_sync();
     }
 
@@ -336,9 +390,23 @@ int launch_igemm(const TmapPack &tm, const float *x, const IgemmGeom &g, const G
         attr_set[dev] = true;
     }
     const int tiles_m = (g.rows + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
-    conv_igemm_kernel<BN><<<tiles_m * tiles_n, kThreads, Cfg::smem_bytes, stream>>>(tm, x, g, p, terms);
+    const int cluster_k = g.ckk > kMaxK ? 2 : 1;
+    static_assert(kPartOffset + kBM * BN * 4 <= kStages * Cfg::stage_bytes, "rank 1's partial tile must fit the ring");
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim          = dim3(tiles_m * tiles_n, cluster_k, 1);
+    cfg.blockDim         = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::smem_bytes;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_k;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = cluster_k > 1 ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, conv_igemm_kernel<BN>, tm, x, g, p, terms, cluster_k);
     ++g_launch_count;
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
         set_last_error("conv_igemm_kernel<%d> launch failed: %s", BN, cudaGetErrorString(e));
@@ -355,7 +423,7 @@ int g_conv_mode = 0;
 bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW)
 {
     const int64_t ckk = C * KH * KW, rows = N * OH * OW;
-    return g_conv_mode != 1 && ckk <= 1152 && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
+    return g_conv_mode != 1 && ckk <= 2 * kMaxK && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
 }
 
 // w_big / w_small: the weights as a K-major [OC][ldw] matrix (ldw a multiple of 4, 16-byte aligned) and its low part.

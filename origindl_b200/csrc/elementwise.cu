@@ -543,8 +543,9 @@ __global__ void __launch_bounds__(256) nchw_to_rows_kernel(const float *__restri
 }
 
 // gb[oc] = sum over n, hw of gy[n][oc][hw]: grid (OC, N, slabs of one plane); every block streams a contiguous piece
-// of one (n, oc) plane (no per-element index arithmetic), reduces it and issues one atomic.
-__global__ void __launch_bounds__(256) channel_sum_kernel(const float *__restrict__ gy, float *__restrict__ gb, int OC,
+// of one (n, oc) plane (no per-element index arithmetic), reduces it and stores its partial sum at
+// partial[(n * slabs + z) * OC + oc]; colsum_finish_launch then adds the partials of a channel in a fixed order.
+__global__ void __launch_bounds__(256) channel_sum_kernel(const float *__restrict__ gy, float *__restrict__ partial, int OC,
                                                           int HW)
 {
     __shared__ float red[256];
@@ -562,7 +563,7 @@ __global__ void __launch_bounds__(256) channel_sum_kernel(const float *__restric
         __syncthreads();
     }
     if (threadIdx.x == 0)
-        atomicAdd(gb + oc, red[0]);
+        partial[(static_cast<size_t>(n) * gridDim.z + blockIdx.z) * OC + oc] = red[0];
 }
 
 }  // namespace
@@ -766,9 +767,12 @@ int channel_sum_launch(const float *gy, float *gb, int64_t N, int64_t OC, int64_
     if (slabs > 64)
         slabs = 64;
     dim3 grid((unsigned)OC, (unsigned)N, (unsigned)slabs);
-    channel_sum_kernel<<<grid, 256, 0, s>>>(gy, gb, (int)OC, (int)HW);
+    float *partial = colsum_partial_scratch((int)(N * slabs), OC);
+    if (!partial)
+        return kCudaError;
+    channel_sum_kernel<<<grid, 256, 0, s>>>(gy, partial, (int)OC, (int)HW);
     ODL_LAUNCH_CHECK("channel_sum_kernel");
-    return kOk;
+    return colsum_finish_launch(partial, (int)(N * slabs), OC, (int)OC, gb, s);
 }
 
 }  // namespace odl

@@ -22,7 +22,9 @@ import torch
 
 from . import capi, ops
 
-CONV_LAYERS = {1: (3, 16, 6, 2, 2, 320), 2: (16, 32, 3, 2, 1, 160), 3: (32, 32, 1, 1, 0, 80), 4: (64, 64, 3, 1, 1, 40)}
+# 1-4: the benchmark's conv shapes; 5: a deep 256 -> 256 3x3 layer (K = 2304: the implicit forward splits K over a CTA pair)
+CONV_LAYERS = {1: (3, 16, 6, 2, 2, 320), 2: (16, 32, 3, 2, 1, 160), 3: (32, 32, 1, 1, 0, 80), 4: (64, 64, 3, 1, 1, 40),
+               5: (256, 256, 3, 1, 1, 20)}
 
 
 def timed(fn, iters):

@@ -398,8 +398,10 @@ def test_conv2d_vs_oracle(ops, orc, N, C, H, W, OC, k, s, p):
 IGEMM_CASES = CONV_CASES + [(3, 3, 33, 29, 16, 6, 2, 2),      # ragged pixel count, K = 108 (not a multiple of 32)
                             (2, 5, 11, 13, 70, 3, 1, 1),      # K = 45 (not a multiple of 4: padded weights), 64 < OC
                             (1, 8, 14, 14, 130, 3, 2, 0),     # OC > 128: two column tiles
-                            (1, 128, 6, 6, 32, 3, 1, 1),      # K = 1152, the longest reduction of the implicit path
-                            (1, 130, 6, 6, 8, 3, 1, 1)]       # K = 1170: falls back to the explicit path
+                            (1, 128, 6, 6, 32, 3, 1, 1),      # K = 1152, the longest reduction one CTA takes
+                            (1, 130, 6, 6, 8, 3, 1, 1),       # K = 1170: a cluster of two CTAs splits K (37 K-blocks: 19 + 18)
+                            (2, 256, 7, 9, 200, 3, 1, 1),     # K = 2304 = 256 channels x 3 x 3, the longest implicit reduction
+                            (1, 260, 5, 5, 12, 3, 1, 1)]      # K = 2340: falls back to the explicit path
 
 
 @pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES)
@@ -469,6 +471,30 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
                 capi.lib().odl_debug_set_conv_mode(conv_mode)
                 gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
                 assert max_rel_err(host(gx), dx_o) <= 1e-5 and max_rel_err(host(gw), dw_o) <= 1e-5
+    finally:
+        capi.lib().odl_debug_set_conv_mode(0)
+    capi.device_status()
+
+
+@pytest.mark.parametrize("N,C,H,W,OC,k,s,p", [(4, 3, 64, 64, 16, 6, 2, 2), (4, 16, 40, 40, 32, 3, 2, 1), (4, 64, 20, 20, 64, 3, 1, 1),
+                                              (2, 20, 9, 9, 300, 1, 1, 0)])
+def test_conv2d_backward_is_reproducible(ops, N, C, H, W, OC, k, s, p):
+    """Same inputs, same bits, in every path and both gradient layouts: the reductions over pixels (bias gradient, direct
+    and implicit-GEMM weight gradients, split-K) add their partial sums in a fixed order."""
+    from origindl_b200 import capi
+
+    g = torch.Generator(device="cuda").manual_seed(N + C + OC)
+    x = torch.randn(N, C, H, W, device="cuda", generator=g)
+    w = torch.randn(OC, C, k, k, device="cuda", generator=g)
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    gy = torch.randn(N, OC, OH, OW, device="cuda", generator=g)
+    try:
+        for conv_mode in (0, 2, 1):
+            capi.lib().odl_debug_set_conv_mode(conv_mode)
+            for layout in (0, 1):
+                runs = [ops.conv2d_backward(gy, x, w, s, p, gy_layout=layout) for _ in range(3)]
+                for other in runs[1:]:
+                    assert all(torch.equal(a, b) for a, b in zip(runs[0], other)), (conv_mode, layout)
     finally:
         capi.lib().odl_debug_set_conv_mode(0)
     capi.device_status()
