@@ -278,6 +278,10 @@ int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int l
 int odl_mlp_backward_layer(void *handle, int layer, void *stream);
 /* optimizer.step(): one fused launch over the flat buffers; grad_scale multiplies the gradients first. */
 int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream);
+/* The same update for the parameters of one layer only (call once per layer and step, any order; first_of_step != 0
+ * on the first call of a step advances the step counter all layers share).  A data-parallel caller updates each layer
+ * as soon as its gradient bucket is reduced, so that the early layers' updates overlap the last bucket's all-reduce. */
+int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int first_of_step, void *stream);
 /* forward_loss + backward of every layer + optimizer_step. */
 int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
 /* Device pointers to the scalar loss and to the logits [batch, sizes[n-1]] of the last forward. */

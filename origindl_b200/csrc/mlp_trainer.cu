@@ -348,6 +348,30 @@ int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream)
                       grad_scale, ST(stream));
 }
 
+// The same update restricted to the parameters of one layer ([W_layer, b_layer], contiguous in the flat buffers), so that a
+// data-parallel caller can update every layer as soon as ITS gradient bucket has been reduced -- the updates of the
+// layers reduced early then overlap the all-reduce of the last bucket.  Call once per layer and step, in any order;
+// first_of_step != 0 on the first call of a step advances the step counter (Adam's t) that all layers of the step share.
+int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int first_of_step, void *stream)
+{
+    Mlp *h = H(handle);
+    if (layer < 0 || layer >= h->L)
+    {
+        set_last_error("mlp: layer %d out of range", layer);
+        return kInvalidArgument;
+    }
+    if (first_of_step)
+        h->step_count += 1;
+    const int64_t o = h->w_off[layer];
+    const int64_t n = (layer + 1 < h->L ? h->w_off[layer + 1] : h->total) - o;
+    float *ps       = h->params_small ? h->params_small + o : nullptr;
+    if (h->optimizer == 1)
+        return adam_launch(h->params + o, h->grads + o, h->m + o, h->v + o, ps, n, h->step_count, h->lr, h->beta1, h->beta2,
+                           h->eps, h->hook_wd, grad_scale, ST(stream));
+    return sgd_launch(h->params + o, h->grads + o, h->m ? h->m + o : nullptr, ps, n, h->lr, h->momentum, 0.0f, 0, h->hook_wd,
+                      grad_scale, ST(stream));
+}
+
 int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
 {
     int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);

@@ -189,6 +189,7 @@ class MLPTrainer:
 
         compute = torch.cuda.current_stream()
         capi.call("odl_mlp_forward_loss", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
+        reduced = {}
         for layer in dp.reduce_order(self.n_layers):
             capi.call("odl_mlp_backward_layer", self._h, layer, s)
             if self.overlap:
@@ -197,12 +198,18 @@ class MLPTrainer:
                 self._comm_stream.wait_event(ev)
                 with torch.cuda.stream(self._comm_stream):
                     dist.all_reduce(self._buckets[layer], op=dist.ReduceOp.SUM, group=self.pg)
-        if self.overlap:
-            compute.wait_stream(self._comm_stream)
-        else:
+                    reduced[layer] = torch.cuda.Event()
+                    reduced[layer].record(self._comm_stream)
+        if not self.overlap:
             for layer in range(self.n_layers - 1, -1, -1):
                 dist.all_reduce(self._buckets[layer], op=dist.ReduceOp.SUM, group=self.pg)
-        capi.call("odl_mlp_optimizer_step", self._h, 1.0 / self.world, s)
+            capi.call("odl_mlp_optimizer_step", self._h, 1.0 / self.world, s)
+            return self._loss_view[0]
+        # update each layer as soon as ITS bucket is reduced: the head-side layers' updates run while the last bucket
+        # (layer 0, whose gradient is the last GEMM of backward) is still being reduced
+        for i, layer in enumerate(dp.reduce_order(self.n_layers)):
+            compute.wait_event(reduced[layer])
+            capi.call("odl_mlp_optimizer_step_layer", self._h, layer, 1.0 / self.world, int(i == 0), s)
         return self._loss_view[0]
 
     def capture(self, x: torch.Tensor, labels: torch.Tensor):
