@@ -652,18 +652,47 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         bn = 128;
     if (bn != 64 && bn != 128 && bn != 256)
     {
-        // widest tile that still fills the machine reasonably
-        const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
-        const int64_t tiles128 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 127) / 128);
+        // Pick the tile width with a small cost model fitted to measurements on B200.  One K-block (32 of K) costs a
+        // CTA nearly the same time whatever the tile width -- 0.94 / 0.98 / 1.27 us for 64 / 128 / 256 columns in 3xTF32
+        // (the A operand's shared-memory reads and the MMA issue do not shrink with N) -- so the widest tile is by far
+        // the most efficient per SM, and a machine that a wide tiling leaves half empty is filled by splitting K over
+        // a cluster (launch_bn) rather than by narrower tiles.  time = waves * (K-blocks per CTA * t_kb + fixed costs).
+        const int tm           = (p.M + kBM - 1) / kBM;
         const int64_t k_blocks = (p.K + 31) / 32;
-        if (p.N > 128 && tiles256 >= 148 && !(p.flags & kEpiNCHW))
-            bn = 256;
-        else if (p.N > 128 && p.flags == 0 && tiles256 * 2 <= 148 && k_blocks >= 64)
-            bn = 256;  // long reduction, few tiles, plain epilogue (dW of a skinny layer): wide tiles + split-K
-        else if (p.N > 64 && tiles128 >= 111)
-            bn = 128;
+        const int64_t tiles256 = static_cast<int64_t>(tm) * ((p.N + 255) / 256);
+        if (p.N > 128 && p.flags == 0 && tiles256 * 2 <= 148 && k_blocks >= 64)
+        {
+            bn = 256;  // long reduction, few tiles, plain epilogue (dW of a skinny layer): wide tiles + many K slices
+        }
         else
-            bn = 64;  // small problems are bound by the latency of one CTA's K loop: spread them over more SMs
+        {
+            static const int widths[3]    = {256, 128, 64};
+            static const double t_kb3[3]  = {1.27, 0.98, 0.94}, t_kb1[3] = {0.60, 0.50, 0.45};
+            static const double fixed[3]  = {14.0, 8.0, 6.0};
+            static const int max_clus[3]  = {2, 2, 4};
+            double best = 1e30;
+            for (int i = 0; i < 3; ++i)
+            {
+                const int w = widths[i];
+                if ((w == 256 && ((p.flags & kEpiNCHW) || p.N <= 128)) || (w == 128 && p.N <= 64))
+                    continue;
+                const int64_t tiles = static_cast<int64_t>(tm) * ((p.N + w - 1) / w);
+                int c = 1;
+                if (tiles * 2 <= 148)
+                {
+                    const int64_t want = std::min<int64_t>(148 / tiles, k_blocks / 4);
+                    c = (want >= 4 && max_clus[i] >= 4) ? 4 : (want >= 2 ? 2 : 1);
+                }
+                const double waves = static_cast<double>((tiles * c + 147) / 148);
+                const double t = waves * (static_cast<double>((k_blocks + c - 1) / c) * (terms == 3 ? t_kb3[i] : t_kb1[i]) +
+                                          fixed[i] + (c > 1 ? 5.0 : 0.0));
+                if (t < best)
+                {
+                    best = t;
+                    bn   = w;
+                }
+            }
+        }
     }
     if (gemm_pair_eligible(p, bn, a_mn, b_mn, terms))
         return gemm_pair_launch(A, A_small, lda, a_mn, B, B_small, ldb, b_mn, p, terms, stream);

@@ -500,6 +500,31 @@ def test_conv2d_backward_is_reproducible(ops, N, C, H, W, OC, k, s, p):
     capi.device_status()
 
 
+@pytest.mark.parametrize("C,OC,k,s,p,hw", [(3, 16, 6, 2, 2, 320), (16, 32, 3, 2, 1, 160), (32, 32, 1, 1, 0, 80), (64, 64, 3, 1, 1, 40)])
+def test_conv2d_benchmark_layers_at_full_size(ops, orc, C, OC, k, s, p, hw):
+    """The four conv shapes of the benchmark at batch 16: forward against the oracle (the reference's CPU arithmetic);
+    backward -- where the scalar oracle needs tens of seconds per layer -- against float64 gradients of the same
+    convolution (torch autograd as the checker), all three gradients within 1e-5."""
+    N = 16
+    rng = np.random.default_rng(C + OC + hw)
+    x = rng.uniform(0, 1, (N, C, hw, hw)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = (0.1 * rng.standard_normal(OC)).astype(np.float32)
+    OH = (hw + 2 * p - k) // s + 1
+    y_o = np.empty((N, OC, OH, OH), np.float32)
+    orc.oracle_conv2d_forward(x, w, fptr(b), y_o, N, C, hw, hw, OC, k, k, s, p)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    assert max_rel_err(host(ops.conv2d_forward(xd, wd, bd, s, p)), y_o) <= 1e-5
+    gy = torch.randn(N, OC, OH, OH, device="cuda", generator=torch.Generator(device="cuda").manual_seed(hw))
+    gx, gw, gb = ops.conv2d_backward(gy, xd, wd, s, p, gy_layout=0)
+    x64, w64 = xd.double().requires_grad_(), wd.double().requires_grad_()
+    torch.nn.functional.conv2d(x64, w64, None, stride=s, padding=p).backward(gy.double())
+    for got, want in ((gx, x64.grad), (gw, w64.grad), (gb, gy.double().sum((0, 2, 3)))):
+        assert ((got.double() - want).abs().max() / want.abs().max()).item() <= 1e-5
+    ops_capi = __import__("origindl_b200.capi", fromlist=["capi"])
+    ops_capi.device_status()
+
+
 def test_conv2d_golden_vectors_from_reference(ops):
     g = np.load(GOLDEN / "reference_vectors.npz")
     N, C, H, W, OC, k, s, p = (int(v) for v in g["conv_cfg"])
