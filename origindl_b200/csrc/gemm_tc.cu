@@ -193,6 +193,10 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     {
                         ptx::tma_load_2d(sa, ma, &full_bar[s], k0, m0);
                     }
+                    else if (a_mn & 2)
+                    {
+                        ptx::tma_load_3d(sa, ma, &full_bar[s], 0, k0, m0 / 32);  // all four 32 x BK boxes in one copy
+                    }
                     else
                     {
 #pragma unroll
@@ -208,6 +212,10 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     if (!b_mn)
                     {
                         ptx::tma_load_2d(sb, mb, &full_bar[s], k0, n0);
+                    }
+                    else if (b_mn & 2)
+                    {
+                        ptx::tma_load_3d(sb, mb, &full_bar[s], 0, k0, n0 / 32);
                     }
                     else
                     {
@@ -506,6 +514,22 @@ int make_tmap(CUtensorMap *out, const float *ptr, int64_t rows, int64_t cols, in
     return kOk;
 }
 
+int make_tmap_mn3d(CUtensorMap *out, const float *ptr, int64_t k_rows, int64_t mn_cols, int64_t ld, int box_k, int boxes,
+                   CUtensorMapSwizzle swizzle)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn || (mn_cols & 31))
+        return kCudaError;  // the caller falls back to separate 2-D copies
+    cuuint64_t dims[3]    = {32, static_cast<cuuint64_t>(k_rows), static_cast<cuuint64_t>(mn_cols / 32)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, 128};
+    cuuint32_t box[3]     = {32, static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(boxes)};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? kOk : kCudaError;
+}
+
 namespace
 {
 template <int BN, int BK>
@@ -708,7 +732,18 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
         bk = g_bk_override;
     if (bk == 16 && bn != 256)
         bk = 32;
+    // MN-major operands whose extent is a multiple of 32: one 3-D copy per operand and K-slab instead of one 2-D copy
+    // per 32 x BK box
+    {
+        CUtensorMap probe;
+        if (a_mn && make_tmap_mn3d(&probe, A, p.K, p.M, lda, bk, kBM / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) == kOk)
+            a_mn |= 2;
+        if (b_mn && make_tmap_mn3d(&probe, B, p.K, p.N, ldb, bk, bn / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) == kOk)
+            b_mn |= 2;
+    }
     auto mk = [&](CUtensorMap *m, const float *ptr, int64_t ld, int mn, int64_t extent_mn, int box_rows_kmajor) {
+        if (mn & 2)
+            return make_tmap_mn3d(m, ptr, p.K, extent_mn, ld, bk, box_rows_kmajor / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
         return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
                   : make_tmap(m, ptr, extent_mn, p.K, ld, bk, box_rows_kmajor,
                               bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);

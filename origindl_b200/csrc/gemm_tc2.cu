@@ -181,6 +181,10 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                     {
                         ptx::tma_load_2d_pair(sa, ma, bar, k0, m0);
                     }
+                    else if (a_mn & 2)
+                    {
+                        ptx::tma_load_3d_pair(sa, ma, bar, 0, k0, m0 / 32);  // all four 32 x 32 boxes in one copy
+                    }
                     else
                     {
 #pragma unroll
@@ -196,6 +200,10 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
                     if (!b_mn)
                     {
                         ptx::tma_load_2d_pair(sb, mb, bar, k0, nb0);
+                    }
+                    else if (b_mn & 2)
+                    {
+                        ptx::tma_load_3d_pair(sb, mb, bar, 0, k0, nb0 / 32);
                     }
                     else
                     {
@@ -381,7 +389,18 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
     TmapPack tm;
     std::memset(&tm, 0, sizeof(tm));
     int rc;
+    // MN-major operands whose extent is a multiple of 32: one 3-D copy per operand and K-slab instead of one 2-D copy
+    // per 32 x 32 box (the producer thread otherwise issues 16 copies per stage, which bounds plain TF32)
+    CUtensorMap probe;
+    if (a_mn && make_tmap_mn3d(&probe, A, p.K, p.M, lda, kBK, kBM / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) == kOk)
+        a_mn |= 2;
+    if (b_mn && make_tmap_mn3d(&probe, B, p.K, p.N, ldb, kBK, BN / 64, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) == kOk)
+        b_mn |= 2;
+    if (g_pair_mode == 3)
+        a_mn &= 1, b_mn &= 1;  // test hook: separate 2-D copies
     auto mk = [&](CUtensorMap *m, const float *ptr, int64_t ld, int mn, int64_t extent_mn, int box_rows_kmajor) {
+        if (mn & 2)
+            return make_tmap_mn3d(m, ptr, p.K, extent_mn, ld, kBK, box_rows_kmajor / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
         return mn ? make_tmap(m, ptr, p.K, extent_mn, ld, 32, kBK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
                   : make_tmap(m, ptr, extent_mn, p.K, ld, kBK, box_rows_kmajor, CU_TENSOR_MAP_SWIZZLE_128B);
     };

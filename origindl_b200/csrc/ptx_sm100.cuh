@@ -175,6 +175,16 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, ui
         : "memory");
 }
 
+// 3-D tile load (used for MN-major operands: {32 mn, k, mn / 32} moves several 32 x 32 boxes with one instruction).
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, uint64_t *bar, int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- TMEM allocation (one warp, .sync.aligned)
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols)
 {
@@ -332,6 +342,17 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const void *tma
         "[%2];"
         :
         : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const void *tmap, uint32_t bar_cluster_addr, int32_t c0,
+                                                 int32_t c1, int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], "
+        "[%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
 
