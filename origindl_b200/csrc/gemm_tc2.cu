@@ -357,9 +357,233 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
         atomicExch(p.err, 1);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Plain-TF32 variant with a 256 x 512 tile per pair.  Plain TF32 never drains the accumulator mid-way, so the second
+// TMEM buffer of the kernel above is free to hold 256 more columns: each CTA then loads one 128-row A tile and TWO
+// 128-row blocks of B per K-slab (48 KB for 2 x 128 x 256 x 32 products instead of 32 KB for half of that), i.e. 0.75 of
+// the operand bytes per product.  That matters because plain TF32 on this kernel is bound by what the L2 -> SM fabric
+// delivers (about 8-10 TB/s over all SMs), not by the tensor pipe.  Per K-slab the leader issues 4 K-steps x 2 MMAs
+// (N = 256 each, columns 0..255 and 256..511 of the accumulator).  Four 48 KB stages; the epilogue streams the
+// accumulator out of TMEM 32 columns at a time.
+constexpr int kWideBN     = 512;
+constexpr int kWideBBlock = 128 * kBK * 4;               // one 128-row block of B
+constexpr int kWideStage  = kBM * kBK * 4 + 2 * kWideBBlock;  // 48 KB
+constexpr int kWideStages = 4;
+constexpr int kWideSmem   = 1024 + kAuxBytes + kWideStages * kWideStage;
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_wide_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *tiles        = base;
+    float *stg_all        = reinterpret_cast<float *>(base);
+    uint8_t *aux_base     = base + kWideStages * kWideStage;
+    uint64_t *full_bar    = reinterpret_cast<uint64_t *>(aux_base);
+    uint64_t *empty_bar   = full_bar + kMaxStages;
+    uint64_t *acc_full    = empty_bar + kMaxStages;
+    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(acc_full + 4);
+    volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *early_out        = const_cast<int *>(abort_f) + 1;
+
+    const int warp      = threadIdx.x >> 5;
+    const int lane      = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader   = rank == 0;
+
+    if (threadIdx.x == 0)
+    {
+        *early_out = (leader && p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        *abort_f   = 0;
+    }
+    __syncthreads();
+    ptx::cluster_sync();
+    const bool skip = ptx::ld_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(early_out), 0)) != 0;
+
+    const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+    const int tiles_n = (p.N + kWideBN - 1) / kWideBN;
+    int tile_m, tile_n;
+    {
+        const int pair      = blockIdx.x >> 1;
+        const int per_group = kGroupM * tiles_n;
+        const int g         = pair / per_group;
+        const int first_m   = g * kGroupM;
+        const int gsz       = min(tiles_m - first_m, kGroupM);
+        const int local     = pair - g * per_group;
+        tile_m              = first_m + local % gsz;
+        tile_n              = local / gsz;
+    }
+    const int m0     = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
+    const int n0     = tile_n * kWideBN;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+
+    if (!skip)
+    {
+        if (warp == 0 && lane == 0)
+        {
+            ptx::prefetch_tmap(&tm.a);
+            ptx::prefetch_tmap(&tm.b);
+            for (int s = 0; s < kWideStages; ++s)
+            {
+                ptx::mbar_init(&full_bar[s], 1);
+                ptx::mbar_init(&empty_bar[s], 1);
+            }
+            ptx::mbar_init(acc_full, 1);
+            ptx::fence_mbar_init();
+        }
+        if (warp == 1)
+        {
+            ptx::tmem_alloc_pair(tmem_slot, 512);
+            ptx::tmem_relinquish_pair();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = skip ? 0u : *tmem_slot;
+
+    if (skip)
+    {
+        // nothing
+    }
+    else if (warp == 0)
+    {
+        // ================================================================= TMA producer (both CTAs)
+        if (lane == 0)
+        {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb)
+            {
+                const int s       = kb % kWideStages;
+                const uint32_t ph = (kb / kWideStages) & 1;
+                if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
+                    break;
+                if (leader)
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * kWideStage);
+                const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
+                uint8_t *sa  = tiles + s * kWideStage;
+                const int k0 = kb * kBK;
+                if (!a_mn)
+                    ptx::tma_load_2d_pair(sa, &tm.a, bar, k0, m0);
+                else if (a_mn & 2)
+                    ptx::tma_load_3d_pair(sa, &tm.a, bar, 0, k0, m0 / 32);
+                else
+                    for (int j = 0; j < kBM / 32; ++j)
+                        ptx::tma_load_2d_pair(sa + j * 4096, &tm.a, bar, m0 + 32 * j, k0);
+                for (int blk = 0; blk < 2; ++blk)
+                {
+                    // block blk of this CTA: rows n0 + 256 blk + 128 rank .. + 127 of B (its half of MMA number blk)
+                    uint8_t *sb   = sa + kBM * kBK * 4 + blk * kWideBBlock;
+                    const int nb0 = n0 + 256 * blk + 128 * static_cast<int>(rank);
+                    if (!b_mn)
+                        ptx::tma_load_2d_pair(sb, &tm.b, bar, k0, nb0);
+                    else if (b_mn & 2)
+                        ptx::tma_load_3d_pair(sb, &tm.b, bar, 0, k0, nb0 / 32);
+                    else
+                        for (int j = 0; j < 4; ++j)
+                            ptx::tma_load_2d_pair(sb + j * 4096, &tm.b, bar, nb0 + 32 * j, k0);
+                }
+                ++issued;
+            }
+            if (*abort_f && leader)
+            {
+                const int first = issued > kWideStages ? issued - kWideStages : 0;
+                for (int kb = first; kb < issued; ++kb)
+                    ptx::mbar_wait(&full_bar[kb % kWideStages], (kb / kWideStages) & 1, nullptr);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ================================================================= MMA issuer (leader only)
+        if (lane == 0 && leader)
+        {
+            const uint32_t idesc  = ptx::make_idesc_tf32(2 * kBM, 256, a_mn != 0, b_mn != 0);
+            const uint32_t a_step = a_mn ? 1024u : 32u;
+            const uint32_t b_step = b_mn ? 1024u : 32u;
+            const uint32_t a_lbo  = a_mn ? 4096u : 16u;
+            const uint32_t b_lbo  = b_mn ? 4096u : 16u;
+            const uint32_t a_sbo  = a_mn ? 512u : 1024u;
+            const uint32_t b_sbo  = b_mn ? 512u : 1024u;
+            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            bool ok               = true;
+            for (int kb = 0; kb < num_kb; ++kb)
+            {
+                const int s       = kb % kWideStages;
+                const uint32_t ph = (kb / kWideStages) & 1;
+                if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
+                {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t sa = ptx::smem_u32(tiles + s * kWideStage);
+                const uint32_t sb = sa + kBM * kBK * 4;
+#pragma unroll
+                for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                {
+                    const uint64_t da   = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t db0  = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                    const uint64_t db1  = ptx::make_smem_desc(sb + kWideBBlock + kk * b_step, b_lbo, b_sbo, b_lay);
+                    const uint32_t accf = (kb == 0 && kk == 0) ? 0u : 1u;
+                    ptx::mma_tf32_ss_pair(tmem_base, da, db0, idesc, accf);
+                    ptx::mma_tf32_ss_pair(tmem_base + 256, da, db1, idesc, accf);
+                }
+                ptx::mma_commit_pair_both(&empty_bar[s]);
+            }
+            if (ok)
+                ptx::mma_commit_pair_both(acc_full);
+        }
+    }
+    else
+    {
+        // ================================================================= epilogue (warps 2..9, both CTAs)
+        const int e  = warp - 2;
+        const int q  = warp & 3;
+        const int h  = e >> 2;
+        const int cw = h * 256;  // this warp streams columns cw .. cw + 255 of the 512-wide tile
+        const bool have = __all_sync(0xffffffffu, ptx::mbar_wait(acc_full, 0, abort_f));
+        if (have)
+        {
+            ptx::tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + cw;
+            for (int j = 0; j < 8; ++j)
+            {
+                if (n0 + cw + 32 * j >= p.N)
+                    break;
+                uint32_t r[32];
+                float acc[32];
+                ptx::tmem_ld_32x32(taddr + 32 * j, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    acc[i] = __uint_as_float(r[i]);
+                // the operand ring is dead (acc_full fired): its first bytes serve as the per-warp transpose slabs
+                gemm_epilogue_store<256, 32>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw + 32 * j, q, lane);
+            }
+        }
+        ptx::tc_fence_before_sync();
+    }
+
+    __syncthreads();
+    ptx::cluster_sync();
+    if (!skip && warp == 1)
+    {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_f && p.err != nullptr)
+        atomicExch(p.err, 1);
+}
+
 }  // namespace
 
-// Test hook: 0 = use the pair kernel where it pays (automatic), 1 = never, 2 = whenever the shape allows it.
+// Test hook: 0 = use the pair kernel where it pays (automatic), 1 = never, 2 = whenever the shape allows it,
+// 3 = separate 2-D copies for MN-major operands, 4 = never the 256 x 512 plain-TF32 tile, 5 = like 2 and the 256 x 512
+// tile for every plain-TF32 problem.
 int g_pair_mode = 0;
 extern int g_slabs;
 
@@ -375,7 +599,7 @@ bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int ter
     (void)a_mn, (void)b_mn, (void)terms;
     if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiSplitK)))
         return false;
-    if (g_pair_mode == 2)
+    if (g_pair_mode == 2 || g_pair_mode == 5)
         return true;
     const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
     return pairs >= 74;
@@ -414,6 +638,48 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
             return rc;
         if ((rc = mk(&tm.b_small, B_small, ldb, b_mn, p.N, BN / 2)))
             return rc;
+    }
+    // plain TF32, plain drains, enough 256 x 512 tiles for every pair of SMs: the wide tile (fewer operand bytes per
+    // product); g_slabs / g_chunk_kb (test hooks of the narrow kernel) turn it off
+    const int64_t wide_pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + kWideBN - 1) / kWideBN);
+    if (terms == 1 && g_pair_mode != 4 && g_slabs == 0 && g_chunk_kb == 0 &&
+        (g_pair_mode == 5 || (wide_pairs >= 74 && (p.N % kWideBN == 0 || p.N >= 8 * kWideBN) && p.K >= 4 * kBK)))
+    {
+        static bool wide_attr[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        dev &= 63;
+        if (!wide_attr[dev])
+        {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc2_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem);
+            if (e != cudaSuccess)
+            {
+                set_last_error("cudaFuncSetAttribute(wide pair kernel, smem=%d) failed: %s", kWideSmem, cudaGetErrorString(e));
+                return kCudaError;
+            }
+            wide_attr[dev] = true;
+        }
+        cudaLaunchConfig_t cfg;
+        std::memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim          = dim3(static_cast<unsigned>(2 * wide_pairs), 1, 1);
+        cfg.blockDim         = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kWideSmem;
+        cfg.stream           = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs                = attr;
+        cfg.numAttrs             = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_wide_kernel, tm, p, a_mn, b_mn);
+        ++g_launch_count;
+        if (e != cudaSuccess)
+        {
+            set_last_error("gemm_tc2_wide_kernel launch failed: %s", cudaGetErrorString(e));
+            return kCudaError;
+        }
+        return kOk;
     }
     int slabs = (terms == 1 && p.K >= 8 * kBK) ? 2 : 1;
     if (g_slabs == 1 || g_slabs == 2)

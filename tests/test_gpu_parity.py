@@ -210,6 +210,46 @@ def test_gemm_cta_pair_kernel(ops, M, N, K, ta, tb, precision):
     assert torch.equal(ds, ops.split_tf32(d))
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(129, 256, 32), (256, 300, 64), (300, 520, 100), (1024, 1024, 1024), (2048, 768, 515),
+                                   (512, 1600, 288)])
+def test_gemm_wide_tf32_pair_tile(ops, M, N, K, ta, tb):
+    """Plain TF32 on the 256 x 512 pair tile (two 256-column MMAs per K-step into one 512-column accumulator), forced on
+    shapes with ragged row / column / K tails and second halves that are partly or wholly outside the matrix, with the
+    full epilogue; against float64 within the TF32 bound and bit-identical to the 256 x 256 pair tile."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(M + N + K + 2 * ta + tb + 5)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    outs = {}
+    capi.call("odl_debug_set_tile_n", 256)
+    try:
+        for mode in (5, 2):
+            capi.call("odl_debug_set_pair_mode", mode)
+            colsum = torch.zeros(N, device="cuda")
+            d, ds = ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True,
+                             mask_src=dev(mask), colsum=colsum, want_small=True, precision=1)
+            outs[mode] = (d, ds, colsum)
+    finally:
+        capi.call("odl_debug_set_pair_mode", 0)
+        capi.call("odl_debug_set_tile_n", 0)
+    capi.device_status()
+    d, ds, colsum = outs[5]
+    opa = a.T.astype(np.float64) if ta else a.astype(np.float64)
+    opb = b.T.astype(np.float64) if tb else b.astype(np.float64)
+    pre = opa @ opb + bias
+    ref = np.maximum(pre, 0) * (mask > 0)
+    tol = TOL[1] * np.abs(pre).max()
+    safe = np.abs(pre) > tol
+    assert np.abs(host(d) - ref)[safe].max() <= tol
+    assert max_rel_err(host(colsum), ref.sum(0)) <= 10 * TOL[1]
+    assert torch.equal(ds, ops.split_tf32(d))
+    assert torch.equal(d, outs[2][0]) and torch.equal(colsum, outs[2][2])  # same products, same accumulation order
+
+
 def test_gemm_epilogues(ops):
     rng = np.random.default_rng(3)
     M, N, K = 200, 333, 150
