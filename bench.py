@@ -345,6 +345,25 @@ def run_ours(args):
                             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                             "peak_source": f"{peaks['source']}: bf16 burst {peaks['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
                             "traffic": GEMM_DRAM_TRAFFIC_BYTES}
+        # the opt-in plain-TF32 mode on the same Linear layer (no operand splits, one MMA per product): context only,
+        # the headline above stays on the default fp32-accurate mode
+        def lin_step_tf32():
+            y = ops.linear_forward(x, w, b, relu=True, precision=capi.PRECISION_TF32)
+            return ops.linear_backward(x, w, dy, y, precision=capi.PRECISION_TF32)
+
+        for _ in range(3):
+            lin_step_tf32()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(k):
+            lin_step_tf32()
+        e1.record()
+        torch.cuda.synchronize()
+        tf32_ms = e0.elapsed_time(e1) / k
+        capi.device_status()
+        line["linear_fwd_bwd_tf32_mode"] = {"ms": tf32_ms, "tflops": 6 * n ** 3 / (tf32_ms / 1e3) / 1e12,
+                                            "frac_of_tf32_roofline": 6 * n ** 3 / (tf32_ms / 1e3) / 1e12 / tf32_peak,
+                                            "tolerance": "5e-3 (opt-in mode)"}
         if peaks.get("bf16_tflops_sustained"):
             # context: the same kernel against the SUSTAINED library figure (seconds-long loop under the power cap), which
             # is the regime the training step runs in; `peak` / `frac` above stay on the stricter burst figure
