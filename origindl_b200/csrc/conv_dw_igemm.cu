@@ -12,9 +12,9 @@
 //     it and of its low part arrive by TMA from a 2D map over [N*OC][OH*OW] (pixels past the image end read as zeros;
 //     rows past OC belong to the next image and only ever reach accumulator columns that are not stored).
 // A K-block is 32 consecutive pixels of ONE image.  The K-blocks (N * ceil(OH*OW / 32)) are divided among gridDim.y
-// splits of at most 36 blocks each (the accumulator stays in TMEM for the CTA's whole range: truncating accumulation
-// costs about 7.5e-9 per accumulated element); split z stores its partial gw into slice z of a scratch buffer and a
-// second pass adds the slices in order, so the result has the same bits on every run.
+// splits of at most 16 blocks each (the accumulator stays in TMEM for the CTA's whole range: truncating accumulation
+// costs about 7.5e-9 per accumulated element relative to the largest result); split z stores its partial gw into slice z
+// of a scratch buffer and a second pass adds the slices in order, so the result has the same bits on every run.
 // warp 0 lane 0: TMA producer; warp 1 lane 0: MMA issuer; warps 2..9: gather, then epilogue.  Every wait is bounded.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -39,7 +39,7 @@ constexpr int kWorkers  = 8;
 constexpr int kThreads  = 64 + 32 * kWorkers;
 constexpr int kStages   = 2;
 constexpr int kAuxBytes = 256;
-constexpr int kMaxKb    = 36;   // K-blocks one CTA accumulates in TMEM (1152 pixels)
+constexpr int kMaxKb    = 16;   // K-blocks one CTA accumulates in TMEM (512 pixels: 3.8e-6 of truncation error)
 
 struct DwGeom
 {
@@ -355,8 +355,28 @@ bool conv_dw_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t 
     const int64_t chunks = (ohw + kBK - 1) / kBK;
     // the TMA map over gy needs a 16-byte row pitch; 32-bit element offsets into x; a bounded number of splits
     return g_conv_mode != 1 && (ohw & 3) == 0 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20) &&
-           N * OC < (int64_t(1) << 31) && ckk * OC <= (int64_t(1) << 24) && N * chunks <= 65535 * int64_t(kMaxKb);
+           N * OC < (int64_t(1) << 31) && ckk * OC <= (int64_t(1) << 24) && N * chunks <= 60000 * int64_t(kMaxKb);
 }
+
+namespace
+{
+// K-blocks per split: enough splits that no CTA accumulates more than kMaxKb blocks in TMEM, then as many as fill the
+// last wave of CTAs (two per SM) they start.
+int plan_kb_per_split(int64_t total_kb, int64_t tiles)
+{
+    const int64_t slots  = 296;
+    const int64_t needed = (total_kb + kMaxKb - 1) / kMaxKb;
+    const int64_t waves  = (tiles * needed + slots - 1) / slots;
+    int64_t splits       = waves * slots / tiles;
+    if (splits < needed)
+        splits = needed;
+    if (splits > total_kb)
+        splits = total_kb;
+    if (splits < 1)
+        splits = 1;
+    return static_cast<int>((total_kb + splits - 1) / splits);
+}
+}  // namespace
 
 // Number of floats of scratch conv_dw_igemm_launch needs for its split slices.
 size_t conv_dw_igemm_scratch(int64_t N, int64_t C, int64_t OC, int KH, int KW, int OH, int OW)
@@ -364,9 +384,7 @@ size_t conv_dw_igemm_scratch(int64_t N, int64_t C, int64_t OC, int KH, int KW, i
     const int64_t ckk = C * KH * KW, chunks = (static_cast<int64_t>(OH) * OW + kBK - 1) / kBK, total_kb = N * chunks;
     const int bn      = OC <= 64 ? 64 : 128;
     const int64_t tiles = ((ckk + kBM - 1) / kBM) * ((OC + bn - 1) / bn);
-    int64_t want      = 296 / tiles < 1 ? 1 : 296 / tiles;
-    int64_t per       = (total_kb + want - 1) / want;
-    per               = per > kMaxKb ? kMaxKb : per;
+    const int64_t per    = plan_kb_per_split(total_kb, tiles);
     const int64_t splits = (total_kb + per - 1) / per;
     return static_cast<size_t>(splits) * OC * ckk;
 }
@@ -386,10 +404,7 @@ int conv_dw_igemm_launch(const float *x, const float *gy, const float *gy_small,
     g.slice    = OC * static_cast<int64_t>(g.ckk);
     const int bn      = OC <= 64 ? 64 : 128;
     const int tiles   = ((g.ckk + kBM - 1) / kBM) * (((int)OC + bn - 1) / bn);
-    const int want    = 296 / tiles < 1 ? 1 : 296 / tiles;  // two CTAs per SM
-    g.kb_per_split    = (g.total_kb + want - 1) / want;
-    if (g.kb_per_split > kMaxKb)
-        g.kb_per_split = kMaxKb;
+    g.kb_per_split    = plan_kb_per_split(g.total_kb, tiles);
     const int splits = (g.total_kb + g.kb_per_split - 1) / g.kb_per_split;
     GemmParams p;
     std::memset(&p, 0, sizeof(p));

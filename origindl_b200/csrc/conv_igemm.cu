@@ -11,9 +11,9 @@
 //
 // One CTA = 128 output pixels x BN output channels; warp 0 lane 0: TMA producer of the weight tiles; warp 1 lane 0: MMA
 // issuer (TMEM accumulator, all of K in one pass: the truncating accumulation costs about 7.5e-9 * K relative error,
-// so one CTA takes at most 1152 of K; for 1152 < K <= 2304 -- 256 channels x 3 x 3 -- the launcher starts clusters of
-// two CTAs that split K, the second handing its partial tile to the first through distributed shared memory; longer
-// reductions go to the explicit path); warps 2..9:
+// so one CTA takes at most 576 of K; for longer reductions up to 2304 -- 256 channels x 3 x 3 -- the launcher starts
+// clusters of two to four CTAs that split K and hand their partial tiles to the first one, one after the other, through
+// distributed shared memory; still longer reductions go to the explicit path); warps 2..9:
 // gather, then epilogue (bias / folded BatchNorm scale / ReLU / SiLU, NCHW store).  Two 48 KB (BN = 64) stages per CTA
 // so that two CTAs share an SM and one's prologue and epilogue overlap the other's main loop.  Every wait is bounded.
 #include <cuda.h>
@@ -40,7 +40,8 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads  = 64 + 32 * kEpiWarps;
 constexpr int kStages   = 2;
 constexpr int kAuxBytes = 256;
-constexpr int kMaxK     = 1152;                  // longest reduction one CTA takes (a cluster of two CTAs: twice that)
+constexpr int kMaxK     = 576;                   // longest reduction one CTA keeps in TMEM (4.3e-6 of truncation error);
+constexpr int kMaxCluster = 4;                   // a cluster of up to four CTAs splits longer ones: K <= 2304
 constexpr int kPartOffset = 40960;               // where rank 1's partial tile lands in rank 0's dead operand ring (after
                                                  // the epilogue's transpose slabs: 8 warps x 32 x 36 floats)
 constexpr int kTabBytes = (kMaxK + 32) * 8;      // per-k lookup table {offset, kh << 16 | kw}, padded to a K-block
@@ -168,9 +169,9 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
                     ptx::mbar_wait_quiet(&b_full[kb % kStages], (kb / kStages) & 1, nullptr);
             }
         }
-        if (cluster_k > 1)
+        __syncwarp();
+        for (int r = 1; r < cluster_k; ++r)  // the barriers of the epilogue warps' hand-over below
         {
-            __syncwarp();
             ptx::cluster_sync();
             ptx::cluster_sync();
         }
@@ -220,9 +221,9 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
             if (ok)
                 ptx::mma_commit(acc_full);
         }
-        if (cluster_k > 1)
+        __syncwarp();
+        for (int r = 1; r < cluster_k; ++r)
         {
-            __syncwarp();
             ptx::cluster_sync();
             ptx::cluster_sync();
         }
@@ -330,30 +331,32 @@ conv_igemm_kernel(const __grid_constant__ TmapPack tm, const float *__restrict__
         }
         if (cluster_k > 1)
         {
-            // K split over the two CTAs of the cluster: rank 1 writes its partial tile into rank 0's dead operand ring
-            // (layout [warp][column][lane]), rank 0 adds it and runs the epilogue.
-            __syncwarp();
-            ptx::cluster_sync();  // both CTAs are past their last MMA
+            // K split over the CTAs of the cluster: ranks 1, 2, ... in turn write their partial tile into rank 0's dead
+            // operand ring (one staging slot, layout [warp][column][lane]) and rank 0 adds it -- a fixed order -- then
+            // runs the epilogue.  Two cluster barriers per rank: slot free / all MMAs done, and data visible.
             const uint32_t rank = ptx::cluster_ctarank();
             float *part         = stg_all + kPartOffset / 4 + static_cast<size_t>(e) * Cfg::warp_cols * 32;
-            if (rank != 0 && have)
+            for (int r = 1; r < cluster_k; ++r)
             {
-                const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(part), 0);
+                __syncwarp();
+                ptx::cluster_sync();
+                if (static_cast<int>(rank) == r && have)
+                {
+                    const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(part), 0);
 #pragma unroll
-                for (int i = 0; i < Cfg::warp_cols; ++i)
-                    ptx::st_shared_cluster_f32(dst + (i * 32 + lane) * 4, acc[i]);
-            }
-            ptx::cluster_sync();
-            if (rank == 0)
-            {
+                    for (int i = 0; i < Cfg::warp_cols; ++i)
+                        ptx::st_shared_cluster_f32(dst + (i * 32 + lane) * 4, acc[i]);
+                }
+                ptx::cluster_sync();
+                if (rank == 0)
+                {
 #pragma unroll
-                for (int i = 0; i < Cfg::warp_cols; ++i)
-                    acc[i] += part[i * 32 + lane];
+                    for (int i = 0; i < Cfg::warp_cols; ++i)
+                        acc[i] += part[i * 32 + lane];
+                }
             }
-            else
-            {
+            if (rank != 0)
                 have = false;
-            }
         }
         if (have)
             gemm_epilogue_store<BN, Cfg::warp_cols>(p, acc, stg_all + e * 32 * kStgLd, m0, n0, cw, q, lane);
@@ -390,7 +393,7 @@ int launch_igemm(const TmapPack &tm, const float *x, const IgemmGeom &g, const G
         attr_set[dev] = true;
     }
     const int tiles_m = (g.rows + kBM - 1) / kBM, tiles_n = (p.N + BN - 1) / BN;
-    const int cluster_k = g.ckk > kMaxK ? 2 : 1;
+    const int cluster_k = (g.ckk + kMaxK - 1) / kMaxK;  // 1..kMaxCluster (the caller checked eligibility)
     static_assert(kPartOffset + kBM * BN * 4 <= kStages * Cfg::stage_bytes, "rank 1's partial tile must fit the ring");
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
@@ -423,7 +426,7 @@ int g_conv_mode = 0;
 bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW)
 {
     const int64_t ckk = C * KH * KW, rows = N * OH * OW;
-    return g_conv_mode != 1 && ckk <= 2 * kMaxK && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
+    return g_conv_mode != 1 && ckk <= kMaxCluster * kMaxK && OC <= 1024 && rows < (int64_t(1) << 31) - 256 && N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
 }
 
 // w_big / w_small: the weights as a K-major [OC][ldw] matrix (ldw a multiple of 4, 16-byte aligned) and its low part.

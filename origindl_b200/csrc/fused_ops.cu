@@ -259,15 +259,14 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     const size_t ctb    = a256(static_cast<size_t>(ckk) * ldt * 4);
     arena_reset();
     const bool dx_direct = gx && conv_dx_direct_eligible(N, C, H, W, OC, KH, KW, S);
-    // weight gradient without a column matrix: the implicit GEMM over pixels (the correct gradient layout only: gy must be
-    // a real, 16-byte-aligned NCHW tensor), or for small layers a direct fp32 kernel, which wins only for the very
-    // shortest rows of gw (C*KH*KW <= 64: 0.041 against 0.063 ms for a 32 -> 32 1x1 layer on 80 x 80 x 16; 0.188 against
-    // 0.172 ms for 3 -> 16 6x6 on 320 x 320 x 16)
+    // weight gradient without a column matrix: for small layers a direct fp32 kernel (measured 0.188 / 0.095 / 0.041 ms
+    // against 0.206 / 0.099 / 0.063 ms for the benchmark's first three conv layers), else the implicit GEMM over pixels
+    // (the correct gradient layout only: gy must be a real, 16-byte-aligned NCHW tensor)
     const bool dw_igemm_ok = gw && mode == 0 && !(reinterpret_cast<uintptr_t>(gy) & 15) &&
                              conv_dw_igemm_eligible(N, C, H, W, OC, KH, KW, OH, OW);
     const bool dw_direct_ok = gw && conv_dw_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW);
-    const bool dw_igemm  = dw_igemm_ok && (!dw_direct_ok || ckk > 64);
-    const bool dw_direct = dw_direct_ok && !dw_igemm;
+    const bool dw_direct = dw_direct_ok;
+    const bool dw_igemm  = dw_igemm_ok && !dw_direct;
     // stride 1, the correct gradient layout: gx is itself a convolution of gy (no column-gradient matrix, no col2im)
     const bool dx_igemm = gx && !dx_direct && mode == 0 && conv_dx_igemm_eligible(N, C, H, W, OC, KH, KW, S, P, OH, OW);
     const size_t wfb    = a256(static_cast<size_t>(C) * pad4(OC * KH * KW) * 4);

@@ -438,9 +438,10 @@ def test_conv2d_vs_oracle(ops, orc, N, C, H, W, OC, k, s, p):
 IGEMM_CASES = CONV_CASES + [(3, 3, 33, 29, 16, 6, 2, 2),      # ragged pixel count, K = 108 (not a multiple of 32)
                             (2, 5, 11, 13, 70, 3, 1, 1),      # K = 45 (not a multiple of 4: padded weights), 64 < OC
                             (1, 8, 14, 14, 130, 3, 2, 0),     # OC > 128: two column tiles
-                            (1, 128, 6, 6, 32, 3, 1, 1),      # K = 1152, the longest reduction one CTA takes
-                            (1, 130, 6, 6, 8, 3, 1, 1),       # K = 1170: a cluster of two CTAs splits K (37 K-blocks: 19 + 18)
-                            (2, 256, 7, 9, 200, 3, 1, 1),     # K = 2304 = 256 channels x 3 x 3, the longest implicit reduction
+                            (1, 64, 6, 6, 32, 3, 1, 1),       # K = 576, the longest reduction one CTA keeps in TMEM
+                            (1, 128, 6, 6, 32, 3, 1, 1),      # K = 1152: a cluster of two CTAs splits K
+                            (1, 130, 6, 6, 8, 3, 1, 1),       # K = 1170: three CTAs (37 K-blocks: 13 + 13 + 11)
+                            (2, 256, 7, 9, 200, 3, 1, 1),     # K = 2304 = 256 channels x 3 x 3: four CTAs, the longest implicit reduction
                             (1, 260, 5, 5, 12, 3, 1, 1)]      # K = 2340: falls back to the explicit path
 
 
