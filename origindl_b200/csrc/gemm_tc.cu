@@ -183,26 +183,26 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                 ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
                 for (int sl = 0; sl < slabs; ++sl)
                 {
-                uint8_t *st  = tiles + s * stage_bytes + sl * slab_bytes;
-                const int k0 = ((kb_first + kb) * slabs + sl) * BK;
-                for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
-                {
-                    uint8_t *sa           = st + t * Cfg::a_bytes;
-                    const CUtensorMap *ma = t ? &tm.a_small : &tm.a;
-                    if (!a_mn)
+                    uint8_t *st  = tiles + s * stage_bytes + sl * slab_bytes;
+                    const int k0 = ((kb_first + kb) * slabs + sl) * BK;
+                    for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
                     {
-                        ptx::tma_load_2d(sa, ma, &full_bar[s], k0, m0);
-                    }
-                    else if (a_mn & 2)
-                    {
-                        ptx::tma_load_3d(sa, ma, &full_bar[s], 0, k0, m0 / 32);  // all four 32 x BK boxes in one copy
-                    }
-                    else
-                    {
-#pragma unroll
-                        for (int j = 0; j < kBM / 32; ++j)
-                            ptx::tma_load_2d(sa + j * Cfg::mn_box, ma, &full_bar[s], m0 + 32 * j, k0);
-                    }
+                        uint8_t *sa           = st + t * Cfg::a_bytes;
+                        const CUtensorMap *ma = t ? &tm.a_small : &tm.a;
+                        if (!a_mn)
+                        {
+                            ptx::tma_load_2d(sa, ma, &full_bar[s], k0, m0);
+                        }
+                        else if (a_mn & 2)
+                        {
+                            ptx::tma_load_3d(sa, ma, &full_bar[s], 0, k0, m0 / 32);  // all four 32 x BK boxes in one copy
+                        }
+                        else
+                        {
+    #pragma unroll
+                            for (int j = 0; j < kBM / 32; ++j)
+                                ptx::tma_load_2d(sa + j * Cfg::mn_box, ma, &full_bar[s], m0 + 32 * j, k0);
+                        }
                 }
                 uint8_t *sb0 = st + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
                 for (int t = 0; t < (terms == 3 ? 2 : 1); ++t)
@@ -285,29 +285,29 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const in
                     ptx::tc_fence_after_sync();
                     for (int sl = 0; sl < slabs; ++sl)
                     {
-                    const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes + sl * slab_bytes);
-                    const uint32_t sas = sa + Cfg::a_bytes;
-                    const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
-                    const uint32_t sbs = sb + Cfg::b_bytes;
-#pragma unroll
-                    for (int kk = 0; kk < BK / kUmmaK; ++kk)
-                    {
-                        const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
-                        const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
-                        if (terms == 3)
+                        const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes + sl * slab_bytes);
+                        const uint32_t sas = sa + Cfg::a_bytes;
+                        const uint32_t sb  = sa + (terms == 3 ? 2 : 1) * Cfg::a_bytes;
+                        const uint32_t sbs = sb + Cfg::b_bytes;
+    #pragma unroll
+                        for (int kk = 0; kk < BK / kUmmaK; ++kk)
                         {
-                            const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
-                            const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
-                            // small cross terms first, the dominant term last
-                            ptx::mma_tf32_ss(tmem_d, das, db, idesc, first ? 0u : 1u);
-                            ptx::mma_tf32_ss(tmem_d, da, dbs, idesc, 1);
-                            ptx::mma_tf32_ss(tmem_d, da, db, idesc, 1);
-                        }
-                        else
-                        {
-                            ptx::mma_tf32_ss(tmem_d, da, db, idesc, first ? 0u : 1u);
-                        }
-                        first = false;
+                            const uint64_t da = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                            const uint64_t db = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                            if (terms == 3)
+                            {
+                                const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
+                                const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
+                                // small cross terms first, the dominant term last
+                                ptx::mma_tf32_ss(tmem_d, das, db, idesc, first ? 0u : 1u);
+                                ptx::mma_tf32_ss(tmem_d, da, dbs, idesc, 1);
+                                ptx::mma_tf32_ss(tmem_d, da, db, idesc, 1);
+                            }
+                            else
+                            {
+                                ptx::mma_tf32_ss(tmem_d, da, db, idesc, first ? 0u : 1u);
+                            }
+                            first = false;
                     }
                     }
                     ptx::mma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
