@@ -272,8 +272,9 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     const size_t wfb    = a256(static_cast<size_t>(C) * pad4(OC * KH * KW) * 4);
     const size_t gysb = a256(static_cast<size_t>(rows) * OC * 4);
     const size_t slb  = dw_igemm ? a256(conv_dw_igemm_scratch(N, C, OC, KH, KW, OH, OW) * 4) : 0;
-    int rc = arena_reserve((dx_igemm ? 2 * wfb : 0) + (dw_igemm ? gysb + slb : 0) + (gw && !dw_direct && !dw_igemm ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb + (gx && !dx_direct && !dx_igemm ? ctb : 0) +
-                           2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
+    int rc = arena_reserve((dx_igemm ? 2 * wfb : 0) + (dw_igemm ? gysb + slb : 0) +
+                           (gw && !dw_direct && !dw_igemm ? colb * (terms == 3 ? 2 : 1) : 0) + 2 * gyb +
+                           (gx && !dx_direct && !dx_igemm ? ctb : 0) + 2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
     if (gb)
