@@ -9,6 +9,8 @@
 //   origin::Optimizer, SGD, Adam, WeightDecay   src/optim/*.cpp, include/origin/optim/hooks.h
 //   origin::MemoryPool                    src/mat/origin/memory/memory_pool.cpp:37-176 (size-binned caching allocator)
 //   origin::save / load / Checkpoint / load_checkpoint   src/io/model_io.cpp:114-273, src/io/checkpoint.cpp:15-226
+//   origin::Dataset, DataLoader           include/origin/data/dataset.h, src/data/dataloader.cpp:11-146 (data set resident
+//                                         in device memory, batches assembled by a gather kernel)
 //
 // Differences that are deliberate: tensors of this layer live on the device only (fp32 data, int32/int64 labels);
 // nn::Linear and nn::MLP run the fused Linear(+ReLU) operator (one kernel forward, three backward) instead of
@@ -1709,5 +1711,160 @@ inline Checkpoint load_checkpoint(const std::string &filepath)
     }
     return ck;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Dataset / DataLoader (include/origin/data/dataset.h:12-26, include/origin/data/dataloader.h:14-52,
+// src/data/dataloader.cpp:11-146).  Same interface, batch order and error behaviour: samples are flattened to
+// {batch, elements}; integer labels come out as int64, other labels as float32; the last batch of an epoch is short;
+// next() past the end throws std::runtime_error.  What differs is where the work happens: the reference calls get_item()
+// for every sample of every batch and assembles the batch on the host.  Here the data set is read ONCE (get_item() for
+// every index at the first next(), device-to-device copies into one resident matrix) and every batch is one row-gather
+// kernel (odl_gather_rows) driven by the epoch's index list, which is uploaded at reset().  A data set whose get_item() is
+// not a pure function of the index (augmentation) must pass cache = false; batches are then gathered from fresh
+// get_item() calls as in the reference.  The reference seeds its shuffle from std::random_device; `seed` makes the order
+// reproducible (0 = from std::random_device).
+class Dataset
+{
+  public:
+    virtual ~Dataset() = default;
+    virtual std::pair<Tensor, Tensor> get_item(size_t index) = 0;
+    virtual size_t size() const = 0;
+    bool valid_index(size_t index) const { return index < size(); }
+};
+
+class DataLoader
+{
+  public:
+    DataLoader(Dataset &dataset, size_t batch_size = 1, bool shuffle = false, uint64_t seed = 0, bool cache = true)
+        : dataset_(&dataset), batch_size_(batch_size), shuffle_(shuffle), cache_(cache),
+          gen_(seed ? seed : std::random_device{}())
+    {
+        if (batch_size_ == 0)
+            throw std::invalid_argument("DataLoader: batch size must be positive");
+        reset_indices();
+    }
+
+    bool has_next() const { return current_index_ < indices_.size(); }
+    size_t dataset_size() const { return dataset_->size(); }
+    size_t batch_size() const { return batch_size_; }
+    void reset() { reset_indices(); }
+
+    std::pair<Tensor, Tensor> next()
+    {
+        if (!has_next())
+            throw std::runtime_error(
+                "DataLoader::next() called when no more data available. Use has_next() to check before calling next().");
+        const size_t rows = std::min(batch_size_, indices_.size() - current_index_);
+        if (!cache_)
+        {
+            // gather this batch's samples from fresh get_item() calls, then the same device-side assembly
+            std::vector<size_t> ids(indices_.begin() + current_index_, indices_.begin() + current_index_ + rows);
+            Resident batch = read(ids);
+            current_index_ += rows;
+            return {batch.x, batch.t};
+        }
+        if (!all_.x.defined())
+        {
+            std::vector<size_t> ids(dataset_->size());
+            for (size_t i = 0; i < ids.size(); ++i)
+                ids[i] = i;
+            all_ = read(ids);
+        }
+        if (!dev_indices_.defined())
+        {
+            std::vector<int64_t> idx(indices_.begin(), indices_.end());
+            dev_indices_ = Tensor(idx, Shape{idx.size()}, dtype(DataType::kInt64));
+        }
+        const int64_t cols = static_cast<int64_t>(all_.x.shape()[1]), n = static_cast<int64_t>(all_.x.shape()[0]);
+        Tensor x = Tensor::empty(Shape{rows, static_cast<size_t>(cols)});
+        const int64_t *idx = dev_indices_.data_ptr<int64_t>() + current_index_;
+        Tensor t;
+        if (all_.t.dtype() == DataType::kInt64)
+        {
+            t = Tensor::empty(Shape{rows}, dtype(DataType::kInt64));
+            odl_check(odl_gather_rows(all_.x.data_ptr<float>(), cols, n, idx, static_cast<int64_t>(rows), cols, x.data_ptr<float>(),
+                                      cols, all_.t.data_ptr<int64_t>(), t.data_ptr<int64_t>(), nullptr));
+        }
+        else
+        {
+            t = Tensor::empty(Shape{rows});
+            odl_check(odl_gather_rows(all_.x.data_ptr<float>(), cols, n, idx, static_cast<int64_t>(rows), cols, x.data_ptr<float>(),
+                                      cols, nullptr, nullptr, nullptr));
+            odl_check(odl_gather_rows(all_.t.data_ptr<float>(), 1, n, idx, static_cast<int64_t>(rows), 1, t.data_ptr<float>(), 1,
+                                      nullptr, nullptr, nullptr));
+        }
+        current_index_ += rows;
+        return {x, t};
+    }
+
+  private:
+    struct Resident
+    {
+        Tensor x;  // {samples, elements} float32
+        Tensor t;  // {samples} int64 (integer labels) or float32
+    };
+
+    // Samples ids[0..] as one device matrix and one label vector (DataLoader::next's per-sample loop, done with
+    // device-to-device copies; integer labels of any width become int64 as in the reference).
+    Resident read(const std::vector<size_t> &ids)
+    {
+        Resident r;
+        if (ids.empty())
+            return r;
+        auto first            = dataset_->get_item(ids[0]);
+        const size_t elements = first.first.elements();
+        const DataType ldt    = first.second.dtype();
+        const bool int_labels = ldt != DataType::kFloat32;
+        r.x                   = Tensor::empty(Shape{ids.size(), elements});
+        Tensor raw = Tensor::empty(Shape{ids.size()}, dtype(ldt));  // labels in the data set's own type
+        for (size_t i = 0; i < ids.size(); ++i)
+        {
+            auto item = i == 0 ? first : dataset_->get_item(ids[i]);
+            if (item.first.elements() != elements)
+                throw std::runtime_error("Inconsistent input shapes in dataset: expected " + std::to_string(elements) +
+                                         " elements, got " + std::to_string(item.first.elements()));
+            if (item.first.dtype() != DataType::kFloat32 || item.second.dtype() != ldt || item.second.elements() != 1)
+                throw std::runtime_error("DataLoader: inputs must be float32 and labels single values of one type");
+            cuda_check(cudaMemcpyAsync(r.x.data_ptr<float>() + i * elements, item.first.data_ptr<float>(), elements * 4,
+                                       cudaMemcpyDeviceToDevice, nullptr),
+                       "DataLoader: sample copy");
+            cuda_check(cudaMemcpyAsync(static_cast<char *>(raw.data_ptr<void>()) + i * element_size(ldt),
+                                       item.second.data_ptr<void>(), element_size(ldt), cudaMemcpyDeviceToDevice, nullptr),
+                       "DataLoader: label copy");
+        }
+        if (!int_labels || ldt == DataType::kInt64)
+        {
+            r.t = raw;
+        }
+        else
+        {
+            std::vector<int32_t> narrow = raw.to_vector<int32_t>();
+            std::vector<int64_t> wide(narrow.begin(), narrow.end());
+            r.t = Tensor(wide, Shape{wide.size()}, dtype(DataType::kInt64));
+        }
+        synchronize();  // the items' storage may be released once this returns
+        return r;
+    }
+
+    void reset_indices()
+    {
+        indices_.resize(dataset_->size());
+        for (size_t i = 0; i < indices_.size(); ++i)
+            indices_[i] = i;
+        if (shuffle_)
+            std::shuffle(indices_.begin(), indices_.end(), gen_);
+        current_index_ = 0;
+        dev_indices_   = Tensor();
+    }
+
+    Dataset *dataset_;
+    size_t batch_size_;
+    bool shuffle_, cache_;
+    std::mt19937_64 gen_;
+    std::vector<size_t> indices_;
+    size_t current_index_ = 0;
+    Resident all_;
+    Tensor dev_indices_;
+};
 
 }  // namespace origin

@@ -499,6 +499,146 @@ static void checkpoint_cases()
 }
 
 // ---- memory pool: bins and reuse (src/mat/origin/memory/memory_pool.cpp)
+// ---- DataLoader: the cases of tests/unit_test/data/test_dataloader.cpp (BasicIteration, Reset, Shuffle, BatchSizeOne,
+//      EmptyDataset) plus the VALUES of every batch, integer labels (int64 out), multi-element samples, the uncached mode
+//      and training straight from the loader.
+namespace
+{
+class IndexDataset : public Dataset
+{
+  public:
+    IndexDataset(size_t n, size_t width, bool int_labels) : n_(n), width_(width), int_labels_(int_labels) {}
+    std::pair<Tensor, Tensor> get_item(size_t index) override
+    {
+        if (index >= n_)
+            throw std::out_of_range("Index out of range");
+        ++calls;
+        std::vector<float> v(width_);
+        for (size_t j = 0; j < width_; ++j)
+            v[j] = static_cast<float>(index) + 0.25f * static_cast<float>(j);
+        Tensor x = width_ == 4 ? Tensor(v, Shape{2, 2}) : Tensor(v, Shape{width_});
+        Tensor t = int_labels_ ? Tensor(std::vector<int32_t>{static_cast<int32_t>(index % 10)}, Shape{}, dtype(DataType::kInt32))
+                               : Tensor(std::vector<float>{static_cast<float>(index % 10)}, Shape{});
+        return {x, t};
+    }
+    size_t size() const override { return n_; }
+    size_t calls = 0;
+
+  private:
+    size_t n_, width_;
+    bool int_labels_;
+};
+}  // namespace
+
+static void dataloader_cases()
+{
+    {  // BasicIteration: 10 samples in batches of 3 -> 3, 3, 3, 1; values follow the index order
+        IndexDataset ds(10, 1, false);
+        DataLoader loader(ds, 3, false);
+        EXPECT_TRUE(loader.has_next() && loader.batch_size() == 3 && loader.dataset_size() == 10);
+        size_t seen = 0;
+        for (size_t want : {3u, 3u, 3u, 1u})
+        {
+            auto [x, t] = loader.next();
+            EXPECT_TRUE(x.shape() == Shape({want, 1}) && t.shape() == Shape({want}) && t.dtype() == DataType::kFloat32);
+            auto xv = x.to_vector<float>(), tv = t.to_vector<float>();
+            for (size_t i = 0; i < want; ++i, ++seen)
+                EXPECT_TRUE(xv[i] == static_cast<float>(seen) && tv[i] == static_cast<float>(seen % 10));
+        }
+        EXPECT_TRUE(!loader.has_next());
+        EXPECT_THROW(loader.next());
+        EXPECT_TRUE(ds.calls == 10);  // the data set was read once
+    }
+    {  // Reset
+        IndexDataset ds(5, 1, false);
+        DataLoader loader(ds, 2, false);
+        loader.next();
+        EXPECT_TRUE(loader.has_next());
+        loader.reset();
+        auto [x, t] = loader.next();
+        EXPECT_TRUE(x.shape()[0] == 2 && x.to_vector<float>()[0] == 0.0f);
+    }
+    {  // Shuffle: a permutation, reproducible for one seed, different after reset(); int32 labels come out as int64
+        IndexDataset ds(50, 4, true);
+        DataLoader a(ds, 50, true, 7), b(ds, 50, true, 7);
+        auto [xa, ta] = a.next();
+        auto [xb, tb] = b.next();
+        EXPECT_TRUE(xa.shape() == Shape({50, 4}) && ta.dtype() == DataType::kInt64);
+        auto va = xa.to_vector<float>(), vb = xb.to_vector<float>();
+        auto la = ta.to_vector<int64_t>();
+        EXPECT_TRUE(va == vb);
+        std::vector<int> hit(50, 0);
+        bool in_order = true, rows_ok = true;
+        for (size_t i = 0; i < 50; ++i)
+        {
+            const int id = static_cast<int>(va[4 * i]);
+            hit[id]++;
+            in_order = in_order && id == static_cast<int>(i);
+            rows_ok  = rows_ok && va[4 * i + 3] == static_cast<float>(id) + 0.75f && la[i] == id % 10;
+        }
+        EXPECT_TRUE(rows_ok && !in_order && *std::min_element(hit.begin(), hit.end()) == 1);
+        a.reset();
+        EXPECT_TRUE(a.next().first.to_vector<float>() != va);
+    }
+    {  // BatchSizeOne
+        IndexDataset ds(5, 1, false);
+        DataLoader loader(ds, 1, false);
+        for (size_t i = 0; i < 5; ++i)
+        {
+            EXPECT_TRUE(loader.has_next());
+            auto [x, t] = loader.next();
+            EXPECT_TRUE(x.shape()[0] == 1 && t.shape()[0] == 1 && x.to_vector<float>()[0] == static_cast<float>(i));
+        }
+        EXPECT_TRUE(!loader.has_next());
+    }
+    {  // EmptyDataset
+        IndexDataset ds(0, 1, false);
+        DataLoader loader(ds, 1, false);
+        EXPECT_TRUE(!loader.has_next() && loader.dataset_size() == 0);
+        EXPECT_THROW(loader.next());
+    }
+    {  // uncached mode: get_item() runs for every sample of every epoch, batches are the same
+        IndexDataset ds(7, 4, true);
+        DataLoader cached(ds, 3, false), fresh(ds, 3, false, 0, false);
+        while (cached.has_next())
+        {
+            auto c = cached.next();
+            auto f = fresh.next();
+            EXPECT_TRUE(c.first.to_vector<float>() == f.first.to_vector<float>() &&
+                        c.second.to_vector<int64_t>() == f.second.to_vector<int64_t>());
+        }
+        EXPECT_TRUE(!fresh.has_next());
+        const size_t before = ds.calls;
+        fresh.reset();
+        while (fresh.has_next())
+            fresh.next();
+        EXPECT_TRUE(ds.calls == before + 7);
+    }
+    {  // training from the loader: the loss of a small classifier falls
+        IndexDataset ds(64, 4, true);
+        DataLoader loader(ds, 16, true, 3);
+        nn::MLP model({4, 32, 10});
+        Adam opt(model, 1e-2f);
+        float first = 0.f, last = 0.f;
+        for (int epoch = 0; epoch < 30; ++epoch)
+        {
+            loader.reset();
+            while (loader.has_next())
+            {
+                auto [x, t] = loader.next();
+                Tensor loss = functional::softmax_cross_entropy(model(x), t);
+                model.zero_grad();
+                loss.backward();
+                opt.step();
+                last = loss.item<float>();
+                if (epoch == 0 && first == 0.f)
+                    first = last;
+            }
+        }
+        EXPECT_TRUE(last < 0.7f * first);
+    }
+}
+
 static void memory_pool()
 {
     EXPECT_TRUE(MemoryPool::bin_size(1) == 256 && MemoryPool::bin_size(257) == 512 && MemoryPool::bin_size(300000) == 524288);
@@ -535,7 +675,8 @@ int main(int argc, char **argv)
         {"conv2d", conv2d_cases},             {"weight_decay_and_adam", weight_decay_and_adam},
         {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
         {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases},
-        {"batch_norm_silu", batch_norm_cases}};
+        {"batch_norm_silu", batch_norm_cases},
+        {"dataloader", dataloader_cases}};
     for (auto &t : tests)
     {
         const int before = g_failed;
