@@ -5,6 +5,8 @@
 //   origin::Operator forward()/backward() include/origin/core/operator.h:12-125 (tape: src/core/tensor_impl.cpp:78-278)
 //   origin::functional::mat_mul, relu, custom_linear, softmax_cross_entropy, conv2d, sum, broadcast_to, sum_to
 //   origin::nn::Module, Linear, MLP       src/nn/module.cpp, src/nn/layers/linear.cpp, src/nn/models/mlp.cpp
+//   origin::nn::Conv2d, BatchNorm1d, ReLU, SiLU, Flatten; origin::Sequential; functional::reshape, flatten
+//                                         src/nn/layers/conv2d.cpp, batch_norm1d.cpp, relu.cpp, flatten.cpp, src/nn/sequential.cpp
 //   functional::batch_norm, silu; nn::BatchNorm2d   src/operators/normalization/batch_norm.cpp, src/nn/layers/batch_norm2d.cpp
 //   origin::Optimizer, SGD, Adam, WeightDecay   src/optim/*.cpp, include/origin/optim/hooks.h
 //   origin::MemoryPool                    src/mat/origin/memory/memory_pool.cpp:37-176 (size-binned caching allocator)
@@ -998,6 +1000,48 @@ inline Tensor custom_linear(const Tensor &x, const Tensor &weight, int in_featur
 {
     return std::make_shared<LinearOp>(in_features, out_features, false)->call1({x, weight});
 }
+// A view of the same storage under another shape; the gradient is the upstream gradient under the input's shape
+// (src/operators/shape/reshape.cpp; flatten: src/operators/shape/flatten.cpp).  No kernel runs in either direction.
+class Reshape : public Operator
+{
+  public:
+    explicit Reshape(Shape shape) : shape_(std::move(shape)) {}
+    std::vector<Tensor> forward(const std::vector<Tensor> &xs) override
+    {
+        if (xs.size() != 1)
+            throw std::runtime_error("Reshape operator requires exactly 1 input, but got " + std::to_string(xs.size()));
+        return {xs[0].reshape(shape_)};
+    }
+    std::vector<Tensor> backward(const std::vector<Tensor> &gys) override { return {gys[0].reshape(inputs_[0].shape())}; }
+
+  private:
+    Shape shape_;
+};
+
+inline Tensor reshape(const Tensor &x, const Shape &shape) { return std::make_shared<Reshape>(shape)->call1({x}); }
+// Dimensions start_dim..end_dim (negative values count from the end) collapse into one (functional::flatten).
+inline Tensor flatten(const Tensor &x, int start_dim = 1, int end_dim = -1)
+{
+    const int nd = static_cast<int>(x.ndim());
+    const int a = start_dim < 0 ? start_dim + nd : start_dim, b = end_dim < 0 ? end_dim + nd : end_dim;
+    if (a < 0 || b >= nd || a > b)
+        throw std::invalid_argument("flatten: invalid dimensions [" + std::to_string(start_dim) + ", " +
+                                    std::to_string(end_dim) + "] for shape " + x.shape().to_string());
+    std::vector<size_t> d;
+    size_t merged = 1;
+    for (int i = 0; i < nd; ++i)
+    {
+        if (i < a || i > b)
+            d.push_back(x.shape()[i]);
+        else
+        {
+            merged *= x.shape()[i];
+            if (i == b)
+                d.push_back(merged);
+        }
+    }
+    return reshape(x, Shape(d));
+}
 inline Tensor softmax_cross_entropy(const Tensor &x, const Tensor &target)
 {
     return std::make_shared<SoftmaxCrossEntropy>()->call1({x, target});
@@ -1213,7 +1257,149 @@ class MLP : public Module
     std::vector<Linear *> layers_;
 };
 
+// weight {out, in, kh, kw} = randn * sqrt(2 / (in * kh * kw)), bias {out} = 0 (src/nn/layers/conv2d.cpp:15-109).  The
+// kernels take one stride and one padding for both image axes: unequal pairs are refused.
+class Conv2d : public Module
+{
+  public:
+    Conv2d(int in_channels, int out_channels, std::pair<int, int> kernel_size, std::pair<int, int> stride = {1, 1},
+           std::pair<int, int> pad = {0, 0}, bool bias = true)
+        : stride_(stride.first), pad_(pad.first), use_bias_(bias)
+    {
+        if (in_channels <= 0)
+            throw std::invalid_argument("Conv2d: in_channels must be positive, but got " + std::to_string(in_channels));
+        if (out_channels <= 0)
+            throw std::invalid_argument("Conv2d: out_channels must be positive, but got " + std::to_string(out_channels));
+        if (kernel_size.first <= 0 || kernel_size.second <= 0)
+            throw std::invalid_argument("Conv2d: kernel_size must be positive");
+        if (stride.first <= 0 || stride.second <= 0)
+            throw std::invalid_argument("Conv2d: stride must be positive");
+        if (pad.first < 0 || pad.second < 0)
+            throw std::invalid_argument("Conv2d: pad must be non-negative");
+        if (stride.first != stride.second || pad.first != pad.second)
+            throw std::invalid_argument("Conv2d: stride and pad must be the same for both image axes");
+        const Shape ws{(size_t)out_channels, (size_t)in_channels, (size_t)kernel_size.first, (size_t)kernel_size.second};
+        Tensor w  = Tensor::randn(ws, TensorOptions().requires_grad(true));
+        Tensor sc = Tensor::empty(ws, TensorOptions().requires_grad(true));
+        const float std_dev = std::sqrt(2.0f / (float)(in_channels * kernel_size.first * kernel_size.second));
+        odl_check(odl_scale(w.data_ptr<float>(), std_dev, sc.data_ptr<float>(), detail::i64(w.elements()), nullptr));
+        weight_ = Parameter(sc);
+        register_parameter("weight", weight_);
+        if (use_bias_)
+        {
+            bias_ = Parameter(Tensor::zeros(Shape{(size_t)out_channels}, TensorOptions().requires_grad(true)));
+            register_parameter("bias", bias_);
+        }
+    }
+    Conv2d(int in_channels, int out_channels, int kernel_size, int stride = 1, int pad = 0, bool bias = true)
+        : Conv2d(in_channels, out_channels, {kernel_size, kernel_size}, {stride, stride}, {pad, pad}, bias)
+    {
+    }
+    Tensor forward(const Tensor &input) override
+    {
+        return functional::conv2d(input, weight_, use_bias_ ? &bias_ : nullptr, stride_, pad_);
+    }
+    Parameter *weight() { return &weight_; }
+    Parameter *bias() { return use_bias_ ? &bias_ : nullptr; }
+
+  private:
+    int stride_, pad_;
+    bool use_bias_;
+    Parameter weight_, bias_;
+};
+
+// BatchNorm over {N, C} inputs (src/nn/layers/batch_norm1d.cpp): the same kernels with one value per channel and sample.
+class BatchNorm1d : public Module
+{
+  public:
+    explicit BatchNorm1d(int num_features, float eps = 1e-5f, float momentum = 0.1f, int act = ODL_ACT_NONE)
+        : num_features_(num_features), eps_(eps), momentum_(momentum), act_(act)
+    {
+        if (num_features <= 0)
+            throw std::invalid_argument("BatchNorm1d: num_features must be positive, but got " + std::to_string(num_features));
+        const Shape s{(size_t)num_features};
+        gamma_        = Parameter(Tensor::ones(s, TensorOptions().requires_grad(true)));
+        beta_         = Parameter(Tensor::zeros(s, TensorOptions().requires_grad(true)));
+        running_mean_ = Tensor::zeros(s);
+        running_var_  = Tensor::ones(s);
+        register_parameter("weight", gamma_);
+        register_parameter("bias", beta_);
+    }
+    Tensor forward(const Tensor &input) override
+    {
+        if (input.ndim() != 2 || input.shape()[1] != (size_t)num_features_)
+            throw std::runtime_error("BatchNorm1d forward: input must be (N, " + std::to_string(num_features_) +
+                                     "), but got shape " + input.shape().to_string());
+        auto op = std::make_shared<functional::BatchNorm>(is_training(), eps_, momentum_, 2, act_, is_training());
+        return op->call1({input, gamma_, beta_, running_mean_, running_var_});
+    }
+    const Tensor &running_mean() const { return running_mean_; }
+    const Tensor &running_var() const { return running_var_; }
+
+  private:
+    int num_features_;
+    float eps_, momentum_;
+    int act_;
+    Parameter gamma_, beta_;
+    Tensor running_mean_, running_var_;
+};
+
+// Parameter-free layers (src/nn/layers/relu.cpp, flatten.cpp).
+class ReLU : public Module
+{
+  public:
+    Tensor forward(const Tensor &input) override { return functional::relu(input); }
+};
+class SiLU : public Module
+{
+  public:
+    Tensor forward(const Tensor &input) override { return functional::silu(input); }
+};
+class Flatten : public Module
+{
+  public:
+    explicit Flatten(int start_dim = 1, int end_dim = -1) : start_dim_(start_dim), end_dim_(end_dim) {}
+    Tensor forward(const Tensor &input) override { return functional::flatten(input, start_dim_, end_dim_); }
+
+  private:
+    int start_dim_, end_dim_;
+};
+
 }  // namespace nn
+
+// Modules applied one after the other (include/origin/nn/sequential.h, src/nn/sequential.cpp:7-62): add(), forward(),
+// parameters(), operator[], size() as in the reference.  One deliberate difference: the reference keeps the children in
+// a private vector that Module::named_parameters() never sees, so its state_dict() of a Sequential is empty; here the
+// children are registered under "0", "1", ... and state_dict() / load_state_dict() / checkpoints cover them.
+class Sequential : public nn::Module
+{
+  public:
+    void add(std::unique_ptr<nn::Module> module)
+    {
+        if (!module)
+            throw std::invalid_argument("Sequential::add: null module");
+        order_.push_back(module.get());
+        register_module(std::to_string(order_.size() - 1), std::move(module));
+    }
+    Tensor forward(const Tensor &input) override
+    {
+        Tensor out = input;
+        for (nn::Module *m : order_)
+            out = m->forward(out);
+        return out;
+    }
+    nn::Module &operator[](size_t index)
+    {
+        if (index >= order_.size())
+            throw std::runtime_error("Index " + std::to_string(index) + " out of range for Sequential with " +
+                                     std::to_string(order_.size()) + " modules");
+        return *order_[index];
+    }
+    size_t size() const { return order_.size(); }
+
+  private:
+    std::vector<nn::Module *> order_;
+};
 
 // ------------------------------------------------------------------------------------------------ optimizers
 class Optimizer

@@ -639,6 +639,88 @@ static void dataloader_cases()
     }
 }
 
+// ---- Sequential of the layers of the reference's CNN example (conv -> BatchNorm2d -> ReLU -> conv -> Flatten -> Linear):
+//      against the same chain written with the functional API on the SAME parameters, gradients included; state dict
+//      names; error cases of Sequential::operator[] and flatten (tests/unit_test/nn/test_sequential.cpp style).
+static void sequential_cnn()
+{
+    Sequential net;
+    net.add(std::make_unique<nn::Conv2d>(3, 8, 3, 1, 1));
+    net.add(std::make_unique<nn::BatchNorm2d>(8));
+    net.add(std::make_unique<nn::ReLU>());
+    net.add(std::make_unique<nn::Conv2d>(8, 6, 3, 2, 1));
+    net.add(std::make_unique<nn::Flatten>());
+    net.add(std::make_unique<nn::Linear>(6 * 5 * 6, 5));
+    EXPECT_TRUE(net.size() == 6);
+    EXPECT_THROW(net[6]);
+    EXPECT_TRUE(net.parameters().size() == 8);
+    auto sd = net.state_dict();
+    EXPECT_TRUE(sd.size() == 8 && sd.count("0.weight") && sd.count("1.bias") && sd.count("3.bias") && sd.count("5.weight"));
+
+    Tensor x = Tensor::randn(Shape{4, 3, 10, 12}, TensorOptions(), 11);
+    Tensor t(std::vector<int32_t>{0, 3, 1, 4}, Shape{4}, dtype(DataType::kInt32));
+    Tensor y = net(x);
+    EXPECT_TRUE(y.shape() == Shape({4, 5}));
+    Tensor loss = functional::softmax_cross_entropy(y, t);
+    net.zero_grad();
+    loss.backward();
+    std::vector<std::vector<float>> grads;
+    for (Parameter *p : net.parameters())
+        grads.push_back(p->grad().to_vector<float>());
+
+    // the same chain through the functional API
+    auto &c1 = static_cast<nn::Conv2d &>(net[0]);
+    auto &bn = static_cast<nn::BatchNorm2d &>(net[1]);
+    auto &c2 = static_cast<nn::Conv2d &>(net[3]);
+    auto &fc = static_cast<nn::Linear &>(net[5]);
+    Tensor rm = Tensor::zeros(Shape{8}), rv = Tensor::ones(Shape{8});
+    Tensor h  = functional::conv2d(x, *c1.weight(), c1.bias(), 1, 1);
+    h         = functional::batch_norm(h, *bn.weight(), *bn.bias(), rm, rv, true);
+    h         = functional::relu(h);
+    h         = functional::conv2d(h, *c2.weight(), c2.bias(), 2, 1);
+    h         = functional::flatten(h);
+    EXPECT_TRUE(h.shape() == Shape({4, 180}));
+    h          = fc(h);
+    expect_tensor(h, y.to_vector<float>(), 1e-6f);
+    Tensor loss2 = functional::softmax_cross_entropy(h, t);
+    net.zero_grad();
+    loss2.backward();
+    size_t i = 0;
+    for (Parameter *p : net.parameters())
+        expect_tensor(p->grad(), grads[i++], 1e-6f);
+
+    // flatten / reshape: shapes, errors, gradient shape
+    Tensor z = Tensor::randn(Shape{2, 3, 4, 5}, TensorOptions().requires_grad(true), 5);
+    EXPECT_TRUE(functional::flatten(z, 1, 2).shape() == Shape({2, 12, 5}));
+    EXPECT_TRUE(functional::flatten(z, 0, -1).shape() == Shape({120}));
+    EXPECT_THROW(functional::flatten(z, 2, 1));
+    EXPECT_THROW(functional::flatten(z, 0, 4));
+    EXPECT_THROW(functional::reshape(z, Shape{7, 7}));
+    Tensor s = functional::sum(functional::flatten(z) * 2.0f);
+    s.backward();
+    EXPECT_TRUE(z.grad().shape() == z.shape());
+    expect_tensor(z.grad(), std::vector<float>(120, 2.0f), 0.f);
+
+    // it trains: evaluation mode uses the running statistics the training steps produced
+    SGD opt(net, 0.05f);
+    float first = 0.f, last = 0.f;
+    for (int step = 0; step < 40; ++step)
+    {
+        Tensor l = functional::softmax_cross_entropy(net(x), t);
+        net.zero_grad();
+        l.backward();
+        opt.step();
+        last = l.item<float>();
+        if (step == 0)
+            first = last;
+    }
+    EXPECT_TRUE(last < 0.5f * first);
+    net.eval();
+    EXPECT_TRUE(net(x).shape() == Shape({4, 5}) && !net[1].is_training());
+    EXPECT_THROW(nn::Conv2d(3, 8, {3, 3}, {1, 2}));
+    EXPECT_THROW(nn::Conv2d(0, 8, 3));
+}
+
 static void memory_pool()
 {
     EXPECT_TRUE(MemoryPool::bin_size(1) == 256 && MemoryPool::bin_size(257) == 512 && MemoryPool::bin_size(300000) == 524288);
@@ -676,7 +758,7 @@ int main(int argc, char **argv)
         {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
         {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases},
         {"batch_norm_silu", batch_norm_cases},
-        {"dataloader", dataloader_cases}};
+        {"dataloader", dataloader_cases},     {"sequential_cnn", sequential_cnn}};
     for (auto &t : tests)
     {
         const int before = g_failed;
