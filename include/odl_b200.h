@@ -284,6 +284,13 @@ int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream);
 int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int first_of_step, void *stream);
 /* forward_loss + backward of every layer + optimizer_step. */
 int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
+/* Whole-step CUDA graph (the host overhead of Operator::operator() / TensorImpl::backward, src/core/tensor_impl.cpp:101-203,
+ * is the dominant cost at small batch sizes): odl_mlp_capture records forward + loss + backward on the given STATIC device
+ * buffers x[batch, sizes[0]] / labels[batch] into one graph (stream must be a non-default stream; one un-recorded pass
+ * runs first to size scratch memory, parameters and optimizer state stay untouched); odl_mlp_replay runs one optimisation
+ * step from it (graph launch + optimizer launch).  The caller refills x / labels in place between replays. */
+int odl_mlp_capture(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
+int odl_mlp_replay(void *handle, void *stream);
 /* Device pointers to the scalar loss and to the logits [batch, sizes[n-1]] of the last forward. */
 float *odl_mlp_loss_ptr(void *handle);
 float *odl_mlp_logits_ptr(void *handle);

@@ -143,6 +143,8 @@ _MLP_SIGNATURES = {
     "odl_mlp_backward_layer": [_P, c_int, _P],
     "odl_mlp_optimizer_step": [_P, c_float, _P],
     "odl_mlp_optimizer_step_layer": [_P, c_int, c_float, c_int, _P],
+    "odl_mlp_capture": [_P, _P, _P, c_int, _P],
+    "odl_mlp_replay": [_P, _P],
     "odl_mlp_train_step": [_P, _P, _P, c_int, _P],
     "odl_mlp_grad_bucket": [_P, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)],
     "odl_mlp_set_optimizer_state": [_P, _P, _P, c_int, _P],

@@ -49,6 +49,8 @@ struct Mlp
     const float *cur_x = nullptr;
     int64_t max_width = 0;
     std::vector<void *> allocs;
+    cudaGraphExec_t step_graph = nullptr;  // forward + loss + backward of one step on fixed input buffers (odl_mlp_capture)
+    long long graph_launches   = 0;        // kernels one replay of it runs
 
     template <typename T>
     int alloc(T **p, size_t count)
@@ -66,6 +68,8 @@ struct Mlp
     }
     ~Mlp()
     {
+        if (step_graph)
+            cudaGraphExecDestroy(step_graph);
         for (void *q : allocs)
             cudaFree(q);
     }
@@ -380,6 +384,76 @@ int odl_mlp_train_step(void *handle, const float *x, const void *labels, int lab
     for (int l = H(handle)->L - 1; l >= 0; --l)
         if ((rc = odl_mlp_backward_layer(handle, l, stream)))
             return rc;
+    return odl_mlp_optimizer_step(handle, 1.0f, stream);
+}
+
+// Whole-step CUDA graph: records forward + loss + backward of every layer on the given STATIC input buffers into one
+// graph (the optimizer launch stays outside: Adam's bias corrections are host scalars that change every step).  One
+// un-recorded forward + backward runs first so that every scratch buffer has its final size -- allocation cannot be
+// captured; parameters and optimizer state are not touched by it.  `stream` must be a real (non-default) stream; the
+// capture is thread-local, so other threads (a loader copying the next batch) are not disturbed.  The caller refills x
+// and labels in place between odl_mlp_replay calls.
+int odl_mlp_capture(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
+{
+    Mlp *h = H(handle);
+    if (!stream)
+    {
+        set_last_error("mlp capture: needs a non-default stream");
+        return kInvalidArgument;
+    }
+    cudaStream_t s = ST(stream);
+    auto record = [&]() -> int {
+        int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
+        for (int l = h->L - 1; l >= 0 && !rc; --l)
+            rc = odl_mlp_backward_layer(handle, l, stream);
+        return rc;
+    };
+    int rc = record();  // warm-up: sizes the scratch buffers, sets the kernels' attributes
+    if (rc)
+        return rc;
+    ODL_CUDA_TRY(cudaStreamSynchronize(s));
+    if (h->step_graph)
+    {
+        cudaGraphExecDestroy(h->step_graph);
+        h->step_graph = nullptr;
+    }
+    const long long before = g_launch_count;
+    ODL_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    rc = record();
+    cudaGraph_t graph = nullptr;
+    cudaError_t e     = cudaStreamEndCapture(s, &graph);
+    h->graph_launches = g_launch_count - before;
+    g_launch_count    = before;  // recorded, not run
+    if (rc || e != cudaSuccess || !graph)
+    {
+        if (graph)
+            cudaGraphDestroy(graph);
+        if (!rc)
+            set_last_error("mlp capture: cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
+        return rc ? rc : kCudaError;
+    }
+    e = cudaGraphInstantiate(&h->step_graph, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess)
+    {
+        h->step_graph = nullptr;
+        set_last_error("mlp capture: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
+// One optimisation step from the recorded graph: replay, then the optimizer launch.
+int odl_mlp_replay(void *handle, void *stream)
+{
+    Mlp *h = H(handle);
+    if (!h->step_graph)
+    {
+        set_last_error("mlp replay: odl_mlp_capture has not been called");
+        return kInvalidArgument;
+    }
+    ODL_CUDA_TRY(cudaGraphLaunch(h->step_graph, ST(stream)));
+    g_launch_count += h->graph_launches;
     return odl_mlp_optimizer_step(handle, 1.0f, stream);
 }
 

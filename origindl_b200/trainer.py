@@ -243,6 +243,26 @@ class MLPTrainer:
 
         return step
 
+    def capture_native(self, x: torch.Tensor, labels: torch.Tensor):
+        """The same whole-step graph recorded by the library itself (odl_mlp_capture / odl_mlp_replay -- what a C++ host
+        uses): returns a function that runs one optimisation step on the STATIC buffers `x` / `labels`.  Single-GPU only."""
+        if self.pg is not None:
+            raise NotImplementedError("graph capture of the data-parallel step is not implemented")
+        assert x.is_cuda and x.is_contiguous() and tuple(x.shape) == (self.batch, self.sizes[0])
+        is64 = int(labels.dtype == torch.int64)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        capi.call("odl_mlp_capture", self._h, x.data_ptr(), labels.data_ptr(), is64, side.cuda_stream)
+        side.synchronize()
+
+        def step() -> torch.Tensor:
+            side.wait_stream(torch.cuda.current_stream())  # the caller refilled x / labels on its own stream
+            capi.call("odl_mlp_replay", self._h, side.cuda_stream)
+            torch.cuda.current_stream().wait_stream(side)
+            return self._loss_view[0]
+
+        return step
+
     def close(self) -> None:
         if self._h is not None:
             capi.call("odl_mlp_destroy", self._h)

@@ -181,3 +181,31 @@ def test_training_and_reductions_are_reproducible_bit_for_bit(trainer_cls):
     assert torch.equal(sums[0], sums[1]) and torch.equal(sums[0], sums[2])
     want = (a.double() @ b.double()).sum(0)
     assert ((sums[0].double() - want).abs().max() / want.abs().max()).item() <= 1e-5
+
+
+def test_library_recorded_graph_step_equals_eager_step(trainer_cls):
+    """odl_mlp_capture / odl_mlp_replay (the whole-step graph recorded inside the library, for C++ hosts): bit-identical
+    to eager steps, inputs refilled in place between replays, optimizer state advanced once per replay."""
+    rng = np.random.default_rng(41)
+    sizes, batch = [784, 300, 100, 10], 128
+    params = _libs.mlp_params(rng, sizes)
+    xs = torch.from_numpy(rng.standard_normal((3, batch, 784)).astype(np.float32)).cuda()
+    ts = torch.from_numpy(rng.integers(0, 10, (3, batch)).astype(np.int32)).cuda()
+    eager = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+    eager.set_params(params)
+    want = [eager.train_step(xs[i % 3], ts[i % 3]).item() for i in range(7)]
+    graphed = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
+    graphed.set_params(params)
+    x, t = xs[0].clone(), ts[0].clone()
+    step = graphed.capture_native(x, t)          # records; parameters and optimizer state untouched
+    got = []
+    for i in range(7):
+        x.copy_(xs[i % 3]), t.copy_(ts[i % 3])
+        got.append(step().item())
+    assert got == want
+    assert np.array_equal(graphed.get_params(), eager.get_params())
+    from origindl_b200 import capi
+
+    capi.device_status()
+    eager.close()
+    graphed.close()
