@@ -721,6 +721,54 @@ static void sequential_cnn()
     EXPECT_THROW(nn::Conv2d(0, 8, 3));
 }
 
+// ---- The fused, device-resident MLP trainer of the C ABI driven from C++: eager steps (odl_mlp_train_step) against the
+//      whole-step CUDA graph recorded by the library (odl_mlp_capture / odl_mlp_replay) -- same losses, same parameters.
+static void mlp_graph_step()
+{
+    const int32_t sizes[] = {64, 96, 48, 10};
+    const int64_t batch   = 32;
+    void *eager = nullptr, *graphed = nullptr;
+    odl_check(odl_mlp_create(sizes, 4, batch, 1, 1e-3f, 0.f, 1e-4f, ODL_PRECISION_3XTF32, &eager));
+    odl_check(odl_mlp_create(sizes, 4, batch, 1, 1e-3f, 0.f, 1e-4f, ODL_PRECISION_3XTF32, &graphed));
+    const int64_t n = odl_mlp_param_count(eager);
+    std::vector<float> p0(n);
+    std::mt19937 gen(3);
+    std::normal_distribution<float> nd(0.f, 0.1f);
+    for (auto &v : p0)
+        v = nd(gen);
+    odl_check(odl_mlp_set_params(eager, p0.data(), nullptr));
+    odl_check(odl_mlp_set_params(graphed, p0.data(), nullptr));
+    Tensor x = Tensor::randn(Shape{(size_t)batch, 64}, TensorOptions(), 9);
+    std::vector<int32_t> lab(batch);
+    for (int i = 0; i < batch; ++i)
+        lab[i] = i % 10;
+    Tensor t(lab, Shape{(size_t)batch}, dtype(DataType::kInt32));
+    synchronize();
+    cudaStream_t stream;
+    cuda_check(cudaStreamCreate(&stream), "stream");
+    odl_check(odl_mlp_capture(graphed, x.data_ptr<float>(), t.data_ptr<void>(), 0, stream));
+    EXPECT_TRUE(odl_mlp_step_count(graphed) == 0);  // recording takes no optimisation step
+    float le = 0.f, lg = 0.f;
+    for (int step = 0; step < 5; ++step)
+    {
+        odl_check(odl_mlp_train_step(eager, x.data_ptr<float>(), t.data_ptr<void>(), 0, stream));
+        cuda_check(cudaMemcpyAsync(&le, odl_mlp_loss_ptr(eager), 4, cudaMemcpyDeviceToHost, stream), "loss");
+        odl_check(odl_mlp_replay(graphed, stream));
+        cuda_check(cudaMemcpyAsync(&lg, odl_mlp_loss_ptr(graphed), 4, cudaMemcpyDeviceToHost, stream), "loss");
+        cuda_check(cudaStreamSynchronize(stream), "sync");
+        EXPECT_TRUE(le == lg && std::isfinite(le));
+    }
+    std::vector<float> pe(n), pg(n);
+    odl_check(odl_mlp_get_packed(eager, 0, pe.data(), stream));
+    odl_check(odl_mlp_get_packed(graphed, 0, pg.data(), stream));
+    cuda_check(cudaStreamSynchronize(stream), "sync");
+    EXPECT_TRUE(pe == pg && odl_mlp_step_count(graphed) == 5);
+    EXPECT_TRUE(odl_mlp_capture(graphed, x.data_ptr<float>(), t.data_ptr<void>(), 0, nullptr) != 0);  // default stream refused
+    odl_check(odl_mlp_destroy(eager));
+    odl_check(odl_mlp_destroy(graphed));
+    cudaStreamDestroy(stream);
+}
+
 static void memory_pool()
 {
     EXPECT_TRUE(MemoryPool::bin_size(1) == 256 && MemoryPool::bin_size(257) == 512 && MemoryPool::bin_size(300000) == 524288);
@@ -758,7 +806,8 @@ int main(int argc, char **argv)
         {"linear_regression", linear_regression}, {"mlp_training", mlp_training},
         {"memory_pool", memory_pool},         {"checkpoint", checkpoint_cases},
         {"batch_norm_silu", batch_norm_cases},
-        {"dataloader", dataloader_cases},     {"sequential_cnn", sequential_cnn}};
+        {"dataloader", dataloader_cases},     {"sequential_cnn", sequential_cnn},
+        {"mlp_graph_step", mlp_graph_step}};
     for (auto &t : tests)
     {
         const int before = g_failed;
