@@ -58,6 +58,7 @@ def main():
     ap.add_argument("--conv-mode", type=int, default=0, help="conv: 2 = implicit-GEMM weight gradient also for small layers")
     ap.add_argument("--sizes", default="4096,4096,4096,4096,4096,4096,4096,1000", help="mlp: layer widths")
     ap.add_argument("--optimizer", default="sgd", help="mlp: sgd (momentum 0.9) or adam")
+    ap.add_argument("--graph", action="store_true", help="mlp: also time the step replayed from the library's CUDA graph")
     ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
     a = ap.parse_args()
     capi.init(0)
@@ -112,6 +113,11 @@ def main():
             tr.train_step(x, t)
         ms = timed(lambda: tr.train_step(x, t), a.iters)
         flops = 6.0 * a.batch * sum(i * o for i, o in zip(sizes[:-1], sizes[1:])) - 2.0 * a.batch * sizes[0] * sizes[1]
+        if a.graph:
+            step = tr.capture_native(x, t)
+            ms_g = timed(step, a.iters)
+            print(f"mlp {a.sizes} batch {a.batch}: {ms_g:.3f} ms per step from the library-recorded CUDA graph "
+                  f"({a.batch / ms_g * 1e3:.0f} samples/s)")
         print(f"mlp {a.sizes} batch {a.batch} {a.optimizer} {a.precision}: {ms:.3f} ms per training step, "
               f"{a.batch / ms * 1e3:.0f} samples/s, {flops / ms / 1e9:.1f} TFLOP/s (no dX for the first layer), "
               f"loss {float(tr.loss_tensor()):.4f}")
