@@ -27,6 +27,7 @@ extern "C" {
 #define ODL_ERR_KERNEL_TIMEOUT 4
 #define ODL_ERR_TOO_LARGE 5
 #define ODL_ERR_NOT_INITIALIZED 6
+#define ODL_ERR_STALE_GRAPH 7 /* a recorded step graph refers to scratch memory that was replaced since: capture again */
 
 /* GEMM arithmetic: 3xTF32 (default, fp32-class accuracy: three tf32 MMAs per product) or plain TF32. */
 #define ODL_PRECISION_3XTF32 0
@@ -65,6 +66,12 @@ int odl_device_status(void *stream);
 
 /* Bytes currently held by the library's device scratch arena (operand splits, padded copies, im2col columns). */
 int64_t odl_scratch_bytes(void);
+
+/* Counts how often the library has replaced one of its scratch blocks (the arena above or the column-sum scratch) by a
+ * larger one.  Anything that recorded kernel launches of this library into a CUDA graph holds raw addresses inside
+ * those blocks; when this number differs from its value at recording time the graph must be recorded again
+ * (odl_mlp_replay checks this itself and returns ODL_ERR_STALE_GRAPH).  No counterpart in the reference. */
+long long odl_scratch_generation(void);
 
 /* Number of kernels this library has launched in the process so far (a benchmark reports the delta over its timed
  * region).  No counterpart in the reference. */
@@ -167,7 +174,10 @@ int odl_softmax_cross_entropy(const float *logits, const void *labels, int label
  * loss needs lives in a fixed 256 KiB array inside the library image (held by every GPU that loads the library until
  * the process exits) instead of the growable arena, so the call itself performs no allocation of any kind.
  * Limits: B <= ODL_STATIC_SOFTMAX_MAX_ROWS, else ODL_ERR_TOO_LARGE.  The first call on a device resolves the array's
- * device address (a symbol lookup, no allocation); make that first call before any stream capture.  All calls share
+ * device address with the device current at that moment (cudaGetSymbolAddress).  CUDA loads a library's device code
+ * lazily, so that look-up is also what places the array's 256 KiB on the GPU: make the first call (any small batch)
+ * during start-up, before the host's own pool takes the remaining memory and before any stream capture; every later call
+ * on that device touches no allocator at all.  All calls share
  * the one array, which keeps the previous call's contents: nothing in it needs clearing (every call overwrites the
  * rows it reads), but two calls that overlap on the GPU race on it -- keep them on one stream. */
 #define ODL_STATIC_SOFTMAX_MAX_ROWS 65536
@@ -288,7 +298,10 @@ int odl_mlp_train_step(void *handle, const float *x, const void *labels, int lab
  * is the dominant cost at small batch sizes): odl_mlp_capture records forward + loss + backward on the given STATIC device
  * buffers x[batch, sizes[0]] / labels[batch] into one graph (stream must be a non-default stream; one un-recorded pass
  * runs first to size scratch memory, parameters and optimizer state stay untouched); odl_mlp_replay runs one optimisation
- * step from it (graph launch + optimizer launch).  The caller refills x / labels in place between replays. */
+ * step from it (graph launch + optimizer launch).  The caller refills x / labels in place between replays.
+ * The graph holds addresses inside the library's scratch blocks.  Any later call that makes those blocks grow (a forward
+ * at a larger batch, a conv layer, a second model) replaces them; odl_mlp_replay then launches nothing and returns
+ * ODL_ERR_STALE_GRAPH until odl_mlp_capture has recorded the step again. */
 int odl_mlp_capture(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
 int odl_mlp_replay(void *handle, void *stream);
 /* Device pointers to the scalar loss and to the logits [batch, sizes[n-1]] of the last forward. */

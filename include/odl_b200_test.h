@@ -1,0 +1,39 @@
+/*
+ * odl_b200_test -- kernel-selection overrides of libodl_b200.so, for test programs only.
+ *
+ * The launchers of the library choose tile widths, split-K forms, CTA pairing and the conv algorithm from the problem
+ * size.  Parity tests need every one of those code paths on small shapes the automatic choice would never send there,
+ * so the library exports these setters.  They write PROCESS-GLOBAL ints that the launchers read without locking: call
+ * them from the one thread that also issues the library calls, and reset each to 0 (automatic) afterwards.  A product
+ * host has no reason to call them; none has a counterpart in the reference (its one run-time kernel switch is the
+ * ORIGIN_KERNEL_ALGO environment variable, src/utils/env_config.cpp:14-36).  All return ODL_OK.
+ */
+#ifndef ODL_B200_TEST_H_
+#define ODL_B200_TEST_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GEMM column-tile width: 64, 128 or 256; 0 = automatic. */
+int odl_debug_set_tile_n(int bn);
+/* K-blocks of 32 accumulated in TMEM between two drains into registers; 0 = automatic (2 in 3xTF32). */
+int odl_debug_set_chunk(int chunk_kb);
+/* Split-K: 1 = never, n > 1 = n slices summed by a second pass, -n = a thread-block cluster of n along K; 0 = automatic. */
+int odl_debug_set_split_k(int splits);
+/* K elements per pipeline stage of the 256-wide tile of the one-CTA kernel: 16 or 32; 0 = automatic. */
+int odl_debug_set_bk(int bk);
+/* K-slabs per pipeline stage in plain TF32: 1 or 2; 0 = automatic. */
+int odl_debug_set_slabs(int n);
+/* CTA pairs (cta_group::2): 0 = where it pays, 1 = never, 2 = whenever the shape allows, 3 = 2-D copies for MN-major
+ * operands, 4 = never the 256 x 512 plain-TF32 tile, 5 = like 2 plus that tile for every plain-TF32 problem,
+ * 6 = never the persistent kernel, 7 = the persistent kernel whenever the shape allows. */
+int odl_debug_set_pair_mode(int mode);
+/* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
+ * kernel for small layers. */
+int odl_debug_set_conv_mode(int mode);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ODL_B200_TEST_H_ */

@@ -14,6 +14,7 @@ _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libodl_b200.so"
 
 OK = 0
+ERR_STALE_GRAPH = 7
 PRECISION_3XTF32 = 0
 PRECISION_TF32 = 1
 EPI_BIAS, EPI_RELU, EPI_MASK, EPI_COLSUM, EPI_SMALL = 1, 2, 4, 8, 16
@@ -71,10 +72,11 @@ _SIGNATURES = {
 
 
 def declared_symbols() -> list[str]:
-    """Names of every function declared in include/odl_b200.h (parsed from the header)."""
+    """Names of every function declared in include/*.h (parsed from the headers: the product ABI odl_b200.h and the
+    test-only overrides odl_b200_test.h)."""
     import re
 
-    text = (_HERE.parent / "include" / "odl_b200.h").read_text()
+    text = "".join(h.read_text() for h in sorted((_HERE.parent / "include").glob("*.h")))
     return sorted(set(re.findall(r"\b(odl_[a-z0-9_]+)\s*\(", text)))
 
 
@@ -159,7 +161,8 @@ _MLP_SIGNATURES = {
 }
 _SIGNATURES.update(_MLP_SIGNATURES)
 _POINTER_RETURNS = {"odl_mlp_loss_ptr": [_P], "odl_mlp_logits_ptr": [_P]}
-_I64_RETURNS = {"odl_mlp_param_count": [_P], "odl_mlp_step_count": [_P], "odl_launch_count": []}
+_I64_RETURNS = {"odl_mlp_param_count": [_P], "odl_mlp_step_count": [_P], "odl_launch_count": [],
+                "odl_scratch_generation": []}
 
 
 def _declare_extra(L: ctypes.CDLL) -> None:

@@ -29,7 +29,21 @@ struct DeviceState
 };
 DeviceState g_state;
 std::mutex g_mu;
+long long g_scratch_generation = 0;
 }  // namespace
+
+// Library-owned scratch blocks (the arena below, the column-sum scratch of split.cu) are replaced when a call needs
+// more than they hold.  Every replacement bumps this counter, so that whoever recorded raw scratch addresses (a CUDA
+// graph of the training step) can tell that they are stale.
+long long scratch_generation()
+{
+    return g_scratch_generation;
+}
+
+void bump_scratch_generation()
+{
+    ++g_scratch_generation;
+}
 
 void set_last_error(const char *fmt, ...)
 {
@@ -89,6 +103,7 @@ void *arena_alloc(size_t bytes)
         }
         g_state.arena    = static_cast<char *>(p);
         g_state.capacity = want;
+        bump_scratch_generation();
     }
     void *out = g_state.arena + g_state.used;
     g_state.used += bytes;
@@ -342,6 +357,11 @@ int odl_device_status(void *stream)
 int64_t odl_scratch_bytes(void)
 {
     return static_cast<int64_t>(g_state.capacity);
+}
+
+long long odl_scratch_generation(void)
+{
+    return scratch_generation();
 }
 
 int odl_debug_set_split_k(int splits)

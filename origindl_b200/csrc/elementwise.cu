@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float *__restrict
     if (label < 0 || label >= C)
     {
         if (lane == 0)
-            atomicExch(err, 2);
+            if (err)
+                atomicExch(err, 2);
         return;
     }
     const bool cached = C <= 32 * kSmCache;
@@ -610,6 +611,12 @@ int add_bias_launch(const float *x, const float *b, float *y, int64_t M, int64_t
 int softmax_ce_launch(const float *logits, const int32_t *t32, const int64_t *t64, int64_t B, int64_t C, float *loss,
                       float *dlogits, float *row_loss_scratch, float grad_scale, cudaStream_t s)
 {
+    if (!is_ready())
+    {
+        // the kernel reports an out-of-range label through the per-device flag odl_init allocates
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
     if (!logits || (!t32 && !t64) || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff)
     {
         set_last_error("softmax_ce: invalid argument (B=%lld C=%lld)", (long long)B, (long long)C);

@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const float *__restric
         const int64_t s = idx[r];
         const bool ok   = s >= 0 && s < n_src;
         if (!ok && lane == 0)
-            atomicExch(err, 3);
+            if (err)
+                atomicExch(err, 3);
         if (labels_dst && lane == 0)
             labels_dst[r] = ok ? labels_src[s] : -1;
         float *out = dst + r * ld_dst;
@@ -62,6 +63,12 @@ extern "C" int odl_gather_rows(const float *src, int64_t ld_src, int64_t n_src, 
                                int64_t cols, float *dst, int64_t ld_dst, const int64_t *labels_src, int64_t *labels_dst,
                                void *stream)
 {
+    if (!is_ready())
+    {
+        // the kernel reports an out-of-range index through the per-device flag odl_init allocates
+        set_last_error("odl_init has not been called");
+        return kNotInitialized;
+    }
     if (!src || !idx || !dst || n_src <= 0 || n_idx <= 0 || cols <= 0 || ld_src < cols || ld_dst < cols ||
         (labels_dst && !labels_src))
     {

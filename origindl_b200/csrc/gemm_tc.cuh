@@ -16,6 +16,7 @@ enum Status : int
     kKernelTimeout   = 4,   // a bounded wait inside a kernel ran out (device error flag was set)
     kTooLarge        = 5,   // size exceeds what the entry point supports
     kNotInitialized  = 6,
+    kStaleGraph      = 7,   // a recorded graph holds scratch addresses that have since been replaced: record it again
 };
 
 // Epilogue flags (bit set).  Order of application on each accumulator value v at (m, n):

@@ -16,6 +16,9 @@ bool is_ready();
 void arena_reset();
 int arena_reserve(size_t total_bytes);
 void *arena_alloc(size_t bytes);
+// Counts replacements of library-owned scratch blocks (arena, column-sum scratch): recorded graphs compare it.
+long long scratch_generation();
+void bump_scratch_generation();
 
 size_t operand_scratch(const float *ptr, const float *small, int64_t ld, int64_t rows, int64_t cols, int terms);
 

@@ -51,6 +51,8 @@ struct Mlp
     std::vector<void *> allocs;
     cudaGraphExec_t step_graph = nullptr;  // forward + loss + backward of one step on fixed input buffers (odl_mlp_capture)
     long long graph_launches   = 0;        // kernels one replay of it runs
+    long long graph_generation = -1;       // scratch_generation() when it was recorded: its scratch addresses are valid
+                                           // only while no scratch block has been replaced since
 
     template <typename T>
     int alloc(T **p, size_t count)
@@ -417,7 +419,8 @@ int odl_mlp_capture(void *handle, const float *x, const void *labels, int labels
         cudaGraphExecDestroy(h->step_graph);
         h->step_graph = nullptr;
     }
-    const long long before = g_launch_count;
+    const long long before     = g_launch_count;
+    const long long generation = scratch_generation();
     ODL_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     rc = record();
     cudaGraph_t graph = nullptr;
@@ -440,6 +443,15 @@ int odl_mlp_capture(void *handle, const float *x, const void *labels, int labels
         set_last_error("mlp capture: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
         return kCudaError;
     }
+    if (scratch_generation() != generation)
+    {
+        // cannot happen after the sizing pass above (growing drains the device, which a capture refuses); kept as a guard
+        cudaGraphExecDestroy(h->step_graph);
+        h->step_graph = nullptr;
+        set_last_error("mlp capture: scratch memory was replaced while recording");
+        return kStaleGraph;
+    }
+    h->graph_generation = generation;
     return kOk;
 }
 
@@ -451,6 +463,12 @@ int odl_mlp_replay(void *handle, void *stream)
     {
         set_last_error("mlp replay: odl_mlp_capture has not been called");
         return kInvalidArgument;
+    }
+    if (scratch_generation() != h->graph_generation)
+    {
+        set_last_error("mlp replay: the library's scratch memory was replaced after odl_mlp_capture (a later call needed "
+                       "more of it); the recorded step holds stale addresses -- call odl_mlp_capture again");
+        return kStaleGraph;
     }
     ODL_CUDA_TRY(cudaGraphLaunch(h->step_graph, ST(stream)));
     g_launch_count += h->graph_launches;

@@ -74,7 +74,8 @@ extern "C" int odl_softmax_cross_entropy_static(const float *logits, const void 
         return odl::kTooLarge;
     }
     float *scratch = nullptr;
-    int rc         = static_scratch(&scratch);  // first call on a device: resolves the symbol (no allocation)
+    int rc         = static_scratch(&scratch);  // first call on a device: resolves the symbol, which also makes the
+                                                // lazily loaded module image (and with it the array) resident
     if (rc)
         return rc;
     return odl::softmax_ce_launch(logits, labels_are_int64 ? nullptr : static_cast<const int32_t *>(labels),

@@ -130,19 +130,36 @@ __device__ __forceinline__ void store_vec(float *__restrict__ p, const float (&v
         p[0] = v[0];
 }
 
-// Finishes a channel once its last block has added its partial sums: returns true in exactly one thread of the grid
-// per channel, with the totals in (s, q).
+// Finishes a channel once its last block has stored its partial sums.  Called by every thread of the block with the
+// block's sums in thread 0; returns true in exactly one thread of the grid per channel, with the totals in (s, q).
+// No floating-point atomics: every block stores its pair into its own slot of acc[C][gridDim.y][2], and the block that
+// arrives last adds the slots in a fixed order (thread t takes slots t, t + kThreads, ... ascending, then the fixed
+// shuffle tree of block_sum2), so the statistics have the same bits on every run whatever order the blocks finish in.
 __device__ __forceinline__ bool channel_done(double *acc, unsigned *done, int c, double &s, double &q)
 {
-    atomicAdd(acc + 2 * c, s);
-    atomicAdd(acc + 2 * c + 1, q);
-    __threadfence();
-    if (atomicAdd(done + c, 1u) != gridDim.y - 1)
+    __shared__ int is_last;
+    const int nb       = gridDim.y;
+    double *slots      = acc + 2 * static_cast<int64_t>(c) * nb;
+    if (threadIdx.x == 0)
+    {
+        slots[2 * blockIdx.y]     = s;
+        slots[2 * blockIdx.y + 1] = q;
+        __threadfence();
+        is_last = atomicAdd(done + c, 1u) == static_cast<unsigned>(nb - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!is_last)
         return false;
     __threadfence();
-    s = atomicAdd(acc + 2 * c, 0.0);
-    q = atomicAdd(acc + 2 * c + 1, 0.0);
-    return true;
+    double a = 0.0, b = 0.0;
+    for (int i = threadIdx.x; i < nb; i += kThreads)
+    {
+        a += __ldcg(slots + 2 * i);
+        b += __ldcg(slots + 2 * i + 1);
+    }
+    block_sum2(a, b);
+    s = a, q = b;
+    return threadIdx.x == 0;
 }
 
 // ---- forward, training: per-channel sum and sum of squares; the last block of a channel finishes the statistics
@@ -168,7 +185,7 @@ __global__ void __launch_bounds__(kThreads) bn_stats_kernel(const float *__restr
     }
     block_sum2(s, q);
     const int c = blockIdx.x;
-    if (threadIdx.x == 0 && channel_done(acc, done, c, s, q))
+    if (channel_done(acc, done, c, s, q))
     {
         const double count = static_cast<double>(g.N) * g.HW;
         const double mean  = s / count;
@@ -237,7 +254,7 @@ __global__ void __launch_bounds__(kThreads)
         }
     }
     block_sum2(s, q);
-    if (threadIdx.x == 0 && channel_done(acc, done, c, s, q))
+    if (channel_done(acc, done, c, s, q))
     {
         const float sum_g = static_cast<float>(s), sum_q = static_cast<float>(q);
         const float count = static_cast<float>(static_cast<int64_t>(g.N) * g.HW);
@@ -400,12 +417,11 @@ int odl_batch_norm_forward(const float *x, const float *gamma, const float *beta
     if (training)
     {
         arena_reset();
-        const size_t acc_bytes = sizeof(double) * 2 * C, all = acc_bytes + sizeof(unsigned) * C;
+        const size_t acc_bytes = sizeof(double) * 2 * C * grid.y, all = acc_bytes + sizeof(unsigned) * C;
         if ((rc = arena_reserve(all + 256)))
             return rc;
         double *acc    = static_cast<double *>(arena_alloc(acc_bytes));
         unsigned *done = static_cast<unsigned *>(arena_alloc(sizeof(unsigned) * C));
-        ODL_CUDA_TRY(cudaMemsetAsync(acc, 0, acc_bytes, s));
         ODL_CUDA_TRY(cudaMemsetAsync(done, 0, sizeof(unsigned) * C, s));
         if (vec4_ok(g, x, x))
             bn_stats_kernel<4><<<grid, kThreads, 0, s>>>(x, g, acc, done, save_mean, save_var, running_mean, running_var,
@@ -445,13 +461,12 @@ int odl_batch_norm_backward(const float *gy, const float *x, const float *gamma,
         return rc;
     cudaStream_t s = ST(stream);
     arena_reset();
-    const size_t acc_bytes = sizeof(double) * 2 * C;
+    const size_t acc_bytes = sizeof(double) * 2 * C * grid.y;
     if ((rc = arena_reserve(acc_bytes + sizeof(unsigned) * C + sizeof(float) * 2 * C + 512)))
         return rc;
     double *acc    = static_cast<double *>(arena_alloc(acc_bytes));
     unsigned *done = static_cast<unsigned *>(arena_alloc(sizeof(unsigned) * C));
     float *means   = static_cast<float *>(arena_alloc(sizeof(float) * 2 * C));
-    ODL_CUDA_TRY(cudaMemsetAsync(acc, 0, acc_bytes, s));
     ODL_CUDA_TRY(cudaMemsetAsync(done, 0, sizeof(unsigned) * C, s));
     const bool v4 = vec4_ok(g, x, gy) && vec4_ok(g, x, gx);
     if (v4)

@@ -11,6 +11,7 @@
 
 #include "gemm_tc.cuh"
 #include "host_util.h"
+#include "internal.h"
 
 namespace odl
 {
@@ -206,6 +207,7 @@ int colsum_scratch(size_t floats, size_t groups)
             return kCudaError;
         }
         g_partial_floats = floats, g_done_count = groups;
+        bump_scratch_generation();
     }
     return kOk;
 }

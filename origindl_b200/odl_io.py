@@ -60,7 +60,12 @@ def load(filepath: str, with_devices: bool = False):
     except OSError as e:
         raise OdlFormatError(f"Failed to open file for reading: {filepath}") from e
     with f:
+        size = os.fstat(f.fileno()).st_size
+
         def take(n: int, what: str) -> bytes:
+            # a length field of a truncated or corrupt file must not become an allocation: compare with what is left
+            if n > size - f.tell():
+                raise OdlFormatError(f"Failed to read {what} from file")
             b = f.read(n)
             if len(b) != n:
                 raise OdlFormatError(f"Failed to read {what} from file")
@@ -73,6 +78,8 @@ def load(filepath: str, with_devices: bool = False):
         if version != VERSION:
             raise OdlFormatError(f"Unsupported file version: {version}")
         (count,) = struct.unpack("<Q", take(8, "parameter count"))
+        if count > size:  # every record takes more than one byte
+            raise OdlFormatError(f"Invalid file format or corrupted file: {filepath}")
         tensors, devices = {}, {}
         for _ in range(count):
             (n,) = struct.unpack("<Q", take(8, "string length"))
@@ -85,6 +92,11 @@ def load(filepath: str, with_devices: bool = False):
             if code not in CODE_DTYPES:
                 raise OdlFormatError(f"Unsupported dtype for loading: {code}")
             dt = CODE_DTYPES[code]
+            n_elem = 1
+            for d in shape:
+                n_elem *= d
+            if n_elem * np.dtype(dt).itemsize > size - f.tell():
+                raise OdlFormatError(f"Failed to read tensor data for parameter '{name}' from file")
             arr = np.empty(shape, dtype=dt)
             if f.readinto(memoryview(arr.reshape(-1)).cast("B")) != arr.nbytes:
                 raise OdlFormatError(f"Failed to read tensor data for parameter '{name}' from file")

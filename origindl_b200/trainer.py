@@ -235,8 +235,13 @@ class MLPTrainer:
                 for layer in dp.reduce_order(self.n_layers):
                     capi.call("odl_mlp_backward_layer", self._h, layer, s)
         torch.cuda.current_stream().wait_stream(side)
+        generation = capi.lib().odl_scratch_generation()
 
         def step() -> torch.Tensor:
+            # the graph holds addresses inside the library's scratch blocks; a later call that made them grow replaced them
+            if capi.lib().odl_scratch_generation() != generation:
+                raise capi.OdlError(capi.ERR_STALE_GRAPH, "the library's scratch memory was replaced after capture(); "
+                                                          "capture the step again")
             graph.replay()
             capi.call("odl_mlp_optimizer_step", self._h, 1.0, capi.stream_handle())
             return self._loss_view[0]

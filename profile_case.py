@@ -1,15 +1,15 @@
 """Small, self-terminating cases of each kernel of the library, sized for profiler captures.
 
-    python -m origindl_b200.profile_case gemm    --n 4096 [--precision 3xtf32|tf32] [--layout nt|nn|tn] [--iters 3]
-    python -m origindl_b200.profile_case split   --n 8192
-    python -m origindl_b200.profile_case adam    --n 67108864
-    python -m origindl_b200.profile_case softmax --rows 8192 --cols 1024
-    python -m origindl_b200.profile_case conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
-    python -m origindl_b200.profile_case linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
-    python -m origindl_b200.profile_case batchnorm --n 64 --cols 64 --rows 25600   (N x C x HW, training fwd + bwd, fused SiLU)
-    python -m origindl_b200.profile_case gather  --rows 65536 --cols 1024       (batch assembly from a resident data set)
-    python -m origindl_b200.profile_case mlp --sizes 4096,4096,4096,4096,4096,4096,4096,1000 --batch 8192 --optimizer sgd --iters 10
-    python -m origindl_b200.profile_case checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
+    python profile_case.py gemm    --n 4096 [--precision 3xtf32|tf32] [--layout nt|nn|tn] [--iters 3]
+    python profile_case.py split   --n 8192
+    python profile_case.py adam    --n 67108864
+    python profile_case.py softmax --rows 8192 --cols 1024
+    python profile_case.py conv    --layer 1          (the four conv shapes of the benchmark, batch 16)
+    python profile_case.py linear  --m 8192 --n 8192 --k 8192   (forward, dX, dW, dY pass timed apart)
+    python profile_case.py batchnorm --n 64 --cols 64 --rows 25600   (N x C x HW, training fwd + bwd, fused SiLU)
+    python profile_case.py gather  --rows 65536 --cols 1024       (batch assembly from a resident data set)
+    python profile_case.py mlp --sizes 4096,4096,4096,4096,4096,4096,4096,1000 --batch 8192 --optimizer sgd --iters 10
+    python profile_case.py checkpoint --n 4096 --layers 4        (save / load of an Adam-trained MLP, host wall clock)
 
 Each case keeps its inputs above the 126 MB L2 where the kernel is HBM-bound, holds well under a few GB on the
 device, launches the kernel `--iters` times after one warm-up launch and prints the CUDA-event time per launch.
@@ -20,7 +20,7 @@ import argparse
 
 import torch
 
-from . import capi, ops
+from origindl_b200 import capi, ops
 
 # 1-4: the benchmark's conv shapes; 5: a deep 256 -> 256 3x3 layer (K = 2304: the implicit forward splits K over a CTA pair)
 CONV_LAYERS = {1: (3, 16, 6, 2, 2, 320), 2: (16, 32, 3, 2, 1, 160), 3: (32, 32, 1, 1, 0, 80), 4: (64, 64, 3, 1, 1, 40),
@@ -71,7 +71,7 @@ def main():
 
         import numpy as np
 
-        from .trainer import MLPTrainer
+        from origindl_b200.trainer import MLPTrainer
 
         sizes = [a.n] * (a.layers + 1)
         tr = MLPTrainer(sizes, 128)
@@ -98,7 +98,7 @@ def main():
     elif a.case == "mlp":
         import numpy as np
 
-        from .trainer import MLPTrainer
+        from origindl_b200.trainer import MLPTrainer
 
         sizes = [int(v) for v in a.sizes.split(",")]
         kw = dict(optimizer="sgd", lr=1e-2, momentum=0.9) if a.optimizer == "sgd" else dict(optimizer="adam", lr=1e-3)

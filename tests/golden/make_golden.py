@@ -176,6 +176,19 @@ def main():
     elif "c1_losses_fp64" in have:
         out["c1_losses_fp64"] = have["c1_losses_fp64"]
 
+    # ---- sensitivity of the REFERENCE ITSELF on that configuration: the same run with one input element moved by one
+    #      unit in the last place.  The spread between the two reference curves is the yardstick for "how close can any
+    #      implementation that is not bit-identical stay to the reference's curve" on this (random-label) problem.
+    if "c1_losses_ulp" in have:
+        out["c1_losses_ulp"] = have["c1_losses_ulp"]
+    elif "c1_losses" in out:
+        sizes = np.array([784, 1000, 1000, 10], np.int32)
+        params, x, t = c1_inputs()
+        x[0, 0, 0] = np.nextafter(x[0, 0, 0], np.float32(2.0))
+        losses = np.empty(len(out["c1_losses"]), np.float32)
+        _libs.ref_check(ref.odlref_mlp_train(sizes, 4, params, x, t, 512, 4, len(losses), 1, 1e-3, 0.0, 1e-4, losses, None))
+        out["c1_losses_ulp"] = losses
+
     # ---- the well-conditioned 200-step configuration (SGD momentum, teacher labels)
     if "stable_losses" in have:
         out.update({k: have[k] for k in ("stable_losses", "stable_param_sample")})

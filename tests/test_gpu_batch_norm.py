@@ -124,6 +124,24 @@ def test_training_forward_and_backward_match_the_oracle(ops, shape, act):
         assert max_rel_err(db.cpu().numpy(), g64.sum(axis=(0, 2))) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(16, 16, 160 * 160), (70000, 3, 1)])
+def test_statistics_and_gradients_are_reproducible_bit_for_bit(ops, shape):
+    """Per-block partial sums are added in a fixed order by the block that finishes last (no floating-point atomics), so
+    repeated runs give the same bits although the blocks of a channel finish in a different order every time."""
+    n, c, hw = shape
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn((n, c) if hw == 1 else (n, c, hw, 1), device="cuda", generator=gen) * 3 + 1
+    dy = torch.randn(x.shape, device="cuda", generator=gen)
+    gamma, beta = torch.rand(c, device="cuda", generator=gen) + 0.5, torch.randn(c, device="cuda", generator=gen)
+    runs = []
+    for _ in range(4):
+        y, mean, var = ops.batch_norm_forward(x, gamma, beta, training=True, act=2)
+        gx, dg, db = ops.batch_norm_backward(dy, x, gamma, beta, mean, var, act=2)
+        runs.append([t.clone() for t in (y, mean, var, gx, dg, db)])
+    for other in runs[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(runs[0], other))
+
+
 def test_running_statistics_follow_the_layer(ops):
     g, inp = np.load(GOLDEN), mk.layer_inputs()
     steps, n, c, hw = inp["xs"].shape

@@ -209,3 +209,50 @@ def test_library_recorded_graph_step_equals_eager_step(trainer_cls):
     capi.device_status()
     eager.close()
     graphed.close()
+
+
+def test_replay_refuses_a_graph_whose_scratch_was_replaced(trainer_cls):
+    """A recorded step holds raw addresses inside the library's scratch blocks (staged copies of operands whose pitch
+    breaks the 16-byte rule -- the 10-wide head here -- and the column-sum scratch).  A later call that needs more
+    scratch replaces those blocks; replaying the old graph would then write freed memory.  Both graph front ends must
+    refuse instead (ODL_ERR_STALE_GRAPH, nothing launched) and work again after a new capture."""
+    from origindl_b200 import capi, ops
+
+    rng = np.random.default_rng(43)
+    sizes, batch = [64, 48, 10], 32
+    params = _libs.mlp_params(rng, sizes)
+    x = torch.from_numpy(rng.standard_normal((batch, 64)).astype(np.float32)).cuda()
+    t = torch.from_numpy(rng.integers(0, 10, batch).astype(np.int32)).cuda()
+    native = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3)
+    native.set_params(params)
+    step_native = native.capture_native(x, t)
+    torch_graph = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3)
+    torch_graph.set_params(params)
+    step_torch = torch_graph.capture(x, t)
+    first = step_native().item()
+    assert step_torch().item() == first
+    gen = capi.lib().odl_scratch_generation()
+    # an unaligned GEMM far larger than anything so far: its staged operand copies make the arena grow
+    need = max(int(capi.lib().odl_scratch_bytes()), 1 << 20)
+    rows = need // (4 * 1001) + 64
+    a, b = torch.randn(rows, 1001, device="cuda"), torch.randn(1001, 3, device="cuda")
+    ops.gemm(a, b)
+    assert capi.lib().odl_scratch_generation() > gen
+    launches = capi.lib().odl_launch_count()
+    params_before = native.get_params()
+    with pytest.raises(capi.OdlError) as e1:
+        step_native()
+    assert e1.value.status == capi.ERR_STALE_GRAPH
+    with pytest.raises(capi.OdlError) as e2:
+        step_torch()
+    assert e2.value.status == capi.ERR_STALE_GRAPH
+    assert capi.lib().odl_launch_count() == launches               # nothing ran
+    assert np.array_equal(native.get_params(), params_before)
+    step_native = native.capture_native(x, t)                       # record again: works, and continues the same run
+    eager = trainer_cls(sizes, batch, optimizer="adam", lr=1e-3)
+    eager.set_params(params)
+    want = [eager.train_step(x, t).item() for _ in range(3)]
+    assert [first, step_native().item(), step_native().item()] == want
+    capi.device_status()
+    for tr in (native, torch_graph, eager):
+        tr.close()

@@ -97,6 +97,19 @@ def test_rejects_what_the_reference_rejects(tmp_path):
             odl_io.load(str(p))
     with pytest.raises(odl_io.OdlFormatError, match="Failed to open file"):
         odl_io.load(str(tmp_path / "missing.odl"))
+    # length fields far beyond the file: refused from the file size alone, before anything of that size is allocated
+    huge = {
+        "huge_name": good[:16] + struct.pack("<Q", 1 << 60) + good[24:],
+        "huge_count": good[:8] + struct.pack("<Q", 1 << 62) + good[16:],
+    }
+    nl = struct.unpack_from("<Q", good, 16)[0]   # first record: name length, name, rank, dims ...
+    dim0 = 16 + 8 + nl + 8
+    huge["huge_dim"] = good[:dim0] + struct.pack("<Q", 1 << 50) + good[dim0 + 8:]
+    for name, blob in huge.items():
+        p = tmp_path / f"{name}.odl"
+        p.write_bytes(blob)
+        with pytest.raises(odl_io.OdlFormatError):
+            odl_io.load(str(p))
     # an unsupported dtype code (int64 = 4) in an otherwise valid record
     rec = min(records(GOLDEN / "ref_state.odl"), key=len)
     name_len = struct.unpack_from("<Q", rec, 0)[0]
