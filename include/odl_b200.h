@@ -28,6 +28,8 @@ extern "C" {
 #define ODL_ERR_TOO_LARGE 5
 #define ODL_ERR_NOT_INITIALIZED 6
 #define ODL_ERR_STALE_GRAPH 7 /* a recorded step graph refers to scratch memory that was replaced since: capture again */
+#define ODL_ERR_COMM 8          /* the communicator reported an error, NCCL is unavailable, or it was aborted earlier */
+#define ODL_ERR_COMM_TIMEOUT 9  /* a collective did not complete within the watchdog's limit; communicator aborted */
 
 /* GEMM arithmetic: 3xTF32 (default, fp32-class accuracy: three tf32 MMAs per product) or plain TF32. */
 #define ODL_PRECISION_3XTF32 0
@@ -309,6 +311,44 @@ float *odl_mlp_loss_ptr(void *handle);
 float *odl_mlp_logits_ptr(void *handle);
 /* Contiguous device range [dW_layer, db_layer] of the flat gradient buffer (layer = -1: the whole buffer). */
 int odl_mlp_grad_bucket(void *handle, int layer, float **ptr, int64_t *count);
+
+/* ---- data-parallel training: communicator, overlapped gradient all-reduce, failure detection ------------------------- */
+
+/* The reference has no multi-GPU path (no collective, stream or peer copy anywhere in its tree); these entry points are
+ * the new layer the data-parallel MLP step needs.  One process (or host thread) per GPU; every rank holds full replicas
+ * of the parameters and optimizer state and its own rows of the batch; after the backward of layer l the contiguous
+ * gradient range [dW_l, db_l] is summed over all ranks with ncclAllReduce on a stream of its own while layers l-1 ... 0
+ * are still computing, and the fused optimizer scales by 1 / world.  NCCL is bound at run time (dlopen of "libnccl.so.2",
+ * or of the path in the environment variable ODL_NCCL_LIBRARY): the library itself links only the CUDA runtime. */
+
+#define ODL_COMM_UNIQUE_ID_BYTES 128
+/* Rank 0 makes the 128-byte rendezvous token (ncclGetUniqueId) and hands it to the other ranks by any host channel. */
+int odl_comm_unique_id(void *id_bytes);
+/* Join the communicator described by the token (ncclCommInitRank; collective over all `world` ranks; the calling thread's
+ * current CUDA device is the rank's GPU). */
+int odl_comm_create(const void *id_bytes, int rank, int world, void **comm);
+int odl_comm_destroy(void *comm);
+/* buf[0..count) = sum over ranks, in place, enqueued on `stream`. */
+int odl_comm_allreduce(void *comm, float *buf, int64_t count, void *stream);
+/* Errors NCCL noticed asynchronously (ncclCommGetAsyncError): ODL_OK or ODL_ERR_COMM.  The counterpart, for
+ * collectives, of CUDA_CHECK_ASYNC (include/origin/mat/origin/cuda/cuda_utils.cuh:14-33). */
+int odl_comm_status(void *comm);
+/* Host watchdog: polls done(arg) (non-zero = the watched work has completed) and odl_comm_status until completion, an
+ * error, or timeout_ms.  On error / time-out the communicator is aborted (kernels waiting for a peer that never joined
+ * end, the CUDA context stays usable) and ODL_ERR_COMM / ODL_ERR_COMM_TIMEOUT is returned; every later call on that
+ * communicator returns ODL_ERR_COMM. */
+int odl_comm_watch(void *comm, int timeout_ms, int (*done)(void *), void *arg);
+
+/* Attach a communicator to an MLP (the handle does not take ownership).  dw0_panels (1..8) splits the weight gradient of
+ * layer 0 -- the last GEMM of backward, whose all-reduce would otherwise overlap nothing -- into that many row panels,
+ * each reduced while the next one is computed; 0 lets the library choose. */
+int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels);
+/* One data-parallel optimisation step on this rank's rows x[batch, sizes[0]]: forward, loss, backward with the overlapped
+ * per-layer all-reduce, then each layer's fused update as soon as its bucket is reduced.  Everything is enqueued; the call
+ * does not wait for the GPU. */
+int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
+/* Watchdog over the last enqueued data-parallel step (odl_comm_watch on its last all-reduce). */
+int odl_mlp_dp_wait(void *handle, int timeout_ms);
 
 /* ---- input pipeline --------------------------------------------------------------------------------------------- */
 

@@ -33,6 +33,10 @@ int odl_debug_set_pair_mode(int mode);
  * kernel for small layers. */
 int odl_debug_set_conv_mode(int mode);
 
+/* Device address of the int that kernels raise when a bounded wait runs out (what odl_device_status reads and clears);
+ * NULL before odl_init.  For a test kernel that lets such a wait run out on purpose (tests/cuda/). */
+int *odl_debug_error_flag(void);
+
 #ifdef __cplusplus
 }
 #endif

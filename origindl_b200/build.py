@@ -79,5 +79,40 @@ def build_host_tests() -> Path:
     return exe
 
 
+def build_fake_nccl() -> Path:
+    """Compile the stand-in NCCL library the CPU tests of the communicator's failure handling load (tests/cpp/fake_nccl.c)."""
+    root = HERE.parent
+    src = root / "tests" / "cpp" / "fake_nccl.c"
+    out_dir = root / "tests" / "cpp" / "build"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    lib = out_dir / "libfake_nccl.so"
+    if lib.exists() and lib.stat().st_mtime >= src.stat().st_mtime:
+        return lib
+    r = subprocess.run([os.environ.get("CC", "gcc"), "-O1", "-Wall", "-shared", "-fPIC", str(src), "-o", str(lib)],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the fake NCCL library failed:\n" + r.stdout + r.stderr)
+    return lib
+
+
+def build_test_kernels() -> Path:
+    """Compile the test-only CUDA sources under tests/cuda/ into tests/cuda/build/libodl_test_kernels.so (they reuse the
+    library's device headers; nothing in the product links or loads them)."""
+    root = HERE.parent
+    srcs = sorted((root / "tests" / "cuda").glob("*.cu"))
+    out_dir = root / "tests" / "cuda" / "build"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    lib = out_dir / "libodl_test_kernels.so"
+    newest = max([s.stat().st_mtime for s in srcs] + [_newest_header()])
+    if lib.exists() and lib.stat().st_mtime >= newest:
+        return lib
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+           "-shared", "-cudart", "static", *map(str, srcs), "-o", str(lib)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the test kernels failed:\n" + r.stdout + r.stderr)
+    return lib
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))

@@ -15,6 +15,7 @@ LIB_PATH = _HERE / "libodl_b200.so"
 
 OK = 0
 ERR_STALE_GRAPH = 7
+ERR_COMM, ERR_COMM_TIMEOUT = 8, 9
 PRECISION_3XTF32 = 0
 PRECISION_TF32 = 1
 EPI_BIAS, EPI_RELU, EPI_MASK, EPI_COLSUM, EPI_SMALL = 1, 2, 4, 8, 16
@@ -158,6 +159,14 @@ _MLP_SIGNATURES = {
     "odl_conv2d_bn_act_forward": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, c_int,
                                   c_int, _P],
     "odl_gather_rows": [_P, _I64, _I64, _P, _I64, _I64, _P, _I64, _P, _P, _P],
+    "odl_comm_unique_id": [_P],
+    "odl_comm_create": [_P, c_int, c_int, ctypes.POINTER(c_void_p)],
+    "odl_comm_destroy": [_P],
+    "odl_comm_allreduce": [_P, _P, _I64, _P],
+    "odl_comm_status": [_P],
+    "odl_mlp_dp_attach": [_P, _P, c_int],
+    "odl_mlp_train_step_dp": [_P, _P, _P, c_int, _P],
+    "odl_mlp_dp_wait": [_P, c_int],
 }
 _SIGNATURES.update(_MLP_SIGNATURES)
 _POINTER_RETURNS = {"odl_mlp_loss_ptr": [_P], "odl_mlp_logits_ptr": [_P]}

@@ -593,6 +593,13 @@ extern "C" int odl_debug_set_slabs(int n)
     return 0;
 }
 
+// Test hook: device address of the per-device error flag (NULL before odl_init), for test kernels that raise it the way
+// a timed-out GEMM does.
+extern "C" int *odl_debug_error_flag(void)
+{
+    return odl::device_error_flag();
+}
+
 // Test hook: 0 = pair (2-CTA) GEMM kernel where it pays, 1 = never, 2 = whenever the shape allows it.
 extern "C" int odl_debug_set_pair_mode(int mode)
 {

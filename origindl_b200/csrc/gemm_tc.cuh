@@ -16,6 +16,8 @@ enum Status : int
     kKernelTimeout   = 4,   // a bounded wait inside a kernel ran out (device error flag was set)
     kTooLarge        = 5,   // size exceeds what the entry point supports
     kNotInitialized  = 6,
+    kCommError       = 8,   // the communicator (NCCL) reported an error, is unavailable, or was aborted earlier
+    kCommTimeout     = 9,   // a collective did not complete within the watchdog's limit; the communicator was aborted
     kStaleGraph      = 7,   // a recorded graph holds scratch addresses that have since been replaced: record it again
 };
 

@@ -45,6 +45,17 @@ int gemm_dispatch(int transA, int transB, int64_t M, int64_t N, int64_t K, const
                   const float *bias, const float *mask_src, int64_t ld_mask, float *colsum, int flags, int precision,
                   cudaStream_t stream, bool reset_arena, int ohw = 0, const float *scale = nullptr);
 
+// Communicator of the data-parallel step (comm_nccl.cpp): NCCL bound at run time, error polling, host watchdog.
+struct Comm;
+int comm_create(const void *id_bytes, int rank, int world, Comm **out);
+int comm_destroy(Comm *c);
+int comm_world(const Comm *c);
+int comm_rank(const Comm *c);
+int comm_allreduce_sum(Comm *c, float *buf, int64_t count, cudaStream_t stream);
+int comm_poll(Comm *c);
+int comm_abort(Comm *c);
+int comm_watch(Comm *c, int timeout_ms, int (*done)(void *), void *arg);
+
 int relu_forward_launch(const float *x, float *y, float *y_small, int64_t n, cudaStream_t s);
 int relu_backward_launch(const float *gy, const float *ref, float *gx, int64_t n, cudaStream_t s);
 int add_bias_launch(const float *x, const float *b, float *y, int64_t M, int64_t N, cudaStream_t s);

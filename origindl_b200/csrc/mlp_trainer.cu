@@ -18,6 +18,7 @@
 #include "gemm_tc.cuh"
 #include "host_util.h"
 #include "internal.h"
+#include "nvtx_ranges.h"
 
 namespace odl
 {
@@ -51,6 +52,13 @@ struct Mlp
     std::vector<void *> allocs;
     cudaGraphExec_t step_graph = nullptr;  // forward + loss + backward of one step on fixed input buffers (odl_mlp_capture)
     long long graph_launches   = 0;        // kernels one replay of it runs
+    // data-parallel step (odl_mlp_dp_attach): communicator (not owned), its stream, and per gradient piece one event
+    // "gradients final" (compute stream) and one "reduced" (communication stream).  Pieces: layers L-1 ... 1, then the
+    // dw0_panels row panels of layer 0.
+    Comm *comm               = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    int dw0_panels           = 1;
+    std::vector<cudaEvent_t> ev_ready, ev_reduced;
     long long graph_generation = -1;       // scratch_generation() when it was recorded: its scratch addresses are valid
                                            // only while no scratch block has been replaced since
 
@@ -68,8 +76,21 @@ struct Mlp
         *p = static_cast<T *>(q);
         return kOk;
     }
+    void drop_dp()
+    {
+        for (cudaEvent_t e : ev_ready)
+            cudaEventDestroy(e);
+        for (cudaEvent_t e : ev_reduced)
+            cudaEventDestroy(e);
+        ev_ready.clear(), ev_reduced.clear();
+        if (comm_stream)
+            cudaStreamDestroy(comm_stream);
+        comm_stream = nullptr;
+        comm        = nullptr;
+    }
     ~Mlp()
     {
+        drop_dp();
         if (step_graph)
             cudaGraphExecDestroy(step_graph);
         for (void *q : allocs)
@@ -282,6 +303,7 @@ int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int l
     cudaStream_t s = ST(stream);
     const int64_t B = h->batch;
     int rc;
+    NvtxRange range("odl forward + loss");
     h->cur_x = x;
     if (three(h))
     {
@@ -324,6 +346,7 @@ int odl_mlp_backward_layer(void *handle, int layer, void *stream)
     }
     cudaStream_t s   = ST(stream);
     const int64_t B  = h->batch;
+    NvtxRange range("odl backward layer", layer);
     const int cur    = (h->L - 1 - layer) & 1;  // ping-pong: the head's gradient sits in gbuf[0]
     const float *g   = h->gbuf[cur], *g_s = h->gbuf_small[cur];
     const float *xin = layer == 0 ? h->cur_x : h->act[layer - 1];
@@ -346,6 +369,7 @@ int odl_mlp_backward_layer(void *handle, int layer, void *stream)
 int odl_mlp_optimizer_step(void *handle, float grad_scale, void *stream)
 {
     Mlp *h = H(handle);
+    NvtxRange range("odl optimizer");
     h->step_count += 1;
     if (h->optimizer == 1)
         return adam_launch(h->params, h->grads, h->m, h->v, h->params_small, h->total, h->step_count, h->lr, h->beta1,
@@ -368,6 +392,7 @@ int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int 
     }
     if (first_of_step)
         h->step_count += 1;
+    NvtxRange range("odl optimizer layer", layer);
     const int64_t o = h->w_off[layer];
     const int64_t n = (layer + 1 < h->L ? h->w_off[layer + 1] : h->total) - o;
     float *ps       = h->params_small ? h->params_small + o : nullptr;
@@ -387,6 +412,140 @@ int odl_mlp_train_step(void *handle, const float *x, const void *labels, int lab
         if ((rc = odl_mlp_backward_layer(handle, l, stream)))
             return rc;
     return odl_mlp_optimizer_step(handle, 1.0f, stream);
+}
+
+// ---- data-parallel step -------------------------------------------------------------------------------------------
+int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels)
+{
+    Mlp *h = H(handle);
+    if (!h || !comm || dw0_panels < 0 || dw0_panels > 8)
+    {
+        set_last_error("mlp_dp_attach: invalid argument (dw0_panels=%d)", dw0_panels);
+        return kInvalidArgument;
+    }
+    h->drop_dp();
+    Comm *c = static_cast<Comm *>(comm);
+    // Row panels of dW_0 {in, out}: rows [k0, k1) are a contiguous range of the flat gradient buffer and one GEMM on the
+    // columns k0 ... k1 of x.  Worth it only where the bucket is large and other ranks exist; every panel must keep the
+    // 32-column granularity of the one-copy-per-operand tensor maps.
+    const int64_t in0 = h->sizes[0], out0 = h->sizes[1];
+    int panels = dw0_panels;
+    if (panels == 0)
+        panels = (comm_world(c) > 1 && in0 * out0 >= (int64_t(1) << 24)) ? 4 : 1;
+    while (panels > 1 && (in0 % (32 * panels) != 0))
+        --panels;
+    h->dw0_panels = panels;
+    ODL_CUDA_TRY(cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
+    const int pieces = (h->L - 1) + panels;
+    for (int i = 0; i < pieces; ++i)
+    {
+        cudaEvent_t a = nullptr, b = nullptr;
+        ODL_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        h->ev_ready.push_back(a);
+        ODL_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        h->ev_reduced.push_back(b);
+    }
+    h->comm = c;
+    return kOk;
+}
+
+namespace
+{
+// Piece i's gradients are final on `s`: sum them over the ranks on the communication stream.
+int reduce_piece(Mlp *h, int piece, float *ptr, int64_t count, cudaStream_t s, int layer)
+{
+    NvtxRange range("odl all-reduce layer", layer);
+    ODL_CUDA_TRY(cudaEventRecord(h->ev_ready[piece], s));
+    ODL_CUDA_TRY(cudaStreamWaitEvent(h->comm_stream, h->ev_ready[piece], 0));
+    int rc = comm_allreduce_sum(h->comm, ptr, count, h->comm_stream);
+    if (rc)
+        return rc;
+    ODL_CUDA_TRY(cudaEventRecord(h->ev_reduced[piece], h->comm_stream));
+    return kOk;
+}
+}  // namespace
+
+int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
+{
+    Mlp *h = H(handle);
+    if (!h->comm)
+    {
+        set_last_error("mlp_train_step_dp: odl_mlp_dp_attach has not been called");
+        return kInvalidArgument;
+    }
+    cudaStream_t s = ST(stream);
+    int rc         = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
+    if (rc)
+        return rc;
+    // head first: bucket l = [dW_l, db_l] (db_l came out of layer l+1's dX epilogue) is final after layer l's dW GEMM
+    for (int l = h->L - 1; l >= 1; --l)
+    {
+        if ((rc = odl_mlp_backward_layer(handle, l, stream)))
+            return rc;
+        const int64_t o = h->w_off[l];
+        const int64_t n = (l + 1 < h->L ? h->w_off[l + 1] : h->total) - o;
+        if ((rc = reduce_piece(h, h->L - 1 - l, h->grads + o, n, s, l)))
+            return rc;
+    }
+    const int first0 = h->L - 1;  // piece index of layer 0's first panel
+    if (h->dw0_panels == 1)
+    {
+        if ((rc = odl_mlp_backward_layer(handle, 0, stream)))
+            return rc;
+        const int64_t n = (h->L > 1 ? h->w_off[1] : h->total);
+        if ((rc = reduce_piece(h, first0, h->grads, n, s, 0)))
+            return rc;
+    }
+    else
+    {
+        // layer 0 has no dX: its backward is the one GEMM dW_0{in,out} = x^T . g, done here panel by panel
+        const int64_t B = h->batch, in0 = h->sizes[0], out0 = h->sizes[1];
+        const int cur   = (h->L - 1) & 1;
+        const float *g = h->gbuf[cur], *g_s = three(h) ? h->gbuf_small[cur] : nullptr;
+        const int64_t rows = in0 / h->dw0_panels;
+        const int64_t end  = (h->L > 1 ? h->w_off[1] : h->total);  // the last panel carries db_0 and the padding
+        for (int p = 0; p < h->dw0_panels; ++p)
+        {
+            NvtxRange range("odl backward layer 0 panel", p);
+            const int64_t k0 = p * rows;
+            rc = gemm_dispatch(1, 0, rows, out0, B, h->cur_x + k0, three(h) ? h->x_small + k0 : nullptr, in0, g, g_s, out0,
+                               h->grads + h->w_off[0] + k0 * out0, nullptr, out0, nullptr, nullptr, 0, nullptr, 0,
+                               h->precision, s, true);
+            if (rc)
+                return rc;
+            const int64_t lo = h->w_off[0] + k0 * out0;
+            const int64_t hi = (p + 1 == h->dw0_panels) ? end : h->w_off[0] + (k0 + rows) * out0;
+            if ((rc = reduce_piece(h, first0 + p, h->grads + lo, hi - lo, s, 0)))
+                return rc;
+        }
+    }
+    // update every layer as soon as ITS bucket is reduced: the head-side updates run while layer 0 is still in flight
+    const float scale = 1.0f / static_cast<float>(comm_world(h->comm));
+    for (int l = h->L - 1; l >= 0; --l)
+    {
+        if (l > 0)
+            ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_reduced[h->L - 1 - l], 0));
+        else
+            for (int p = 0; p < h->dw0_panels; ++p)
+                ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_reduced[first0 + p], 0));
+        if ((rc = odl_mlp_optimizer_step_layer(handle, l, scale, l == h->L - 1 ? 1 : 0, stream)))
+            return rc;
+    }
+    return kOk;
+}
+
+int odl_mlp_dp_wait(void *handle, int timeout_ms)
+{
+    Mlp *h = H(handle);
+    if (!h->comm || h->ev_reduced.empty())
+    {
+        set_last_error("mlp_dp_wait: odl_mlp_dp_attach has not been called");
+        return kInvalidArgument;
+    }
+    // the communication stream runs its collectives in order: the last piece's event covers the whole step
+    cudaEvent_t last = h->ev_reduced.back();
+    auto done = [](void *ev) -> int { return cudaEventQuery(static_cast<cudaEvent_t>(ev)) != cudaErrorNotReady ? 1 : 0; };
+    return comm_watch(h->comm, timeout_ms, done, last);
 }
 
 // Whole-step CUDA graph: records forward + loss + backward of every layer on the given STATIC input buffers into one

@@ -51,3 +51,18 @@ def allreduce_gradients(flat_grads, sizes, group=None) -> None:
     for layer in reduce_order(len(buckets)):
         off, n = buckets[layer]
         dist.all_reduce(flat_grads[off:off + n], op=dist.ReduceOp.SUM, group=group)
+
+
+COMM_OK, COMM_FAILED = 0, 8  # 8 = ODL_ERR_COMM of the C ABI
+
+
+def guarded(collective, *args, **kwargs) -> tuple[int, str]:
+    """Run a collective step and turn what a broken process group raises -- a peer that left, a time-out of the
+    group's own watchdog, a transport error -- into (status, message) instead of an exception from deep inside the
+    step, so that a training loop can stop cleanly, checkpoint and rebuild the group.  The process group's `timeout=`
+    bounds the wait; nothing here waits on its own."""
+    try:
+        collective(*args, **kwargs)
+        return COMM_OK, ""
+    except Exception as e:  # torch raises RuntimeError / DistBackendError / DistNetworkError depending on the backend
+        return COMM_FAILED, f"{type(e).__name__}: {e}"

@@ -8,8 +8,11 @@ Mirrors the reference's training loop (tests/example/mnist/mlp_mnist.cpp:176-437
 Data parallelism (one process per GPU): every rank holds full parameter / optimizer replicas and its own slice of
 the batch.  After layer l's backward the rank's gradient bucket [dW_l, db_l] -- one contiguous range of the flat
 gradient buffer -- is summed across ranks with NCCL on a side stream while layers l-1 ... 0 keep computing; the
-optimizer then scales by 1/world_size inside its fused update.  torch supplies streams, events and the process
-group; all arithmetic is in libodl_b200.so.
+optimizer then scales by 1/world_size inside its fused update.  By default the whole data-parallel step, collectives
+included, is ONE call into the library (odl_mlp_train_step_dp: the library owns the communicator, the communication
+stream and the events, so a C++ host runs the very same step); the process group is then only the channel that hands
+NCCL's rendezvous token to the other ranks.  `native_dp=False` keeps the older driver that issues the same all-reduces
+through torch.distributed from Python (same bits).  All arithmetic is in libodl_b200.so.
 """
 from __future__ import annotations
 
@@ -23,7 +26,8 @@ from . import capi, dp
 
 class MLPTrainer:
     def __init__(self, sizes, batch, optimizer="adam", lr=1e-3, momentum=0.0, hook_weight_decay=0.0,
-                 precision=capi.PRECISION_3XTF32, device=0, process_group=None, overlap=True):
+                 precision=capi.PRECISION_3XTF32, device=0, process_group=None, overlap=True, native_dp=True,
+                 dw0_panels=0):
         capi.init(device)
         self.sizes = [int(s) for s in sizes]
         self.batch = int(batch)
@@ -39,12 +43,25 @@ class MLPTrainer:
         self.world = 1
         self.overlap = overlap
         self._buckets = None
+        self._comm = None
         if process_group is not None:
             import torch.distributed as dist
 
             self.world = dist.get_world_size(process_group)
-            self._comm_stream = torch.cuda.Stream()
-            self._buckets = [self._bucket_tensor(l) for l in range(self.n_layers)]
+            if native_dp and overlap:
+                # the library's own communicator: rank 0 makes NCCL's rendezvous token, the process group carries it
+                token = ctypes.create_string_buffer(128)
+                if dist.get_rank(process_group) == 0:
+                    capi.call("odl_comm_unique_id", token)
+                box = [token.raw]
+                dist.broadcast_object_list(box, src=dist.get_global_rank(process_group, 0), group=process_group)
+                comm = ctypes.c_void_p()
+                capi.call("odl_comm_create", box[0], dist.get_rank(process_group), self.world, ctypes.byref(comm))
+                self._comm = comm
+                capi.call("odl_mlp_dp_attach", self._h, self._comm, int(dw0_panels))
+            else:
+                self._comm_stream = torch.cuda.Stream()
+                self._buckets = [self._bucket_tensor(l) for l in range(self.n_layers)]
         self._loss_view = self._view(capi.lib().odl_mlp_loss_ptr(self._h), 1)
 
     # -- raw device memory of the library wrapped as torch tensors (no copy) so that NCCL can reduce it in place
@@ -185,6 +202,9 @@ class MLPTrainer:
         if self.pg is None:
             capi.call("odl_mlp_train_step", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
             return self._loss_view[0]
+        if self._comm is not None:
+            capi.call("odl_mlp_train_step_dp", self._h, x.data_ptr(), labels.data_ptr(), is64, s)
+            return self._loss_view[0]
         import torch.distributed as dist
 
         compute = torch.cuda.current_stream()
@@ -268,10 +288,26 @@ class MLPTrainer:
 
         return step
 
+    def wait(self, timeout_ms: int = 60000) -> None:
+        """Host watchdog over the last data-parallel step: returns once its last all-reduce has completed; raises
+        OdlError (ERR_COMM / ERR_COMM_TIMEOUT) and aborts the communicator when NCCL reports an asynchronous error or
+        the collective does not complete in time (a peer that never joined).  Native data-parallel mode only."""
+        if self._comm is None:
+            raise RuntimeError("wait() needs the library's own communicator (process_group given, native_dp=True)")
+        capi.call("odl_mlp_dp_wait", self._h, int(timeout_ms))
+
+    def comm_status(self) -> None:
+        """Raise OdlError(ERR_COMM) if NCCL has noticed an asynchronous error on the library's communicator."""
+        if self._comm is not None:
+            capi.call("odl_comm_status", self._comm)
+
     def close(self) -> None:
         if self._h is not None:
             capi.call("odl_mlp_destroy", self._h)
             self._h = None
+        if self._comm is not None:
+            capi.call("odl_comm_destroy", self._comm)
+            self._comm = None
 
     def __del__(self):
         try:

@@ -1,8 +1,12 @@
 """GPU, two ranks over NCCL (skipped on a one-GPU machine): the data-parallel MLP trainer -- batch rows sharded by rank,
 per-layer gradient buckets all-reduced head first on a side stream while earlier layers still run their backward, 1/world
-folded into the optimizer -- reproduces single-GPU training on the global batch.  Checks: replicas stay bit-identical,
-overlapped and non-overlapped reduction give the same bits, parameters and the mean of the per-rank losses equal the
-full-batch run up to fp32 rounding (1e-5).  The host-side plan is also covered on CPU over gloo (test_dp_gloo.py)."""
+folded into the optimizer -- reproduces single-GPU training on the global batch.  Four drivers of the same step run on
+the same inputs: the library's own step behind the C ABI (odl_mlp_train_step_dp: its own NCCL communicator, stream and
+events) with layer 0's weight gradient in one piece and in four row panels, and the older Python driver over
+torch.distributed with and without overlap.  Checks: replicas stay bit-identical, all four drivers give the same bits,
+parameters and the mean of the per-rank losses equal the full-batch run up to fp32 rounding (1e-5), and the watchdog /
+status poll of the library's communicator report a healthy step.  The host-side plan and the failure paths are covered
+on CPU (test_dp_gloo.py, test_comm_failure_detection.py)."""
 import os
 import sys
 from pathlib import Path
@@ -15,7 +19,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent))
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 
 pytestmark = pytest.mark.gpu
-SIZES, GLOBAL_B, STEPS = [200, 384, 256, 10], 256, 6
+SIZES, GLOBAL_B, STEPS = [256, 384, 256, 10], 256, 6
 KW = dict(optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
 
 
@@ -43,16 +47,24 @@ def _worker(rank, world, port, out_dir):
     lo, hi = dp.shard_rows(GLOBAL_B, rank, world)
     xd, td = torch.from_numpy(xs[:, lo:hi].copy()).cuda(), torch.from_numpy(ts[:, lo:hi].copy()).cuda()
     results = {}
-    for overlap in (True, False):
-        tr = MLPTrainer(SIZES, hi - lo, device=rank, process_group=dist.group.WORLD, overlap=overlap, **KW)
+    drivers = {"native": dict(native_dp=True, dw0_panels=1), "native_panels": dict(native_dp=True, dw0_panels=4),
+               "python_overlap": dict(native_dp=False, overlap=True), "python_serial": dict(native_dp=False, overlap=False)}
+    for name, kw in drivers.items():
+        tr = MLPTrainer(SIZES, hi - lo, device=rank, process_group=dist.group.WORLD, **kw, **KW)
         tr.set_params(params)
-        losses = torch.stack([tr.train_step(xd[s % 2], td[s % 2]).clone() for s in range(STEPS)])
+        losses = []
+        for s in range(STEPS):
+            losses.append(tr.train_step(xd[s % 2], td[s % 2]).clone())
+            if kw["native_dp"]:
+                tr.wait(20000)       # host watchdog: the step's last all-reduce completed, no asynchronous error
+                tr.comm_status()
+        losses = torch.stack(losses)
+        torch.cuda.synchronize()
         dist.all_reduce(losses)  # the global loss is the mean of the per-rank means
-        results[overlap] = (tr.get_params(), (losses / world).cpu().numpy())
+        results[name] = (tr.get_params(), (losses / world).cpu().numpy())
         tr.close()
     capi.device_status()
-    np.savez(Path(out_dir) / f"rank_{rank}.npz", p_overlap=results[True][0], p_serial=results[False][0],
-             loss=results[True][1])
+    np.savez(Path(out_dir) / f"rank_{rank}.npz", loss=results["native"][1], **{"p_" + k: v[0] for k, v in results.items()})
     dist.barrier()
     dist.destroy_process_group()
 
@@ -68,8 +80,9 @@ def test_two_rank_nccl_training_equals_full_batch(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, 29100 + os.getpid() % 800, str(tmp_path)), nprocs=world, join=True)
     r0, r1 = np.load(tmp_path / "rank_0.npz"), np.load(tmp_path / "rank_1.npz")
-    assert np.array_equal(r0["p_overlap"], r1["p_overlap"])      # replicas stay identical
-    assert np.array_equal(r0["p_overlap"], r0["p_serial"])       # overlap changes the schedule, not the arithmetic
+    for name in ("native", "native_panels", "python_overlap", "python_serial"):
+        assert np.array_equal(r0["p_" + name], r1["p_" + name]), name       # replicas stay identical
+        assert np.array_equal(r0["p_" + name], r0["p_native"]), name        # the schedule changes, not the arithmetic
     capi.init(0)
     params, xs, ts = _inputs()
     full = MLPTrainer(SIZES, GLOBAL_B, **KW)
@@ -79,5 +92,5 @@ def test_two_rank_nccl_training_equals_full_batch(tmp_path):
     import _libs
 
     assert np.abs(r0["loss"] - want).max() <= 1e-5
-    assert _libs.max_rel_err(r0["p_overlap"], full.get_params()) <= 1e-5
+    assert _libs.max_rel_err(r0["p_native"], full.get_params()) <= 1e-5
     full.close()

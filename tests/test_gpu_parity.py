@@ -624,3 +624,39 @@ def test_skinny_linear_backward_row_samples(ops, M, N, K):
     assert ((dw[c].double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
     ref = dy.double().sum(0)
     assert ((db.double() - ref).abs().max() / ref.abs().max()).item() <= 1e-5
+
+
+@pytest.mark.parametrize("n", [2048, 4096, 8192])
+def test_full_size_linear_forward_backward_rows_against_the_oracle(ops, orc, n):
+    """M = N = K = n of the benchmark's Linear sweep, every operand layout of the layer (forward x.W^T, dX = g.W with an
+    MN-major B, dW = g^T.x with both operands MN-major) against the ORACLE ITSELF, by row subset: row i of a product of
+    the reference depends only on row i of its left operand, one fp32 accumulator, k ascending
+    (src/mat/origin/cpu/math/matmul.cpp:29-41), so calling the oracle on 16 sampled rows of the left operand gives the
+    reference's exact values for those rows of y and dX, and -- with the left operand g^T -- of dW; db is compared in
+    full.  The ReLU mask comes from the same y on both sides (y is an input of the backward call), so a value within
+    rounding of zero cannot flip one side's mask."""
+    gen = torch.Generator(device="cuda").manual_seed(n)
+    x, w = torch.randn((n, n), device="cuda", generator=gen), torch.randn((n, n), device="cuda", generator=gen)
+    b, dy = 0.1 * torch.randn((n,), device="cuda", generator=gen), torch.randn((n, n), device="cuda", generator=gen)
+    y = ops.linear_forward(x, w, b, relu=True)
+    dx, dw, db = ops.linear_backward(x, w, dy, y)
+    rows = np.sort(np.random.default_rng(n).choice(n, 16, replace=False))
+    xh, wh, bh, yh = host(x), host(w), host(b), host(y)
+    gh = host(dy) * (yh > 0)                                            # ReLU::backward: gy * mask, exact in fp32
+    r = len(rows)
+    # forward: y[rows] = relu(x[rows] . W^T + b)
+    y_o = np.empty((r, n), np.float32)
+    orc.oracle_linear_forward(np.ascontiguousarray(xh[rows]), wh, fptr(bh), y_o, r, n, n, 0, 1)
+    assert max_rel_err(yh[rows], y_o) <= 1e-5
+    # dX[rows] = g[rows] . W     (W is [N, K]: already the [reduce, out] matrix)
+    dx_o = np.empty((r, n), np.float32)
+    orc.oracle_matmul(np.ascontiguousarray(gh[rows]), wh, dx_o, r, n, n)
+    assert max_rel_err(host(dx[torch.from_numpy(rows).cuda()]), dx_o) <= 1e-5
+    # dW[rows] = (g^T)[rows] . x  (rows of g^T = columns of g)
+    dw_o = np.empty((r, n), np.float32)
+    orc.oracle_matmul(np.ascontiguousarray(gh[:, rows].T), xh, dw_o, r, n, n)
+    assert max_rel_err(host(dw[torch.from_numpy(rows).cuda()]), dw_o) <= 1e-5
+    # db = column sums of g, all of it (one fp32 accumulator over m, ascending, on the oracle)
+    db_o = np.empty(n, np.float32)
+    orc.oracle_colsum(gh, db_o, n, n)
+    assert max_rel_err(host(db), db_o) <= 1e-5
