@@ -230,7 +230,7 @@ def test_replay_refuses_a_graph_whose_scratch_was_replaced(trainer_cls):
     torch_graph.set_params(params)
     step_torch = torch_graph.capture(x, t)
     first = step_native().item()
-    assert step_torch().item() == first
+    step_torch()                                                    # (its capture ran two eager warm-up steps of its own)
     gen = capi.lib().odl_scratch_generation()
     # an unaligned GEMM far larger than anything so far: its staged operand copies make the arena grow
     need = max(int(capi.lib().odl_scratch_bytes()), 1 << 20)
