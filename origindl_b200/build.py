@@ -79,6 +79,26 @@ def build_host_tests() -> Path:
     return exe
 
 
+def build_dp_host() -> Path:
+    """Compile the plain C++ host of the data-parallel step (tests/cpp/dp_two_ranks.cpp: C ABI + CUDA runtime only)."""
+    root = HERE.parent
+    src = root / "tests" / "cpp" / "dp_two_ranks.cpp"
+    out_dir = root / "tests" / "cpp" / "build"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / "dp_two_ranks"
+    deps = [src, root / "include" / "odl_b200.h"]
+    if exe.exists() and exe.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
+        return exe
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-I", str(root / "include"), "-I", str(cuda / "include"),
+           str(src), "-o", str(exe), "-L", str(HERE), "-lodl_b200", "-L", str(cuda / "lib64"), "-lcudart_static", "-ldl", "-lrt",
+           "-lpthread", f"-Wl,-rpath,{HERE}", "-Wl,-rpath,$ORIGIN/../../../origindl_b200"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the data-parallel C++ host failed:\n" + r.stdout + r.stderr)
+    return exe
+
+
 def build_fake_nccl() -> Path:
     """Compile the stand-in NCCL library the CPU tests of the communicator's failure handling load (tests/cpp/fake_nccl.c)."""
     root = HERE.parent
