@@ -66,21 +66,32 @@ def test_stable_200_step_curve_tracks_reference_within_1e3(trainer_cls):
 
 def test_mnist_shaped_adam_curve_tracks_reference_like_exact_arithmetic(trainer_cls):
     """784-1000-1000-10, batch 512, Adam lr 1e-3, weight decay 1e-4, random labels, seed 42 (the MNIST-shaped
-    benchmark configuration).  This run is chaotic: a float64 restatement of the very same step (no fp32 rounding at
-    all; golden `c1_losses_fp64`) leaves the 1e-3 band around the reference's curve after about a dozen steps.  So the
-    bar here is: inside 1e-3 while exact arithmetic is (first 10 steps), and over all 200 steps no further from the
-    reference than twice the drift of exact arithmetic."""
+    benchmark configuration).  This run is chaotic, and two yardsticks in the golden file say so:
+      * `c1_losses_ulp`: the UNMODIFIED REFERENCE run again with ONE input element moved by one unit in the last place
+        leaves the 1e-3 band around its own original curve at step 19 and ends 0.39 away from it;
+      * `c1_losses_fp64`: a float64 restatement of the same step (no fp32 rounding at all) leaves it at step 19 too.
+    No implementation that is not bit-identical to the reference can therefore hold 1e-3 over 200 steps here.  The bar:
+    inside 1e-3 while the reference's own perturbed run is (first 10 steps, with margin), in the band for at least as
+    long as that run minus a few steps, and over all 200 steps no further from the reference than twice the reference's
+    own spread.  (A well-conditioned 200-step run is held to 1e-3 at every step in the test above.)"""
     from golden.make_golden import c1_inputs
 
     g = np.load(GOLDEN / "reference_vectors.npz")
-    ref, f64 = g["c1_losses"], g["c1_losses_fp64"]
+    ref, f64, ulp = g["c1_losses"], g["c1_losses_fp64"], g["c1_losses_ulp"]
     params, x, t = c1_inputs()
     tr = trainer_cls([784, 1000, 1000, 10], 512, optimizer="adam", lr=1e-3, hook_weight_decay=1e-4)
     tr.set_params(params)
     losses = run(tr, x, t, len(ref))
-    dev = np.abs(losses - ref)
-    assert np.abs(f64[:10] - ref[:10]).max() <= 1e-3      # the yardstick itself is inside the band here
+    dev, spread = np.abs(losses - ref), np.abs(ulp - ref)
+
+    def steps_in_band(d):
+        out = np.nonzero(d > 1e-3)[0]
+        return len(d) if out.size == 0 else int(out[0])
+
+    assert np.abs(f64[:10] - ref[:10]).max() <= 1e-3 and spread[:10].max() <= 1e-3   # the yardsticks are inside here
     assert dev[:10].max() <= 1e-3
+    assert steps_in_band(dev) >= steps_in_band(spread) - 5
+    assert dev.max() <= max(1e-3, 2.0 * spread.max())
     assert dev.max() <= max(1e-3, 2.0 * np.abs(f64 - ref).max())
     assert losses[-1] < 0.5 * losses[0]                  # and it trains
     tr.close()

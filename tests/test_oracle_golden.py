@@ -86,3 +86,20 @@ def test_golden_c1_curve_prefix():
     losses, _, _ = _libs.oracle_mlp_train([784, 1000, 1000, 10], params, x, t, 2, opt="adam", lr=1e-3, hook_wd=1e-4)
     assert np.array_equal(losses, g["c1_losses"][:2])
     assert abs(float(g["c1_losses"][0]) - np.log(10)) < 0.5   # untrained 10-class model
+
+
+def test_reference_is_chaotic_on_the_mnist_shaped_configuration():
+    """The sensitivity yardstick in the golden file, made by the unmodified reference itself: its 200-step curve with one
+    input element moved by one unit in the last place agrees with the original for the first steps (same program, same
+    seeds), then leaves the 1e-3 band before step 30 and ends far outside it -- so "within 1e-3 over 200 steps" on this
+    configuration can only be met by a bit-identical implementation, and the GPU test holds the CUDA path to the
+    reference's own spread instead."""
+    g = np.load(GOLDEN / "reference_vectors.npz")
+    ref, ulp = g["c1_losses"], g["c1_losses_ulp"]
+    assert len(ref) == len(ulp) == 200
+    spread = np.abs(ref - ulp)
+    assert spread[:4].max() == 0.0                     # a 1-ulp change of one of 401 408 inputs is invisible at first
+    assert spread[:10].max() <= 1e-3
+    first_out = int(np.nonzero(spread > 1e-3)[0][0])
+    assert 10 < first_out < 30
+    assert spread.max() > 0.1
