@@ -29,9 +29,16 @@ int odl_debug_set_slabs(int n);
  * operands, 4 = never the 256 x 512 plain-TF32 tile, 5 = like 2 plus that tile for every plain-TF32 problem,
  * 6 = never the persistent kernel, 7 = the persistent kernel whenever the shape allows. */
 int odl_debug_set_pair_mode(int mode);
+/* CTA pairs the persistent kernel walks its tiles with; 0 = as many as the GPU holds at once.  Small values make small
+ * test shapes run several rounds and a split last round. */
+int odl_debug_set_persistent_pairs(int pairs);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
  * kernel for small layers. */
 int odl_debug_set_conv_mode(int mode);
+
+/* Number of NVTX ranges the training-step entry points have opened in this process: 0 unless the environment variable
+ * ODL_NVTX is set to a non-zero value (lets a test see the switch work without a profiler attached). */
+long long odl_debug_nvtx_ranges(void);
 
 /* Device address of the int that kernels raise when a bounded wait runs out (what odl_device_status reads and clears);
  * NULL before odl_init.  For a test kernel that lets such a wait run out on purpose (tests/cuda/). */

@@ -593,6 +593,13 @@ extern "C" int odl_debug_set_slabs(int n)
     return 0;
 }
 
+// Test hook: CTA pairs the persistent GEMM kernel walks its tiles with (0 = as many as the GPU holds at once).
+extern "C" int odl_debug_set_persistent_pairs(int pairs)
+{
+    odl::g_persist_pairs = pairs;
+    return 0;
+}
+
 // Test hook: device address of the per-device error flag (NULL before odl_init), for test kernels that raise it the way
 // a timed-out GEMM does.
 extern "C" int *odl_debug_error_flag(void)

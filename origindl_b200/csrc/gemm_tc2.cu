@@ -358,6 +358,386 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Persistent 3xTF32 variant: as many CTA pairs as the GPU holds at once (74 on 148 SMs), each walking a static list of
+// work units (pair p takes units p, p + P, p + 2P, ...).  What it buys over one tile per pair:
+//   * the epilogue of a tile (registers -> shared-memory slab -> global, with bias / ReLU / mask / column sums) runs
+//     while the producer and the MMA thread are already on the next tile: the stage ring and the two TMEM accumulator
+//     buffers simply keep rotating across tiles, so the MMA thread is ahead by two drains (128 of K) before it has to
+//     wait for the epilogue warps, and set-up (barriers, TMEM allocation, first-load latency) is paid once per SM;
+//   * the pairs start every round together, so a round's tiles stream the same K range at about the same time and
+//     share their operand panels in L2 instead of drifting apart;
+//   * a short last round is split along K: when the tiles left over after the full rounds would occupy at most half of
+//     the pairs, each of them becomes TWO units (first and second half of K) on two pairs.  Both pairs park their
+//     partial tile in scratch and take a ticket; whoever comes second adds the other's values to its own registers and
+//     runs the epilogue.  Nobody waits for anybody, and a + b == b + a, so the result does not depend on who was second.
+// Shared memory: three 64 KB stages, eight unpadded (XOR-swizzled) 4 KB transpose slabs beside the live ring, barriers.
+struct PersistPlan
+{
+    int tiles_m, tiles_n;
+    int full_units;   // whole tiles, one unit each: units [0, full_units)
+    int split_tiles;  // tiles of the short last round, two units each: units [full_units, full_units + 2 * split_tiles)
+    int num_kb;       // K-blocks of 32
+    int kb_mid;       // first K-block of a split tile's second half
+    int chunk_kb;     // K-blocks accumulated in TMEM between two drains
+    float *partial;   // [split_tiles][2 ranks][2 halves][128 x 256] parked partial tiles
+    unsigned *tickets;  // [split_tiles][2 ranks], zero between launches (the second arriver resets its ticket)
+};
+
+constexpr int kPStages   = 3;
+constexpr int kPSlab     = 32 * 32 * 4;  // one warp's transpose slab
+constexpr int kPSmem     = 1024 + kPStages * PairCfg<256>::stage_bytes(3) + kEpiWarps * kPSlab + 256;
+
+__device__ __forceinline__ void epilogue_warps_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const int a_mn, const int b_mn,
+                           const PersistPlan plan)
+{
+    constexpr int BN = 256;
+    using Cfg        = PairCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int stage_bytes = Cfg::stage_bytes(3);
+    uint8_t *tiles        = base;
+    float *slabs          = reinterpret_cast<float *>(base + kPStages * stage_bytes);
+    uint8_t *aux_base     = base + kPStages * stage_bytes + kEpiWarps * kPSlab;
+    uint64_t *full_bar    = reinterpret_cast<uint64_t *>(aux_base);
+    uint64_t *empty_bar   = full_bar + kPStages;
+    uint64_t *acc_full    = empty_bar + kPStages;
+    uint64_t *acc_empty   = acc_full + 2;
+    uint32_t *tmem_slot   = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *early_out        = const_cast<int *>(abort_f) + 1;
+    int *ticket_box       = early_out + 1;
+
+    const int warp      = threadIdx.x >> 5;
+    const int lane      = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader   = rank == 0;
+    const int pair      = blockIdx.x >> 1;
+    const int n_pairs   = gridDim.x >> 1;
+    const int n_units   = plan.full_units + 2 * plan.split_tiles;
+
+    if (threadIdx.x == 0)
+    {
+        *early_out = (leader && p.err != nullptr && *reinterpret_cast<volatile int *>(p.err) != 0) ? 1 : 0;
+        *abort_f   = 0;
+    }
+    __syncthreads();
+    ptx::cluster_sync();
+    const bool skip = ptx::ld_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(early_out), 0)) != 0;
+
+    if (!skip)
+    {
+        if (warp == 0 && lane == 0)
+        {
+            ptx::prefetch_tmap(&tm.a);
+            ptx::prefetch_tmap(&tm.b);
+            ptx::prefetch_tmap(&tm.a_small);
+            ptx::prefetch_tmap(&tm.b_small);
+            for (int s = 0; s < kPStages; ++s)
+            {
+                ptx::mbar_init(&full_bar[s], 1);
+                ptx::mbar_init(&empty_bar[s], 1);
+            }
+            for (int b = 0; b < 2; ++b)
+            {
+                ptx::mbar_init(&acc_full[b], 1);
+                ptx::mbar_init(&acc_empty[b], 2 * kEpiWarps);
+            }
+            ptx::fence_mbar_init();
+        }
+        if (warp == 1)
+        {
+            ptx::tmem_alloc_pair(tmem_slot, Cfg::tmem_cols);
+            ptx::tmem_relinquish_pair();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = skip ? 0u : *tmem_slot;
+
+    // unit -> tile, K range; every role walks the same list
+    auto unit_tile = [&](int u, int &tile, int &kb0, int &kb1, int &half) {
+        if (u < plan.full_units)
+        {
+            tile = u, kb0 = 0, kb1 = plan.num_kb, half = -1;
+        }
+        else
+        {
+            const int v = u - plan.full_units;
+            tile        = plan.full_units + (v >> 1);
+            half        = v & 1;
+            kb0         = half ? plan.kb_mid : 0;
+            kb1         = half ? plan.num_kb : plan.kb_mid;
+        }
+    };
+    auto tile_origin = [&](int tile, int &tile_m, int &tile_n) {
+        const int per_group = kGroupM * plan.tiles_n;
+        const int g         = tile / per_group;
+        const int first_m   = g * kGroupM;
+        const int gsz       = min(plan.tiles_m - first_m, kGroupM);
+        const int local     = tile - g * per_group;
+        tile_m              = first_m + local % gsz;
+        tile_n              = local / gsz;
+    };
+
+    if (skip)
+    {
+        // nothing
+    }
+    else if (warp == 0)
+    {
+        // ================================================================= TMA producer (both CTAs)
+        if (lane == 0)
+        {
+            uint32_t gk = 0;  // K-blocks issued so far: the ring position carries over from tile to tile
+            bool ok     = true;
+            for (int u = pair; u < n_units && ok; u += n_pairs)
+            {
+                int tile, kb0, kb1, half, tile_m, tile_n;
+                unit_tile(u, tile, kb0, kb1, half);
+                tile_origin(tile, tile_m, tile_n);
+                const int m0  = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
+                const int nb0 = tile_n * BN + static_cast<int>(rank) * (BN / 2);
+                for (int kb = kb0; kb < kb1; ++kb, ++gk)
+                {
+                    const int s       = gk % kPStages;
+                    const uint32_t ph = (gk / kPStages) & 1;
+                    if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_f))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    if (leader)
+                        ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * stage_bytes);
+                    const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[s]), 0);
+                    uint8_t *st  = tiles + s * stage_bytes;
+                    const int k0 = kb * kBK;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                    {
+                        uint8_t *sa           = st + t * Cfg::a_bytes;
+                        const CUtensorMap *ma = t ? &tm.a_small : &tm.a;
+                        if (!a_mn)
+                            ptx::tma_load_2d_pair(sa, ma, bar, k0, m0);
+                        else if (a_mn & 2)
+                            ptx::tma_load_3d_pair(sa, ma, bar, 0, k0, m0 / 32);
+                        else
+                            for (int j = 0; j < kBM / 32; ++j)
+                                ptx::tma_load_2d_pair(sa + j * Cfg::mn_box, ma, bar, m0 + 32 * j, k0);
+                    }
+                    uint8_t *sb0 = st + 2 * Cfg::a_bytes;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                    {
+                        uint8_t *sb           = sb0 + t * Cfg::b_bytes;
+                        const CUtensorMap *mb = t ? &tm.b_small : &tm.b;
+                        if (!b_mn)
+                            ptx::tma_load_2d_pair(sb, mb, bar, k0, nb0);
+                        else if (b_mn & 2)
+                            ptx::tma_load_3d_pair(sb, mb, bar, 0, k0, nb0 / 32);
+                        else
+                            for (int j = 0; j < BN / 64; ++j)
+                                ptx::tma_load_2d_pair(sb + j * Cfg::mn_box, mb, bar, nb0 + 32 * j, k0);
+                    }
+                }
+            }
+            if (*abort_f && leader)
+            {
+                // let the copies still in flight land before the CTA goes away
+                const uint32_t first = gk > kPStages ? gk - kPStages : 0;
+                for (uint32_t k = first; k < gk; ++k)
+                    ptx::mbar_wait(&full_bar[k % kPStages], (k / kPStages) & 1, nullptr);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        // ================================================================= MMA issuer (leader only)
+        if (lane == 0 && leader)
+        {
+            const uint32_t idesc  = ptx::make_idesc_tf32(2 * kBM, BN, a_mn != 0, b_mn != 0);
+            const uint32_t a_step = a_mn ? 1024u : 32u;
+            const uint32_t b_step = b_mn ? 1024u : 32u;
+            const uint32_t a_lbo  = a_mn ? Cfg::mn_box : 16u;
+            const uint32_t b_lbo  = b_mn ? Cfg::mn_box : 16u;
+            const uint32_t a_sbo  = a_mn ? 512u : 1024u;
+            const uint32_t b_sbo  = b_mn ? 512u : 1024u;
+            const uint32_t a_lay  = a_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+            uint32_t gk = 0, gc = 0;  // K-blocks consumed and accumulator chunks started so far, over all tiles
+            bool ok     = true;
+            for (int u = pair; u < n_units && ok; u += n_pairs)
+            {
+                int tile, kb0, kb1, half;
+                unit_tile(u, tile, kb0, kb1, half);
+                for (int kb = kb0; kb < kb1 && ok; ++gc)
+                {
+                    const int buf         = gc & 1;
+                    const uint32_t use    = gc >> 1;
+                    const uint32_t tmem_d = tmem_base + buf * BN;
+                    if (!ptx::mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_f))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const int kb_end = min(kb + plan.chunk_kb, kb1);
+                    for (bool first = true; kb < kb_end; ++kb, ++gk)
+                    {
+                        const int s       = gk % kPStages;
+                        const uint32_t ph = (gk / kPStages) & 1;
+                        if (!ptx::mbar_wait(&full_bar[s], ph, abort_f))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t sa  = ptx::smem_u32(tiles + s * stage_bytes);
+                        const uint32_t sas = sa + Cfg::a_bytes;
+                        const uint32_t sb  = sa + 2 * Cfg::a_bytes;
+                        const uint32_t sbs = sb + Cfg::b_bytes;
+#pragma unroll
+                        for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+                        {
+                            const uint64_t da  = ptx::make_smem_desc(sa + kk * a_step, a_lbo, a_sbo, a_lay);
+                            const uint64_t db  = ptx::make_smem_desc(sb + kk * b_step, b_lbo, b_sbo, b_lay);
+                            const uint64_t das = ptx::make_smem_desc(sas + kk * a_step, a_lbo, a_sbo, a_lay);
+                            const uint64_t dbs = ptx::make_smem_desc(sbs + kk * b_step, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32_ss_pair(tmem_d, das, db, idesc, first ? 0u : 1u);
+                            ptx::mma_tf32_ss_pair(tmem_d, da, dbs, idesc, 1);
+                            ptx::mma_tf32_ss_pair(tmem_d, da, db, idesc, 1);
+                            first = false;
+                        }
+                        ptx::mma_commit_pair_both(&empty_bar[s]);
+                    }
+                    if (ok)
+                        ptx::mma_commit_pair_both(&acc_full[buf]);
+                }
+            }
+        }
+    }
+    else
+    {
+        // ================================================================= accumulate + epilogue (warps 2..9, both CTAs)
+        const int e  = warp - 2;
+        const int q  = warp & 3;
+        const int h  = e >> 2;
+        const int cw = h * Cfg::warp_cols;
+        float *slab  = slabs + e * (kPSlab / 4);
+        const bool direct = epilogue_direct_ok(p);  // rows of D from registers with 256-bit stores, no transpose slab
+        float acc[Cfg::warp_cols];
+        uint32_t gc = 0;
+        bool have   = true;
+        for (int u = pair; u < n_units && have; u += n_pairs)
+        {
+            int tile, kb0, kb1, half, tile_m, tile_n;
+            unit_tile(u, tile, kb0, kb1, half);
+            tile_origin(tile, tile_m, tile_n);
+            const int m0      = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
+            const int n0      = tile_n * BN;
+            const int nchunks = (kb1 - kb0 + plan.chunk_kb - 1) / plan.chunk_kb;
+            for (int c = 0; c < nchunks; ++c, ++gc)
+            {
+                const int buf      = gc & 1;
+                const uint32_t use = gc >> 1;
+                have = __all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], use & 1, abort_f));
+                if (!have)
+                    break;
+                ptx::tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * BN + cw;
+#pragma unroll
+                for (int j = 0; j < Cfg::warp_cols / 32; ++j)
+                {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(taddr + 32 * j, r);
+                    ptx::tmem_ld_wait();
+                    if (c == 0)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            acc[32 * j + i] = __uint_as_float(r[i]);
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            acc[32 * j + i] += __uint_as_float(r[i]);
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty[buf]), 0));
+            }
+            if (!have)
+                break;
+            bool store = true;
+            if (half >= 0)
+            {
+                // half of a split tile: park the partial tile, take a ticket; the second arriver combines and stores
+                const int st      = tile - plan.full_units;
+                const size_t slot = (static_cast<size_t>(st) * 2 + rank) * 2;
+                float4 *mine      = reinterpret_cast<float4 *>(plan.partial + (slot + half) * (kBM * BN)) + (e * 32) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < Cfg::warp_cols / 4; ++i)
+                    mine[i * 32] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                __threadfence();  // this thread's part of the partial tile is visible device-wide before the ticket is taken
+                epilogue_warps_sync();
+                if (warp == 2 && lane == 0)
+                {
+                    __threadfence();
+                    *ticket_box = static_cast<int>(atomicAdd(plan.tickets + st * 2 + rank, 1u));
+                }
+                epilogue_warps_sync();
+                store = *ticket_box != 0;
+                if (store)
+                {
+                    __threadfence();
+                    const float4 *other =
+                        reinterpret_cast<const float4 *>(plan.partial + (slot + (half ^ 1)) * (kBM * BN)) + (e * 32) * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < Cfg::warp_cols / 4; ++i)
+                    {
+                        const float4 o = __ldcg(other + i * 32);
+                        acc[4 * i] += o.x, acc[4 * i + 1] += o.y, acc[4 * i + 2] += o.z, acc[4 * i + 3] += o.w;
+                    }
+                }
+                epilogue_warps_sync();  // everybody has read the ticket before the next unit may overwrite the box
+                if (store && warp == 2 && lane == 0)
+                    plan.tickets[st * 2 + rank] = 0;  // ready for the next launch
+            }
+            if (store)
+            {
+                if (direct)
+                    gemm_epilogue_direct<Cfg::warp_cols>(p, acc, m0, n0, cw, q, lane);
+                else
+                    gemm_epilogue_store<256, Cfg::warp_cols, true>(p, acc, slab, m0, n0, cw, q, lane);
+            }
+        }
+        ptx::tc_fence_before_sync();
+    }
+
+    // ---- teardown: nobody in the pair still uses TMEM or signals a barrier of the other CTA
+    __syncthreads();
+    ptx::cluster_sync();
+    if (!skip && warp == 1)
+    {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, Cfg::tmem_cols);
+    }
+    if (threadIdx.x == 0 && *abort_f && p.err != nullptr)
+        atomicExch(p.err, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // Plain-TF32 variant with a 256 x 512 tile per pair.  Plain TF32 never drains the accumulator mid-way, so the second
 // TMEM buffer of the kernel above is free to hold 256 more columns: each CTA then loads one 128-row A tile and TWO
 // 128-row blocks of B per K-slab (48 KB for 2 x 128 x 256 x 32 products instead of 32 KB for half of that), i.e. 0.75 of
@@ -583,9 +963,78 @@ gemm_tc2_wide_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, co
 
 // Test hook: 0 = use the pair kernel where it pays (automatic), 1 = never, 2 = whenever the shape allows it,
 // 3 = separate 2-D copies for MN-major operands, 4 = never the 256 x 512 plain-TF32 tile, 5 = like 2 and the 256 x 512
-// tile for every plain-TF32 problem.
+// tile for every plain-TF32 problem, 6 = never the persistent kernel, 7 = like 2 and the persistent kernel for every
+// 3xTF32 problem.
 int g_pair_mode = 0;
+// Test hook: CTA pairs the persistent kernel uses (0 = as many as the GPU holds at once).
+int g_persist_pairs = 0;
 extern int g_slabs;
+
+namespace
+{
+// Scratch of the persistent kernel's split last round: parked partial tiles and their tickets.  Grown on demand (the
+// device is drained first), never shrunk; tickets are zero between launches.
+float *g_part           = nullptr;
+size_t g_part_floats    = 0;
+unsigned *g_tickets     = nullptr;
+size_t g_ticket_count   = 0;
+
+int tail_split_scratch(size_t floats, size_t tickets)
+{
+    if (floats <= g_part_floats && tickets <= g_ticket_count)
+        return kOk;
+    if (cudaDeviceSynchronize() != cudaSuccess)
+        return kCudaError;
+    cudaFree(g_part);
+    cudaFree(g_tickets);
+    g_part = nullptr, g_tickets = nullptr, g_part_floats = 0, g_ticket_count = 0;
+    tickets = tickets < 256 ? 256 : tickets;
+    if (cudaMalloc(&g_part, floats * 4) != cudaSuccess || cudaMalloc(&g_tickets, tickets * 4) != cudaSuccess ||
+        cudaMemset(g_tickets, 0, tickets * 4) != cudaSuccess)
+    {
+        set_last_error("gemm: cannot allocate %zu bytes of scratch for the split last round", floats * 4 + tickets * 4);
+        return kCudaError;
+    }
+    g_part_floats = floats, g_ticket_count = tickets;
+    bump_scratch_generation();
+    return kOk;
+}
+
+// CTA pairs of the persistent kernel the device holds at once (74 on a full B200), asked of the driver once per device.
+int resident_pairs()
+{
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (cached[dev] == 0)
+    {
+        cudaFuncSetAttribute(gemm_tc2_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmem);
+        cudaDeviceProp prop;
+        int sms = cudaGetDeviceProperties(&prop, dev) == cudaSuccess ? prop.multiProcessorCount : 148;
+        cudaLaunchConfig_t cfg;
+        std::memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim          = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+        cfg.blockDim         = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kPSmem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs                = attr;
+        cfg.numAttrs             = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_persistent_kernel, &cfg) != cudaSuccess || n <= 0)
+        {
+            cudaGetLastError();
+            n = -1;  // unknown: the persistent kernel stays off on this device
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+}  // namespace
 
 // True when gemm_tc_launch should hand this problem to the pair kernel: whenever there is at least one pair per two SMs.
 // Measured on B200 at 8192^3 with the kernels alternated inside one run (the GPU sits at its power cap during long
@@ -599,7 +1048,7 @@ bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int ter
     (void)a_mn, (void)b_mn, (void)terms;
     if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiSplitK)))
         return false;
-    if (g_pair_mode == 2 || g_pair_mode == 5)
+    if (g_pair_mode == 2 || g_pair_mode == 5 || g_pair_mode == 7)
         return true;
     const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
     return pairs >= 74;
@@ -680,6 +1129,60 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
             return kCudaError;
         }
         return kOk;
+    }
+    // 3xTF32 with more tiles than the GPU holds pairs: the persistent kernel (epilogue overlapped with the next tile's
+    // main loop, short last round split along K).  g_pair_mode 6 = never, 7 = for every 3xTF32 problem that reaches here.
+    if (terms == 3 && g_pair_mode != 6 && g_pair_mode != 3)
+    {
+        const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM), tiles_n = (p.N + BN - 1) / BN;
+        const int T       = tiles_m * tiles_n;
+        int P             = resident_pairs();
+        if (g_persist_pairs > 0 && P > 0)
+            P = g_persist_pairs < P ? g_persist_pairs : P;
+        if (P > 0 && (T > P || g_pair_mode == 7))
+        {
+            PersistPlan plan;
+            plan.tiles_m = tiles_m, plan.tiles_n = tiles_n;
+            plan.num_kb   = (p.K + kBK - 1) / kBK;
+            plan.chunk_kb = g_chunk_kb > 0 ? g_chunk_kb : 64 / kBK;
+            if (plan.chunk_kb > plan.num_kb)
+                plan.chunk_kb = plan.num_kb;
+            plan.full_units = T, plan.split_tiles = 0, plan.kb_mid = 0, plan.partial = nullptr, plan.tickets = nullptr;
+            const int R = T % P;
+            if (R > 0 && 2 * R <= P && plan.num_kb >= 4 * plan.chunk_kb)
+            {
+                plan.split_tiles = R;
+                plan.full_units  = T - R;
+                plan.kb_mid      = ((plan.num_kb / 2 + plan.chunk_kb - 1) / plan.chunk_kb) * plan.chunk_kb;
+                if ((rc = tail_split_scratch(static_cast<size_t>(R) * 4 * kBM * BN, static_cast<size_t>(R) * 2)))
+                    return rc;
+                plan.partial = g_part, plan.tickets = g_tickets;
+            }
+            const int units = plan.full_units + 2 * plan.split_tiles;
+            cudaLaunchConfig_t cfg;
+            std::memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim          = dim3(static_cast<unsigned>(2 * (units < P ? units : P)), 1, 1);
+            cfg.blockDim         = dim3(kThreads, 1, 1);
+            cfg.dynamicSmemBytes = kPSmem;
+            cfg.stream           = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id               = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs                = attr;
+            cfg.numAttrs             = 1;
+            GemmParams q   = p;
+            q.kb_per_split = plan.num_kb;
+            cudaError_t e  = cudaLaunchKernelEx(&cfg, gemm_tc2_persistent_kernel, tm, q, a_mn, b_mn, plan);
+            ++g_launch_count;
+            if (e != cudaSuccess)
+            {
+                set_last_error("gemm_tc2_persistent_kernel launch failed: %s", cudaGetErrorString(e));
+                return kCudaError;
+            }
+            return kOk;
+        }
     }
     int slabs = (terms == 1 && p.K >= 8 * kBK) ? 2 : 1;
     if (g_slabs == 1 || g_slabs == 2)

@@ -668,4 +668,10 @@ int odl_mlp_grad_bucket(void *handle, int layer, float **ptr, int64_t *count)
     return kOk;
 }
 
+// Test hook: NVTX ranges opened so far in this process (0 unless ODL_NVTX is set).
+long long odl_debug_nvtx_ranges(void)
+{
+    return nvtx_range_count();
+}
+
 }  // extern "C"

@@ -267,3 +267,39 @@ def test_replay_refuses_a_graph_whose_scratch_was_replaced(trainer_cls):
     capi.device_status()
     for tr in (native, torch_graph, eager):
         tr.close()
+
+
+def test_nvtx_ranges_follow_the_environment_switch():
+    """ODL_NVTX=1 wraps forward + loss, each layer's backward and the optimizer in NVTX ranges (for timeline tools); the
+    default run opens none.  The switch is read once per process, so each setting runs in a process of its own."""
+    import subprocess
+    import sys
+    import textwrap
+
+    code = textwrap.dedent(f"""
+        import ctypes, sys
+        sys.path.insert(0, {str(Path(__file__).resolve().parent.parent)!r})
+        import numpy as np, torch
+        from origindl_b200 import capi
+        from origindl_b200.trainer import MLPTrainer
+        capi.init(0)
+        tr = MLPTrainer([32, 48, 24, 10], 16, optimizer="adam")
+        tr.set_params(np.zeros(tr.param_count, np.float32))
+        x, t = torch.randn(16, 32, device="cuda"), torch.zeros(16, dtype=torch.int32, device="cuda")
+        for _ in range(2):
+            tr.train_step(x, t)
+        torch.cuda.synchronize()
+        fn = capi.lib().odl_debug_nvtx_ranges
+        fn.restype = ctypes.c_longlong
+        print("ranges", fn())
+    """)
+    import os
+
+    counts = {}
+    for setting in ("0", "1"):
+        r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, ODL_NVTX=setting), capture_output=True,
+                           text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        counts[setting] = int(r.stdout.split("ranges")[1])
+    assert counts["0"] == 0
+    assert counts["1"] == 2 * (1 + 3 + 1)        # per step: forward + loss, three layers' backward, the optimizer

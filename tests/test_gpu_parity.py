@@ -211,6 +211,64 @@ def test_gemm_cta_pair_kernel(ops, M, N, K, ta, tb, precision):
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K,pairs", [(129, 256, 32, 0), (300, 520, 100, 4), (1024, 1024, 1024, 3), (1024, 1024, 1024, 7),
+                                         (1024, 1024, 1024, 16), (2048, 768, 515, 5), (2048, 768, 515, 11), (1500, 1300, 700, 9)])
+def test_gemm_persistent_pair_kernel(ops, M, N, K, pairs, ta, tb):
+    """The persistent 3xTF32 pair kernel, forced on small shapes with a small number of CTA pairs so that every pair
+    walks several tiles (epilogue of tile i overlapping the main loop of tile i + 1, stage ring and accumulator buffers
+    carried across tiles) and, where the last round is short, its tiles are split along K between two pairs (partial
+    tiles parked in scratch, the second arriver combines).  Ragged row / column / K tails, all four operand layouts,
+    the full epilogue -- once with column sums (transpose-slab stores) and once without (rows written straight from
+    registers with 256-bit stores where D's rows are 32-byte aligned).  Checked against float64; where no tile is split
+    the result must be bit-identical to the one-tile-per-pair kernel (same products, same order), and a second launch
+    must give the same bits (tickets reset)."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(M + N + K + 2 * ta + tb + pairs)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    opa = a.T.astype(np.float64) if ta else a.astype(np.float64)
+    opb = b.T.astype(np.float64) if tb else b.astype(np.float64)
+    pre = opa @ opb + bias
+    ref = np.maximum(pre, 0) * (mask > 0)
+    tol = TOL[0] * np.abs(pre).max()
+    safe = np.abs(pre) > tol
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    p_eff = pairs if pairs else 74
+    r = tiles % p_eff
+    split = r > 0 and 2 * r <= p_eff and (K + 31) // 32 >= 8
+    for with_colsum in (True, False):
+        outs = []
+        capi.call("odl_debug_set_tile_n", 256)
+        try:
+            for mode, n_pairs in ((7, pairs), (7, pairs), (2, 0)):
+                capi.call("odl_debug_set_pair_mode", mode)
+                capi.call("odl_debug_set_persistent_pairs", n_pairs)
+                colsum = torch.zeros(N, device="cuda") if with_colsum else None
+                d, ds = ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True,
+                                 mask_src=dev(mask), colsum=colsum, want_small=True)
+                outs.append((d, ds) + ((colsum,) if with_colsum else ()))
+        finally:
+            capi.call("odl_debug_set_pair_mode", 0)
+            capi.call("odl_debug_set_tile_n", 0)
+            capi.call("odl_debug_set_persistent_pairs", 0)
+        capi.device_status()
+        d, ds = outs[0][:2]
+        assert np.abs(host(d) - ref)[safe].max() <= tol
+        assert np.abs(host(d) - ref).max() <= 2 * tol
+        if with_colsum:
+            assert max_rel_err(host(outs[0][2]), ref.sum(0)) <= 10 * TOL[0]
+        assert torch.equal(ds, ops.split_tf32(d))
+        assert all(torch.equal(x, y) for x, y in zip(outs[0], outs[1]))          # same bits on a second launch
+        if not split:
+            assert all(torch.equal(x, y) for x, y in zip(outs[0][:2], outs[2][:2]))  # identical to one tile per pair
+            if with_colsum:   # (the column sums add the same 32-row slabs in another fixed order: butterfly vs slab)
+                assert max_rel_err(host(outs[0][2]), host(outs[2][2])) <= 1e-5
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(129, 256, 32), (256, 300, 64), (300, 520, 100), (1024, 1024, 1024), (2048, 768, 515),
                                    (512, 1600, 288)])
 def test_gemm_wide_tf32_pair_tile(ops, M, N, K, ta, tb):
