@@ -30,7 +30,8 @@ int odl_debug_set_slabs(int n);
  * 6 = never the persistent kernel, 7 = the persistent kernel whenever the shape allows. */
 int odl_debug_set_pair_mode(int mode);
 /* CTA pairs the persistent kernel walks its tiles with; 0 = as many as the GPU holds at once.  Small values make small
- * test shapes run several rounds and a split last round. */
+ * test shapes run several rounds and a split last round.  A negative value -n uses n pairs with the fixed assignment
+ * (pair p takes units p, p + n, ...) instead of drawing units from the global counter. */
 int odl_debug_set_persistent_pairs(int pairs);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
  * kernel for small layers. */

@@ -348,6 +348,8 @@ int odl_device_status(void *stream)
             set_last_error("gather_rows: sample index out of range");
             return kInvalidArgument;
         }
+        gemm_pair_recover(s);  // a persistent GEMM that gave up may have left its unit counters mid-launch
+        ODL_CUDA_TRY(cudaStreamSynchronize(s));
         set_last_error("a kernel gave up on a bounded wait (pipeline barrier never completed)");
         return kKernelTimeout;
     }

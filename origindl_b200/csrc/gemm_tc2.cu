@@ -358,8 +358,14 @@ gemm_tc2_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, const i
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Persistent 3xTF32 variant: as many CTA pairs as the GPU holds at once (74 on 148 SMs), each walking a static list of
-// work units (pair p takes units p, p + P, p + 2P, ...).  What it buys over one tile per pair:
+// Persistent 3xTF32 variant: as many CTA pairs as the GPU holds at once (74 on 148 SMs), each taking work units (tiles)
+// off one list until it is empty.  Units are handed out in order by a counter in global memory: the leader's producer
+// thread draws the next index and publishes it to every role of both CTAs through a two-slot mailbox (shared-memory
+// slots + mbarriers, the peer's copy written through the cluster window).  Drawing instead of a fixed p, p + P, p + 2P
+// assignment matters when the pairs do not all run at once -- another kernel (an NCCL all-reduce overlapping the
+// backward pass) holds some SMs: pairs that start late then simply find fewer units left, instead of the whole GEMM
+// waiting for a late pair to work through a fixed share.  Which pair computes a unit has no influence on its bits.
+// What the kernel buys over one tile per pair:
 //   * the epilogue of a tile (registers -> shared-memory slab -> global, with bias / ReLU / mask / column sums) runs
 //     while the producer and the MMA thread are already on the next tile: the stage ring and the two TMEM accumulator
 //     buffers simply keep rotating across tiles, so the MMA thread is ahead by two drains (128 of K) before it has to
@@ -381,6 +387,8 @@ struct PersistPlan
     int chunk_kb;     // K-blocks accumulated in TMEM between two drains
     float *partial;   // [split_tiles][2 ranks][2 halves][128 x 256] parked partial tiles
     unsigned *tickets;  // [split_tiles][2 ranks], zero between launches (the second arriver resets its ticket)
+    unsigned *counters;  // [0] next unit to hand out, [1] pairs that found the list empty; both zero between launches
+                         // (the last pair to finish resets them); nullptr = fixed assignment p, p + P, ... (test hook)
 };
 
 constexpr int kPStages   = 3;
@@ -412,6 +420,9 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
     volatile int *abort_f = reinterpret_cast<volatile int *>(tmem_slot + 1);
     int *early_out        = const_cast<int *>(abort_f) + 1;
     int *ticket_box       = early_out + 1;
+    int *mail_slot        = ticket_box + 1;                                  // [2] unit index, -1 = list empty
+    uint64_t *mail_full   = reinterpret_cast<uint64_t *>(aux_base + 128);    // [2] per CTA: slot published
+    uint64_t *mail_empty  = mail_full + 2;                                   // [2] leader's: all 18 readers have read
 
     const int warp      = threadIdx.x >> 5;
     const int lane      = threadIdx.x & 31;
@@ -420,6 +431,7 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
     const int pair      = blockIdx.x >> 1;
     const int n_pairs   = gridDim.x >> 1;
     const int n_units   = plan.full_units + 2 * plan.split_tiles;
+    const bool drawn    = plan.counters != nullptr;
 
     if (threadIdx.x == 0)
     {
@@ -447,6 +459,8 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             {
                 ptx::mbar_init(&acc_full[b], 1);
                 ptx::mbar_init(&acc_empty[b], 2 * kEpiWarps);
+                ptx::mbar_init(&mail_full[b], 1);
+                ptx::mbar_init(&mail_empty[b], 2 * (kEpiWarps + 1));  // per CTA: eight epilogue warps + MMA thread / producer
             }
             ptx::fence_mbar_init();
         }
@@ -461,6 +475,48 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
     ptx::cluster_sync();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = skip ? 0u : *tmem_slot;
+
+    // ---- which unit is this pair's i-th?  Fixed assignment: pair + i * n_pairs.  Drawn: the leader's producer thread
+    //      takes the next index off the global counter and puts it into mailbox slot i & 1 of BOTH CTAs (its peer's through
+    //      the cluster window, released by the arrive that follows); every other role -- the peer's producer, the MMA
+    //      thread, the sixteen epilogue warps -- waits for the slot, reads it and tells the leader it has (mail_empty).
+    //      -1 ends the walk.  All waits are bounded like every other wait of the kernel.
+    auto draw_and_publish = [&](uint32_t i) -> int {  // leader producer thread only
+        if (!drawn)
+        {
+            const int u = pair + static_cast<int>(i) * n_pairs;
+            return u < n_units ? u : -1;
+        }
+        const int slot = i & 1;
+        if (!ptx::mbar_wait(&mail_empty[slot], ((i >> 1) & 1) ^ 1, abort_f))
+            return -2;
+        const unsigned got = atomicAdd(plan.counters, 1u);
+        const int u        = got < static_cast<unsigned>(n_units) ? static_cast<int>(got) : -1;
+        if (u < 0 && atomicAdd(plan.counters + 1, 1u) == static_cast<unsigned>(n_pairs - 1))
+        {
+            // every pair has now drawn past the end: nobody draws again in this launch; leave both counters at zero
+            plan.counters[0] = 0;
+            plan.counters[1] = 0;
+        }
+        mail_slot[slot] = u;
+        ptx::st_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(&mail_slot[slot]), 1), static_cast<uint32_t>(u));
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&mail_full[slot]), 0));
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&mail_full[slot]), 1));
+        return u;
+    };
+    auto read_mail = [&](uint32_t i) -> int {  // one thread of every other role (a whole warp may call it: lane 0 acts)
+        if (!drawn)
+        {
+            const int u = pair + static_cast<int>(i) * n_pairs;
+            return u < n_units ? u : -1;
+        }
+        const int slot = i & 1;
+        if (!ptx::mbar_wait_cluster(&mail_full[slot], (i >> 1) & 1, abort_f))
+            return -2;
+        const int u = *reinterpret_cast<volatile int *>(&mail_slot[slot]);
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&mail_empty[slot]), 0));
+        return u;
+    };
 
     // unit -> tile, K range; every role walks the same list
     auto unit_tile = [&](int u, int &tile, int &kb0, int &kb1, int &half) {
@@ -498,8 +554,11 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         {
             uint32_t gk = 0;  // K-blocks issued so far: the ring position carries over from tile to tile
             bool ok     = true;
-            for (int u = pair; u < n_units && ok; u += n_pairs)
+            for (uint32_t i = 0; ok; ++i)
             {
+                const int u = leader ? draw_and_publish(i) : read_mail(i);
+                if (u < 0)
+                    break;
                 int tile, kb0, kb1, half, tile_m, tile_n;
                 unit_tile(u, tile, kb0, kb1, half);
                 tile_origin(tile, tile_m, tile_n);
@@ -573,8 +632,11 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
             uint32_t gk = 0, gc = 0;  // K-blocks consumed and accumulator chunks started so far, over all tiles
             bool ok     = true;
-            for (int u = pair; u < n_units && ok; u += n_pairs)
+            for (uint32_t i = 0; ok; ++i)
             {
+                const int u = read_mail(i);
+                if (u < 0)
+                    break;
                 int tile, kb0, kb1, half;
                 unit_tile(u, tile, kb0, kb1, half);
                 for (int kb = kb0; kb < kb1 && ok; ++gc)
@@ -635,8 +697,14 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         float acc[Cfg::warp_cols];
         uint32_t gc = 0;
         bool have   = true;
-        for (int u = pair; u < n_units && have; u += n_pairs)
+        for (uint32_t i = 0; have; ++i)
         {
+            int u = 0;
+            if (lane == 0)
+                u = read_mail(i);
+            u = __shfl_sync(0xffffffffu, u, 0);
+            if (u < 0)
+                break;
             int tile, kb0, kb1, half, tile_m, tile_n;
             unit_tile(u, tile, kb0, kb1, half);
             tile_origin(tile, tile_m, tile_n);
@@ -979,6 +1047,28 @@ size_t g_part_floats    = 0;
 unsigned *g_tickets     = nullptr;
 size_t g_ticket_count   = 0;
 
+// Unit counters of the persistent kernel: a ring of (next unit, finished pairs) slots, one slot per launch in turn, so
+// that launches in flight on different streams never share one.  A launch leaves its slot at zero.
+constexpr int kCounterSlots = 32;
+unsigned *g_counters        = nullptr;
+unsigned g_counter_seq      = 0;
+
+int unit_counters(unsigned **out)
+{
+    if (!g_counters)
+    {
+        if (cudaMalloc(&g_counters, kCounterSlots * 2 * sizeof(unsigned)) != cudaSuccess ||
+            cudaMemset(g_counters, 0, kCounterSlots * 2 * sizeof(unsigned)) != cudaSuccess)
+        {
+            g_counters = nullptr;
+            set_last_error("gemm: cannot allocate the unit counters of the persistent kernel");
+            return kCudaError;
+        }
+    }
+    *out = g_counters + 2 * (g_counter_seq++ % kCounterSlots);
+    return kOk;
+}
+
 int tail_split_scratch(size_t floats, size_t tickets)
 {
     if (floats <= g_part_floats && tickets <= g_ticket_count)
@@ -1043,6 +1133,17 @@ int resident_pairs()
 //           shared-memory bandwidth: 240 KB per K-block against 160 KB per CTA of a pair);
 //   TF32 with two K-slabs per stage: K-major x K-major 533 -> 652, MN-major B 443 -> 583, both MN-major 399 -> 506
 //           (with one slab per stage the pair kernel was the slower one for K-major operands: 473).
+// After a kernel gave up on a bounded wait the persistent kernel may have left its unit counters and tickets in the
+// middle of a launch: put them back to zero (called by odl_device_status when it reports the time-out).
+int gemm_pair_recover(cudaStream_t stream)
+{
+    if (g_counters && cudaMemsetAsync(g_counters, 0, kCounterSlots * 2 * sizeof(unsigned), stream) != cudaSuccess)
+        return kCudaError;
+    if (g_tickets && cudaMemsetAsync(g_tickets, 0, g_ticket_count * sizeof(unsigned), stream) != cudaSuccess)
+        return kCudaError;
+    return kOk;
+}
+
 bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms)
 {
     (void)a_mn, (void)b_mn, (void)terms;
@@ -1137,8 +1238,9 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM), tiles_n = (p.N + BN - 1) / BN;
         const int T       = tiles_m * tiles_n;
         int P             = resident_pairs();
-        if (g_persist_pairs > 0 && P > 0)
-            P = g_persist_pairs < P ? g_persist_pairs : P;
+        const int want_p  = g_persist_pairs < 0 ? -g_persist_pairs : g_persist_pairs;
+        if (want_p > 0 && P > 0)
+            P = want_p < P ? want_p : P;
         if (P > 0 && (T > P || g_pair_mode == 7))
         {
             PersistPlan plan;
@@ -1148,6 +1250,9 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
             if (plan.chunk_kb > plan.num_kb)
                 plan.chunk_kb = plan.num_kb;
             plan.full_units = T, plan.split_tiles = 0, plan.kb_mid = 0, plan.partial = nullptr, plan.tickets = nullptr;
+            plan.counters = nullptr;
+            if (g_persist_pairs >= 0 && (rc = unit_counters(&plan.counters)))  // (a negative test-hook value: fixed assignment)
+                return rc;
             const int R = T % P;
             if (R > 0 && 2 * R <= P && plan.num_kb >= 4 * plan.chunk_kb)
             {

@@ -142,6 +142,47 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// The same bounded wait with acquire semantics at CLUSTER scope: for a barrier whose arrival publishes data that the
+// other CTA of the pair wrote into this CTA's shared memory (st.shared::cluster before a release.cluster arrive).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
+{
+    if (mbar_try_wait_cluster(bar, parity))
+        return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins    = 0;
+    while (true)
+    {
+        if (mbar_try_wait_cluster(bar, parity))
+            return true;
+        if ((++spins & 0xff) == 0)
+        {
+            if (abort_flag && *abort_flag)
+                return false;
+            if (globaltimer_ns() - t0 > ODL_WAIT_NS)
+            {
+                if (abort_flag)
+                    *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem()
 {
@@ -298,6 +339,11 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
     uint32_t v;
     asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
     return v;
+}
+
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v)

@@ -212,11 +212,12 @@ def test_gemm_cta_pair_kernel(ops, M, N, K, ta, tb, precision):
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K,pairs", [(129, 256, 32, 0), (300, 520, 100, 4), (1024, 1024, 1024, 3), (1024, 1024, 1024, 7),
-                                         (1024, 1024, 1024, 16), (2048, 768, 515, 5), (2048, 768, 515, 11), (1500, 1300, 700, 9)])
+                                         (1024, 1024, 1024, 16), (2048, 768, 515, 5), (2048, 768, 515, 11), (1500, 1300, 700, 9),
+                                         (1024, 1024, 1024, -7), (2048, 768, 515, -5)])
 def test_gemm_persistent_pair_kernel(ops, M, N, K, pairs, ta, tb):
     """The persistent 3xTF32 pair kernel, forced on small shapes with a small number of CTA pairs so that every pair
-    walks several tiles (epilogue of tile i overlapping the main loop of tile i + 1, stage ring and accumulator buffers
-    carried across tiles) and, where the last round is short, its tiles are split along K between two pairs (partial
+    walks several tiles (drawn from the global unit counter, or -- negative `pairs` -- by the fixed assignment; epilogue of
+    tile i overlapping the main loop of tile i + 1, stage ring and accumulator buffers carried across tiles) and, where the last round is short, its tiles are split along K between two pairs (partial
     tiles parked in scratch, the second arriver combines).  Ragged row / column / K tails, all four operand layouts,
     the full epilogue -- once with column sums (transpose-slab stores) and once without (rows written straight from
     registers with 256-bit stores where D's rows are 32-byte aligned).  Checked against float64; where no tile is split
@@ -236,7 +237,7 @@ def test_gemm_persistent_pair_kernel(ops, M, N, K, pairs, ta, tb):
     tol = TOL[0] * np.abs(pre).max()
     safe = np.abs(pre) > tol
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    p_eff = pairs if pairs else 74
+    p_eff = abs(pairs) if pairs else 74
     r = tiles % p_eff
     split = r > 0 and 2 * r <= p_eff and (K + 31) // 32 >= 8
     for with_colsum in (True, False):
