@@ -34,7 +34,7 @@ int odl_debug_set_pair_mode(int mode);
  * (pair p takes units p, p + n, ...) instead of drawing units from the global counter. */
 int odl_debug_set_persistent_pairs(int pairs);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
- * kernel for small layers. */
+ * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers. */
 int odl_debug_set_conv_mode(int mode);
 
 /* Number of NVTX ranges the training-step entry points have opened in this process: 0 unless the environment variable

@@ -6,9 +6,10 @@
 // explicit path writes col and its 3xTF32 low part to HBM (2 x 177 MB for the first conv layer of the reference's CNN),
 // reads them back in a split-K GEMM whose 16 x 108 output uses a fraction of one tensor-core tile, and needs gy
 // re-laid out as rows.  Here a block stages PIX pixels of gy and of col in shared memory (col gathered from x through a
-// per-block table k -> offset, like the implicit-GEMM forward) and every thread keeps a 4 x KT register tile of
-// (oc, k) sums in plain fp32 FMAs; blocks walk the pixels grid-stride, store their partial gw into their own slice of
-// a scratch buffer, and a second pass adds the slices in a fixed order (same bits every run).  The work is N*OH*OW * OC * C*KH*KW FMAs (0.7 G for that layer) on the CUDA cores.
+// per-block table k -> offset, like the implicit-GEMM forward) and every thread keeps an 8 x 8 register tile of
+// (oc, k) sums in plain fp32 FMAs (see the kernel for how the threads share the pixels); blocks walk the pixels
+// grid-stride, store their partial gw into their own slice of a scratch buffer, and a second pass adds the slices in a
+// fixed order (same bits every run).  The work is N*OH*OW * OC * C*KH*KW FMAs (0.7 G for that layer) on the CUDA cores.
 //
 // gy_layout 0: gy_rows is the permuted NCHW gradient (the true gradient); 1: the NCHW buffer reinterpreted as
 // [N*OH*OW, OC] as the reference does.  Summation order differs from the reference's single accumulator (as it does in
@@ -32,21 +33,25 @@ struct DwGeom
     int ckk, rows;
 };
 
-constexpr int kOcPad = 32;  // gy staging pitch: 4 oc per thread x 8 thread rows
-
-// KT: k values per thread (the block covers 32 * KT columns of col); PIX pixels staged per iteration.
-template <int KT, int PIX>
-__global__ void __launch_bounds__(256) conv_dw_direct_kernel(const float *__restrict__ x, const float *__restrict__ gy,
+// OCP: output channels of the tile (16 or 32, OC padded up); KP: k columns of the tile (32 .. 256, C*KH*KW padded up);
+// PIX: pixels staged per iteration.  A thread owns an 8 (oc) x 8 (k) register tile, so the (OCP / 8) x (KP / 8) threads of
+// one GROUP cover the whole gw tile; the 256 / that many groups of the block each take every G-th staged pixel, and add
+// their tiles in group order at the end.  Per pixel a thread reads 8 gy values and 8 column values (four 128-bit
+// shared-memory reads) for 64 multiply-adds: the kernel is bound by FMA issue, not by shared memory.
+template <int OCP, int KP, int PIX>
+__global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kernel(const float *__restrict__ x, const float *__restrict__ gy,
                                                              float *__restrict__ slices, const DwGeom g, const int layout)
 {
-    constexpr int KP  = 32 * KT;
-    constexpr int KPP = KP + 1;      // odd pitches: the staging threads write down a column without bank conflicts
-    constexpr int OCP = kOcPad + 1;
-    extern __shared__ float smem[];
-    float *col_s = smem;                       // [PIX][KPP]
-    float *gy_s  = col_s + PIX * KPP;          // [PIX][OCP]
-    int2 *ktab   = reinterpret_cast<int2 *>(smem + ((PIX * (KPP + OCP) + 1) & ~1));  // [KP] {offset, kh << 16 | kw}; y = -1 past ckk
-    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    constexpr int TG   = (OCP / 8) * (KP / 8);  // threads of a group
+    constexpr int G    = 256 / TG;              // groups = pixels in flight per accumulate step
+    constexpr int KPP  = KP + 4;                // pitches keep 16-byte alignment; + 4 floats: the 128-bit staging stores
+    constexpr int OCPP = OCP + 4;               // of 8 consecutive pixels fall into distinct 16-byte bank groups
+    static_assert(TG <= 256 && 256 % TG == 0 && PIX % G == 0 && 256 % PIX == 0, "tile / block shape");
+    extern __shared__ float4 smem4[];
+    float *col_s = reinterpret_cast<float *>(smem4);                  // [PIX][KPP]
+    float *gy_s  = col_s + PIX * KPP;                                 // [PIX][OCPP]
+    int2 *ktab   = reinterpret_cast<int2 *>(gy_s + PIX * OCPP);       // [KP] {offset, kh << 16 | kw}; y = -1 past ckk
+    const int tid = threadIdx.x;
     for (int k = tid; k < KP; k += 256)
     {
         int2 e = make_int2(0, -1);
@@ -58,96 +63,164 @@ __global__ void __launch_bounds__(256) conv_dw_direct_kernel(const float *__rest
         }
         ktab[k] = e;
     }
-    float acc[4][KT];
+    const int grp = tid / TG, lt = tid % TG;
+    const int ocg = lt / (KP / 8), kg = lt % (KP / 8);
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < KT; ++j)
+        for (int j = 0; j < 8; ++j)
             acc[i][j] = 0.f;
     const int ohw = g.OH * g.OW;
-    __syncthreads();
-    for (int r0 = blockIdx.x * PIX; r0 < g.rows; r0 += gridDim.x * PIX)
-    {
-        // ---- stage: thread (p = tid % PIX, lane group q = tid / PIX) gathers columns q, q + 256/PIX, ... of pixel p
+    // ---- staging, one iteration ahead through registers: thread (p = tid % PIX, q = tid / PIX) gathers the 4-column chunks
+    //      q, q + Q, ... of pixel p (consecutive threads = consecutive pixels: every global load of a tap is coalesced, stride
+    //      S).  All loads of the NEXT PIX pixels are issued before the multiply-adds of the current ones, so their latency
+    //      hides behind the arithmetic instead of standing between two barriers.
+    constexpr int Q   = 256 / PIX;
+    constexpr int CH  = (KP / 4) / Q;   // column chunks per thread
+    constexpr int GCH = (OCP / 4 + Q - 1) / Q;  // gy chunks per thread
+    static_assert((KP / 4) % Q == 0, "column chunks divide evenly over the staging threads");
+    const int sp = tid % PIX, sq = tid / PIX;
+    float vcol[CH][4], vgy[GCH][4];
+    auto gather = [&](int r0) {
+        const int r   = r0 + sp;
+        const bool ok = r < g.rows;
+        int n = 0, oh = 0, ow = 0;
+        if (ok)
         {
-            constexpr int GROUPS = 256 / PIX;
-            const int p = tid % PIX, q = tid / PIX;
-            const int r = r0 + p;
-            const bool ok = r < g.rows;
-            int n = 0, oh = 0, ow = 0;
-            if (ok)
+            ow          = r % g.OW;
+            const int t = r / g.OW;
+            oh          = t % g.OH;
+            n           = t / g.OH;
+        }
+        const int h0 = oh * g.S - g.P, w0 = ow * g.S - g.P;
+        const int pix_off = (n * g.C * g.H + h0) * g.W + w0;
+        const bool inside = ok && h0 >= 0 && h0 + g.KH <= g.H && w0 >= 0 && w0 + g.KW <= g.W;
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+        {
+            const int ch = sq + c * Q;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
             {
-                ow          = r % g.OW;
-                const int t = r / g.OW;
-                oh          = t % g.OH;
-                n           = t / g.OH;
-            }
-            const int h0 = oh * g.S - g.P, w0 = ow * g.S - g.P;
-            const int pix_off = (n * g.C * g.H + h0) * g.W + w0;
-            for (int k = q; k < KP; k += GROUPS)
-            {
-                const int2 e  = ktab[k];
-                const int hh  = h0 + (e.y >> 16), ww = w0 + (e.y & 0xffff);
-                const bool in = ok && e.y >= 0 && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W;
-                col_s[p * KPP + k] = in ? __ldg(x + pix_off + e.x) : 0.f;
-            }
-            for (int oc = q; oc < kOcPad; oc += GROUPS)
-            {
-                float v = 0.f;
-                if (ok && oc < g.OC)
-                    v = layout == 0 ? __ldg(gy + (static_cast<int64_t>(n) * g.OC + oc) * ohw + (r - n * ohw))
-                                    : __ldg(gy + static_cast<int64_t>(r) * g.OC + oc);
-                gy_s[p * OCP + oc] = v;
+                const int2 e = ktab[4 * ch + j];
+                bool in      = inside && e.y >= 0;
+                if (!inside && ok && e.y >= 0)
+                {
+                    const int hh = h0 + (e.y >> 16), ww = w0 + (e.y & 0xffff);
+                    in           = hh >= 0 && hh < g.H && ww >= 0 && ww < g.W;
+                }
+                vcol[c][j] = in ? __ldg(x + pix_off + e.x) : 0.f;
             }
         }
-        __syncthreads();
-        // ---- accumulate: thread (ty, tx) owns oc = ty + 8 i and k = tx + 32 j
-#pragma unroll 4
-        for (int p = 0; p < PIX; ++p)
+#pragma unroll
+        for (int c = 0; c < GCH; ++c)
         {
-            float gv[4], cv[KT];
+            const int ch = sq + c * Q;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                gv[i] = gy_s[p * OCP + ty + 8 * i];
+            for (int j = 0; j < 4; ++j)
+            {
+                const int oc = 4 * ch + j;
+                vgy[c][j]    = 0.f;
+                if (ok && ch < OCP / 4 && oc < g.OC)
+                    vgy[c][j] = layout == 0 ? __ldg(gy + (static_cast<int64_t>(n) * g.OC + oc) * ohw + (r - n * ohw))
+                                            : __ldg(gy + static_cast<int64_t>(r) * g.OC + oc);
+            }
+        }
+    };
+    __syncthreads();  // ktab is complete
+    const int step = gridDim.x * PIX;
+    int r0         = blockIdx.x * PIX;
+    if (r0 < g.rows)
+        gather(r0);
+    for (; r0 < g.rows; r0 += step)
+    {
 #pragma unroll
-            for (int j = 0; j < KT; ++j)
-                cv[j] = col_s[p * KPP + tx + 32 * j];
+        for (int c = 0; c < CH; ++c)
+            *reinterpret_cast<float4 *>(col_s + sp * KPP + 4 * (sq + c * Q)) =
+                make_float4(vcol[c][0], vcol[c][1], vcol[c][2], vcol[c][3]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+        for (int c = 0; c < GCH; ++c)
+            if (sq + c * Q < OCP / 4)
+                *reinterpret_cast<float4 *>(gy_s + sp * OCPP + 4 * (sq + c * Q)) =
+                    make_float4(vgy[c][0], vgy[c][1], vgy[c][2], vgy[c][3]);
+        __syncthreads();
+        if (r0 + step < g.rows)
+            gather(r0 + step);  // in flight during the multiply-adds below
+        // ---- accumulate: this group's pixels grp, grp + G, ...
+#pragma unroll 2
+        for (int p = grp; p < PIX; p += G)
+        {
+            const float4 g0 = *reinterpret_cast<const float4 *>(gy_s + p * OCPP + 8 * ocg);
+            const float4 g1 = *reinterpret_cast<const float4 *>(gy_s + p * OCPP + 8 * ocg + 4);
+            const float4 c0 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg);
+            const float4 c1 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg + 4);
+            const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                for (int j = 0; j < KT; ++j)
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
                     acc[i][j] = fmaf(gv[i], cv[j], acc[i][j]);
         }
         __syncthreads();
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < KT; ++j)
+    // ---- the groups add their tiles in group order (a fixed order: same bits every run) into a tile in shared memory
+    float *red = col_s;  // [OCP][KP]; the staging area is dead (OCP * KP <= PIX * KPP is checked by the launcher's choice of PIX)
+    for (int gi = 0; gi < G; ++gi)
+    {
+        if (grp == gi)
         {
-            const int oc = ty + 8 * i, k = tx + 32 * j;
-            if (oc < g.OC && k < g.ckk)
-                slices[(static_cast<int64_t>(blockIdx.x) * g.OC + oc) * g.ckk + k] = acc[i][j];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    float *dst = red + (8 * ocg + i) * KP + 8 * kg + j;
+                    *dst       = gi == 0 ? acc[i][j] : *dst + acc[i][j];
+                }
         }
+        __syncthreads();
+    }
+    for (int o = tid; o < OCP * KP; o += 256)
+    {
+        const int oc = o / KP, k = o - oc * KP;
+        if (oc < g.OC && k < g.ckk)
+            slices[(static_cast<int64_t>(blockIdx.x) * g.OC + oc) * g.ckk + k] = red[o];
+    }
 }
 
-template <int KT, int PIX>
+template <int OCP, int KP, int PIX>
 int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int layout, cudaStream_t stream)
 {
-    constexpr int KP   = 32 * KT;
-    const size_t smem  = sizeof(float) * (PIX * (KP + 1 + kOcPad + 1) + 2) + sizeof(int2) * KP;
+    static_assert(OCP * KP <= PIX * (KP + 4), "the reduction tile reuses the column staging area");
+    const size_t smem  = sizeof(float) * (PIX * (KP + 4) + PIX * (OCP + 4)) + sizeof(int2) * KP;
     const int chunks   = (g.rows + PIX - 1) / PIX;
-    const int blocks   = chunks < 148 * 4 ? chunks : 148 * 4;
+    // one resident wave of blocks walking the pixels grid-stride: as many blocks as the GPU holds at once
+    static int resident = 0;
+    if (resident == 0)
+    {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(conv_dw_direct_kernel<OCP, KP, PIX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int per_sm = 0, dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_dw_direct_kernel<OCP, KP, PIX>, 256, smem) != cudaSuccess ||
+            per_sm < 1)
+            per_sm = 1;
+        resident = sms * per_sm;
+    }
+    const int blocks   = chunks < resident ? chunks : resident;
     const int64_t out  = static_cast<int64_t>(g.OC) * g.ckk;
     float *slices      = colsum_partial_scratch(blocks, out);
     if (!slices)
         return kCudaError;
-    conv_dw_direct_kernel<KT, PIX><<<blocks, 256, smem, stream>>>(x, gy, slices, g, layout);
+    conv_dw_direct_kernel<OCP, KP, PIX><<<blocks, 256, smem, stream>>>(x, gy, slices, g, layout);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
     {
-        set_last_error("conv_dw_direct_kernel<%d,%d> launch failed: %s", KT, PIX, cudaGetErrorString(e));
+        set_last_error("conv_dw_direct_kernel<%d,%d,%d> launch failed: %s", OCP, KP, PIX, cudaGetErrorString(e));
         return kCudaError;
     }
     return colsum_finish_launch(slices, blocks, out, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
@@ -171,13 +244,23 @@ int conv_dw_direct_launch(const float *x, const float *gy, float *gw, int64_t N,
     g.ckk  = (int)(C * KH * KW);
     g.rows = (int)(N * OH * OW);
     ODL_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * OC * g.ckk, stream));
+    if (OC <= 16)
+    {
+        if (g.ckk <= 32)
+            return launch_dw<16, 32, 64>(x, gy, gw, g, layout, stream);
+        if (g.ckk <= 64)
+            return launch_dw<16, 64, 64>(x, gy, gw, g, layout, stream);
+        if (g.ckk <= 128)
+            return launch_dw<16, 128, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<16, 256, 64>(x, gy, gw, g, layout, stream);
+    }
     if (g.ckk <= 32)
-        return launch_dw<1, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 32, 64>(x, gy, gw, g, layout, stream);
     if (g.ckk <= 64)
-        return launch_dw<2, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 64, 64>(x, gy, gw, g, layout, stream);
     if (g.ckk <= 128)
-        return launch_dw<4, 64>(x, gy, gw, g, layout, stream);
-    return launch_dw<8, 32>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 128, 64>(x, gy, gw, g, layout, stream);
+    return launch_dw<32, 256, 64>(x, gy, gw, g, layout, stream);
 }
 
 }  // namespace odl

@@ -420,7 +420,8 @@ int launch_igemm(const TmapPack &tm, const float *x, const IgemmGeom &g, const G
 }  // namespace
 
 // Test hook: 0 = implicit GEMM / direct kernels where they apply, 1 = always the explicit im2col + GEMM paths,
-// 2 = like 0 but without the direct weight-gradient kernel (small layers then take the implicit-GEMM one).
+// 2 = like 0 but without the direct weight-gradient kernel (small layers then take the implicit-GEMM one),
+// 3 = like 0 but without the direct forward kernel (small layers then take the implicit-GEMM forward).
 int g_conv_mode = 0;
 
 bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW)

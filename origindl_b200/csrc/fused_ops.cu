@@ -176,6 +176,8 @@ int conv2d_forward(const float *x, const float *w, const float *b, float *y, int
     const int terms     = precision == ODL_PRECISION_3XTF32 ? 3 : 1;
     const int64_t rows  = N * OH * OW;
     const int64_t ckk   = C * KH * KW;
+    if (conv_fwd_direct_eligible(N, C, H, W, OC, KH, KW, OH, OW))
+        return conv_fwd_direct_launch(x, w, b, scale, y, N, C, H, W, OC, KH, KW, S, P, OH, OW, act, stream);
     if (conv_igemm_eligible(N, C, H, W, OC, KH, KW, OH, OW))
     {
         // implicit GEMM: no column matrix; only the (small) weight matrix is prepared -- padded to a pitch of 4 floats

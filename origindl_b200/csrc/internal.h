@@ -85,6 +85,11 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
 int conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H, int64_t W,
                    int64_t OC, int KH, int KW, int S, int P, int act, int precision, cudaStream_t stream,
                    const float *scale = nullptr);
+// Forward conv2d of small layers (OC <= 32, C*KH*KW <= 256) on the CUDA cores: see conv_fwd_direct.cu.
+bool conv_fwd_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
+int conv_fwd_direct_launch(const float *x, const float *w, const float *bias, const float *scale, float *y, int64_t N,
+                           int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int OH, int OW, int act,
+                           cudaStream_t stream);
 bool conv_igemm_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
 int conv_igemm_launch(const float *x, const float *w_big, const float *w_small, int64_t ldw, const float *bias,
                       const float *scale, float *y, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW,

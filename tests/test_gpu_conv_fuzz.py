@@ -1,6 +1,7 @@
 """GPU: seeded random sweep of conv2d forward / backward geometries (channels 1..300, kernels 1..7, strides 1..3, paddings,
-ragged image sizes) against float64 autograd of the same convolution.  The library picks among the implicit-GEMM forward
-(one CTA or a K-splitting cluster), im2col + GEMM, direct and implicit-GEMM gradient kernels from the geometry alone;
+ragged image sizes) against float64 autograd of the same convolution.  The library picks among the direct fp32 forward
+(small layers), the implicit-GEMM forward (one CTA or a K-splitting cluster), im2col + GEMM, direct and implicit-GEMM
+gradient kernels from the geometry alone;
 this sweep walks through those choices.  True-gradient layout; 3xTF32 tolerance 1e-5 (max|a-b| / max|ref|)."""
 import numpy as np
 import pytest
@@ -36,11 +37,16 @@ def test_random_conv_geometries(seed):
         b = torch.randn(OC, device="cuda", generator=g)
         gy = torch.randn(N, OC, OH, OW, device="cuda", generator=g)
         y = ops.conv2d_forward(x, w, b, s, p)
+        capi.lib().odl_debug_set_conv_mode(3)          # small layers on the implicit-GEMM forward instead of the direct kernel
+        try:
+            y_tc = ops.conv2d_forward(x, w, b, s, p)
+        finally:
+            capi.lib().odl_debug_set_conv_mode(0)
         gx, gw, gb = ops.conv2d_backward(gy, x, w, s, p, gy_layout=0)
         capi.device_status()
         x64, w64, b64 = x.double().requires_grad_(), w.double().requires_grad_(), b.double().requires_grad_()
         y64 = torch.nn.functional.conv2d(x64, w64, b64, stride=s, padding=p)
         y64.backward(gy.double())
         case = (seed, done, N, C, H, W, OC, k, s, p)
-        for got, want in ((y, y64.detach()), (gx, x64.grad), (gw, w64.grad), (gb, b64.grad)):
+        for got, want in ((y, y64.detach()), (y_tc, y64.detach()), (gx, x64.grad), (gw, w64.grad), (gb, b64.grad)):
             assert ((got.double() - want).abs().max() / want.abs().max().clamp_min(1e-30)).item() <= 1e-5, case

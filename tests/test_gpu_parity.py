@@ -507,8 +507,10 @@ IGEMM_CASES = CONV_CASES + [(3, 3, 33, 29, 16, 6, 2, 2),      # ragged pixel cou
 @pytest.mark.parametrize("N,C,H,W,OC,k,s,p", IGEMM_CASES)
 @pytest.mark.parametrize("precision", ["3xtf32", "tf32"])
 def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k, s, p, precision):
-    """The forward pass has two implementations -- implicit GEMM (tiles of the column matrix gathered in shared memory) and
-    im2col + GEMM; both against the oracle, with and without bias, with the fused activations."""
+    """The forward pass has three implementations -- a direct fp32 kernel for small layers (OC <= 32, C*KH*KW <= 256: mode 0
+    takes it where it applies), implicit GEMM (tiles of the column matrix gathered in shared memory; mode 3 sends the small
+    layers there too) and im2col + GEMM (mode 1); all against the oracle, with and without bias, with the fused
+    activations.  The direct kernel computes in plain fp32 whatever the precision argument says."""
     from origindl_b200 import capi
 
     prec, tol = (capi.PRECISION_3XTF32, 1e-5) if precision == "3xtf32" else (capi.PRECISION_TF32, 5e-3)
@@ -522,7 +524,7 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
     orc.oracle_conv2d_forward(x, w, None, y_nb, N, C, H, W, OC, k, k, s, p)
     xd, wd, bd = dev(x), dev(w), dev(b)
     try:
-        for mode in (0, 1):
+        for mode in (0, 3, 1):
             capi.lib().odl_debug_set_conv_mode(mode)
             assert max_rel_err(host(ops.conv2d_forward(xd, wd, bd, s, p, precision=prec)), y_o) <= tol
             assert max_rel_err(host(ops.conv2d_forward(xd, wd, None, s, p, precision=prec)), y_nb) <= tol
