@@ -4,7 +4,9 @@
 // memory.  Per SM this halves the B bytes the TMA unit has to land per MMA cycle -- the measured limiter of the 1-CTA
 // kernel -- and leaves room for a third 3xTF32 stage (64 KB per stage and CTA instead of 96 KB).
 //
-// Protocol inside a pair (cluster of 2; rank 0 = leader), all with plain mbarriers, no multicast of any kind:
+// Protocol inside a pair (cluster of 2; rank 0 = leader), all with plain mbarriers.  No load is multicast: every CTA
+// issues its own tiled copies into its own shared memory.  The one cluster-wide instruction is the leader's
+// tcgen05.commit with a CTA mask, which signals a barrier in both CTAs and moves no data.
 //   full[s]      lives in the leader; the leader's producer arms it with the bytes of BOTH CTAs, both producers' TMA
 //                loads report to it (the peer through the barrier's shared::cluster address);
 //   empty[s]     one per CTA; the leader's MMA thread commits to its own and to the peer's after the MMAs of stage s;
