@@ -33,6 +33,9 @@ int odl_debug_set_pair_mode(int mode);
  * test shapes run several rounds and a split last round.  A negative value -n uses n pairs with the fixed assignment
  * (pair p takes units p, p + n, ...) instead of drawing units from the global counter. */
 int odl_debug_set_persistent_pairs(int pairs);
+/* Stream-K in the persistent kernel (even K ranges per pair instead of whole tiles): 0 = where it pays (at most half
+ * as many tiles as pairs), 1 = always, -1 = never. */
+int odl_debug_set_stream_k(int mode);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
  * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers. */
 int odl_debug_set_conv_mode(int mode);

@@ -602,6 +602,13 @@ extern "C" int odl_debug_set_persistent_pairs(int pairs)
     return 0;
 }
 
+// Test hook: 0 = stream-K in the persistent GEMM where it pays, 1 = always, -1 = never.
+extern "C" int odl_debug_set_stream_k(int mode)
+{
+    odl::g_stream_k = mode;
+    return 0;
+}
+
 // Test hook: device address of the per-device error flag (NULL before odl_init), for test kernels that raise it the way
 // a timed-out GEMM does.
 extern "C" int *odl_debug_error_flag(void)

@@ -387,8 +387,16 @@ struct PersistPlan
     int num_kb;       // K-blocks of 32
     int kb_mid;       // first K-block of a split tile's second half
     int chunk_kb;     // K-blocks accumulated in TMEM between two drains
-    float *partial;   // [split_tiles][2 ranks][2 halves][128 x 256] parked partial tiles
-    unsigned *tickets;  // [split_tiles][2 ranks], zero between launches (the second arriver resets its ticket)
+    // Stream-K mode (streamk != 0; for skinny outputs with at most half as many tiles as pairs): the tiles_m * tiles_n
+    // * chunks_per_tile accumulator chunks of the whole problem are cut into one contiguous range per pair, pair p taking
+    // chunks [p * C / P, (p + 1) * C / P): every pair gets the same amount of tensor work whatever the tile count.  A pair
+    // then works on the tail of one tile, some whole tiles and the head of another; a tile cut by range boundaries is
+    // finished by whichever of its contributors arrives last (tickets), adding the parked parts in part order.
+    int streamk;
+    int chunks_per_tile;  // ceil(num_kb / chunk_kb)
+    int max_parts;        // slots per tile in `partial` (2 in the rounds mode)
+    float *partial;   // [tile slots][max_parts][2 ranks][128 x 256] parked partial tiles
+    unsigned *tickets;  // [tile slots][2 ranks], zero between launches (the last arriver resets its ticket)
     unsigned *counters;  // [0] next unit to hand out, [1] pairs that found the list empty; both zero between launches
                          // (the last pair to finish resets them); nullptr = fixed assignment p, p + P, ... (test hook)
 };
@@ -520,21 +528,74 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         return u;
     };
 
-    // unit -> tile, K range; every role walks the same list
-    auto unit_tile = [&](int u, int &tile, int &kb0, int &kb1, int &half) {
-        if (u < plan.full_units)
-        {
-            tile = u, kb0 = 0, kb1 = plan.num_kb, half = -1;
-        }
-        else
-        {
-            const int v = u - plan.full_units;
-            tile        = plan.full_units + (v >> 1);
-            half        = v & 1;
-            kb0         = half ? plan.kb_mid : 0;
-            kb1         = half ? plan.num_kb : plan.kb_mid;
-        }
+    // ---- a unit of work: a tile and a K-block range of it; `part` >= 0 marks a partial tile (part index in K order,
+    //      n_parts contributors, tile_slot = where its parts are parked)
+    struct Unit
+    {
+        int tile, kb0, kb1, part, n_parts, tile_slot;
     };
+    // rounds mode: unit index -> unit
+    auto unit_of_index = [&](int u) -> Unit {
+        if (u < plan.full_units)
+            return Unit{u, 0, plan.num_kb, -1, 1, 0};
+        const int v = u - plan.full_units, half = v & 1;
+        return Unit{plan.full_units + (v >> 1), half ? plan.kb_mid : 0, half ? plan.num_kb : plan.kb_mid, half, 2, v >> 1};
+    };
+    // stream-K mode: this pair's chunk range and the walk through it
+    const long long sk_total = static_cast<long long>(plan.tiles_m) * plan.tiles_n * plan.chunks_per_tile;
+    auto sk_begin = [&](int pr) -> long long { return sk_total * pr / n_pairs; };
+    auto sk_owner = [&](long long chunk) -> int {  // the pair whose range holds `chunk`
+        int pr = static_cast<int>(chunk * n_pairs / sk_total);
+        while (pr + 1 < n_pairs && sk_begin(pr + 1) <= chunk)
+            ++pr;
+        while (pr > 0 && sk_begin(pr) > chunk)
+            --pr;
+        return pr;
+    };
+    auto sk_unit_at = [&](long long c, long long c_end) -> Unit {  // the unit that starts at chunk c of this pair's range
+        const int nch      = plan.chunks_per_tile;
+        const int tile     = static_cast<int>(c / nch);
+        const int ch_lo    = static_cast<int>(c - static_cast<long long>(tile) * nch);
+        const long long left = c_end - c;
+        const int ch_hi    = left >= nch - ch_lo ? nch : ch_lo + static_cast<int>(left);
+        Unit u{tile, ch_lo * plan.chunk_kb, min(plan.num_kb, ch_hi * plan.chunk_kb), -1, 1, tile};
+        if (ch_lo != 0 || ch_hi != nch)
+        {
+            const long long t0 = static_cast<long long>(tile) * nch;
+            const int first    = sk_owner(t0), last = sk_owner(t0 + nch - 1);
+            u.part             = pair - first;
+            u.n_parts          = last - first + 1;
+        }
+        return u;
+    };
+    // One iterator per role: `i` counts this pair's units (mailbox slots in the drawn mode), `c` walks the stream-K range.
+    struct Walk
+    {
+        uint32_t i  = 0;
+        long long c = 0, c_end = 0;
+    };
+    auto walk_init = [&](Walk &wk) {
+        wk.i = 0;
+        wk.c = sk_begin(pair), wk.c_end = sk_begin(pair + 1);
+    };
+    // next unit of this role; fetch = how the rounds mode obtains the unit index (draw / read the mailbox / compute it).
+    // Returns false when the walk is over (or a wait gave up).
+    auto walk_next = [&](Walk &wk, auto &&fetch, Unit &out) -> bool {
+        if (plan.streamk)
+        {
+            if (wk.c >= wk.c_end)
+                return false;
+            out = sk_unit_at(wk.c, wk.c_end);
+            wk.c += (out.kb1 - out.kb0 + plan.chunk_kb - 1) / plan.chunk_kb;
+            return true;
+        }
+        const int u = fetch(wk.i++);
+        if (u < 0)
+            return false;
+        out = unit_of_index(u);
+        return true;
+    };
+
     auto tile_origin = [&](int tile, int &tile_m, int &tile_n) {
         const int per_group = kGroupM * plan.tiles_n;
         const int g         = tile / per_group;
@@ -556,14 +617,14 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         {
             uint32_t gk = 0;  // K-blocks issued so far: the ring position carries over from tile to tile
             bool ok     = true;
-            for (uint32_t i = 0; ok; ++i)
+            Walk wk;
+            walk_init(wk);
+            Unit un;
+            while (ok && walk_next(wk, [&](uint32_t i) { return leader ? draw_and_publish(i) : read_mail(i); }, un))
             {
-                const int u = leader ? draw_and_publish(i) : read_mail(i);
-                if (u < 0)
-                    break;
-                int tile, kb0, kb1, half, tile_m, tile_n;
-                unit_tile(u, tile, kb0, kb1, half);
-                tile_origin(tile, tile_m, tile_n);
+                int tile_m, tile_n;
+                tile_origin(un.tile, tile_m, tile_n);
+                const int kb0 = un.kb0, kb1 = un.kb1;
                 const int m0  = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
                 const int nb0 = tile_n * BN + static_cast<int>(rank) * (BN / 2);
                 for (int kb = kb0; kb < kb1; ++kb, ++gk)
@@ -634,13 +695,12 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             const uint32_t b_lay  = b_mn ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
             uint32_t gk = 0, gc = 0;  // K-blocks consumed and accumulator chunks started so far, over all tiles
             bool ok     = true;
-            for (uint32_t i = 0; ok; ++i)
+            Walk wk;
+            walk_init(wk);
+            Unit un;
+            while (ok && walk_next(wk, read_mail, un))
             {
-                const int u = read_mail(i);
-                if (u < 0)
-                    break;
-                int tile, kb0, kb1, half;
-                unit_tile(u, tile, kb0, kb1, half);
+                const int kb0 = un.kb0, kb1 = un.kb1;
                 for (int kb = kb0; kb < kb1 && ok; ++gc)
                 {
                     const int buf         = gc & 1;
@@ -699,16 +759,20 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         float acc[Cfg::warp_cols];
         uint32_t gc = 0;
         bool have   = true;
-        for (uint32_t i = 0; have; ++i)
-        {
+        Walk wk;
+        walk_init(wk);
+        Unit un;
+        // (every lane walks: in the drawn mode lane 0 reads the mailbox and the index is broadcast)
+        auto warp_fetch = [&](uint32_t i) -> int {
             int u = 0;
             if (lane == 0)
                 u = read_mail(i);
-            u = __shfl_sync(0xffffffffu, u, 0);
-            if (u < 0)
-                break;
-            int tile, kb0, kb1, half, tile_m, tile_n;
-            unit_tile(u, tile, kb0, kb1, half);
+            return __shfl_sync(0xffffffffu, u, 0);
+        };
+        while (have && walk_next(wk, warp_fetch, un))
+        {
+            int tile_m, tile_n;
+            const int tile = un.tile, kb0 = un.kb0, kb1 = un.kb1;
             tile_origin(tile, tile_m, tile_n);
             const int m0      = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
             const int n0      = tile_n * BN;
@@ -749,39 +813,49 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             if (!have)
                 break;
             bool store = true;
-            if (half >= 0)
+            if (un.part >= 0)
             {
-                // half of a split tile: park the partial tile, take a ticket; the second arriver combines and stores
-                const int st      = tile - plan.full_units;
-                const size_t slot = (static_cast<size_t>(st) * 2 + rank) * 2;
-                float4 *mine      = reinterpret_cast<float4 *>(plan.partial + (slot + half) * (kBM * BN)) + (e * 32) * 32 + lane;
+                // part of a tile: park it, take a ticket; whoever holds the LAST ticket adds all parts in part order (a
+                // fixed order, whoever it is -- its own part is read back from its slot like the others) and stores
+                const size_t slot0 = (static_cast<size_t>(un.tile_slot) * plan.max_parts) * 2;
+                auto slot_ptr = [&](int part) {
+                    return reinterpret_cast<float4 *>(plan.partial + (slot0 + static_cast<size_t>(part) * 2 + rank) * (kBM * BN)) +
+                           (e * 32) * 32 + lane;
+                };
+                float4 *mine = slot_ptr(un.part);
 #pragma unroll
                 for (int i = 0; i < Cfg::warp_cols / 4; ++i)
                     mine[i * 32] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
                 __threadfence();  // this thread's part of the partial tile is visible device-wide before the ticket is taken
                 epilogue_warps_sync();
+                unsigned *ticket = plan.tickets + un.tile_slot * 2 + rank;
                 if (warp == 2 && lane == 0)
                 {
                     __threadfence();
-                    *ticket_box = static_cast<int>(atomicAdd(plan.tickets + st * 2 + rank, 1u));
+                    *ticket_box = static_cast<int>(atomicAdd(ticket, 1u));
                 }
                 epilogue_warps_sync();
-                store = *ticket_box != 0;
+                store = *ticket_box == un.n_parts - 1;
                 if (store)
                 {
                     __threadfence();
-                    const float4 *other =
-                        reinterpret_cast<const float4 *>(plan.partial + (slot + (half ^ 1)) * (kBM * BN)) + (e * 32) * 32 + lane;
-#pragma unroll
-                    for (int i = 0; i < Cfg::warp_cols / 4; ++i)
+                    for (int part = 0; part < un.n_parts; ++part)
                     {
-                        const float4 o = __ldcg(other + i * 32);
-                        acc[4 * i] += o.x, acc[4 * i + 1] += o.y, acc[4 * i + 2] += o.z, acc[4 * i + 3] += o.w;
+                        const float4 *src = slot_ptr(part);
+#pragma unroll
+                        for (int i = 0; i < Cfg::warp_cols / 4; ++i)
+                        {
+                            const float4 o = __ldcg(src + i * 32);
+                            if (part == 0)
+                                acc[4 * i] = o.x, acc[4 * i + 1] = o.y, acc[4 * i + 2] = o.z, acc[4 * i + 3] = o.w;
+                            else
+                                acc[4 * i] += o.x, acc[4 * i + 1] += o.y, acc[4 * i + 2] += o.z, acc[4 * i + 3] += o.w;
+                        }
                     }
                 }
                 epilogue_warps_sync();  // everybody has read the ticket before the next unit may overwrite the box
                 if (store && warp == 2 && lane == 0)
-                    plan.tickets[st * 2 + rank] = 0;  // ready for the next launch
+                    *ticket = 0;  // ready for the next launch
             }
             if (store)
             {
@@ -1038,6 +1112,8 @@ gemm_tc2_wide_kernel(const __grid_constant__ TmapPack tm, const GemmParams p, co
 int g_pair_mode = 0;
 // Test hook: CTA pairs the persistent kernel uses (0 = as many as the GPU holds at once).
 int g_persist_pairs = 0;
+// Test hook: 0 = stream-K where it pays, 1 = for every problem the persistent kernel takes, -1 = never.
+int g_stream_k = 0;
 extern int g_slabs;
 
 namespace
@@ -1148,13 +1224,18 @@ int gemm_pair_recover(cudaStream_t stream)
 
 bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms)
 {
-    (void)a_mn, (void)b_mn, (void)terms;
+    (void)a_mn, (void)b_mn;
     if (g_pair_mode == 1 || bn != 256 || p.M <= kBM || (p.flags & (kEpiNCHW | kEpiSplitK)))
         return false;
     if (g_pair_mode == 2 || g_pair_mode == 5 || g_pair_mode == 7)
         return true;
     const int64_t pairs = static_cast<int64_t>((p.M + 255) / 256) * ((p.N + 255) / 256);
-    return pairs >= 74;
+    if (pairs >= 74)
+        return true;
+    // fewer tiles than pairs: the persistent kernel in stream-K mode still fills the GPU when the reduction is long
+    // enough to cut (3xTF32 only; at least eight accumulator chunks = 512 of K per pair)
+    const int64_t chunks = pairs * ((p.K + 63) / 64);
+    return terms == 3 && g_pair_mode != 6 && g_stream_k >= 0 && pairs >= 16 && chunks >= 8 * 74;
 }
 
 int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,
@@ -1243,20 +1324,44 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         const int want_p  = g_persist_pairs < 0 ? -g_persist_pairs : g_persist_pairs;
         if (want_p > 0 && P > 0)
             P = want_p < P ? want_p : P;
-        if (P > 0 && (T > P || g_pair_mode == 7))
+        const int num_kb    = (p.K + kBK - 1) / kBK;
+        int chunk_kb        = g_chunk_kb > 0 ? g_chunk_kb : 64 / kBK;
+        if (chunk_kb > num_kb)
+            chunk_kb = num_kb;
+        const int nch       = (num_kb + chunk_kb - 1) / chunk_kb;
+        // At most half as many tiles as pairs (a skinny output with a long reduction: 256 x 8192 x 8192 has 32 tiles):
+        // whole tiles would leave most pairs idle, so the K ranges are cut evenly over all pairs (stream-K).  Measured on
+        // B200 (TFLOP/s, whole tiles -> stream-K): 256 x 8192 x 8192 158-177 -> 174-187.  With more tiles it LOSES --
+        // 2048^3 (64 tiles) 175 -> 158, 8192 x 1024 x 8192 (128 tiles) 223 -> 206, 3072^3 204 -> 179 -- because pairs that
+        // share an operand panel then sit at different K offsets and stop sharing it in L2, which rounds of whole tiles
+        // started together do; those shapes keep whole tiles.  g_stream_k (test hook): 1 = always, -1 = never.
+        const long long total_chunks = static_cast<long long>(T) * nch;
+        const bool streamk = P > 0 && g_stream_k >= 0 && total_chunks >= 2 &&
+                             (g_stream_k == 1 || (2 * T <= P && total_chunks >= 8LL * P));
+        if (P > 0 && (T > P || g_pair_mode == 7 || streamk))
         {
             PersistPlan plan;
             plan.tiles_m = tiles_m, plan.tiles_n = tiles_n;
-            plan.num_kb   = (p.K + kBK - 1) / kBK;
-            plan.chunk_kb = g_chunk_kb > 0 ? g_chunk_kb : 64 / kBK;
-            if (plan.chunk_kb > plan.num_kb)
-                plan.chunk_kb = plan.num_kb;
+            plan.num_kb   = num_kb;
+            plan.chunk_kb = chunk_kb;
             plan.full_units = T, plan.split_tiles = 0, plan.kb_mid = 0, plan.partial = nullptr, plan.tickets = nullptr;
             plan.counters = nullptr;
-            if (g_persist_pairs >= 0 && (rc = unit_counters(&plan.counters)))  // (a negative test-hook value: fixed assignment)
-                return rc;
+            plan.streamk = 0, plan.chunks_per_tile = nch, plan.max_parts = 2;
             const int R = T % P;
-            if (R > 0 && 2 * R <= P && plan.num_kb >= 4 * plan.chunk_kb)
+            if (streamk)
+            {
+                const int pairs_used = total_chunks < P ? static_cast<int>(total_chunks) : P;
+                const long long per  = total_chunks / pairs_used;  // chunks of the shortest range (>= 1)
+                plan.streamk   = 1;
+                plan.max_parts = static_cast<int>((nch + per - 1) / per) + 1;
+                if ((rc = tail_split_scratch(static_cast<size_t>(T) * plan.max_parts * 2 * kBM * BN, static_cast<size_t>(T) * 2)))
+                    return rc;
+                plan.partial = g_part, plan.tickets = g_tickets;
+                P = pairs_used;
+            }
+            else if (g_persist_pairs >= 0 && (rc = unit_counters(&plan.counters)))  // (negative test-hook value: fixed assignment)
+                return rc;
+            if (!streamk && R > 0 && 2 * R <= P && plan.num_kb >= 4 * plan.chunk_kb)
             {
                 plan.split_tiles = R;
                 plan.full_units  = T - R;
@@ -1265,7 +1370,7 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
                     return rc;
                 plan.partial = g_part, plan.tickets = g_tickets;
             }
-            const int units = plan.full_units + 2 * plan.split_tiles;
+            const int units = streamk ? P : plan.full_units + 2 * plan.split_tiles;
             cudaLaunchConfig_t cfg;
             std::memset(&cfg, 0, sizeof(cfg));
             cfg.gridDim          = dim3(static_cast<unsigned>(2 * (units < P ? units : P)), 1, 1);

@@ -26,6 +26,7 @@ extern int g_bn_override;
 extern int g_chunk_kb;
 extern int g_pair_mode;
 extern int g_persist_pairs;
+extern int g_stream_k;
 int gemm_pair_recover(cudaStream_t stream);
 bool gemm_pair_eligible(const GemmParams &p, int bn, int a_mn, int b_mn, int terms);
 int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn, const float *B, const float *B_small,

@@ -64,7 +64,7 @@ def reference():
     global _reference
     if _reference is False:
         lib = ORACLE_DIR / "_ref" / "libodl_ref.so"
-        if not lib.exists() and Path(os.environ.get("ODL_REFERENCE_TREE", "/root/reference")).exists():
+        if not lib.exists() and Path(os.environ.get("ODL_REFERENCE_TREE", ROOT.parent / "reference")).exists():
             subprocess.run(["make", "-C", str(ORACLE_DIR), "ref", "-j8"], check=False, capture_output=True)
         if not lib.exists():
             _reference = None

@@ -270,6 +270,55 @@ def test_gemm_persistent_pair_kernel(ops, M, N, K, pairs, ta, tb):
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K,pairs", [(512, 512, 2048, 3), (1024, 1024, 1024, 7), (2048, 768, 515, 5), (300, 520, 100, 4),
+                                         (1500, 1300, 700, 9), (256, 1024, 4096, 0), (640, 512, 96, 74)])
+def test_gemm_stream_k(ops, M, N, K, pairs, ta, tb):
+    """Stream-K in the persistent pair kernel, forced: the accumulator chunks of the whole problem are cut into one
+    contiguous range per CTA pair, so pairs work on tails, whole tiles and heads; every tile cut by a range boundary is
+    parked part by part and finished by whichever contributor takes the last ticket, adding the parts in part order.
+    Shapes with two to five parts per tile, ragged tails, more pairs than chunks, all operand layouts, the full epilogue
+    with and without column sums; against float64, and the same bits on a second launch (arrival order must not matter)."""
+    from origindl_b200 import capi
+
+    rng = np.random.default_rng(M + N + K + 2 * ta + tb + pairs + 1)
+    a = rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    mask = rng.standard_normal((M, N)).astype(np.float32)
+    opa = a.T.astype(np.float64) if ta else a.astype(np.float64)
+    opb = b.T.astype(np.float64) if tb else b.astype(np.float64)
+    pre = opa @ opb + bias
+    ref = np.maximum(pre, 0) * (mask > 0)
+    tol = TOL[0] * np.abs(pre).max()
+    safe = np.abs(pre) > tol
+    for with_colsum in (True, False):
+        outs = []
+        capi.call("odl_debug_set_tile_n", 256)
+        capi.call("odl_debug_set_pair_mode", 7)
+        capi.call("odl_debug_set_stream_k", 1)
+        capi.call("odl_debug_set_persistent_pairs", pairs)
+        try:
+            for _ in range(2):
+                colsum = torch.zeros(N, device="cuda") if with_colsum else None
+                d, ds = ops.gemm(dev(a), dev(b), trans_a=bool(ta), trans_b=bool(tb), bias=dev(bias), relu=True,
+                                 mask_src=dev(mask), colsum=colsum, want_small=True)
+                outs.append((d, ds) + ((colsum,) if with_colsum else ()))
+        finally:
+            capi.call("odl_debug_set_pair_mode", 0)
+            capi.call("odl_debug_set_tile_n", 0)
+            capi.call("odl_debug_set_stream_k", 0)
+            capi.call("odl_debug_set_persistent_pairs", 0)
+        capi.device_status()
+        d, ds = outs[0][:2]
+        assert np.abs(host(d) - ref)[safe].max() <= tol
+        assert np.abs(host(d) - ref).max() <= 2 * tol
+        if with_colsum:
+            assert max_rel_err(host(outs[0][2]), ref.sum(0)) <= 10 * TOL[0]
+        assert torch.equal(ds, ops.split_tf32(d))
+        assert all(torch.equal(x, y) for x, y in zip(outs[0], outs[1]))
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(129, 256, 32), (256, 300, 64), (300, 520, 100), (1024, 1024, 1024), (2048, 768, 515),
                                    (512, 1600, 288)])
 def test_gemm_wide_tf32_pair_tile(ops, M, N, K, ta, tb):

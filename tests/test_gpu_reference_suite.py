@@ -27,7 +27,7 @@ PROGRAMS = ["test_matmul", "test_matmul_3d", "test_linear", "test_linear_backwar
 
 
 def _ensure_built():
-    ref = Path(os.environ.get("ODL_REFERENCE_TREE", "/root/reference"))
+    ref = Path(os.environ.get("ODL_REFERENCE_TREE", ROOT.parent / "reference"))
     if ref.exists():
         subprocess.run(["make", "-C", str(ROOT / "shim"), "tests", "-j8", f"REF={ref}"], check=True, capture_output=True)
     if not BUILD.exists():

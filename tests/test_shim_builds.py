@@ -14,7 +14,7 @@ BUILD = ROOT / "shim" / "_build"
 
 
 def test_shim_links_and_cpu_instances_pass():
-    ref = Path(os.environ.get("ODL_REFERENCE_TREE", "/root/reference"))
+    ref = Path(os.environ.get("ODL_REFERENCE_TREE", ROOT.parent / "reference"))
     if ref.exists():
         r = subprocess.run(["make", "-C", str(ROOT / "shim"), "tests", "-j8", f"REF={ref}"], capture_output=True, text=True)
         assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
