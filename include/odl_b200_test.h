@@ -37,7 +37,9 @@ int odl_debug_set_persistent_pairs(int pairs);
  * as many tiles as pairs), 1 = always, -1 = never. */
 int odl_debug_set_stream_k(int mode);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
- * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers. */
+ * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers, 4 = the generic direct
+ * input-gradient kernel also for the shapes that have a compile-time variant, 5 = the compile-time variant with one position
+ * per thread where it would take two. */
 int odl_debug_set_conv_mode(int mode);
 
 /* Number of NVTX ranges the training-step entry points have opened in this process: 0 unless the environment variable

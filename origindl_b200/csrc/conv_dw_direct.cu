@@ -31,18 +31,22 @@ struct DwGeom
 {
     int N, C, H, W, OC, KH, KW, S, P, OH, OW;
     int ckk, rows;
+    int pitch;  // floats per block in the slice buffer: OC * ckk of gw, then OC of gb
 };
 
 // OCP: output channels of the tile (16 or 32, OC padded up); KP: k columns of the tile (32 .. 256, C*KH*KW padded up);
-// PIX: pixels staged per iteration.  A thread owns an 8 (oc) x 8 (k) register tile, so the (OCP / 8) x (KP / 8) threads of
+// PIX: pixels staged per iteration; KPT: k columns per thread (8, or 9 for the 144 = 16 x 3 x 3 columns of a 3 x 3 conv over
+// 16 channels, which a 256-wide tile would pad by 78 %).  A thread owns an 8 (oc) x KPT (k) register tile, so the (OCP / 8) x (KP / KPT) threads of
 // one GROUP cover the whole gw tile; the 256 / that many groups of the block each take every G-th staged pixel, and add
 // their tiles in group order at the end.  Per pixel a thread reads 8 gy values and 8 column values (four 128-bit
 // shared-memory reads) for 64 multiply-adds: the kernel is bound by FMA issue, not by shared memory.
-template <int OCP, int KP, int PIX>
-__global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kernel(const float *__restrict__ x, const float *__restrict__ gy,
-                                                             float *__restrict__ slices, const DwGeom g, const int layout)
+template <int OCP, int KP, int PIX, int KPT>
+__global__ void __launch_bounds__(256, (KP <= 144 ? 2 : 1)) conv_dw_direct_kernel(const float *__restrict__ x, const float *__restrict__ gy,
+                                                             float *__restrict__ slices, const DwGeom g, const int layout,
+                                                             const int with_gb)
 {
-    constexpr int TG   = (OCP / 8) * (KP / 8);  // threads of a group
+    constexpr int TG   = (OCP / 8) * (KP / KPT);  // threads of a group
+    static_assert(KP % KPT == 0 && KP % 4 == 0, "k columns per thread / per staging chunk");
     constexpr int G    = 256 / TG;              // groups = pixels in flight per accumulate step
     constexpr int KPP  = KP + 4;                // pitches keep 16-byte alignment; + 4 floats: the 128-bit staging stores
     constexpr int OCPP = OCP + 4;               // of 8 consecutive pixels fall into distinct 16-byte bank groups
@@ -64,12 +68,12 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
         ktab[k] = e;
     }
     const int grp = tid / TG, lt = tid % TG;
-    const int ocg = lt / (KP / 8), kg = lt % (KP / 8);
-    float acc[8][8];
+    const int ocg = lt / (KP / KPT), kg = lt % (KP / KPT);
+    float acc[8][KPT];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < KPT; ++j)
             acc[i][j] = 0.f;
     const int ohw = g.OH * g.OW;
     // ---- staging, one iteration ahead through registers: thread (p = tid % PIX, q = tid / PIX) gathers the 4-column chunks
@@ -96,21 +100,40 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
         const int h0 = oh * g.S - g.P, w0 = ow * g.S - g.P;
         const int pix_off = (n * g.C * g.H + h0) * g.W + w0;
         const bool inside = ok && h0 >= 0 && h0 + g.KH <= g.H && w0 >= 0 && w0 + g.KW <= g.W;
-#pragma unroll
-        for (int c = 0; c < CH; ++c)
+        if (__all_sync(0xffffffffu, inside))
         {
-            const int ch = sq + c * Q;
+            // every pixel of the warp has its whole window inside the image (all but the border rows and columns): one
+            // table read, one add and one load per element.  The padded columns k >= ckk read offset 0 of the window --
+            // whatever they accumulate is never written out.
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int c = 0; c < CH; ++c)
             {
-                const int2 e = ktab[4 * ch + j];
-                bool in      = inside && e.y >= 0;
-                if (!inside && ok && e.y >= 0)
+                const int4 *tp = reinterpret_cast<const int4 *>(ktab + 4 * (sq + c * Q));
+                const int4 e01 = tp[0], e23 = tp[1];
+                vcol[c][0]     = __ldg(x + pix_off + e01.x);
+                vcol[c][1]     = __ldg(x + pix_off + e01.z);
+                vcol[c][2]     = __ldg(x + pix_off + e23.x);
+                vcol[c][3]     = __ldg(x + pix_off + e23.z);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+            {
+                const int ch = sq + c * Q;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
                 {
-                    const int hh = h0 + (e.y >> 16), ww = w0 + (e.y & 0xffff);
-                    in           = hh >= 0 && hh < g.H && ww >= 0 && ww < g.W;
+                    const int2 e = ktab[4 * ch + j];
+                    bool in      = inside && e.y >= 0;
+                    if (!inside && ok && e.y >= 0)
+                    {
+                        const int hh = h0 + (e.y >> 16), ww = w0 + (e.y & 0xffff);
+                        in           = hh >= 0 && hh < g.H && ww >= 0 && ww < g.W;
+                    }
+                    vcol[c][j] = in ? __ldg(x + pix_off + e.x) : 0.f;
                 }
-                vcol[c][j] = in ? __ldg(x + pix_off + e.x) : 0.f;
             }
         }
 #pragma unroll
@@ -129,6 +152,10 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
         }
     };
     __syncthreads();  // ktab is complete
+    // bias gradient on the side (with_gb; layout 0 only, where a staged row of gy is one pixel's channels): thread
+    // (oc = tid % OCP, part = tid / OCP) adds the pixels part, part + 256 / OCP, ... of every staged block
+    const int b_oc = tid % OCP, b_part = tid / OCP;
+    float gb_acc   = 0.f;
     const int step = gridDim.x * PIX;
     int r0         = blockIdx.x * PIX;
     if (r0 < g.rows)
@@ -153,16 +180,31 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
         {
             const float4 g0 = *reinterpret_cast<const float4 *>(gy_s + p * OCPP + 8 * ocg);
             const float4 g1 = *reinterpret_cast<const float4 *>(gy_s + p * OCPP + 8 * ocg + 4);
-            const float4 c0 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg);
-            const float4 c1 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg + 4);
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float cv[KPT];
+            if (KPT == 8)
+            {
+                const float4 c0 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg);
+                const float4 c1 = *reinterpret_cast<const float4 *>(col_s + p * KPP + 8 * kg + 4);
+                cv[0] = c0.x, cv[1] = c0.y, cv[2] = c0.z, cv[3] = c0.w, cv[4] = c1.x, cv[5] = c1.y, cv[6] = c1.z, cv[7] = c1.w;
+            }
+            else
+            {
+                // an odd stride: scalar reads, the KP / KPT threads of a row on distinct banks
+#pragma unroll
+                for (int j = 0; j < KPT; ++j)
+                    cv[j] = col_s[p * KPP + KPT * kg + j];
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+                for (int j = 0; j < KPT; ++j)
                     acc[i][j] = fmaf(gv[i], cv[j], acc[i][j]);
         }
+        if (with_gb)
+#pragma unroll
+            for (int p = b_part; p < PIX; p += 256 / OCP)
+                gb_acc += gy_s[p * OCPP + b_oc];  // rows past the last pixel were staged as zeros
         __syncthreads();
     }
     // ---- the groups add their tiles in group order (a fixed order: same bits every run) into a tile in shared memory
@@ -174,9 +216,9 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+                for (int j = 0; j < KPT; ++j)
                 {
-                    float *dst = red + (8 * ocg + i) * KP + 8 * kg + j;
+                    float *dst = red + (8 * ocg + i) * KP + KPT * kg + j;
                     *dst       = gi == 0 ? acc[i][j] : *dst + acc[i][j];
                 }
         }
@@ -186,12 +228,25 @@ __global__ void __launch_bounds__(256, (KP <= 128 ? 2 : 1)) conv_dw_direct_kerne
     {
         const int oc = o / KP, k = o - oc * KP;
         if (oc < g.OC && k < g.ckk)
-            slices[(static_cast<int64_t>(blockIdx.x) * g.OC + oc) * g.ckk + k] = red[o];
+            slices[static_cast<int64_t>(blockIdx.x) * g.pitch + oc * g.ckk + k] = red[o];
+    }
+    if (with_gb)
+    {
+        __syncthreads();  // the gw tile has been read
+        red[b_part * OCP + b_oc] = gb_acc;
+        __syncthreads();
+        if (tid < g.OC)
+        {
+            float s = 0.f;
+            for (int part = 0; part < 256 / OCP; ++part)
+                s += red[part * OCP + tid];
+            slices[static_cast<int64_t>(blockIdx.x) * g.pitch + g.OC * g.ckk + tid] = s;
+        }
     }
 }
 
-template <int OCP, int KP, int PIX>
-int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int layout, cudaStream_t stream)
+template <int OCP, int KP, int PIX, int KPT = 8>
+int launch_dw(const float *x, const float *gy, float *gw, float *gb, const DwGeom &g, int layout, cudaStream_t stream)
 {
     static_assert(OCP * KP <= PIX * (KP + 4), "the reduction tile reuses the column staging area");
     const size_t smem  = sizeof(float) * (PIX * (KP + 4) + PIX * (OCP + 4)) + sizeof(int2) * KP;
@@ -201,21 +256,21 @@ int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int l
     if (resident == 0)
     {
         if (smem > 48 * 1024)
-            cudaFuncSetAttribute(conv_dw_direct_kernel<OCP, KP, PIX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(conv_dw_direct_kernel<OCP, KP, PIX, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         int per_sm = 0, dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_dw_direct_kernel<OCP, KP, PIX>, 256, smem) != cudaSuccess ||
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_dw_direct_kernel<OCP, KP, PIX, KPT>, 256, smem) != cudaSuccess ||
             per_sm < 1)
             per_sm = 1;
         resident = sms * per_sm;
     }
     const int blocks   = chunks < resident ? chunks : resident;
     const int64_t out  = static_cast<int64_t>(g.OC) * g.ckk;
-    float *slices      = colsum_partial_scratch(blocks, out);
+    float *slices      = colsum_partial_scratch(blocks, g.pitch);
     if (!slices)
         return kCudaError;
-    conv_dw_direct_kernel<OCP, KP, PIX><<<blocks, 256, smem, stream>>>(x, gy, slices, g, layout);
+    conv_dw_direct_kernel<OCP, KP, PIX, KPT><<<blocks, 256, smem, stream>>>(x, gy, slices, g, layout, gb != nullptr);
     ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
@@ -223,7 +278,10 @@ int launch_dw(const float *x, const float *gy, float *gw, const DwGeom &g, int l
         set_last_error("conv_dw_direct_kernel<%d,%d,%d> launch failed: %s", OCP, KP, PIX, cudaGetErrorString(e));
         return kCudaError;
     }
-    return colsum_finish_launch(slices, blocks, out, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
+    int rc = colsum_finish_launch(slices, blocks, g.pitch, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
+    if (rc == kOk && gb)
+        rc = colsum_finish_launch(slices + out, blocks, g.pitch, g.OC, gb, stream);
+    return rc;
 }
 }  // namespace
 
@@ -235,32 +293,45 @@ bool conv_dw_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t
            N * C * H * W < (int64_t(1) << 31) - (int64_t(1) << 20);
 }
 
-int conv_dw_direct_launch(const float *x, const float *gy, float *gw, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
-                          int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream)
+// gb (optional; layout 0 only): the bias gradient, summed from the rows of gy the kernel stages anyway.
+int conv_dw_direct_launch(const float *x, const float *gy, float *gw, float *gb, int64_t N, int64_t C, int64_t H, int64_t W,
+                          int64_t OC, int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream)
 {
+    if (gb && layout != 0)
+    {
+        set_last_error("conv_dw_direct: the bias gradient rides along only in the true gradient layout");
+        return kInvalidArgument;
+    }
     DwGeom g;
     g.N = (int)N, g.C = (int)C, g.H = (int)H, g.W = (int)W, g.OC = (int)OC, g.KH = KH, g.KW = KW, g.S = S, g.P = P;
     g.OH = OH, g.OW = OW;
     g.ckk  = (int)(C * KH * KW);
-    g.rows = (int)(N * OH * OW);
+    g.rows  = (int)(N * OH * OW);
+    g.pitch = (int)(OC * g.ckk + OC);
     ODL_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * OC * g.ckk, stream));
+    if (gb)
+        ODL_CUDA_TRY(cudaMemsetAsync(gb, 0, sizeof(float) * OC, stream));
     if (OC <= 16)
     {
         if (g.ckk <= 32)
-            return launch_dw<16, 32, 64>(x, gy, gw, g, layout, stream);
+            return launch_dw<16, 32, 64>(x, gy, gw, gb, g, layout, stream);
         if (g.ckk <= 64)
-            return launch_dw<16, 64, 64>(x, gy, gw, g, layout, stream);
+            return launch_dw<16, 64, 64>(x, gy, gw, gb, g, layout, stream);
         if (g.ckk <= 128)
-            return launch_dw<16, 128, 64>(x, gy, gw, g, layout, stream);
-        return launch_dw<16, 256, 64>(x, gy, gw, g, layout, stream);
+            return launch_dw<16, 128, 64>(x, gy, gw, gb, g, layout, stream);
+        if (g.ckk <= 144)
+            return launch_dw<16, 144, 64, 9>(x, gy, gw, gb, g, layout, stream);
+        return launch_dw<16, 256, 64>(x, gy, gw, gb, g, layout, stream);
     }
     if (g.ckk <= 32)
-        return launch_dw<32, 32, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 32, 64>(x, gy, gw, gb, g, layout, stream);
     if (g.ckk <= 64)
-        return launch_dw<32, 64, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 64, 64>(x, gy, gw, gb, g, layout, stream);
     if (g.ckk <= 128)
-        return launch_dw<32, 128, 64>(x, gy, gw, g, layout, stream);
-    return launch_dw<32, 256, 64>(x, gy, gw, g, layout, stream);
+        return launch_dw<32, 128, 64>(x, gy, gw, gb, g, layout, stream);
+    if (g.ckk <= 144)
+        return launch_dw<32, 144, 64, 9>(x, gy, gw, gb, g, layout, stream);
+    return launch_dw<32, 256, 64>(x, gy, gw, gb, g, layout, stream);
 }
 
 }  // namespace odl

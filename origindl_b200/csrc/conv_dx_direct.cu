@@ -27,6 +27,7 @@
 
 namespace odl
 {
+extern int g_conv_mode;
 namespace
 {
 struct DxGeom
@@ -110,6 +111,245 @@ __global__ void __launch_bounds__(256) conv_dx_direct_kernel(const float *__rest
             gx[((static_cast<int64_t>(n) * g.C + c0 + ct) * g.H + hq) * g.W + wq] = acc[ct];
 }
 
+// The same sums with the channel count, the kernel size, the stride and the gradient layout fixed at compile time (the
+// shapes of the reference's CNN): the tap loops unroll into ceil(KT/ST)^2 guarded blocks of OCT products each, the
+// weight reads become constant offsets from one base, and in the row layout the OCT gradients of a tap arrive as
+// 128-bit loads.  Same order of taps and of output channels, so the same bits as the generic kernel.
+template <int CT, int OCT, int KT, int ST, int LAYOUT>
+__global__ void __launch_bounds__(256) conv_dx_direct_fixed_kernel(const float *__restrict__ gy, const float *__restrict__ w,
+                                                                   float *__restrict__ gx, const DxGeom g)
+{
+    constexpr int KHW = KT * KT;
+    constexpr int T   = (KT + ST - 1) / ST;
+    __shared__ float4 ws[OCT * KHW];
+    const int c0 = blockIdx.y * CT;
+    for (int i = threadIdx.x; i < OCT * KHW; i += 256)
+    {
+        const int oc = i / KHW, k = i - oc * KHW;
+        float v[4]   = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ct = 0; ct < CT; ++ct)
+            if (c0 + ct < g.C)
+                v[ct] = __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k);
+        ws[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+    const int64_t total = static_cast<int64_t>(g.N) * g.H * g.W;
+    const int64_t idx   = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total)
+        return;
+    const int wq  = static_cast<int>(idx % g.W);
+    const int t_  = static_cast<int>(idx / g.W);
+    const int hq  = t_ % g.H;
+    const int n   = t_ / g.H;
+    const int ohw = g.OH * g.OW;
+    float acc[CT];
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct)
+        acc[ct] = 0.f;
+    const int hp = hq + g.P, wp = wq + g.P;
+    const int kh0 = hp % ST, kw0 = wp % ST;
+    const int oh0 = hp / ST, ow0 = wp / ST;
+    const float *gn = LAYOUT == 0 ? gy + static_cast<int64_t>(n) * OCT * ohw : gy + static_cast<int64_t>(n) * ohw * OCT;
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+    {
+        const int kh = kh0 + t * ST, oh = oh0 - t;
+        if ((KT % ST != 0 && kh >= KT) || static_cast<unsigned>(oh) >= static_cast<unsigned>(g.OH))
+            continue;
+#pragma unroll
+        for (int u = 0; u < T; ++u)
+        {
+            const int kw = kw0 + u * ST, ow = ow0 - u;
+            if ((KT % ST != 0 && kw >= KT) || static_cast<unsigned>(ow) >= static_cast<unsigned>(g.OW))
+                continue;
+            const int pix     = oh * g.OW + ow;
+            const float4 *wt  = ws + kh * KT + kw;
+            float gv[OCT];
+            if (LAYOUT == 0)
+            {
+                const float *gp = gn + pix;
+#pragma unroll
+                for (int oc = 0; oc < OCT; ++oc)
+                    gv[oc] = __ldg(gp + oc * ohw);
+            }
+            else
+            {
+                const float4 *gp = reinterpret_cast<const float4 *>(gn + static_cast<int64_t>(pix) * OCT);
+#pragma unroll
+                for (int q = 0; q < OCT / 4; ++q)
+                {
+                    const float4 v = __ldg(gp + q);
+                    gv[4 * q] = v.x, gv[4 * q + 1] = v.y, gv[4 * q + 2] = v.z, gv[4 * q + 3] = v.w;
+                }
+            }
+            float s[CT];
+#pragma unroll
+            for (int ct = 0; ct < CT; ++ct)
+                s[ct] = 0.f;
+#pragma unroll
+            for (int oc = 0; oc < OCT; ++oc)
+            {
+                const float4 w4   = wt[oc * KHW];
+                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int ct = 0; ct < CT; ++ct)
+                    s[ct] = __fadd_rn(s[ct], __fmul_rn(gv[oc], wv[ct]));
+            }
+#pragma unroll
+            for (int ct = 0; ct < CT; ++ct)
+                acc[ct] = __fadd_rn(acc[ct], s[ct]);
+        }
+    }
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct)
+        if (c0 + ct < g.C)
+            gx[((static_cast<int64_t>(n) * g.C + c0 + ct) * g.H + hq) * g.W + wq] = acc[ct];
+}
+
+// Two positions per thread, (h, w) and (h, w + ST): they meet the same taps (kh, kw) -- one weight read serves both -- at
+// output columns ow and ow + 1, so the second position's gradients sit right behind the first's.  Needs W to be a
+// multiple of 2 * ST.  Thread j of a row takes w = (j / ST) * 2 * ST + j % ST.
+template <int CT, int OCT, int KT, int ST, int LAYOUT>
+__global__ void __launch_bounds__(256) conv_dx_direct_pair_kernel(const float *__restrict__ gy, const float *__restrict__ w,
+                                                                  float *__restrict__ gx, const DxGeom g)
+{
+    constexpr int KHW = KT * KT;
+    constexpr int T   = (KT + ST - 1) / ST;
+    __shared__ float4 ws[OCT * KHW];
+    const int c0 = blockIdx.y * CT;
+    for (int i = threadIdx.x; i < OCT * KHW; i += 256)
+    {
+        const int oc = i / KHW, k = i - oc * KHW;
+        float v[4]   = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ct = 0; ct < CT; ++ct)
+            if (c0 + ct < g.C)
+                v[ct] = __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k);
+        ws[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+    const int half      = g.W / 2;
+    const int64_t total = static_cast<int64_t>(g.N) * g.H * half;
+    const int64_t idx   = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total)
+        return;
+    const int j   = static_cast<int>(idx % half);
+    const int t_  = static_cast<int>(idx / half);
+    const int hq  = t_ % g.H;
+    const int n   = t_ / g.H;
+    const int wq  = (j / ST) * 2 * ST + j % ST;
+    const int ohw = g.OH * g.OW;
+    float acc[2][CT];
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct)
+        acc[0][ct] = acc[1][ct] = 0.f;
+    const int hp = hq + g.P, wp = wq + g.P;
+    const int kh0 = hp % ST, kw0 = wp % ST;
+    const int oh0 = hp / ST, ow0 = wp / ST;
+    const float *gn = LAYOUT == 0 ? gy + static_cast<int64_t>(n) * OCT * ohw : gy + static_cast<int64_t>(n) * ohw * OCT;
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+    {
+        const int kh = kh0 + t * ST, oh = oh0 - t;
+        if ((KT % ST != 0 && kh >= KT) || static_cast<unsigned>(oh) >= static_cast<unsigned>(g.OH))
+            continue;
+#pragma unroll
+        for (int u = 0; u < T; ++u)
+        {
+            const int kw = kw0 + u * ST, ow = ow0 - u;
+            if (KT % ST != 0 && kw >= KT)
+                continue;
+            const bool va = static_cast<unsigned>(ow) < static_cast<unsigned>(g.OW);
+            const bool vb = static_cast<unsigned>(ow + 1) < static_cast<unsigned>(g.OW);
+            if (!va && !vb)
+                continue;
+            const int pix    = oh * g.OW + ow;
+            const float4 *wt = ws + kh * KT + kw;
+            float ga[OCT], gb[OCT];
+            if (LAYOUT == 0)
+            {
+                const float *gp = gn + pix;
+#pragma unroll
+                for (int oc = 0; oc < OCT; ++oc)
+                {
+                    ga[oc] = va ? __ldg(gp + oc * ohw) : 0.f;
+                    gb[oc] = vb ? __ldg(gp + oc * ohw + 1) : 0.f;
+                }
+            }
+            else
+            {
+                const float4 *gp = reinterpret_cast<const float4 *>(gn + static_cast<int64_t>(pix) * OCT);
+#pragma unroll
+                for (int q = 0; q < OCT / 4; ++q)
+                {
+                    const float4 a = va ? __ldg(gp + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 b = vb ? __ldg(gp + OCT / 4 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ga[4 * q] = a.x, ga[4 * q + 1] = a.y, ga[4 * q + 2] = a.z, ga[4 * q + 3] = a.w;
+                    gb[4 * q] = b.x, gb[4 * q + 1] = b.y, gb[4 * q + 2] = b.z, gb[4 * q + 3] = b.w;
+                }
+            }
+            float sa[CT], sb[CT];
+#pragma unroll
+            for (int ct = 0; ct < CT; ++ct)
+                sa[ct] = sb[ct] = 0.f;
+#pragma unroll
+            for (int oc = 0; oc < OCT; ++oc)
+            {
+                const float4 w4   = wt[oc * KHW];
+                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int ct = 0; ct < CT; ++ct)
+                {
+                    sa[ct] = __fadd_rn(sa[ct], __fmul_rn(ga[oc], wv[ct]));
+                    sb[ct] = __fadd_rn(sb[ct], __fmul_rn(gb[oc], wv[ct]));
+                }
+            }
+            // a tap outside the output for one of the two positions is skipped for it, as the reference's col2im does
+#pragma unroll
+            for (int ct = 0; ct < CT; ++ct)
+            {
+                if (va)
+                    acc[0][ct] = __fadd_rn(acc[0][ct], sa[ct]);
+                if (vb)
+                    acc[1][ct] = __fadd_rn(acc[1][ct], sb[ct]);
+            }
+        }
+    }
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct)
+        if (c0 + ct < g.C)
+        {
+            float *dst = gx + ((static_cast<int64_t>(n) * g.C + c0 + ct) * g.H + hq) * g.W + wq;
+            dst[0]     = acc[0][ct];
+            dst[ST]    = acc[1][ct];
+        }
+}
+
+template <int CT, int OCT, int KT, int ST>
+int launch_dx_fixed(const float *gy, const float *w, float *gx, const DxGeom &g, int layout, cudaStream_t stream)
+{
+    const bool pair     = g.W % (2 * ST) == 0 && g_conv_mode != 5;  // test hook: conv mode 5 keeps one position per thread
+    const int64_t total = static_cast<int64_t>(g.N) * g.H * (pair ? g.W / 2 : g.W);
+    dim3 grid(static_cast<unsigned>((total + 255) / 256), static_cast<unsigned>((g.C + CT - 1) / CT));
+    if (pair && layout == 0)
+        conv_dx_direct_pair_kernel<CT, OCT, KT, ST, 0><<<grid, 256, 0, stream>>>(gy, w, gx, g);
+    else if (pair)
+        conv_dx_direct_pair_kernel<CT, OCT, KT, ST, 1><<<grid, 256, 0, stream>>>(gy, w, gx, g);
+    else if (layout == 0)
+        conv_dx_direct_fixed_kernel<CT, OCT, KT, ST, 0><<<grid, 256, 0, stream>>>(gy, w, gx, g);
+    else
+        conv_dx_direct_fixed_kernel<CT, OCT, KT, ST, 1><<<grid, 256, 0, stream>>>(gy, w, gx, g);
+    ++g_launch_count;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("conv_dx_direct_fixed_kernel<%d,%d,%d,%d> launch failed: %s", CT, OCT, KT, ST, cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
+
 template <int CT>
 int launch_dx(const float *gy, const float *w, float *gx, const DxGeom &g, int layout, cudaStream_t stream)
 {
@@ -137,8 +377,6 @@ int channel_group(int64_t C, int64_t OC, int KH, int KW)
 }
 }  // namespace
 
-extern int g_conv_mode;
-
 bool conv_dx_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S)
 {
     const int64_t products = OC * ((KH + S - 1) / S) * ((KW + S - 1) / S);
@@ -152,7 +390,22 @@ int conv_dx_direct_launch(const float *gy, const float *w, float *gx, int64_t N,
     DxGeom g;
     g.N = (int)N, g.C = (int)C, g.H = (int)H, g.W = (int)W, g.OC = (int)OC, g.KH = KH, g.KW = KW, g.S = S, g.P = P;
     g.OH = OH, g.OW = OW;
-    switch (channel_group(C, OC, KH, KW))
+    // the compile-time shapes (test hook: conv mode 4 keeps the generic kernel); the row layout reads gy 16 bytes at a time
+    const int ct = channel_group(C, OC, KH, KW);
+    if (g_conv_mode != 4 && KH == KW && (layout == 0 || reinterpret_cast<uintptr_t>(gy) % 16 == 0))
+    {
+        if (ct == 3 && OC == 16 && KH == 6 && S == 2)
+            return launch_dx_fixed<3, 16, 6, 2>(gy, w, gx, g, layout, stream);
+        if (ct == 4 && OC == 32 && KH == 3 && S == 2)
+            return launch_dx_fixed<4, 32, 3, 2>(gy, w, gx, g, layout, stream);
+        if (ct == 4 && OC == 32 && KH == 1 && S == 1)
+            return launch_dx_fixed<4, 32, 1, 1>(gy, w, gx, g, layout, stream);
+        if (ct == 4 && OC == 16 && KH == 3 && S == 1)
+            return launch_dx_fixed<4, 16, 3, 1>(gy, w, gx, g, layout, stream);
+        if (ct == 4 && OC == 16 && KH == 3 && S == 2)
+            return launch_dx_fixed<4, 16, 3, 2>(gy, w, gx, g, layout, stream);
+    }
+    switch (ct)
     {
         case 4:
             return launch_dx<4>(gy, w, gx, g, layout, stream);

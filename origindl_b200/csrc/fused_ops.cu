@@ -279,7 +279,9 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
                            (gx && !dx_direct && !dx_igemm ? ctb : 0) + 2 * operand_worst(rows, OC) + operand_worst(OC, ckk));
     if (rc)
         return rc;
-    if (gb)
+    // the direct weight-gradient kernel stages gy pixel by pixel and sums the bias gradient on the side (true layout only)
+    const bool gb_with_dw = gb && dw_direct && mode == 0;
+    if (gb && !gb_with_dw)
     {
         rc = channel_sum_launch(gy, gb, N, OC, hw, stream);
         if (rc)
@@ -307,7 +309,7 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     // Weight gradient of a small conv: direct fp32 kernel, the column matrix only ever exists tile-wise in shared memory
     if (dw_direct)
     {
-        rc = conv_dw_direct_launch(x, gy, gw, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        rc = conv_dw_direct_launch(x, gy, gw, gb_with_dw ? gb : nullptr, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
         if (rc)
             return rc;
         gw = nullptr;

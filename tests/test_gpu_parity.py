@@ -592,7 +592,11 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
                                                             (2, 40, 8, 10, 48, 3, 1, 0),   # stride 1 without padding
                                                             (1, 40, 8, 8, 40, 3, 1, 2),    # stride 1, pad = k - 1
                                                             (3, 3, 40, 36, 16, 6, 2, 2),   # gw over 3 images x 12 pixel blocks
-                                                            (2, 24, 16, 16, 200, 3, 1, 1)])  # two output-channel tiles, 216 k-rows
+                                                            (2, 24, 16, 16, 200, 3, 1, 1),  # two output-channel tiles, 216 k-rows
+                                                            (2, 16, 21, 19, 32, 3, 2, 1),  # the compile-time gx shapes of the CNN:
+                                                            (2, 32, 9, 11, 32, 1, 1, 0),   # 16 -> 32 3x3 / 2, 32 -> 32 1x1,
+                                                            (2, 6, 12, 10, 16, 3, 1, 1),   # 16 output channels 3x3 / 1 and / 2
+                                                            (2, 7, 13, 12, 16, 3, 2, 0)])  # (ragged channel groups)
 def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
     """gx has three implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
     BIT-EXACT against the oracle); for stride 1 in the correct gradient layout the implicit-GEMM convolution of gy with the
@@ -615,6 +619,10 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
             gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
             if direct:
                 assert np.array_equal(host(gx), dx_o)
+                for conv_mode in (4, 5):  # 4: the generic direct kernel where a compile-time shape exists; 5: that shape
+                    capi.lib().odl_debug_set_conv_mode(conv_mode)  # with one position per thread instead of two
+                    gx4, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
+                    assert np.array_equal(host(gx4), dx_o), conv_mode
             else:
                 assert max_rel_err(host(gx), dx_o) <= 1e-5
             assert max_rel_err(host(gw), dw_o) <= 1e-5  # direct fp32 kernel when OC <= 32 and C*KH*KW <= 256
