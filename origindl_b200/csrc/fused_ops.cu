@@ -309,7 +309,10 @@ int conv2d_backward(const float *gy, const float *x, const float *w, float *gx, 
     // Weight gradient of a small conv: direct fp32 kernel, the column matrix only ever exists tile-wise in shared memory
     if (dw_direct)
     {
-        rc = conv_dw_direct_launch(x, gy, gw, gb_with_dw ? gb : nullptr, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
+        // from image tiles in shared memory where a tile's window fits, else from gathered column blocks
+        rc = conv_dw_tile_eligible(N, C, H, W, OC, KH, KW, S, P, OH, OW)
+                 ? conv_dw_tile_launch(x, gy, gw, gb_with_dw ? gb : nullptr, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream)
+                 : conv_dw_direct_launch(x, gy, gw, gb_with_dw ? gb : nullptr, N, C, H, W, OC, KH, KW, S, P, OH, OW, mode, stream);
         if (rc)
             return rc;
         gw = nullptr;

@@ -111,6 +111,9 @@ int conv_dw_igemm_launch(const float *x, const float *gy, const float *gy_small,
 bool conv_dw_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int OH, int OW);
 int conv_dw_direct_launch(const float *x, const float *gy, float *gw, float *gb, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
                           int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream);
+bool conv_dw_tile_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S, int P, int OH, int OW);
+int conv_dw_tile_launch(const float *x, const float *gy, float *gw, float *gb, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
+                        int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream);
 bool conv_dx_direct_eligible(int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC, int KH, int KW, int S);
 int conv_dx_direct_launch(const float *gy, const float *w, float *gx, int64_t N, int64_t C, int64_t H, int64_t W, int64_t OC,
                           int KH, int KW, int S, int P, int OH, int OW, int layout, cudaStream_t stream);

@@ -43,10 +43,16 @@ def test_random_conv_geometries(seed):
         finally:
             capi.lib().odl_debug_set_conv_mode(0)
         gx, gw, gb = ops.conv2d_backward(gy, x, w, s, p, gy_layout=0)
+        capi.lib().odl_debug_set_conv_mode(7)          # small layers: weight gradient from image tiles wherever the window fits
+        try:
+            _, gw_tile, gb_tile = ops.conv2d_backward(gy, x, w, s, p, gy_layout=0, need_gx=False)
+        finally:
+            capi.lib().odl_debug_set_conv_mode(0)
         capi.device_status()
         x64, w64, b64 = x.double().requires_grad_(), w.double().requires_grad_(), b.double().requires_grad_()
         y64 = torch.nn.functional.conv2d(x64, w64, b64, stride=s, padding=p)
         y64.backward(gy.double())
         case = (seed, done, N, C, H, W, OC, k, s, p)
-        for got, want in ((y, y64.detach()), (y_tc, y64.detach()), (gx, x64.grad), (gw, w64.grad), (gb, b64.grad)):
+        for got, want in ((y, y64.detach()), (y_tc, y64.detach()), (gx, x64.grad), (gw, w64.grad), (gb, b64.grad),
+                          (gw_tile, w64.grad), (gb_tile, b64.grad)):
             assert ((got.double() - want).abs().max() / want.abs().max().clamp_min(1e-30)).item() <= 1e-5, case

@@ -626,7 +626,8 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
             else:
                 assert max_rel_err(host(gx), dx_o) <= 1e-5
             assert max_rel_err(host(gw), dw_o) <= 1e-5  # direct fp32 kernel when OC <= 32 and C*KH*KW <= 256
-            for conv_mode in (2, 1):  # 2: small layers through the implicit-GEMM gw kernel too; 1: explicit paths only
+            for conv_mode in (6, 7, 2, 1):  # 6 / 7: gw of small layers from gathered column blocks / from image tiles always;
+                # 2: small layers through the implicit-GEMM gw kernel too; 1: explicit paths only
                 capi.lib().odl_debug_set_conv_mode(conv_mode)
                 gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
                 assert max_rel_err(host(gx), dx_o) <= 1e-5 and max_rel_err(host(gw), dw_o) <= 1e-5
@@ -648,7 +649,7 @@ def test_conv2d_backward_is_reproducible(ops, N, C, H, W, OC, k, s, p):
     OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
     gy = torch.randn(N, OC, OH, OW, device="cuda", generator=g)
     try:
-        for conv_mode in (0, 2, 1):
+        for conv_mode in (0, 6, 7, 2, 1):
             capi.lib().odl_debug_set_conv_mode(conv_mode)
             for layout in (0, 1):
                 runs = [ops.conv2d_backward(gy, x, w, s, p, gy_layout=layout) for _ in range(3)]
