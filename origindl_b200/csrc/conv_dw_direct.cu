@@ -278,10 +278,8 @@ int launch_dw(const float *x, const float *gy, float *gw, float *gb, const DwGeo
         set_last_error("conv_dw_direct_kernel<%d,%d,%d> launch failed: %s", OCP, KP, PIX, cudaGetErrorString(e));
         return kCudaError;
     }
-    int rc = colsum_finish_launch(slices, blocks, g.pitch, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
-    if (rc == kOk && gb)
-        rc = colsum_finish_launch(slices + out, blocks, g.pitch, g.OC, gb, stream);
-    return rc;
+    // gw (and gb, which sits behind it in every slice) = the slices added in slice order
+    return colsum_finish2_launch(slices, blocks, g.pitch, (int)out, gw, g.OC, gb, stream);
 }
 }  // namespace
 
@@ -308,9 +306,6 @@ int conv_dw_direct_launch(const float *x, const float *gy, float *gw, float *gb,
     g.ckk  = (int)(C * KH * KW);
     g.rows  = (int)(N * OH * OW);
     g.pitch = (int)(OC * g.ckk + OC);
-    ODL_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * OC * g.ckk, stream));
-    if (gb)
-        ODL_CUDA_TRY(cudaMemsetAsync(gb, 0, sizeof(float) * OC, stream));
     if (OC <= 16)
     {
         if (g.ckk <= 32)

@@ -266,10 +266,8 @@ int launch_tile(const float *x, const float *gy, float *gw, float *gb, const Til
         set_last_error("conv_dw_tile_kernel<%d,%d,%d> launch failed: %s", OCP, KP, KPT, cudaGetErrorString(e));
         return kCudaError;
     }
-    int rc = colsum_finish_launch(slices, blocks, g.pitch, (int)out, gw, stream);  // gw += sum of the slices (gw was zeroed)
-    if (rc == kOk && gb)
-        rc = colsum_finish_launch(slices + out, blocks, g.pitch, g.OC, gb, stream);
-    return rc;
+    // gw (and gb, which sits behind it in every slice) = the slices added in slice order
+    return colsum_finish2_launch(slices, blocks, g.pitch, (int)out, gw, g.OC, gb, stream);
 }
 
 // Wavefronts of shared memory the column reads of one warp need (the first pixel step; one wavefront serves the lanes whose
@@ -407,9 +405,6 @@ int conv_dw_tile_launch(const float *x, const float *gy, float *gw, float *gb, i
         set_last_error("conv_dw_tile: the bias gradient rides along only in the true gradient layout");
         return kInvalidArgument;
     }
-    ODL_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * OC * g.ckk, stream));
-    if (gb)
-        ODL_CUDA_TRY(cudaMemsetAsync(gb, 0, sizeof(float) * OC, stream));
     if (OC <= 16)
     {
         if (g.ckk <= 32)

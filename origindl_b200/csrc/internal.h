@@ -40,6 +40,8 @@ int gemm_tc_launch(const float *A, const float *A_small, int64_t lda, int a_mn, 
 // the pass that adds them, in a fixed order, to colsum[0..n_cols).
 float *colsum_partial_scratch(int slabs, int64_t pitch);
 int colsum_finish_launch(const float *partial, int slabs, int64_t pitch, int n_cols, float *colsum, cudaStream_t stream);
+int colsum_finish2_launch(const float *partial, int slabs, int64_t pitch, int n_a, float *out_a, int n_b, float *out_b,
+                          cudaStream_t stream);
 int split_launch(const float *src, int64_t ld_src, int rows, int cols, const float *aux, int64_t ld_aux, float *dst_big,
                  float *dst_small, int64_t ld_dst, float *colsum, cudaStream_t stream);
 

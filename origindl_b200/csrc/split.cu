@@ -239,7 +239,50 @@ __global__ void __launch_bounds__(256) colsum_finish_kernel(const float *__restr
         colsum[n] += t;
     }
 }
+// The same sum for a slice buffer that holds two results side by side (columns [0, n_a) go to out_a, the next n_b to
+// out_b); the results are assigned, not added: one launch, no zeroing of the outputs beforehand.
+__global__ void __launch_bounds__(256) colsum_finish2_kernel(const float *__restrict__ partial, int slabs, int64_t pitch, int n_a,
+                                                             float *__restrict__ out_a, int n_b, float *__restrict__ out_b)
+{
+    __shared__ float red[8][33];
+    const int lane = threadIdx.x & 31, chain = threadIdx.x >> 5;
+    const int n = blockIdx.x * 32 + lane;
+    float s     = 0.f;
+    if (n < n_a + n_b)
+#pragma unroll 8
+        for (int y = chain; y < slabs; y += 8)
+            s += __ldcg(partial + y * pitch + n);
+    red[chain][lane] = s;
+    __syncthreads();
+    if (chain == 0 && n < n_a + n_b)
+    {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+            t += red[w][lane];
+        if (n < n_a)
+            out_a[n] = t;
+        else
+            out_b[n - n_a] = t;
+    }
+}
 }  // namespace
+
+int colsum_finish2_launch(const float *partial, int slabs, int64_t pitch, int n_a, float *out_a, int n_b, float *out_b,
+                          cudaStream_t stream)
+{
+    if (!out_b)
+        n_b = 0;
+    colsum_finish2_kernel<<<(n_a + n_b + 31) / 32, 256, 0, stream>>>(partial, slabs, pitch, n_a, out_a, n_b, out_b);
+    ++g_launch_count;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+    {
+        set_last_error("colsum_finish2_kernel launch failed: %s", cudaGetErrorString(e));
+        return kCudaError;
+    }
+    return kOk;
+}
 
 float *colsum_partial_scratch(int slabs, int64_t pitch)
 {
