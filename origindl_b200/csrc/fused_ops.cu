@@ -56,8 +56,11 @@ int linear_forward(const float *x, const float *x_small, const float *w, const f
 
 int linear_backward(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
                     const float *y, float *dx, float *dx_small, const float *dx_mask_src, float *dx_colsum, float *dw,
-                    float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream)
+                    float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream,
+                    cudaEvent_t dw_done)
 {
+    // dw_done (optional): the weight gradient is computed FIRST and the event recorded right behind its GEMM, so that a
+    // caller can start reducing dW over the ranks while dX is still being computed.  Same GEMMs, same results.
     if (w_layout != ODL_W_OUT_IN && w_layout != ODL_W_IN_OUT)
     {
         set_last_error("linear_backward: unknown weight layout %d", w_layout);
@@ -114,6 +117,25 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
         if (rc)
             return rc;
     }
+    auto weight_gradient = [&]() -> int {
+        int rc = kOk;
+        if (dw)
+        {
+            if (w_layout == ODL_W_OUT_IN)  // dW[N,K] = g^T . x
+                rc = gemm_dispatch(1, 0, N, K, M, g, gs, N, x, x_small, K, dw, nullptr, K, nullptr, nullptr, 0, nullptr,
+                                   0, precision, stream, false);
+            else  // dW{K,N} = x^T . g
+                rc = gemm_dispatch(1, 0, K, N, M, x, x_small, K, g, gs, N, dw, nullptr, N, nullptr, nullptr, 0, nullptr,
+                                   0, precision, stream, false);
+            if (rc)
+                return rc;
+        }
+        if (dw_done)
+            ODL_CUDA_TRY(cudaEventRecord(dw_done, stream));
+        return kOk;
+    };
+    if (dw_done && (rc = weight_gradient()))
+        return rc;
     if (dx)
     {
         // dx[M,K] = g[M,N] . W   ([N,K]: B stored [reduce][out] -> transB = 0;  {K,N}: stored [out][reduce] -> 1)
@@ -134,17 +156,8 @@ int linear_backward(const float *x, const float *x_small, const float *w, const 
         if (rc)
             return rc;
     }
-    if (dw)
-    {
-        if (w_layout == ODL_W_OUT_IN)  // dW[N,K] = g^T . x
-            rc = gemm_dispatch(1, 0, N, K, M, g, gs, N, x, x_small, K, dw, nullptr, K, nullptr, nullptr, 0, nullptr,
-                               0, precision, stream, false);
-        else  // dW{K,N} = x^T . g
-            rc = gemm_dispatch(1, 0, K, N, M, x, x_small, K, g, gs, N, dw, nullptr, N, nullptr, nullptr, 0, nullptr,
-                               0, precision, stream, false);
-        if (rc)
-            return rc;
-    }
+    if (!dw_done && (rc = weight_gradient()))
+        return rc;
     return kOk;
 }
 

@@ -84,7 +84,8 @@ int linear_forward(const float *x, const float *x_small, const float *w, const f
                    cudaStream_t stream);
 int linear_backward(const float *x, const float *x_small, const float *w, const float *w_small, const float *dy, const float *dy_small,
                     const float *y, float *dx, float *dx_small, const float *dx_mask_src, float *dx_colsum, float *dw,
-                    float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream);
+                    float *db, int64_t M, int64_t N, int64_t K, int w_layout, int precision, cudaStream_t stream,
+                    cudaEvent_t dw_done = nullptr);
 int conv2d_forward(const float *x, const float *w, const float *b, float *y, int64_t N, int64_t C, int64_t H, int64_t W,
                    int64_t OC, int KH, int KW, int S, int P, int act, int precision, cudaStream_t stream,
                    const float *scale = nullptr);

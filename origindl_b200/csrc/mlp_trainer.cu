@@ -11,6 +11,8 @@
 // Per step: 1 split of the input, L forward GEMMs, 2 loss launches, 1 split of dlogits, 2L-1 backward GEMMs, 1 optimizer.
 #include <cuda_runtime.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -59,8 +61,32 @@ struct Mlp
     cudaStream_t comm_stream = nullptr;
     int dw0_panels           = 1;
     std::vector<cudaEvent_t> ev_ready, ev_reduced;
+    cudaEvent_t ev_step_done = nullptr;    // the communication stream has finished the step (last reduction and update)
     long long graph_generation = -1;       // scratch_generation() when it was recorded: its scratch addresses are valid
                                            // only while no scratch block has been replaced since
+    // Parameter updates overlapped with backward (odl_mlp_train_step): layer l's update runs on a second stream as soon
+    // as layer l's backward has finished, next to the GEMMs of the layers below it (the update is HBM-bound, the GEMMs are
+    // not).  ev_layer_done[l]: layer l's backward is complete on the compute stream; ev_side_done: the second stream has
+    // finished the step.
+    cudaStream_t side_stream = nullptr;
+    std::vector<cudaEvent_t> ev_layer_done;
+    cudaEvent_t ev_side_done = nullptr;
+    int ensure_side()
+    {
+        if (side_stream)
+            return kOk;
+        int least = 0, greatest = 0;
+        ODL_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        ODL_CUDA_TRY(cudaStreamCreateWithPriority(&side_stream, cudaStreamNonBlocking, greatest));
+        for (int l = 0; l < L; ++l)
+        {
+            cudaEvent_t e = nullptr;
+            ODL_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            ev_layer_done.push_back(e);
+        }
+        ODL_CUDA_TRY(cudaEventCreateWithFlags(&ev_side_done, cudaEventDisableTiming));
+        return kOk;
+    }
 
     template <typename T>
     int alloc(T **p, size_t count)
@@ -83,6 +109,9 @@ struct Mlp
         for (cudaEvent_t e : ev_reduced)
             cudaEventDestroy(e);
         ev_ready.clear(), ev_reduced.clear();
+        if (ev_step_done)
+            cudaEventDestroy(ev_step_done);
+        ev_step_done = nullptr;
         if (comm_stream)
             cudaStreamDestroy(comm_stream);
         comm_stream = nullptr;
@@ -91,6 +120,12 @@ struct Mlp
     ~Mlp()
     {
         drop_dp();
+        for (cudaEvent_t e : ev_layer_done)
+            cudaEventDestroy(e);
+        if (ev_side_done)
+            cudaEventDestroy(ev_side_done);
+        if (side_stream)
+            cudaStreamDestroy(side_stream);
         if (step_graph)
             cudaGraphExecDestroy(step_graph);
         for (void *q : allocs)
@@ -336,15 +371,23 @@ int odl_mlp_forward_loss(void *handle, const float *x, const void *labels, int l
 
 // Backward of layer `layer` (call for layer = L-1 ... 0): dW_layer into the flat gradient buffer and, for layer > 0,
 // the gradient w.r.t. the layer below's pre-activation together with that layer's bias gradient.
-int odl_mlp_backward_layer(void *handle, int layer, void *stream)
+}  // extern "C"
+
+namespace odl
 {
-    Mlp *h = H(handle);
+namespace
+{
+// Test hook (odl_debug_set_update_overlap): 0 = parameter updates overlap backward, 1 = one update behind backward.
+int g_update_overlap = 0;
+
+// Backward of one layer.  dw_done (optional): dW is computed before dX and the event recorded right behind its GEMM.
+int backward_layer(Mlp *h, int layer, cudaStream_t s, cudaEvent_t dw_done)
+{
     if (layer < 0 || layer >= h->L)
     {
         set_last_error("mlp: layer %d out of range", layer);
         return kInvalidArgument;
     }
-    cudaStream_t s   = ST(stream);
     const int64_t B  = h->batch;
     NvtxRange range("odl backward layer", layer);
     const int cur    = (h->L - 1 - layer) & 1;  // ping-pong: the head's gradient sits in gbuf[0]
@@ -362,7 +405,33 @@ int odl_mlp_backward_layer(void *handle, int layer, void *stream)
     }
     return linear_backward(xin, xin_s, h->params + h->w_off[layer], three(h) ? h->params_small + h->w_off[layer] : nullptr,
                            g, g_s, nullptr, dx, dx_s, prev_y, prev_db, h->grads + h->w_off[layer], nullptr, B,
-                           h->sizes[layer + 1], h->sizes[layer], ODL_W_IN_OUT, h->precision, s);
+                           h->sizes[layer + 1], h->sizes[layer], ODL_W_IN_OUT, h->precision, s, dw_done);
+}
+
+// The optimizer's update of the flat range [o, o + n) (any range: the update is elementwise).
+int update_range(Mlp *h, int64_t o, int64_t n, float grad_scale, cudaStream_t s)
+{
+    float *ps = h->params_small ? h->params_small + o : nullptr;
+    if (h->optimizer == 1)
+        return adam_launch(h->params + o, h->grads + o, h->m + o, h->v + o, ps, n, h->step_count, h->lr, h->beta1, h->beta2,
+                           h->eps, h->hook_wd, grad_scale, s);
+    return sgd_launch(h->params + o, h->grads + o, h->m ? h->m + o : nullptr, ps, n, h->lr, h->momentum, 0.0f, 0, h->hook_wd,
+                      grad_scale, s);
+}
+}  // namespace
+}  // namespace odl
+
+extern "C" {
+
+int odl_debug_set_update_overlap(int mode)
+{
+    g_update_overlap = mode;
+    return 0;
+}
+
+int odl_mlp_backward_layer(void *handle, int layer, void *stream)
+{
+    return backward_layer(H(handle), layer, ST(stream), nullptr);
 }
 
 // One fused update of every parameter.  grad_scale: 1/world_size after a summing all-reduce, else 1.
@@ -405,13 +474,47 @@ int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int 
 
 int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
 {
+    Mlp *h = H(handle);
     int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
     if (rc)
         return rc;
-    for (int l = H(handle)->L - 1; l >= 0; --l)
+    if (g_update_overlap == 1 || h->L < 2)
+    {
+        for (int l = h->L - 1; l >= 0; --l)
+            if ((rc = odl_mlp_backward_layer(handle, l, stream)))
+                return rc;
+        return odl_mlp_optimizer_step(handle, 1.0f, stream);
+    }
+    // Layer l's parameters are last read by its dX GEMM and its gradient bucket [dW_l, db_l] is final after its dW GEMM:
+    // from there on its update is independent of the rest of backward and runs on the second stream, next to the GEMMs of
+    // the layers below (elementwise: the same bits as one update of the whole buffer).
+    if ((rc = h->ensure_side()))
+        return rc;
+    cudaStream_t s = ST(stream);
+    h->step_count += 1;
+    for (int l = h->L - 1; l >= 0; --l)
+    {
         if ((rc = odl_mlp_backward_layer(handle, l, stream)))
             return rc;
-    return odl_mlp_optimizer_step(handle, 1.0f, stream);
+        const int64_t o = h->w_off[l];
+        const int64_t n = (l + 1 < h->L ? h->w_off[l + 1] : h->total) - o;
+        if (l == 0)
+        {
+            // nothing is left to overlap with: the last layer's update stays on the compute stream
+            NvtxRange range("odl optimizer layer", 0);
+            if ((rc = update_range(h, o, n, 1.0f, s)))
+                return rc;
+            break;
+        }
+        ODL_CUDA_TRY(cudaEventRecord(h->ev_layer_done[l], s));
+        ODL_CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_layer_done[l], 0));
+        NvtxRange range("odl optimizer layer", l);
+        if ((rc = update_range(h, o, n, 1.0f, h->side_stream)))
+            return rc;
+    }
+    ODL_CUDA_TRY(cudaEventRecord(h->ev_side_done, h->side_stream));
+    ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_side_done, 0));
+    return kOk;
 }
 
 // ---- data-parallel step -------------------------------------------------------------------------------------------
@@ -435,7 +538,12 @@ int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels)
     while (panels > 1 && (in0 % (32 * panels) != 0))
         --panels;
     h->dw0_panels = panels;
-    ODL_CUDA_TRY(cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
+    // The communication stream gets the highest priority: when a GEMM ends and both the next GEMM and a waiting
+    // all-reduce could start, the all-reduce's few blocks are placed first and the GEMM takes the remaining SMs (its
+    // pairs draw their tiles from a counter, so it does not wait for the ones that start late).
+    int prio_least = 0, prio_greatest = 0;
+    ODL_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest));
+    ODL_CUDA_TRY(cudaStreamCreateWithPriority(&h->comm_stream, cudaStreamNonBlocking, prio_greatest));
     const int pieces = (h->L - 1) + panels;
     for (int i = 0; i < pieces; ++i)
     {
@@ -445,21 +553,74 @@ int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels)
         ODL_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
         h->ev_reduced.push_back(b);
     }
+    ODL_CUDA_TRY(cudaEventCreateWithFlags(&h->ev_step_done, cudaEventDisableTiming));
     h->comm = c;
     return kOk;
 }
 
 namespace
 {
+// Step timeline for tuning the overlap (environment variable ODL_DP_TRACE=1): timing events on both streams, printed to
+// stderr after the step has drained -- the one synchronisation it adds sits after everything was enqueued.
+struct DpTrace
+{
+    struct Mark
+    {
+        cudaEvent_t ev;
+        char what[48];
+    };
+    std::vector<Mark> marks;
+    bool on = false;
+    void begin()
+    {
+        static const bool enabled = [] {
+            const char *e = std::getenv("ODL_DP_TRACE");
+            return e && *e && *e != '0';
+        }();
+        on = enabled;
+        marks.clear();
+    }
+    void mark(cudaStream_t st, const char *what, int a)
+    {
+        if (!on)
+            return;
+        Mark m;
+        if (cudaEventCreate(&m.ev) != cudaSuccess)
+            return;
+        std::snprintf(m.what, sizeof(m.what), "%s %d", what, a);
+        cudaEventRecord(m.ev, st);
+        marks.push_back(m);
+    }
+    void print(cudaStream_t a, cudaStream_t b)
+    {
+        if (!on || marks.empty())
+            return;
+        cudaStreamSynchronize(a);
+        cudaStreamSynchronize(b);
+        for (size_t i = 0; i < marks.size(); ++i)
+        {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, marks[0].ev, marks[i].ev);
+            std::fprintf(stderr, "[odl dp trace] %8.3f ms  %s\n", ms, marks[i].what);
+        }
+        for (auto &m : marks)
+            cudaEventDestroy(m.ev);
+        marks.clear();
+    }
+};
+thread_local DpTrace g_trace;
+
 // Piece i's gradients are final on `s`: sum them over the ranks on the communication stream.
-int reduce_piece(Mlp *h, int piece, float *ptr, int64_t count, cudaStream_t s, int layer)
+// (ev_ready[piece] has been recorded behind the GEMM that made them final.)
+int reduce_piece(Mlp *h, int piece, float *ptr, int64_t count, int layer)
 {
     NvtxRange range("odl all-reduce layer", layer);
-    ODL_CUDA_TRY(cudaEventRecord(h->ev_ready[piece], s));
     ODL_CUDA_TRY(cudaStreamWaitEvent(h->comm_stream, h->ev_ready[piece], 0));
+    g_trace.mark(h->comm_stream, "  comm: all-reduce may start, piece", piece);
     int rc = comm_allreduce_sum(h->comm, ptr, count, h->comm_stream);
     if (rc)
         return rc;
+    g_trace.mark(h->comm_stream, "  comm: all-reduce done, piece", piece);
     ODL_CUDA_TRY(cudaEventRecord(h->ev_reduced[piece], h->comm_stream));
     return kOk;
 }
@@ -474,31 +635,40 @@ int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int 
         return kInvalidArgument;
     }
     cudaStream_t s = ST(stream);
-    int rc         = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
+    g_trace.begin();
+    g_trace.mark(s, "step start", 0);
+    int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
     if (rc)
         return rc;
-    // head first: bucket l = [dW_l, db_l] (db_l came out of layer l+1's dX epilogue) is final after layer l's dW GEMM
+    g_trace.mark(s, "forward + loss done", 0);
+    // Head first.  Bucket l = [dW_l, db_l] (db_l came out of layer l+1's dX epilogue) is final after layer l's dW GEMM,
+    // which runs BEFORE its dX GEMM here: the all-reduce of bucket l starts behind dW_l and has dX_l and everything below to
+    // hide behind.  The communication stream also runs the updates: layer l's as soon as its bucket is reduced and its dX
+    // GEMM (the last reader of W_l) has finished.
+    const float scale = 1.0f / static_cast<float>(comm_world(h->comm));
+    if ((rc = h->ensure_side()))
+        return rc;
+    h->step_count += 1;
     for (int l = h->L - 1; l >= 1; --l)
     {
-        if ((rc = odl_mlp_backward_layer(handle, l, stream)))
+        const int piece = h->L - 1 - l;
+        if ((rc = backward_layer(h, l, s, h->ev_ready[piece])))
             return rc;
+        g_trace.mark(s, "backward done, layer", l);
         const int64_t o = h->w_off[l];
         const int64_t n = (l + 1 < h->L ? h->w_off[l + 1] : h->total) - o;
-        if ((rc = reduce_piece(h, h->L - 1 - l, h->grads + o, n, s, l)))
+        if ((rc = reduce_piece(h, piece, h->grads + o, n, l)))
             return rc;
+        ODL_CUDA_TRY(cudaEventRecord(h->ev_layer_done[l], s));
+        ODL_CUDA_TRY(cudaStreamWaitEvent(h->comm_stream, h->ev_layer_done[l], 0));
+        if ((rc = update_range(h, o, n, scale, h->comm_stream)))
+            return rc;
+        g_trace.mark(h->comm_stream, "  comm: update done, layer", l);
     }
+    // layer 0 has no dX: its backward is the one GEMM dW_0{in,out} = x^T . g, done here in dw0_panels row panels (rows
+    // [k0, k1) are a contiguous range of the flat gradient buffer), each reduced and updated as soon as it is final
     const int first0 = h->L - 1;  // piece index of layer 0's first panel
-    if (h->dw0_panels == 1)
     {
-        if ((rc = odl_mlp_backward_layer(handle, 0, stream)))
-            return rc;
-        const int64_t n = (h->L > 1 ? h->w_off[1] : h->total);
-        if ((rc = reduce_piece(h, first0, h->grads, n, s, 0)))
-            return rc;
-    }
-    else
-    {
-        // layer 0 has no dX: its backward is the one GEMM dW_0{in,out} = x^T . g, done here panel by panel
         const int64_t B = h->batch, in0 = h->sizes[0], out0 = h->sizes[1];
         const int cur   = (h->L - 1) & 1;
         const float *g = h->gbuf[cur], *g_s = three(h) ? h->gbuf_small[cur] : nullptr;
@@ -513,24 +683,21 @@ int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int 
                                h->precision, s, true);
             if (rc)
                 return rc;
+            g_trace.mark(s, "backward done, layer 0 panel", p);
+            ODL_CUDA_TRY(cudaEventRecord(h->ev_ready[first0 + p], s));
             const int64_t lo = h->w_off[0] + k0 * out0;
             const int64_t hi = (p + 1 == h->dw0_panels) ? end : h->w_off[0] + (k0 + rows) * out0;
-            if ((rc = reduce_piece(h, first0 + p, h->grads + lo, hi - lo, s, 0)))
+            if ((rc = reduce_piece(h, first0 + p, h->grads + lo, hi - lo, 0)))
                 return rc;
+            if ((rc = update_range(h, lo, hi - lo, scale, h->comm_stream)))
+                return rc;
+            g_trace.mark(h->comm_stream, "  comm: update done, layer 0 panel", p);
         }
     }
-    // update every layer as soon as ITS bucket is reduced: the head-side updates run while layer 0 is still in flight
-    const float scale = 1.0f / static_cast<float>(comm_world(h->comm));
-    for (int l = h->L - 1; l >= 0; --l)
-    {
-        if (l > 0)
-            ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_reduced[h->L - 1 - l], 0));
-        else
-            for (int p = 0; p < h->dw0_panels; ++p)
-                ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_reduced[first0 + p], 0));
-        if ((rc = odl_mlp_optimizer_step_layer(handle, l, scale, l == h->L - 1 ? 1 : 0, stream)))
-            return rc;
-    }
+    // the step is complete when the communication stream is: odl_mlp_dp_wait watches this event
+    ODL_CUDA_TRY(cudaEventRecord(h->ev_step_done, h->comm_stream));
+    ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_step_done, 0));
+    g_trace.print(s, h->comm_stream);
     return kOk;
 }
 
@@ -542,8 +709,8 @@ int odl_mlp_dp_wait(void *handle, int timeout_ms)
         set_last_error("mlp_dp_wait: odl_mlp_dp_attach has not been called");
         return kInvalidArgument;
     }
-    // the communication stream runs its collectives in order: the last piece's event covers the whole step
-    cudaEvent_t last = h->ev_reduced.back();
+    // the communication stream runs its collectives and updates in order: its last event covers the whole step
+    cudaEvent_t last = h->ev_step_done;
     auto done = [](void *ev) -> int { return cudaEventQuery(static_cast<cudaEvent_t>(ev)) != cudaErrorNotReady ? 1 : 0; };
     return comm_watch(h->comm, timeout_ms, done, last);
 }
