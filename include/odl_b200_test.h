@@ -36,9 +36,6 @@ int odl_debug_set_persistent_pairs(int pairs);
 /* Stream-K in the persistent kernel (even K ranges per pair instead of whole tiles): 0 = where it pays (at most half
  * as many tiles as pairs), 1 = always, -1 = never. */
 int odl_debug_set_stream_k(int mode);
-/* odl_mlp_train_step: 0 = each layer's parameter update runs on a second stream as soon as that layer's backward is done,
- * 1 = one update of the whole parameter buffer behind backward.  Same bits either way. */
-int odl_debug_set_update_overlap(int mode);
 /* Conv2d: 0 = automatic, 1 = explicit im2col + GEMM everywhere, 2 = implicit-GEMM weight gradient instead of the direct
  * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers, 4 = the generic direct
  * input-gradient kernel also for the shapes that have a compile-time variant, 5 = the compile-time variant with one position

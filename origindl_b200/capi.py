@@ -50,7 +50,6 @@ _SIGNATURES = {
     "odl_debug_set_pair_mode": [c_int],
     "odl_debug_set_persistent_pairs": [c_int],
     "odl_debug_set_stream_k": [c_int],
-    "odl_debug_set_update_overlap": [c_int],
     "odl_debug_set_conv_mode": [c_int],
     "odl_binary": [c_int, _P, _P, _P, _I64, _P],
     "odl_scale": [_P, c_float, _P, _I64, _P],

@@ -64,29 +64,9 @@ struct Mlp
     cudaEvent_t ev_step_done = nullptr;    // the communication stream has finished the step (last reduction and update)
     long long graph_generation = -1;       // scratch_generation() when it was recorded: its scratch addresses are valid
                                            // only while no scratch block has been replaced since
-    // Parameter updates overlapped with backward (odl_mlp_train_step): layer l's update runs on a second stream as soon
-    // as layer l's backward has finished, next to the GEMMs of the layers below it (the update is HBM-bound, the GEMMs are
-    // not).  ev_layer_done[l]: layer l's backward is complete on the compute stream; ev_side_done: the second stream has
-    // finished the step.
-    cudaStream_t side_stream = nullptr;
+    // ev_layer_done[l]: layer l's backward (its dX GEMM, the last reader of W_l) is complete on the compute stream -- what
+    // layer l's update on the communication stream waits for
     std::vector<cudaEvent_t> ev_layer_done;
-    cudaEvent_t ev_side_done = nullptr;
-    int ensure_side()
-    {
-        if (side_stream)
-            return kOk;
-        int least = 0, greatest = 0;
-        ODL_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&least, &greatest));
-        ODL_CUDA_TRY(cudaStreamCreateWithPriority(&side_stream, cudaStreamNonBlocking, greatest));
-        for (int l = 0; l < L; ++l)
-        {
-            cudaEvent_t e = nullptr;
-            ODL_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-            ev_layer_done.push_back(e);
-        }
-        ODL_CUDA_TRY(cudaEventCreateWithFlags(&ev_side_done, cudaEventDisableTiming));
-        return kOk;
-    }
 
     template <typename T>
     int alloc(T **p, size_t count)
@@ -108,7 +88,9 @@ struct Mlp
             cudaEventDestroy(e);
         for (cudaEvent_t e : ev_reduced)
             cudaEventDestroy(e);
-        ev_ready.clear(), ev_reduced.clear();
+        for (cudaEvent_t e : ev_layer_done)
+            cudaEventDestroy(e);
+        ev_ready.clear(), ev_reduced.clear(), ev_layer_done.clear();
         if (ev_step_done)
             cudaEventDestroy(ev_step_done);
         ev_step_done = nullptr;
@@ -120,12 +102,6 @@ struct Mlp
     ~Mlp()
     {
         drop_dp();
-        for (cudaEvent_t e : ev_layer_done)
-            cudaEventDestroy(e);
-        if (ev_side_done)
-            cudaEventDestroy(ev_side_done);
-        if (side_stream)
-            cudaStreamDestroy(side_stream);
         if (step_graph)
             cudaGraphExecDestroy(step_graph);
         for (void *q : allocs)
@@ -377,9 +353,6 @@ namespace odl
 {
 namespace
 {
-// Test hook (odl_debug_set_update_overlap): 0 = parameter updates overlap backward, 1 = one update behind backward.
-int g_update_overlap = 0;
-
 // Backward of one layer.  dw_done (optional): dW is computed before dX and the event recorded right behind its GEMM.
 int backward_layer(Mlp *h, int layer, cudaStream_t s, cudaEvent_t dw_done)
 {
@@ -422,12 +395,6 @@ int update_range(Mlp *h, int64_t o, int64_t n, float grad_scale, cudaStream_t s)
 }  // namespace odl
 
 extern "C" {
-
-int odl_debug_set_update_overlap(int mode)
-{
-    g_update_overlap = mode;
-    return 0;
-}
 
 int odl_mlp_backward_layer(void *handle, int layer, void *stream)
 {
@@ -474,47 +441,16 @@ int odl_mlp_optimizer_step_layer(void *handle, int layer, float grad_scale, int 
 
 int odl_mlp_train_step(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream)
 {
-    Mlp *h = H(handle);
     int rc = odl_mlp_forward_loss(handle, x, labels, labels_are_int64, stream);
     if (rc)
         return rc;
-    if (g_update_overlap == 1 || h->L < 2)
-    {
-        for (int l = h->L - 1; l >= 0; --l)
-            if ((rc = odl_mlp_backward_layer(handle, l, stream)))
-                return rc;
-        return odl_mlp_optimizer_step(handle, 1.0f, stream);
-    }
-    // Layer l's parameters are last read by its dX GEMM and its gradient bucket [dW_l, db_l] is final after its dW GEMM:
-    // from there on its update is independent of the rest of backward and runs on the second stream, next to the GEMMs of
-    // the layers below (elementwise: the same bits as one update of the whole buffer).
-    if ((rc = h->ensure_side()))
-        return rc;
-    cudaStream_t s = ST(stream);
-    h->step_count += 1;
-    for (int l = h->L - 1; l >= 0; --l)
-    {
+    for (int l = H(handle)->L - 1; l >= 0; --l)
         if ((rc = odl_mlp_backward_layer(handle, l, stream)))
             return rc;
-        const int64_t o = h->w_off[l];
-        const int64_t n = (l + 1 < h->L ? h->w_off[l + 1] : h->total) - o;
-        if (l == 0)
-        {
-            // nothing is left to overlap with: the last layer's update stays on the compute stream
-            NvtxRange range("odl optimizer layer", 0);
-            if ((rc = update_range(h, o, n, 1.0f, s)))
-                return rc;
-            break;
-        }
-        ODL_CUDA_TRY(cudaEventRecord(h->ev_layer_done[l], s));
-        ODL_CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_layer_done[l], 0));
-        NvtxRange range("odl optimizer layer", l);
-        if ((rc = update_range(h, o, n, 1.0f, h->side_stream)))
-            return rc;
-    }
-    ODL_CUDA_TRY(cudaEventRecord(h->ev_side_done, h->side_stream));
-    ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_side_done, 0));
-    return kOk;
+    // One update of the whole buffer behind backward.  (Measured: running layer l's update on a second stream as soon as
+    // its backward is done gains nothing -- 51.37 against 51.36 ms on the benchmark step -- because no other kernel's
+    // blocks fit on an SM beside a persistent GEMM CTA, so the update runs between two GEMMs either way.)
+    return odl_mlp_optimizer_step(handle, 1.0f, stream);
 }
 
 // ---- data-parallel step -------------------------------------------------------------------------------------------
@@ -552,6 +488,12 @@ int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels)
         h->ev_ready.push_back(a);
         ODL_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
         h->ev_reduced.push_back(b);
+    }
+    for (int l = 0; l < h->L; ++l)
+    {
+        cudaEvent_t e = nullptr;
+        ODL_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        h->ev_layer_done.push_back(e);
     }
     ODL_CUDA_TRY(cudaEventCreateWithFlags(&h->ev_step_done, cudaEventDisableTiming));
     h->comm = c;
@@ -646,8 +588,6 @@ int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int 
     // hide behind.  The communication stream also runs the updates: layer l's as soon as its bucket is reduced and its dX
     // GEMM (the last reader of W_l) has finished.
     const float scale = 1.0f / static_cast<float>(comm_world(h->comm));
-    if ((rc = h->ensure_side()))
-        return rc;
     h->step_count += 1;
     for (int l = h->L - 1; l >= 1; --l)
     {

@@ -270,7 +270,7 @@ def test_replay_refuses_a_graph_whose_scratch_was_replaced(trainer_cls):
 
 
 def test_nvtx_ranges_follow_the_environment_switch():
-    """ODL_NVTX=1 wraps forward + loss, each layer's backward and each layer's update in NVTX ranges (for timeline tools); the
+    """ODL_NVTX=1 wraps forward + loss, each layer's backward and the optimizer in NVTX ranges (for timeline tools); the
     default run opens none.  The switch is read once per process, so each setting runs in a process of its own."""
     import subprocess
     import sys
@@ -302,36 +302,5 @@ def test_nvtx_ranges_follow_the_environment_switch():
         assert r.returncode == 0, r.stdout + r.stderr
         counts[setting] = int(r.stdout.split("ranges")[1])
     assert counts["0"] == 0
-    assert counts["1"] == 2 * (1 + 3 + 3)        # per step: forward + loss, three layers' backward, three layers' updates
+    assert counts["1"] == 2 * (1 + 3 + 1)        # per step: forward + loss, three layers' backward, the optimizer
 
-
-def test_overlapped_updates_give_the_same_bits(ops):
-    """odl_mlp_train_step runs layer l's parameter update on a second stream next to the GEMMs of the layers below it.
-    The update is elementwise, so parameters, optimizer state and losses must equal, bit for bit, those of the step that
-    updates the whole buffer once behind backward -- for Adam and for SGD with momentum, over several steps."""
-    from origindl_b200 import capi
-    from origindl_b200.trainer import MLPTrainer
-
-    sizes, batch = [96, 160, 128, 64, 10], 256
-    g = torch.Generator(device="cuda").manual_seed(7)
-    xs = torch.randn(4, batch, sizes[0], device="cuda", generator=g)
-    ts = torch.randint(0, sizes[-1], (4, batch), device="cuda", generator=g, dtype=torch.int32)
-    for opt, kw in (("adam", {}), ("sgd", {"momentum": 0.9, "hook_weight_decay": 1e-4})):
-        runs = []
-        for mode in (0, 1):
-            capi.lib().odl_debug_set_update_overlap(mode)
-            try:
-                tr = MLPTrainer(sizes, batch, optimizer=opt, lr=1e-2, device=0, **kw)
-                rng = np.random.default_rng(3)
-                tr.set_params((0.1 * rng.standard_normal(tr.get_params().shape)).astype(np.float32))
-                losses = [float(tr.train_step(xs[i % 4], ts[i % 4]).item()) for i in range(6)]
-                sd = tr.optimizer_state_dict()
-                runs.append((losses, tr.get_params().copy(), {k: np.array(v, copy=True) for k, v in sd.items() if isinstance(v, np.ndarray)}))
-                tr.close()
-            finally:
-                capi.lib().odl_debug_set_update_overlap(0)
-        assert runs[0][0] == runs[1][0], opt
-        assert np.array_equal(runs[0][1], runs[1][1]), opt
-        for k in runs[0][2]:
-            assert np.array_equal(runs[0][2][k], runs[1][2][k]), (opt, k)
-    capi.device_status()
