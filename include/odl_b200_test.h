@@ -40,7 +40,8 @@ int odl_debug_set_stream_k(int mode);
  * kernel for small layers, 3 = implicit-GEMM forward instead of the direct kernel for small layers, 4 = the generic direct
  * input-gradient kernel also for the shapes that have a compile-time variant, 5 = the compile-time variant with one position
  * per thread where it would take two, 6 = the direct weight-gradient kernel that gathers column blocks also where
- * the one that stages image tiles would run, 7 = the latter wherever its window fits shared memory. */
+ * the one that stages image tiles would run, 7 = the latter wherever its window fits shared memory,
+ * 8 = four input channels per thread in the compile-time input-gradient kernels where they would take eight. */
 int odl_debug_set_conv_mode(int mode);
 
 /* Number of NVTX ranges the training-step entry points have opened in this process: 0 unless the environment variable

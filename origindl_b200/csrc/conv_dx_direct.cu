@@ -121,17 +121,19 @@ __global__ void __launch_bounds__(256) conv_dx_direct_fixed_kernel(const float *
 {
     constexpr int KHW = KT * KT;
     constexpr int T   = (KT + ST - 1) / ST;
-    __shared__ float4 ws[OCT * KHW];
+    constexpr int C4 = (CT + 3) / 4;  // 128-bit weight words per (oc, tap): the group's channels, padded to a multiple of 4
+    __shared__ float4 ws[OCT * KHW * C4];
     const int c0 = blockIdx.y * CT;
     for (int i = threadIdx.x; i < OCT * KHW; i += 256)
     {
         const int oc = i / KHW, k = i - oc * KHW;
-        float v[4]   = {0.f, 0.f, 0.f, 0.f};
+        float v[4 * C4];
 #pragma unroll
-        for (int ct = 0; ct < CT; ++ct)
-            if (c0 + ct < g.C)
-                v[ct] = __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k);
-        ws[i] = make_float4(v[0], v[1], v[2], v[3]);
+        for (int ct = 0; ct < 4 * C4; ++ct)
+            v[ct] = (ct < CT && c0 + ct < g.C) ? __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k) : 0.f;
+#pragma unroll
+        for (int q = 0; q < C4; ++q)
+            ws[i * C4 + q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     }
     __syncthreads();
     const int64_t total = static_cast<int64_t>(g.N) * g.H * g.W;
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(256) conv_dx_direct_fixed_kernel(const float *
             if ((KT % ST != 0 && kw >= KT) || static_cast<unsigned>(ow) >= static_cast<unsigned>(g.OW))
                 continue;
             const int pix     = oh * g.OW + ow;
-            const float4 *wt  = ws + kh * KT + kw;
+            const float4 *wt  = ws + (kh * KT + kw) * C4;
             float gv[OCT];
             if (LAYOUT == 0)
             {
@@ -190,8 +192,13 @@ __global__ void __launch_bounds__(256) conv_dx_direct_fixed_kernel(const float *
 #pragma unroll
             for (int oc = 0; oc < OCT; ++oc)
             {
-                const float4 w4   = wt[oc * KHW];
-                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                float wv[4 * C4];
+#pragma unroll
+                for (int q = 0; q < C4; ++q)
+                {
+                    const float4 w4 = wt[oc * KHW * C4 + q];
+                    wv[4 * q] = w4.x, wv[4 * q + 1] = w4.y, wv[4 * q + 2] = w4.z, wv[4 * q + 3] = w4.w;
+                }
 #pragma unroll
                 for (int ct = 0; ct < CT; ++ct)
                     s[ct] = __fadd_rn(s[ct], __fmul_rn(gv[oc], wv[ct]));
@@ -216,17 +223,19 @@ __global__ void __launch_bounds__(256) conv_dx_direct_pair_kernel(const float *_
 {
     constexpr int KHW = KT * KT;
     constexpr int T   = (KT + ST - 1) / ST;
-    __shared__ float4 ws[OCT * KHW];
+    constexpr int C4 = (CT + 3) / 4;  // 128-bit weight words per (oc, tap): the group's channels, padded to a multiple of 4
+    __shared__ float4 ws[OCT * KHW * C4];
     const int c0 = blockIdx.y * CT;
     for (int i = threadIdx.x; i < OCT * KHW; i += 256)
     {
         const int oc = i / KHW, k = i - oc * KHW;
-        float v[4]   = {0.f, 0.f, 0.f, 0.f};
+        float v[4 * C4];
 #pragma unroll
-        for (int ct = 0; ct < CT; ++ct)
-            if (c0 + ct < g.C)
-                v[ct] = __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k);
-        ws[i] = make_float4(v[0], v[1], v[2], v[3]);
+        for (int ct = 0; ct < 4 * C4; ++ct)
+            v[ct] = (ct < CT && c0 + ct < g.C) ? __ldg(w + (static_cast<int64_t>(oc) * g.C + c0 + ct) * KHW + k) : 0.f;
+#pragma unroll
+        for (int q = 0; q < C4; ++q)
+            ws[i * C4 + q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     }
     __syncthreads();
     const int half      = g.W / 2;
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(256) conv_dx_direct_pair_kernel(const float *_
             if (!va && !vb)
                 continue;
             const int pix    = oh * g.OW + ow;
-            const float4 *wt = ws + kh * KT + kw;
+            const float4 *wt = ws + (kh * KT + kw) * C4;
             float ga[OCT], gb[OCT];
             if (LAYOUT == 0)
             {
@@ -296,8 +305,13 @@ __global__ void __launch_bounds__(256) conv_dx_direct_pair_kernel(const float *_
 #pragma unroll
             for (int oc = 0; oc < OCT; ++oc)
             {
-                const float4 w4   = wt[oc * KHW];
-                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                float wv[4 * C4];
+#pragma unroll
+                for (int q = 0; q < C4; ++q)
+                {
+                    const float4 w4 = wt[oc * KHW * C4 + q];
+                    wv[4 * q] = w4.x, wv[4 * q + 1] = w4.y, wv[4 * q + 2] = w4.z, wv[4 * q + 3] = w4.w;
+                }
 #pragma unroll
                 for (int ct = 0; ct < CT; ++ct)
                 {
@@ -396,14 +410,21 @@ int conv_dx_direct_launch(const float *gy, const float *w, float *gx, int64_t N,
     {
         if (ct == 3 && OC == 16 && KH == 6 && S == 2)
             return launch_dx_fixed<3, 16, 6, 2>(gy, w, gx, g, layout, stream);
+        // eight input channels per thread where there are that many: half the gradient loads per product (the first-level
+        // cache's load rate, not arithmetic, bounds the 16 -> 32 channel layer with four)
+        const bool eight = C >= 8 && g_conv_mode != 8;  // test hook: conv mode 8 keeps four channels per thread
         if (ct == 4 && OC == 32 && KH == 3 && S == 2)
-            return launch_dx_fixed<4, 32, 3, 2>(gy, w, gx, g, layout, stream);
+            return eight ? launch_dx_fixed<8, 32, 3, 2>(gy, w, gx, g, layout, stream)
+                         : launch_dx_fixed<4, 32, 3, 2>(gy, w, gx, g, layout, stream);
         if (ct == 4 && OC == 32 && KH == 1 && S == 1)
-            return launch_dx_fixed<4, 32, 1, 1>(gy, w, gx, g, layout, stream);
+            return eight ? launch_dx_fixed<8, 32, 1, 1>(gy, w, gx, g, layout, stream)
+                         : launch_dx_fixed<4, 32, 1, 1>(gy, w, gx, g, layout, stream);
         if (ct == 4 && OC == 16 && KH == 3 && S == 1)
-            return launch_dx_fixed<4, 16, 3, 1>(gy, w, gx, g, layout, stream);
+            return eight ? launch_dx_fixed<8, 16, 3, 1>(gy, w, gx, g, layout, stream)
+                         : launch_dx_fixed<4, 16, 3, 1>(gy, w, gx, g, layout, stream);
         if (ct == 4 && OC == 16 && KH == 3 && S == 2)
-            return launch_dx_fixed<4, 16, 3, 2>(gy, w, gx, g, layout, stream);
+            return eight ? launch_dx_fixed<8, 16, 3, 2>(gy, w, gx, g, layout, stream)
+                         : launch_dx_fixed<4, 16, 3, 2>(gy, w, gx, g, layout, stream);
     }
     switch (ct)
     {

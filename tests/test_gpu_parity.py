@@ -596,7 +596,8 @@ def test_conv2d_forward_implicit_and_explicit_paths(ops, orc, N, C, H, W, OC, k,
                                                             (2, 16, 21, 19, 32, 3, 2, 1),  # the compile-time gx shapes of the CNN:
                                                             (2, 32, 9, 11, 32, 1, 1, 0),   # 16 -> 32 3x3 / 2, 32 -> 32 1x1,
                                                             (2, 6, 12, 10, 16, 3, 1, 1),   # 16 output channels 3x3 / 1 and / 2
-                                                            (2, 7, 13, 12, 16, 3, 2, 0)])  # (ragged channel groups)
+                                                            (2, 7, 13, 12, 16, 3, 2, 0),   # (ragged channel groups)
+                                                            (2, 12, 10, 12, 16, 3, 1, 1)]) # eight channels per thread, ragged
 def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k, s, p):
     """gx has three implementations: a direct fp32 kernel (few products per output; the reference's summation order, so
     BIT-EXACT against the oracle); for stride 1 in the correct gradient layout the implicit-GEMM convolution of gy with the
@@ -619,8 +620,9 @@ def test_conv2d_input_gradient_direct_and_gemm_paths(ops, orc, N, C, H, W, OC, k
             gx, gw, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
             if direct:
                 assert np.array_equal(host(gx), dx_o)
-                for conv_mode in (4, 5):  # 4: the generic direct kernel where a compile-time shape exists; 5: that shape
-                    capi.lib().odl_debug_set_conv_mode(conv_mode)  # with one position per thread instead of two
+                for conv_mode in (4, 5, 8):  # 4: the generic direct kernel where a compile-time shape exists; 5: that shape
+                    # with one position per thread instead of two; 8: four input channels per thread instead of eight
+                    capi.lib().odl_debug_set_conv_mode(conv_mode)
                     gx4, _, _ = ops.conv2d_backward(dev(dy), dev(x), dev(w), s, p, gy_layout=layout, need_gb=False)
                     assert np.array_equal(host(gx4), dx_o), conv_mode
             else:
