@@ -25,7 +25,8 @@ int odl_debug_set_split_k(int splits);
 int odl_debug_set_bk(int bk);
 /* K-slabs per pipeline stage in plain TF32: 1 or 2; 0 = automatic. */
 int odl_debug_set_slabs(int n);
-/* CTA pairs (cta_group::2): 0 = where it pays, 1 = never, 2 = whenever the shape allows, 3 = 2-D copies for MN-major
+/* CTA pairs (cta_group::2): 0 = where it pays, 1 = never, 2 = whenever the shape allows (one tile per pair, never the
+ * persistent kernel), 3 = 2-D copies for MN-major
  * operands, 4 = never the 256 x 512 plain-TF32 tile, 5 = like 2 plus that tile for every plain-TF32 problem,
  * 6 = never the persistent kernel, 7 = the persistent kernel whenever the shape allows. */
 int odl_debug_set_pair_mode(int mode);

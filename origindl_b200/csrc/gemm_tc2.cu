@@ -1314,9 +1314,9 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         }
         return kOk;
     }
-    // 3xTF32 with more tiles than the GPU holds pairs: the persistent kernel (epilogue overlapped with the next tile's
-    // main loop, short last round split along K).  g_pair_mode 6 = never, 7 = for every 3xTF32 problem that reaches here.
-    if (terms == 3 && g_pair_mode != 6 && g_pair_mode != 3)
+    // 3xTF32: the persistent kernel (epilogue overlapped with the next tile's main loop, short last round split along K).
+    // g_pair_mode 2 and 6 = never (one tile per pair launch instead).
+    if (terms == 3 && g_pair_mode != 6 && g_pair_mode != 3 && g_pair_mode != 2)
     {
         const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM), tiles_n = (p.N + BN - 1) / BN;
         const int T       = tiles_m * tiles_n;
@@ -1334,11 +1334,16 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
         // B200 (TFLOP/s, whole tiles -> stream-K): 256 x 8192 x 8192 158-177 -> 174-187.  With more tiles it LOSES --
         // 2048^3 (64 tiles) 175 -> 158, 8192 x 1024 x 8192 (128 tiles) 223 -> 206, 3072^3 204 -> 179 -- because pairs that
         // share an operand panel then sit at different K offsets and stop sharing it in L2, which rounds of whole tiles
-        // started together do; those shapes keep whole tiles.  g_stream_k (test hook): 1 = always, -1 = never.
+        // started together do; those shapes keep whole tiles.  It also loses when the reduction is short: 1024 x 2048 x 2048
+        // (32 tiles, 14 chunks per pair) 130 as whole tiles with the last round split -> 113; taken from 32 chunks per pair.
+        // g_stream_k (test hook): 1 = always, -1 = never.
+        // With no more tiles than pairs the kernel still pays (one round, split along K when at most half the pairs have a
+        // tile): its epilogue stores straight from registers -- 1536^3 113 -> 130, 2048^3 196 -> 208 TFLOP/s against one
+        // tile per pair launch.
         const long long total_chunks = static_cast<long long>(T) * nch;
         const bool streamk = P > 0 && g_stream_k >= 0 && total_chunks >= 2 &&
-                             (g_stream_k == 1 || (2 * T <= P && total_chunks >= 8LL * P));
-        if (P > 0 && (T > P || g_pair_mode == 7 || streamk))
+                             (g_stream_k == 1 || (2 * T <= P && total_chunks >= 32LL * P));
+        if (P > 0)
         {
             PersistPlan plan;
             plan.tiles_m = tiles_m, plan.tiles_n = tiles_n;
