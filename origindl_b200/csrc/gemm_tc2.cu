@@ -403,7 +403,8 @@ struct PersistPlan
 
 constexpr int kPStages   = 3;
 constexpr int kPSlab     = 32 * 32 * 4;  // one warp's transpose slab
-constexpr int kPSmem     = 1024 + kPStages * PairCfg<256>::stage_bytes(3) + kEpiWarps * kPSlab + 256;
+constexpr int kMaxSkUnits = 32;          // units one pair's stream-K range may hold (the launcher checks)
+constexpr int kPSmem     = 1024 + kPStages * PairCfg<256>::stage_bytes(3) + kEpiWarps * kPSlab + 256 + kMaxSkUnits * 6 * 4;
 
 __device__ __forceinline__ void epilogue_warps_sync()
 {
@@ -431,6 +432,8 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
     int *early_out        = const_cast<int *>(abort_f) + 1;
     int *ticket_box       = early_out + 1;
     int *mail_slot        = ticket_box + 1;                                  // [2] unit index, -1 = list empty
+    int *sk_count         = mail_slot + 2;                                   // units in sk_list
+    int *sk_list          = reinterpret_cast<int *>(aux_base + 256);         // [kMaxSkUnits][6]: this pair's stream-K units
     uint64_t *mail_full   = reinterpret_cast<uint64_t *>(aux_base + 128);    // [2] per CTA: slot published
     uint64_t *mail_empty  = mail_full + 2;                                   // [2] leader's: all 18 readers have read
 
@@ -478,6 +481,47 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         {
             ptx::tmem_alloc_pair(tmem_slot, Cfg::tmem_cols);
             ptx::tmem_relinquish_pair();
+        }
+        if (warp == 2 && lane == 0 && plan.streamk)
+        {
+            // Stream-K: the accumulator chunks of the whole problem, cut into one contiguous range per pair; this pair's
+            // range as a list of units (tile, K-block range, part index / part count where a range boundary cuts the tile).
+            const int pair_     = blockIdx.x >> 1;
+            const int n_pairs_  = gridDim.x >> 1;
+            const int nch       = plan.chunks_per_tile;
+            const long long tot = static_cast<long long>(plan.tiles_m) * plan.tiles_n * nch;
+            auto begin_of = [&](int pr) -> long long { return tot * pr / n_pairs_; };
+            auto owner_of = [&](long long chunk) -> int {  // the pair whose range holds `chunk`
+                int pr = static_cast<int>(chunk * n_pairs_ / tot);
+                while (pr + 1 < n_pairs_ && begin_of(pr + 1) <= chunk)
+                    ++pr;
+                while (pr > 0 && begin_of(pr) > chunk)
+                    --pr;
+                return pr;
+            };
+            long long c = begin_of(pair_);
+            const long long c_end = begin_of(pair_ + 1);
+            int n = 0;
+            while (c < c_end && n < kMaxSkUnits)
+            {
+                const int tile       = static_cast<int>(c / nch);
+                const int ch_lo      = static_cast<int>(c - static_cast<long long>(tile) * nch);
+                const long long left = c_end - c;
+                const int ch_hi      = left >= nch - ch_lo ? nch : ch_lo + static_cast<int>(left);
+                int part = -1, n_parts = 1;
+                if (ch_lo != 0 || ch_hi != nch)
+                {
+                    const long long t0 = static_cast<long long>(tile) * nch;
+                    const int first    = owner_of(t0), last = owner_of(t0 + nch - 1);
+                    part               = pair_ - first;
+                    n_parts            = last - first + 1;
+                }
+                int *e = sk_list + 6 * n++;
+                e[0] = tile, e[1] = ch_lo * plan.chunk_kb, e[2] = min(plan.num_kb, ch_hi * plan.chunk_kb);
+                e[3] = part, e[4] = n_parts, e[5] = tile;
+                c += ch_hi - ch_lo;
+            }
+            *sk_count = n;
         }
     }
     ptx::tc_fence_before_sync();
@@ -541,52 +585,37 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         const int v = u - plan.full_units, half = v & 1;
         return Unit{plan.full_units + (v >> 1), half ? plan.kb_mid : 0, half ? plan.num_kb : plan.kb_mid, half, 2, v >> 1};
     };
-    // stream-K mode: this pair's chunk range and the walk through it
-    const long long sk_total = static_cast<long long>(plan.tiles_m) * plan.tiles_n * plan.chunks_per_tile;
-    auto sk_begin = [&](int pr) -> long long { return sk_total * pr / n_pairs; };
-    auto sk_owner = [&](long long chunk) -> int {  // the pair whose range holds `chunk`
-        int pr = static_cast<int>(chunk * n_pairs / sk_total);
-        while (pr + 1 < n_pairs && sk_begin(pr + 1) <= chunk)
-            ++pr;
-        while (pr > 0 && sk_begin(pr) > chunk)
-            --pr;
-        return pr;
-    };
-    auto sk_unit_at = [&](long long c, long long c_end) -> Unit {  // the unit that starts at chunk c of this pair's range
-        const int nch      = plan.chunks_per_tile;
-        const int tile     = static_cast<int>(c / nch);
-        const int ch_lo    = static_cast<int>(c - static_cast<long long>(tile) * nch);
-        const long long left = c_end - c;
-        const int ch_hi    = left >= nch - ch_lo ? nch : ch_lo + static_cast<int>(left);
-        Unit u{tile, ch_lo * plan.chunk_kb, min(plan.num_kb, ch_hi * plan.chunk_kb), -1, 1, tile};
-        if (ch_lo != 0 || ch_hi != nch)
-        {
-            const long long t0 = static_cast<long long>(tile) * nch;
-            const int first    = sk_owner(t0), last = sk_owner(t0 + nch - 1);
-            u.part             = pair - first;
-            u.n_parts          = last - first + 1;
-        }
-        return u;
-    };
-    // One iterator per role: `i` counts this pair's units (mailbox slots in the drawn mode), `c` walks the stream-K range.
+    // next unit of this role.  Rounds mode: fetch(i) obtains the i-th unit index of this pair (draw / read the mailbox /
+    // compute it).  Stream-K mode: the i-th entry of the list one thread made from this pair's chunk range during set-up
+    // (the 64-bit range arithmetic stays out of the roles' registers).  Returns false when the walk is over (or a wait
+    // gave up).
     struct Walk
     {
-        uint32_t i  = 0;
-        long long c = 0, c_end = 0;
+        uint32_t i = 0;
     };
-    auto walk_init = [&](Walk &wk) {
-        wk.i = 0;
-        wk.c = sk_begin(pair), wk.c_end = sk_begin(pair + 1);
+    auto walk_init = [&](Walk &wk) { wk.i = 0; };
+    // The same walk in two steps for the epilogue warps, which hold 128 accumulator registers while a unit is in flight:
+    // a one-register token first, the unit's fields from it where they are needed (before and again after the drains).
+    auto walk_token = [&](Walk &wk, auto &&fetch) -> int {
+        if (plan.streamk)
+            return static_cast<int>(wk.i) < *reinterpret_cast<volatile int *>(sk_count) ? static_cast<int>(wk.i++) : -1;
+        return fetch(wk.i++);
     };
-    // next unit of this role; fetch = how the rounds mode obtains the unit index (draw / read the mailbox / compute it).
-    // Returns false when the walk is over (or a wait gave up).
+    auto unit_from = [&](int token) -> Unit {
+        if (plan.streamk)
+        {
+            const volatile int *e = sk_list + 6 * token;
+            return Unit{e[0], e[1], e[2], e[3], e[4], e[5]};
+        }
+        return unit_of_index(token);
+    };
     auto walk_next = [&](Walk &wk, auto &&fetch, Unit &out) -> bool {
         if (plan.streamk)
         {
-            if (wk.c >= wk.c_end)
+            if (static_cast<int>(wk.i) >= *reinterpret_cast<volatile int *>(sk_count))
                 return false;
-            out = sk_unit_at(wk.c, wk.c_end);
-            wk.c += (out.kb1 - out.kb0 + plan.chunk_kb - 1) / plan.chunk_kb;
+            const int *e = sk_list + 6 * wk.i++;
+            out          = Unit{e[0], e[1], e[2], e[3], e[4], e[5]};
             return true;
         }
         const int u = fetch(wk.i++);
@@ -761,7 +790,6 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         bool have   = true;
         Walk wk;
         walk_init(wk);
-        Unit un;
         // (every lane walks: in the drawn mode lane 0 reads the mailbox and the index is broadcast)
         auto warp_fetch = [&](uint32_t i) -> int {
             int u = 0;
@@ -769,14 +797,14 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
                 u = read_mail(i);
             return __shfl_sync(0xffffffffu, u, 0);
         };
-        while (have && walk_next(wk, warp_fetch, un))
+        int token;
+        while (have && (token = walk_token(wk, warp_fetch)) >= 0)
         {
-            int tile_m, tile_n;
-            const int tile = un.tile, kb0 = un.kb0, kb1 = un.kb1;
-            tile_origin(tile, tile_m, tile_n);
-            const int m0      = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
-            const int n0      = tile_n * BN;
-            const int nchunks = (kb1 - kb0 + plan.chunk_kb - 1) / plan.chunk_kb;
+            int nchunks;
+            {
+                const Unit first = unit_from(token);
+                nchunks          = (first.kb1 - first.kb0 + plan.chunk_kb - 1) / plan.chunk_kb;
+            }
             for (int c = 0; c < nchunks; ++c, ++gc)
             {
                 const int buf      = gc & 1;
@@ -812,7 +840,12 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             }
             if (!have)
                 break;
-            bool store = true;
+            const Unit un = unit_from(token);
+            int tile_m, tile_n;
+            tile_origin(un.tile, tile_m, tile_n);
+            const int m0 = tile_m * 2 * kBM + static_cast<int>(rank) * kBM;
+            const int n0 = tile_n * BN;
+            bool store   = true;
             if (un.part >= 0)
             {
                 // part of a tile: park it, take a ticket; whoever holds the LAST ticket adds all parts in part order (a
@@ -839,17 +872,23 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
                 if (store)
                 {
                     __threadfence();
-                    for (int part = 0; part < un.n_parts; ++part)
+                    {
+                        const float4 *src = slot_ptr(0);
+#pragma unroll
+                        for (int i = 0; i < Cfg::warp_cols / 4; ++i)
+                        {
+                            const float4 o = __ldcg(src + i * 32);
+                            acc[4 * i] = o.x, acc[4 * i + 1] = o.y, acc[4 * i + 2] = o.z, acc[4 * i + 3] = o.w;
+                        }
+                    }
+                    for (int part = 1; part < un.n_parts; ++part)
                     {
                         const float4 *src = slot_ptr(part);
 #pragma unroll
                         for (int i = 0; i < Cfg::warp_cols / 4; ++i)
                         {
                             const float4 o = __ldcg(src + i * 32);
-                            if (part == 0)
-                                acc[4 * i] = o.x, acc[4 * i + 1] = o.y, acc[4 * i + 2] = o.z, acc[4 * i + 3] = o.w;
-                            else
-                                acc[4 * i] += o.x, acc[4 * i + 1] += o.y, acc[4 * i + 2] += o.z, acc[4 * i + 3] += o.w;
+                            acc[4 * i] += o.x, acc[4 * i + 1] += o.y, acc[4 * i + 2] += o.z, acc[4 * i + 3] += o.w;
                         }
                     }
                 }
@@ -1357,6 +1396,11 @@ int gemm_pair_launch(const float *A, const float *A_small, int64_t lda, int a_mn
             {
                 const int pairs_used = total_chunks < P ? static_cast<int>(total_chunks) : P;
                 const long long per  = total_chunks / pairs_used;  // chunks of the shortest range (>= 1)
+                if ((per + 1) / nch + 2 > kMaxSkUnits)
+                {
+                    set_last_error("gemm: stream-K range of %lld chunks over tiles of %d does not fit the unit list", per + 1, nch);
+                    return kInvalidArgument;
+                }
                 plan.streamk   = 1;
                 plan.max_parts = static_cast<int>((nch + per - 1) / per) + 1;
                 if ((rc = tail_split_scratch(static_cast<size_t>(T) * plan.max_parts * 2 * kBM * BN, static_cast<size_t>(T) * 2)))
