@@ -344,10 +344,14 @@ int odl_comm_watch(void *comm, int timeout_ms, int (*done)(void *), void *arg);
  * each reduced while the next one is computed; 0 lets the library choose. */
 int odl_mlp_dp_attach(void *handle, void *comm, int dw0_panels);
 /* One data-parallel optimisation step on this rank's rows x[batch, sizes[0]]: forward, loss, backward with the overlapped
- * per-layer all-reduce, then each layer's fused update as soon as its bucket is reduced.  Everything is enqueued; the call
- * does not wait for the GPU. */
+ * per-layer all-reduce (each layer's weight gradient is computed before its input gradient, so that its bucket's all-reduce
+ * starts behind the dW GEMM), and on the library's communication stream each layer's fused update as soon as its bucket is
+ * reduced and its input-gradient GEMM has finished; `stream` waits for that stream at the end.  Everything is enqueued;
+ * the call does not wait for the GPU.  Environment variable ODL_DP_TRACE=1 prints the step's timeline (timing events on
+ * both streams) to stderr and synchronises after every step. */
 int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int labels_are_int64, void *stream);
-/* Watchdog over the last enqueued data-parallel step (odl_comm_watch on its last all-reduce). */
+/* Watchdog over the last enqueued data-parallel step (odl_comm_watch on the end of its communication stream: the last
+ * all-reduce and update). */
 int odl_mlp_dp_wait(void *handle, int timeout_ms);
 
 /* ---- input pipeline --------------------------------------------------------------------------------------------- */
