@@ -448,8 +448,8 @@ int odl_mlp_train_step(void *handle, const float *x, const void *labels, int lab
         if ((rc = odl_mlp_backward_layer(handle, l, stream)))
             return rc;
     // One update of the whole buffer behind backward.  (Measured: running layer l's update on a second stream as soon as
-    // its backward is done gains nothing -- 51.37 against 51.36 ms on the benchmark step -- because no other kernel's
-    // blocks fit on an SM beside a persistent GEMM CTA, so the update runs between two GEMMs either way.)
+    // its backward is done gains nothing -- 51.37 against 51.36 ms on the benchmark step: a persistent GEMM CTA holds nearly
+    // all of its SM's shared memory and most of its registers, so the update mostly runs between two GEMMs either way.)
     return odl_mlp_optimizer_step(handle, 1.0f, stream);
 }
 
