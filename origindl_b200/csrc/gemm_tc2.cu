@@ -850,11 +850,11 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
             {
                 // part of a tile: park it, take a ticket; whoever holds the LAST ticket adds all parts in part order (a
                 // fixed order, whoever it is -- its own part is read back from its slot like the others) and stores
-                const size_t slot0 = (static_cast<size_t>(un.tile_slot) * plan.max_parts) * 2;
-                auto slot_ptr = [&](int part) {
-                    return reinterpret_cast<float4 *>(plan.partial + (slot0 + static_cast<size_t>(part) * 2 + rank) * (kBM * BN)) +
-                           (e * 32) * 32 + lane;
-                };
+                // parts of this tile, this CTA's half: slot (tile_slot * max_parts + part) * 2 + rank, kBM * BN floats each
+                float4 *const parts0 = reinterpret_cast<float4 *>(plan.partial) +
+                                       (static_cast<size_t>(un.tile_slot) * plan.max_parts * 2 + rank) * (kBM * BN / 4) +
+                                       (e * 32) * 32 + lane;
+                auto slot_ptr = [&](int part) { return parts0 + static_cast<size_t>(part) * (2 * kBM * BN / 4); };
                 float4 *mine = slot_ptr(un.part);
 #pragma unroll
                 for (int i = 0; i < Cfg::warp_cols / 4; ++i)
@@ -881,6 +881,7 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
                             acc[4 * i] = o.x, acc[4 * i + 1] = o.y, acc[4 * i + 2] = o.z, acc[4 * i + 3] = o.w;
                         }
                     }
+#pragma unroll 1
                     for (int part = 1; part < un.n_parts; ++part)
                     {
                         const float4 *src = slot_ptr(part);
