@@ -533,7 +533,7 @@ struct DpTrace
         cudaEventRecord(m.ev, st);
         marks.push_back(m);
     }
-    void print(cudaStream_t a, cudaStream_t b)
+    void print(cudaStream_t a, cudaStream_t b, int rank)
     {
         if (!on || marks.empty())
             return;
@@ -543,7 +543,7 @@ struct DpTrace
         {
             float ms = 0.f;
             cudaEventElapsedTime(&ms, marks[0].ev, marks[i].ev);
-            std::fprintf(stderr, "[odl dp trace] %8.3f ms  %s\n", ms, marks[i].what);
+            std::fprintf(stderr, "[odl dp trace, rank %d] %8.3f ms  %s\n", rank, ms, marks[i].what);
         }
         for (auto &m : marks)
             cudaEventDestroy(m.ev);
@@ -637,7 +637,7 @@ int odl_mlp_train_step_dp(void *handle, const float *x, const void *labels, int 
     // the step is complete when the communication stream is: odl_mlp_dp_wait watches this event
     ODL_CUDA_TRY(cudaEventRecord(h->ev_step_done, h->comm_stream));
     ODL_CUDA_TRY(cudaStreamWaitEvent(s, h->ev_step_done, 0));
-    g_trace.print(s, h->comm_stream);
+    g_trace.print(s, h->comm_stream, comm_rank(h->comm));
     return kOk;
 }
 
