@@ -568,7 +568,7 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
         if (!ptx::mbar_wait_cluster(&mail_full[slot], (i >> 1) & 1, abort_f))
             return -2;
         const int u = *reinterpret_cast<volatile int *>(&mail_slot[slot]);
-        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&mail_empty[slot]), 0));
+        ptx::mbar_arrive_cluster_relaxed(ptx::map_to_cta(ptx::smem_u32(&mail_empty[slot]), 0), static_cast<uint32_t>(u));
         return u;
     };
 
@@ -836,7 +836,7 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0)
-                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty[buf]), 0));
+                    ptx::mbar_arrive_cluster_relaxed(ptx::map_to_cta(ptx::smem_u32(&acc_empty[buf]), 0));
             }
             if (!have)
                 break;

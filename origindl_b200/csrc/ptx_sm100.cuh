@@ -362,6 +362,23 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// The same arrive without release semantics: it does not wait for the thread's earlier global stores to be performed (a
+// release at cluster scope does, which costs an epilogue warp a round trip to L2 behind every tile it has just written).
+// For signals that publish no memory: "this TMEM buffer has been read" (ordered by tcgen05.wait::ld and the tcgen05
+// fences), "this mailbox slot has been read" -- `after` is a value the arrive must follow (the word just read from the
+// slot): the move makes the arrive wait for the load that produced it.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr, uint32_t after = 0)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 t;\n\t"
+        "mov.b32 t, %1;\n\t"
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n\t"
+        "}" ::"r"(cluster_addr),
+        "r"(after)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols)
 {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),

@@ -60,6 +60,7 @@ def main():
     ap.add_argument("--optimizer", default="sgd", help="mlp: sgd (momentum 0.9) or adam")
     ap.add_argument("--graph", action="store_true", help="mlp: also time the step replayed from the library's CUDA graph")
     ap.add_argument("--yardstick", action="store_true", help="gemm: also time torch.matmul (TF32 and fp32) for context")
+    ap.add_argument("--rect", action="store_true", help="gemm: an M x N x K problem from --m / --n / --k instead of n cubed")
     a = ap.parse_args()
     capi.init(0)
     torch.manual_seed(0)
@@ -147,11 +148,14 @@ def main():
               f"(4 B read + 4 B written per element)")
     elif a.case == "gemm":
         n = a.n
+        M, N, K = (a.m, a.n, a.k) if a.rect else (n, n, n)
         ta, tb = {"nt": (False, True), "nn": (False, False), "tn": (True, False)}[a.layout]
-        A, B = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+        A = torch.randn((K, M) if ta else (M, K), device="cuda")
+        B = torch.randn((N, K) if tb else (K, N), device="cuda")
         As, Bs = ops.split_tf32(A), ops.split_tf32(B)
         ms = timed(lambda: ops.gemm(A, B, trans_a=ta, trans_b=tb, a_small=As, b_small=Bs, precision=prec), a.iters)
-        print(f"gemm {a.layout} {a.precision} n={n}: {ms:.4f} ms/launch, {2 * n ** 3 / ms / 1e9:.1f} TFLOP/s")
+        shape = f"{M}x{N}x{K}" if a.rect else f"n={n}"
+        print(f"gemm {a.layout} {a.precision} {shape}: {ms:.4f} ms/launch, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
         if a.yardstick:
             # context only: the vendor library's single-pass TF32 and fp32 GEMMs on the same operands
             At, Bt = (A.t() if ta else A), (B.t() if tb else B)
