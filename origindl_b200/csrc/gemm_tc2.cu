@@ -835,6 +835,8 @@ gemm_tc2_persistent_kernel(const __grid_constant__ TmapPack tm, const GemmParams
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
+                // relaxed: the buffer's TMEM reads are complete (wait::ld) and fenced; a release at cluster scope would also
+                // wait for the global stores of the tile this warp has just written, behind every tile
                 if (lane == 0)
                     ptx::mbar_arrive_cluster_relaxed(ptx::map_to_cta(ptx::smem_u32(&acc_empty[buf]), 0));
             }
